@@ -1,0 +1,407 @@
+#!/usr/bin/env python
+"""Benchmark of the paged NVFP4 decode path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N --steps K ...   # the CPU oracle path
+
+One "step" is one decode step of one attention layer over the whole batch:
+Q quantisation + split-KV paged decode (the LSE merge is part of the decode call
+when it splits).  The workload is the uniform batch-decode configuration:
+32 sequences x 4096 context, 32 query heads / 8 KV heads / head_dim 128,
+128-token pages, key shift applied when the pages were written, no BF16 tail.
+
+Prints ONE JSON line (rank 0).
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, CTX, HQ, HKV, D, PAGE = 32, 4096, 32, 8, 128, 128
+PAGES_PER_ROW = CTX // PAGE
+POOL_PAGES = ROWS * PAGES_PER_ROW          # 1024 pages = 151 MB of NVFP4 K+V per pool
+NUM_POOLS = 2                              # alternate so that L2 (126 MB) cannot hold a step's KV
+KV_BYTES = ROWS * CTX * HKV * 144          # algorithmic bytes of one step (144 B per token-head)
+METRIC = "decode_attn_tokens_per_s"
+UNIT = "tokens/s"
+WORKLOAD = ("uniform batch decode: 32 seq x 4096 ctx, Hq32/Hkv8/D128, page 128, "
+            "NVFP4 K/V (key shift applied at write), tail 0, bf16 out, 1 layer")
+
+
+# --------------------------------------------------------------------------- CPU arm
+def _cpu_row(args):
+    """One sequence of the workload through the CPU oracle (quantises Q/K/V itself)."""
+    seed, ctx = args
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+
+    import nvfp4_oracle as O
+
+    rng = np.random.default_rng(seed)
+    pages = ctx // PAGE
+    q = O.bf16_round(rng.standard_normal((1, HQ, D)).astype(np.float32))
+    off = rng.standard_normal((HKV, D)).astype(np.float32) * 2.0
+    k = O.bf16_round(rng.standard_normal((pages, PAGE, HKV, D)).astype(np.float32) + off)
+    mu = O.bf16_round(k.reshape(-1, HKV, D).astype(np.float64).mean(0).astype(np.float32))
+    k = O.bf16_round(k - mu)
+    v = O.bf16_round(rng.standard_normal((pages, PAGE, HKV, D)).astype(np.float32))
+    table = rng.permutation(pages).astype(np.int32).reshape(1, pages)
+    t0 = time.perf_counter()
+    out = O.reference_decode(q, k, v, table, np.array([ctx]), np.array([0]), np.array([0]),
+                             D ** -0.5)
+    return time.perf_counter() - t0, float(np.abs(out).sum())
+
+
+def cpu_path(steps: int, warmup: int, rows_per_step: int | None = None):
+    """Time the CPU oracle on a bounded sample of the workload, all host cores."""
+    import multiprocessing as mp
+
+    cores = os.cpu_count() or 1
+    rows = rows_per_step or min(ROWS, cores)
+    ctx = mp.get_context("spawn")
+    os.environ.setdefault("OMP_NUM_THREADS", "1")
+    workers = min(cores, rows)
+    busy = 0.0
+    with ctx.Pool(workers) as pool:
+        for w in range(warmup):
+            pool.map(_cpu_row, [(1000 + w * rows + r, CTX) for r in range(rows)])
+        for s in range(steps):
+            # input generation happens inside the workers but outside their timers
+            busy += sum(t for t, _ in pool.map(_cpu_row, [(s * rows + r, CTX) for r in range(rows)]))
+    dt = busy / workers  # wall time of the oracle work with every worker busy
+    return dict(
+        value=rows * steps / dt,
+        ms_per_step=1e3 * dt / steps,
+        cores=min(cores, rows),
+        rows=rows,
+        sample=f"{steps} step(s) of {rows} of the {ROWS} sequences (4096 ctx each, Q/K/V/P "
+               f"quantisation included), one process per sequence on {min(cores, rows)} cores",
+    )
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 3))
+    res = cpu_path(steps, min(args.warmup, 1))
+    line = {
+        "impl": "reference",
+        "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": res["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "nvfp4", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "arm": "numpy restatement of the reference's torch oracle"},
+        "cpu_baseline": {"value": res["value"], "unit": UNIT, "cores": res["cores"],
+                         "kind": "port", "sample": res["sample"]},
+        "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([p.strip() for p in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for s in self.samples:
+            if len(s) < 6:
+                continue
+            try:
+                mhz.append(float(s[0]))
+                mx = float(s[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, s[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def build_pools(device):
+    """Two disjoint page pools in the vLLM block layout, filled by the library's quantisers."""
+    import torch
+
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import quantize_kv_kernel as qkv
+
+    block = 2 * (PAGE * HKV * 64 + HKV * 1024)
+    o1 = PAGE * HKV * 64
+    o2 = o1 + HKV * 1024
+    o3 = o2 + o1
+    pools = []
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1234)
+    for _ in range(NUM_POOLS):
+        cache = torch.empty(POOL_PAGES, block, dtype=torch.uint8, device=device)
+        flat = cache.view(-1)
+        kview = flat.as_strided((POOL_PAGES, PAGE, HKV, 64), (block, HKV * 64, 64, 1), 0)
+        vview = flat.as_strided((POOL_PAGES, HKV, D, 64), (block, D * 64, 64, 1), o2)
+        ksf = qkv.scale_view(flat, POOL_PAGES, HKV, block, o1)
+        vsf = qkv.scale_view(flat, POOL_PAGES, HKV, block, o3)
+        chunk = 128
+        offset = torch.randn(HKV, D, device=device, generator=gen) * 2.0
+        shift = None
+        for lo in range(0, POOL_PAGES, chunk):
+            k = (torch.randn(chunk * PAGE, HKV, D, device=device, generator=gen) + offset).to(torch.bfloat16)
+            v = torch.randn(chunk * PAGE, HKV, D, device=device, generator=gen).to(torch.bfloat16)
+            if shift is None:
+                shift = k.double().mean(0).to(torch.bfloat16).contiguous()  # per-channel K mean
+            src = torch.arange(chunk, dtype=torch.int32, device=device) * PAGE
+            dst = torch.arange(lo, lo + chunk, dtype=torch.int32, device=device)
+            qkv.quantize_key_tokens_into(k, kview, ksf, src, dst, key_shift=shift)
+            qkv.quantize_value_tokens_into(v, vview, vsf, src, dst)
+        table = torch.randperm(POOL_PAGES, device=device, generator=gen).to(torch.int32).reshape(
+            ROWS, PAGES_PER_ROW)
+        pools.append(dict(cache=cache, k=kview, ksf=ksf, v=vview, vsf=vsf, table=table, block=block))
+    return pools
+
+
+def run_gpu(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import nvfp4_attn_kernel_b200._lib as L
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import fp4_decode
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the kernels")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = L.load()
+    impl = {"auto": L.IMPL_AUTO, "generic": L.IMPL_GENERIC, "sm100": L.IMPL_SM100}[args.decode_impl]
+
+    pools = build_pools(device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(99 + rank)
+    q = torch.randn(ROWS, HQ, D, device=device, generator=gen).to(torch.bfloat16)
+    q_fp4 = torch.zeros(ROWS, 1, HQ, 64, dtype=torch.uint8, device=device)
+    q_sf = torch.zeros(ROWS, HQ * 1024, dtype=torch.uint8, device=device)
+    out = torch.zeros(ROWS, HQ, D, dtype=torch.bfloat16, device=device)
+    seqused = torch.full((ROWS,), CTX, dtype=torch.int32, device=device)
+    splits = args.num_splits
+    ws_bytes = lib.nvfp4_decode_workspace_bytes(ROWS, HQ, splits)
+    workspace = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def decode_args(pool):
+        a = L.DecodeArgs()
+        a.q_fp4, a.q_sf = q_fp4.data_ptr(), q_sf.data_ptr()
+        a.k_packed, a.k_pitch = pool["k"].data_ptr(), pool["block"]
+        a.k_sf, a.k_sf_pitch = pool["ksf"].data_ptr(), pool["block"]
+        a.v_packed, a.v_pitch = pool["v"].data_ptr(), pool["block"]
+        a.v_sf, a.v_sf_pitch = pool["vsf"].data_ptr(), pool["block"]
+        a.num_pages = POOL_PAGES
+        a.page_table, a.page_table_row_stride, a.max_pages = pool["table"].data_ptr(), PAGES_PER_ROW, PAGES_PER_ROW
+        a.seqused_fp4 = seqused.data_ptr()
+        a.out = out.data_ptr()
+        a.rows, a.heads_q, a.heads_kv = ROWS, HQ, HKV
+        a.softmax_scale = D ** -0.5
+        a.num_splits, a.impl = splits, impl
+        a.workspace, a.workspace_bytes = workspace.data_ptr(), ws_bytes
+        a.status = status.data_ptr()
+        return a
+
+    dargs = [decode_args(p) for p in pools]
+
+    def step(i, stream, with_q=True):
+        if with_q:
+            L.check(lib.nvfp4_quantize_q(q.data_ptr(), q.stride(0), q.stride(1), None, q_fp4.data_ptr(),
+                                         q_sf.data_ptr(), None, ROWS, HQ, HKV, stream))
+        L.check(lib.nvfp4_decode(ctypes.byref(dargs[i % NUM_POOLS]), stream))
+
+    def timed_graph(with_q, steps, warmup):
+        """Capture NUM_POOLS steps into a CUDA graph, replay, time with events on its stream."""
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(4):
+                step(i, side.cuda_stream, with_q)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(NUM_POOLS):
+                step(i, torch.cuda.current_stream().cuda_stream, with_q)
+        reps = max(1, steps // NUM_POOLS)
+        for _ in range(max(1, warmup // NUM_POOLS)):
+            graph.replay()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(reps):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        return start.elapsed_time(end), reps * NUM_POOLS
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms, done = timed_graph(True, args.steps, args.warmup)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / done
+    # the decode kernel alone (roofline numerator is the KV stream)
+    ms_k, done_k = timed_graph(False, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    kernel_s = ms_k / done_k * 1e-3
+
+    # end to end through the public operator with host buffers
+    q_host = q.cpu().pin_memory()
+    out_host = torch.empty_like(out, device="cpu").pin_memory()
+    q_sf_scratch = torch.zeros(ROWS, 1, HQ, 2, 32, 4, 4, dtype=torch.uint8, device=device)
+    q_fp4_scratch = torch.zeros(ROWS, 1, HQ, 64, dtype=torch.uint8, device=device)
+    q_dev = torch.empty_like(q)
+
+    def e2e_step(i):
+        pool = pools[i % NUM_POOLS]
+        q_dev.copy_(q_host, non_blocking=True)
+        fp4_decode(q_dev, pool["k"], pool["ksf"], pool["v"], pool["vsf"], pool["table"], seqused,
+                   out=out, trusted_metadata=True, num_splits=splits,
+                   query_fp4_scratch=q_fp4_scratch, query_scales_scratch=q_sf_scratch)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = min(args.steps, 200)
+    for i in range(max(3, min(args.warmup, 10))):
+        e2e_step(i)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e2.record()
+    torch.cuda.synchronize()
+    e2e_ms = s2.elapsed_time(e2)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+        dist.barrier()
+
+    bad = int(status.item())
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except (OSError, ValueError):
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        achieved = KV_BYTES / kernel_s / 1e9
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            res = cpu_path(1, 0)
+            cpu = {"value": res["value"], "unit": UNIT, "cores": res["cores"], "kind": "port",
+                   "sample": res["sample"]}
+        launches_per_step = 2 + (1 if splits > 1 else 0)
+        line = {
+            "metric": METRIC, "value": world * ROWS / (ms_step * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": done, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "nvfp4", "data": "synthetic",
+            "config": {
+                "workload": WORKLOAD,
+                "l2": f"{NUM_POOLS} rotating page pools of {KV_BYTES / 1e6:.0f} MB each (> 126 MB L2), "
+                      "alternated every step",
+                "timing": "CUDA-graph replay, CUDA events on the replay stream, max over ranks",
+                "decode_impl": args.decode_impl, "num_splits": splits,
+                "sharding": "independent batch of 32 sequences per GPU, no collective",
+            },
+            "hbm_gbs": achieved, "frac_of_8000": achieved / 8000.0,
+            "decode_kernel_us": kernel_s * 1e6,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak,
+                         "peak_source": "measured" if peaks else "fallback",
+                         "traffic": args.ncu_traffic},
+            "cpu_baseline": cpu,
+            "e2e": {"value": world * ROWS * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
+            "gpu_launches": done * launches_per_step,
+            "clocks": clocks,
+            "device_status_word": bad,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=30)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--decode-impl", default="auto", choices=["auto", "generic", "sm100"])
+    ap.add_argument("--num-splits", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ncu-traffic", type=float, default=None,
+                    help="dram bytes per decode launch from an ncu capture (reported as roofline.traffic)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,225 @@
+/*
+ * nvfp4_b200 — C ABI of the B200 (sm_100a) paged NVFP4/BF16 hybrid decode-attention path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t).  Nothing here allocates device
+ * memory unless stated, nothing synchronises the stream, and every call is
+ * safe to record into a CUDA graph unless stated.  All functions return 0 on
+ * success and a non-zero code on failure; nvfp4_last_error() then holds a
+ * human-readable message for the calling thread.
+ *
+ * Formats (identical to the reference project, so buffers are interchangeable):
+ *   E2M1  : 4-bit float, two per byte, even element in the LOW nibble.
+ *   scale : E4M3 byte per 16 elements, value = e2m1 * e4m3, no second-level scale.
+ *   K page: packed [page][128 tok][Hkv][64 B]; scales, per page and head, one
+ *           1024-byte block: byte (g/4)*512 + (tok%32)*16 + (tok/32)*4 + g%4
+ *           for 16-channel group g of token tok.
+ *   V page: packed [page][Hkv][128 ch][64 B] (byte j of a channel row = tokens
+ *           2j, 2j+1); groups run along TOKENS; scale block as for K with the
+ *           channel in place of the token and the 16-token group in place of g.
+ *   Q     : packed [rows][1][Hq][64 B]; scales [rows][Hq*1024 B], head h of KV
+ *           head kv=h/G, slot r=h%G: byte kv*1024 + (g/4)*512 + (r%32)*16 +
+ *           (r/32)*4 + g%4; the unwritten slots must be zero.
+ * Page pitches are free (>= dense size, 16-byte aligned; scale pitches 16-byte
+ * aligned), so the four regions may be carved out of one vLLM block.
+ *
+ * Citations "ref:" name the file:line of the reference project interface that
+ * the entry point stands in for.
+ */
+#ifndef NVFP4_B200_H_
+#define NVFP4_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NVFP4_PAGE_SIZE 128
+#define NVFP4_HEAD_DIM 128
+
+/* error codes */
+#define NVFP4_OK 0
+#define NVFP4_ERR_INVALID 1     /* bad argument (message says which) */
+#define NVFP4_ERR_CUDA 2        /* a CUDA runtime/driver call failed */
+#define NVFP4_ERR_UNSUPPORTED 3 /* shape or device outside what the kernels cover */
+
+/* bits of the sticky device status word (nvfp4_decode_args.status) */
+#define NVFP4_STATUS_BAD_PAGE_ID 1u   /* a consumed page-table entry was outside [0, num_pages) */
+#define NVFP4_STATUS_BAD_TAIL_ID 2u   /* tail length > 0 with a tail id outside [0, tail_pages) */
+#define NVFP4_STATUS_WAIT_TIMEOUT 4u  /* a bounded device-side wait gave up */
+#define NVFP4_STATUS_BAD_LENGTH 8u    /* seqused_fp4 not a multiple of 128 / beyond the table, tail length > 128 */
+
+/* decode implementations */
+#define NVFP4_IMPL_AUTO 0
+#define NVFP4_IMPL_GENERIC 1 /* CUDA-core kernel, any G = Hq/Hkv in {1,2,4,8,16,32} */
+#define NVFP4_IMPL_SM100 2   /* tcgen05 block-scaled MMA kernel, G <= 8 */
+
+const char* nvfp4_last_error(void);
+int nvfp4_version(void);
+
+/* 1 if the CUDA device can run the kernels (compute capability 10.x), 0 if not,
+ * negative on a CUDA error. */
+int nvfp4_device_supported(int device);
+
+/*
+ * Q quantiser.  ref: quantize_query, src/nvfp4_decode_kernel/_quantize.py:14-117 and
+ * quantize_decode_q_to_padded_fp4, quantize_q_kernel.py:304-505.
+ *   q_bf16      [src_rows][Hq][128] bf16, strides in ELEMENTS, last stride 1
+ *   row_indices nullable int32[rows]: compact row i reads source row row_indices[i]
+ *   q_fp4       out, [rows][1][Hq][64] bytes, every byte rewritten
+ *   q_sf        out, [rows][Hq*1024] bytes; only the G=Hq/Hkv live slots of each
+ *               KV head are written (the caller zeroes the buffer once)
+ *   q_padded    nullable out, bf16 [>=rows][128][Hq][128]; only [row][0][h][:] is written
+ */
+int nvfp4_quantize_q(const void* q_bf16, int64_t q_row_stride, int64_t q_head_stride,
+                     const int32_t* row_indices, void* q_fp4, void* q_sf, void* q_padded,
+                     int rows, int heads_q, int heads_kv, void* stream);
+
+/*
+ * K / V page quantiser, dense or indexed, optional per-layer destinations and an
+ * optional fused per-channel key shift.
+ * ref: quantize_key_pages / quantize_value_pages / quantize_key_tokens_into /
+ * quantize_value_tokens_into, quantize_kv_kernel.py:661-822; shift: nvfp4_vllm/impl.py:145-152.
+ *   which          0 = K, 1 = V
+ *   tokens_bf16    flat [tokens][Hkv][128] bf16, dense inside a token; token_stride in elements
+ *   key_shift_bf16 nullable bf16 [layers][Hkv][128] (K only): k <- bf16(k - shift) before quantising
+ *   packed/sf      destination regions with page pitches in BYTES
+ *   src_tokens     nullable int32[work]: first token of work item w (default w*128)
+ *   dst_pages      nullable int32[work]: destination page of w (default w); negative = skip
+ *   packed_bases / sf_bases  nullable int64[layers]: per-layer destination base addresses
+ *                  (then packed/sf only fix the layout and may be NULL)
+ *   src_layer_stride tokens between consecutive layers of the source
+ */
+int nvfp4_quantize_kv_pages(int which, const void* tokens_bf16, int64_t token_stride,
+                            const void* key_shift_bf16, void* packed, int64_t packed_pitch,
+                            void* sf, int64_t sf_pitch, const int32_t* src_tokens,
+                            const int32_t* dst_pages, const int64_t* packed_bases,
+                            const int64_t* sf_bases, int work, int layers,
+                            int64_t src_layer_stride, int heads_kv, void* stream);
+
+/*
+ * BF16 tail append for one layer (with the key shift fused).
+ * ref: write_kv / _tail_write_kernel, src/nvfp4_vllm/write.py:79-130,280-337.
+ * Token t of row r lands at tail[slot(r)][seq_len[r] + t - row_end[r] - seqused_fp4[r]]
+ * when slot(r) >= 0 and that offset is >= 0.
+ *   key/value      [tokens][Hkv][128] bf16, token strides in elements
+ *   tail_key/value this layer's [slots][128][Hkv][128] bf16; tail_slot_stride in elements
+ */
+int nvfp4_tail_append(const void* key, const void* value, int64_t key_token_stride,
+                      int64_t value_token_stride, const void* key_shift_bf16, void* tail_key,
+                      void* tail_value, int64_t tail_slot_stride,
+                      const int32_t* query_start_loc, const int32_t* seq_lens,
+                      const int32_t* seqused_fp4, const int32_t* row_to_slot, int num_tokens,
+                      int num_reqs, int heads_kv, void* stream);
+
+/*
+ * Zero the tail page (all layers) of every row that starts a request this step
+ * (seq_len <= query_len).  ref: reset_new_request_tails, write.py:133-215.
+ */
+int nvfp4_tail_reset(void* tail_key, void* tail_value, int64_t tail_layer_stride,
+                     int64_t tail_slot_stride, int layers, const int32_t* query_start_loc,
+                     const int32_t* seq_lens, const int32_t* row_to_slot, int num_reqs,
+                     int heads_kv, void* stream);
+
+/*
+ * Tail flush (promotion): quantise every filled tail page of every layer into
+ * its block, K and V in ONE launch.  ref: promote.launch, src/nvfp4_vllm/promote.py:33-62.
+ *   tail_key/value [layers][slots][128][Hkv][128] bf16 seen as flat tokens
+ *   src_tokens     int32[work] first tail token of item w (slot*128), dst_pages int32[work] (-1 = skip)
+ *   bases          int64[4][layers]: K packed, K scales, V packed, V scales base addresses
+ */
+int nvfp4_tail_flush(const void* tail_key, const void* tail_value, int64_t src_layer_stride,
+                     const int32_t* src_tokens, const int32_t* dst_pages, const int64_t* bases,
+                     int64_t k_pitch, int64_t k_sf_pitch, int64_t v_pitch, int64_t v_sf_pitch,
+                     int work, int layers, int heads_kv, void* stream);
+
+/*
+ * Split-KV paged decode.  ref: fp4_decode, src/nvfp4_decode_kernel/interface.py:17-182;
+ * decode_fp4 / decode_fp4_split, _decode.py:532-1171.
+ */
+typedef struct nvfp4_decode_args {
+  /* query */
+  const void* q_fp4;          /* [rows][1][Hq][64] */
+  const void* q_sf;           /* [rows][Hq*1024] */
+  const void* q_bf16;         /* nullable: bf16 query used against the BF16 tail */
+  int64_t q_bf16_row_stride;  /* elements */
+  int64_t q_bf16_head_stride; /* elements */
+  /* NVFP4 pages */
+  const void* k_packed;
+  int64_t k_pitch; /* bytes per page */
+  const void* k_sf;
+  int64_t k_sf_pitch;
+  const void* v_packed;
+  int64_t v_pitch;
+  const void* v_sf;
+  int64_t v_sf_pitch;
+  int64_t num_pages;
+  const int32_t* page_table;     /* [rows][max_pages], row stride in elements */
+  int64_t page_table_row_stride;
+  int32_t max_pages;
+  const int32_t* seqused_fp4;    /* [rows], multiples of 128 */
+  /* BF16 tail (all four NULL/0 when the call has no tail) */
+  const void* tail_key;          /* [tail_pages][128][Hkv][128] bf16 */
+  const void* tail_value;
+  int64_t tail_pages;
+  const int32_t* tail_ids;       /* [rows] */
+  const int32_t* seqused_tail;   /* [rows] in [0,128] */
+  /* outputs */
+  void* out;                     /* nullable bf16 [>=rows][Hq][128] */
+  const int32_t* out_indices;    /* nullable int32[rows] */
+  float* o_partial;              /* nullable fp32 [S][rows][Hq][128]: normalised partial O */
+  float* lse_partial;            /* nullable fp32 [S][rows][Hq]: natural-log LSE, -inf if empty */
+  /* shape */
+  int32_t rows;
+  int32_t heads_q;
+  int32_t heads_kv;
+  float softmax_scale;
+  int32_t num_splits;            /* >= 1; split s owns pages [s*ceil(n/S), min((s+1)*ceil(n/S), n)), the tail belongs to split 0 */
+  int32_t impl;                  /* NVFP4_IMPL_* */
+  /* scratch for num_splits > 1 when o_partial/lse_partial are NULL */
+  void* workspace;
+  size_t workspace_bytes;
+  uint32_t* status;              /* nullable sticky device status word */
+} nvfp4_decode_args;
+
+/*
+ * With out != NULL the merged bf16 result is written (for num_splits > 1 the
+ * partials go through o_partial/lse_partial if given, else through workspace).
+ * With out == NULL the call only emits the partials (used by the cross-GPU
+ * page-range split, where the merge happens after the exchange).
+ */
+int nvfp4_decode(const nvfp4_decode_args* args, void* stream);
+
+size_t nvfp4_decode_workspace_bytes(int rows, int heads_q, int num_splits);
+
+/* 1 if this build of the library carries the given NVFP4_IMPL_* decode kernel for a
+ * group size heads_q / heads_kv, else 0. */
+int nvfp4_decode_impl_available(int impl, int heads_q, int heads_kv);
+
+/*
+ * LSE merge of split partials.  ref: flash_attn_combine,
+ * src/nvfp4_decode_kernel/split_k_combine.py:694-768.
+ *   o_parts   fp32 [S][rows][Hq][128] with split stride o_split_stride (elements)
+ *   lse_parts fp32 [S][rows][Hq] with split stride lse_split_stride (elements)
+ *   out       [>=rows][Hq][128], bf16 (out_is_f32 = 0) or fp32 (1); out_indices nullable;
+ *             lse_out nullable fp32 [rows][Hq]
+ */
+int nvfp4_lse_merge(const float* o_parts, int64_t o_split_stride, const float* lse_parts,
+                    int64_t lse_split_stride, int num_splits, int rows, int heads_q, void* out,
+                    int out_is_f32, const int32_t* out_indices, float* lse_out, void* stream);
+
+/*
+ * Same merge with one base pointer per split (partials that live in different
+ * allocations, e.g. peer GPUs' buffers mapped into this process).
+ *   o_part_ptrs / lse_part_ptrs: DEVICE arrays of num_splits pointers.
+ */
+int nvfp4_lse_merge_ptrs(const float* const* o_part_ptrs, const float* const* lse_part_ptrs,
+                         int num_splits, int rows, int heads_q, void* out, int out_is_f32,
+                         const int32_t* out_indices, float* lse_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4_B200_H_ */

@@ -1,0 +1,340 @@
+// C ABI of the library: argument validation, error reporting, dispatch.
+// No torch types, no allocation, no stream synchronisation.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/nvfp4_b200.h"
+#include "nvfp4_kernels.h"
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(e == cudaErrorNotSupported ? NVFP4_ERR_UNSUPPORTED : NVFP4_ERR_CUDA, "%s: %s", what,
+              cudaGetErrorString(e));
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool valid_group(int heads_q, int heads_kv) {
+  if (heads_kv < 1 || heads_q < 1 || heads_q % heads_kv) return false;
+  const int g = heads_q / heads_kv;
+  return g == 1 || g == 2 || g == 4 || g == 8 || g == 16 || g == 32;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* nvfp4_last_error(void) { return g_error; }
+
+int nvfp4_version(void) { return 100; }
+
+int nvfp4_device_supported(int device) {
+  cudaDeviceProp prop;
+  cudaError_t e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) {
+    cuda_fail(e, "cudaGetDeviceProperties");
+    return -1;
+  }
+  return prop.major == 10 ? 1 : 0;
+}
+
+int nvfp4_quantize_q(const void* q_bf16, int64_t q_row_stride, int64_t q_head_stride,
+                     const int32_t* row_indices, void* q_fp4, void* q_sf, void* q_padded, int rows,
+                     int heads_q, int heads_kv, void* stream) {
+  if (rows < 0) return fail(NVFP4_ERR_INVALID, "rows must be non-negative, got %d", rows);
+  if (rows == 0) return NVFP4_OK;
+  if (!q_bf16 || !q_fp4 || !q_sf) return fail(NVFP4_ERR_INVALID, "q_bf16, q_fp4 and q_sf must be non-null");
+  if (heads_kv < 1 || heads_q < 1 || heads_q % heads_kv)
+    return fail(NVFP4_ERR_INVALID, "query heads must be divisible by heads_kv (%d, %d)", heads_q, heads_kv);
+  if (heads_q / heads_kv > 128)
+    return fail(NVFP4_ERR_INVALID, "at most 128 query heads per KV head fit one scale block");
+  if (!aligned16(q_bf16) || !aligned16(q_fp4) || !aligned16(q_sf) || (q_padded && !aligned16(q_padded)) ||
+      (q_row_stride % 8) || (q_head_stride % 8))
+    return fail(NVFP4_ERR_INVALID, "query buffers and strides must keep 16-byte alignment");
+  cudaError_t e = nvfp4::launch_quantize_q(q_bf16, q_row_stride, q_head_stride, row_indices, q_fp4,
+                                           q_sf, q_padded, rows, heads_q, heads_kv,
+                                           static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "quantize_q launch");
+}
+
+int nvfp4_quantize_kv_pages(int which, const void* tokens_bf16, int64_t token_stride,
+                            const void* key_shift_bf16, void* packed, int64_t packed_pitch, void* sf,
+                            int64_t sf_pitch, const int32_t* src_tokens, const int32_t* dst_pages,
+                            const int64_t* packed_bases, const int64_t* sf_bases, int work,
+                            int layers, int64_t src_layer_stride, int heads_kv, void* stream) {
+  if (which != 0 && which != 1) return fail(NVFP4_ERR_INVALID, "which must be 0 (K) or 1 (V)");
+  if (work < 0 || layers < 1) return fail(NVFP4_ERR_INVALID, "work must be >= 0 and layers >= 1");
+  if (work == 0) return NVFP4_OK;
+  if (heads_kv < 1 || heads_kv > 128) return fail(NVFP4_ERR_INVALID, "heads_kv out of range: %d", heads_kv);
+  if (!tokens_bf16) return fail(NVFP4_ERR_INVALID, "tokens_bf16 must be non-null");
+  if ((!packed_bases) != (!sf_bases))
+    return fail(NVFP4_ERR_INVALID, "packed_bases and sf_bases must be given together");
+  if (!packed_bases && (!packed || !sf))
+    return fail(NVFP4_ERR_INVALID, "packed and sf must be non-null without a base table");
+  if (layers > 1 && !packed_bases)
+    return fail(NVFP4_ERR_INVALID, "layers > 1 needs per-layer destination bases");
+  const int64_t dense_packed = (int64_t)128 * heads_kv * 64, dense_sf = (int64_t)heads_kv * 1024;
+  if (packed_pitch < dense_packed || (packed_pitch % 16))
+    return fail(NVFP4_ERR_INVALID, "packed page pitch must be >= %lld bytes and 16-byte aligned, got %lld",
+                (long long)dense_packed, (long long)packed_pitch);
+  if (sf_pitch < dense_sf || (sf_pitch % 16))
+    return fail(NVFP4_ERR_INVALID, "scale page pitch must be >= %lld bytes and 16-byte aligned, got %lld",
+                (long long)dense_sf, (long long)sf_pitch);
+  if (token_stride < (int64_t)heads_kv * 128 || (token_stride % 8) || !aligned16(tokens_bf16))
+    return fail(NVFP4_ERR_INVALID, "token source must be dense within a token and 16-byte aligned");
+  if ((packed && !aligned16(packed)) || (sf && !aligned16(sf)) || (key_shift_bf16 && !aligned16(key_shift_bf16)))
+    return fail(NVFP4_ERR_INVALID, "destination regions must be 16-byte aligned");
+  if (which == 1 && key_shift_bf16) return fail(NVFP4_ERR_INVALID, "the key shift applies to K only");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e =
+      which == 0 ? nvfp4::launch_quantize_k(tokens_bf16, token_stride, key_shift_bf16, packed,
+                                            packed_pitch, sf, sf_pitch, src_tokens, dst_pages,
+                                            packed_bases, sf_bases, work, layers, src_layer_stride,
+                                            heads_kv, st)
+                 : nvfp4::launch_quantize_v(tokens_bf16, token_stride, packed, packed_pitch, sf,
+                                            sf_pitch, src_tokens, dst_pages, packed_bases, sf_bases,
+                                            work, layers, src_layer_stride, heads_kv, st);
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "quantize_kv_pages launch");
+}
+
+int nvfp4_tail_append(const void* key, const void* value, int64_t key_token_stride,
+                      int64_t value_token_stride, const void* key_shift_bf16, void* tail_key,
+                      void* tail_value, int64_t tail_slot_stride, const int32_t* query_start_loc,
+                      const int32_t* seq_lens, const int32_t* seqused_fp4, const int32_t* row_to_slot,
+                      int num_tokens, int num_reqs, int heads_kv, void* stream) {
+  if (num_tokens < 0 || num_reqs < 0) return fail(NVFP4_ERR_INVALID, "negative token or row count");
+  if (num_tokens == 0 || num_reqs == 0) return NVFP4_OK;
+  if (!key || !value || !tail_key || !tail_value || !query_start_loc || !seq_lens || !seqused_fp4 || !row_to_slot)
+    return fail(NVFP4_ERR_INVALID, "tail_append: null argument");
+  if (heads_kv < 1) return fail(NVFP4_ERR_INVALID, "heads_kv must be positive");
+  const int64_t width = (int64_t)heads_kv * 128;
+  if (key_token_stride < width || value_token_stride < width || (key_token_stride % 8) ||
+      (value_token_stride % 8) || tail_slot_stride < 128 * width || !aligned16(key) ||
+      !aligned16(value) || !aligned16(tail_key) || !aligned16(tail_value) ||
+      (key_shift_bf16 && !aligned16(key_shift_bf16)))
+    return fail(NVFP4_ERR_INVALID, "tail_append: strides must cover a token and keep 16-byte alignment");
+  cudaError_t e = nvfp4::launch_tail_append(key, value, key_token_stride, value_token_stride,
+                                            key_shift_bf16, tail_key, tail_value, tail_slot_stride,
+                                            query_start_loc, seq_lens, seqused_fp4, row_to_slot,
+                                            num_tokens, num_reqs, heads_kv,
+                                            static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "tail_append launch");
+}
+
+int nvfp4_tail_reset(void* tail_key, void* tail_value, int64_t tail_layer_stride,
+                     int64_t tail_slot_stride, int layers, const int32_t* query_start_loc,
+                     const int32_t* seq_lens, const int32_t* row_to_slot, int num_reqs, int heads_kv,
+                     void* stream) {
+  if (layers < 0 || num_reqs < 0) return fail(NVFP4_ERR_INVALID, "negative layer or row count");
+  if (layers == 0 || num_reqs == 0) return NVFP4_OK;
+  if (!tail_key || !tail_value || !query_start_loc || !seq_lens || !row_to_slot)
+    return fail(NVFP4_ERR_INVALID, "tail_reset: null argument");
+  if (num_reqs > 65535) return fail(NVFP4_ERR_INVALID, "tail_reset: too many rows");
+  const int64_t width = (int64_t)heads_kv * 128;
+  if (heads_kv < 1 || tail_slot_stride < 128 * width || !aligned16(tail_key) || !aligned16(tail_value) ||
+      (tail_slot_stride % 8) || (tail_layer_stride % 8))
+    return fail(NVFP4_ERR_INVALID, "tail_reset: strides must cover a page and keep 16-byte alignment");
+  cudaError_t e = nvfp4::launch_tail_reset(tail_key, tail_value, tail_layer_stride, tail_slot_stride,
+                                           layers, query_start_loc, seq_lens, row_to_slot, num_reqs,
+                                           heads_kv, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "tail_reset launch");
+}
+
+int nvfp4_tail_flush(const void* tail_key, const void* tail_value, int64_t src_layer_stride,
+                     const int32_t* src_tokens, const int32_t* dst_pages, const int64_t* bases,
+                     int64_t k_pitch, int64_t k_sf_pitch, int64_t v_pitch, int64_t v_sf_pitch,
+                     int work, int layers, int heads_kv, void* stream) {
+  if (work < 0 || layers < 0) return fail(NVFP4_ERR_INVALID, "negative work or layer count");
+  if (work == 0 || layers == 0) return NVFP4_OK;
+  if (!tail_key || !tail_value || !src_tokens || !dst_pages || !bases)
+    return fail(NVFP4_ERR_INVALID, "tail_flush: null argument");
+  if (heads_kv < 1 || heads_kv > 128) return fail(NVFP4_ERR_INVALID, "heads_kv out of range: %d", heads_kv);
+  const int64_t dense_packed = (int64_t)128 * heads_kv * 64, dense_sf = (int64_t)heads_kv * 1024;
+  if (k_pitch < dense_packed || v_pitch < dense_packed || k_sf_pitch < dense_sf || v_sf_pitch < dense_sf ||
+      (k_pitch % 16) || (v_pitch % 16) || (k_sf_pitch % 16) || (v_sf_pitch % 16))
+    return fail(NVFP4_ERR_INVALID, "tail_flush: page pitches must cover a dense page and be 16-byte aligned");
+  if (!aligned16(tail_key) || !aligned16(tail_value))
+    return fail(NVFP4_ERR_INVALID, "tail_flush: tail buffers must be 16-byte aligned");
+  if (layers > 65535 || work > 65535) return fail(NVFP4_ERR_INVALID, "tail_flush: grid too large");
+  cudaError_t e = nvfp4::launch_tail_flush(tail_key, tail_value, src_layer_stride, src_tokens,
+                                           dst_pages, bases, k_pitch, k_sf_pitch, v_pitch, v_sf_pitch,
+                                           work, layers, heads_kv, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "tail_flush launch");
+}
+
+size_t nvfp4_decode_workspace_bytes(int rows, int heads_q, int num_splits) {
+  if (rows <= 0 || heads_q <= 0 || num_splits <= 1) return 0;
+  return (size_t)num_splits * rows * heads_q * (128 + 1) * sizeof(float);
+}
+
+int nvfp4_decode_impl_available(int impl, int heads_q, int heads_kv) {
+  if (!valid_group(heads_q, heads_kv)) return 0;
+  if (impl == NVFP4_IMPL_GENERIC || impl == NVFP4_IMPL_AUTO) return 1;
+  if (impl == NVFP4_IMPL_SM100) {
+    nvfp4::DecodeParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.heads_q = heads_q;
+    p.heads_kv = heads_kv;
+    return nvfp4::decode_sm100_supports(p) ? 1 : 0;
+  }
+  return 0;
+}
+
+int nvfp4_decode(const nvfp4_decode_args* a, void* stream) {
+  if (!a) return fail(NVFP4_ERR_INVALID, "decode: null argument block");
+  if (a->rows < 0) return fail(NVFP4_ERR_INVALID, "decode: negative row count");
+  if (a->rows == 0) return NVFP4_OK;
+  if (!valid_group(a->heads_q, a->heads_kv))
+    return fail(NVFP4_ERR_UNSUPPORTED,
+                "decode: heads_q/heads_kv = %d/%d; the ratio must be one of 1,2,4,8,16,32", a->heads_q,
+                a->heads_kv);
+  if (!(a->softmax_scale > 0.f) || !(a->softmax_scale < 3.0e38f))
+    return fail(NVFP4_ERR_INVALID, "softmax_scale must be finite and positive");
+  if (a->num_splits < 1 || a->num_splits > 1024)
+    return fail(NVFP4_ERR_INVALID, "num_splits must be in [1, 1024], got %d", a->num_splits);
+  if (!a->q_fp4 || !a->q_sf || !a->k_packed || !a->k_sf || !a->v_packed || !a->v_sf || !a->page_table ||
+      !a->seqused_fp4)
+    return fail(NVFP4_ERR_INVALID, "decode: a required pointer is null");
+  if (a->rows > 65535 || a->heads_kv > 65535)
+    return fail(NVFP4_ERR_INVALID, "decode: rows and heads_kv are limited to 65535");
+  const int64_t dense_packed = (int64_t)128 * a->heads_kv * 64, dense_sf = (int64_t)a->heads_kv * 1024;
+  if (a->k_pitch < dense_packed || a->v_pitch < dense_packed || (a->k_pitch % 16) || (a->v_pitch % 16))
+    return fail(NVFP4_ERR_INVALID, "decode: packed page pitch must be >= %lld bytes and 16-byte aligned",
+                (long long)dense_packed);
+  if (a->k_sf_pitch < dense_sf || a->v_sf_pitch < dense_sf || (a->k_sf_pitch % 16) || (a->v_sf_pitch % 16))
+    return fail(NVFP4_ERR_INVALID, "decode: scale page pitch must be >= %lld bytes and 16-byte aligned",
+                (long long)dense_sf);
+  if (!aligned16(a->q_fp4) || !aligned16(a->q_sf) || !aligned16(a->k_packed) || !aligned16(a->k_sf) ||
+      !aligned16(a->v_packed) || !aligned16(a->v_sf))
+    return fail(NVFP4_ERR_INVALID, "decode: query and page regions must be 16-byte aligned");
+  if (a->max_pages < 0 || a->page_table_row_stride < a->max_pages || a->num_pages < 0)
+    return fail(NVFP4_ERR_INVALID, "decode: page table extents are inconsistent");
+  const bool any_tail = a->tail_key || a->tail_value || a->tail_ids || a->seqused_tail;
+  const bool all_tail = a->tail_key && a->tail_value && a->tail_ids && a->seqused_tail;
+  if (any_tail && !all_tail)
+    return fail(NVFP4_ERR_INVALID, "decode: tail_key, tail_value, tail_ids and seqused_tail go together");
+  if (all_tail && (!aligned16(a->tail_key) || !aligned16(a->tail_value) || a->tail_pages < 1))
+    return fail(NVFP4_ERR_INVALID, "decode: tail buffers must be 16-byte aligned and non-empty");
+  if (a->q_bf16 && (!aligned16(a->q_bf16) || (a->q_bf16_row_stride % 8) || (a->q_bf16_head_stride % 8)))
+    return fail(NVFP4_ERR_INVALID, "decode: the BF16 query must keep 16-byte alignment");
+  if ((a->o_partial == nullptr) != (a->lse_partial == nullptr))
+    return fail(NVFP4_ERR_INVALID, "decode: o_partial and lse_partial go together");
+  if (!a->out && !a->o_partial)
+    return fail(NVFP4_ERR_INVALID, "decode: neither out nor the partial outputs were given");
+  if (a->out_indices && a->num_splits > 1)
+    return fail(NVFP4_ERR_INVALID, "decode: out_indices cannot be combined with num_splits > 1");
+
+  nvfp4::DecodeParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.q_fp4 = static_cast<const uint8_t*>(a->q_fp4);
+  p.q_sf = static_cast<const uint8_t*>(a->q_sf);
+  p.q_bf16 = static_cast<const uint16_t*>(a->q_bf16);
+  p.q_row_stride = a->q_bf16_row_stride;
+  p.q_head_stride = a->q_bf16_head_stride;
+  p.k_packed = static_cast<const uint8_t*>(a->k_packed); p.k_pitch = a->k_pitch;
+  p.k_sf = static_cast<const uint8_t*>(a->k_sf); p.k_sf_pitch = a->k_sf_pitch;
+  p.v_packed = static_cast<const uint8_t*>(a->v_packed); p.v_pitch = a->v_pitch;
+  p.v_sf = static_cast<const uint8_t*>(a->v_sf); p.v_sf_pitch = a->v_sf_pitch;
+  p.num_pages = a->num_pages;
+  p.page_table = a->page_table;
+  p.page_table_row_stride = a->page_table_row_stride;
+  p.max_pages = a->max_pages;
+  p.seqused_fp4 = a->seqused_fp4;
+  p.tail_key = static_cast<const uint16_t*>(a->tail_key);
+  p.tail_value = static_cast<const uint16_t*>(a->tail_value);
+  p.tail_pages = a->tail_pages;
+  p.tail_ids = a->tail_ids;
+  p.seqused_tail = a->seqused_tail;
+  p.rows = a->rows; p.heads_q = a->heads_q; p.heads_kv = a->heads_kv;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  p.num_splits = a->num_splits;
+  p.status = a->status;
+
+  float* o_part = a->o_partial;
+  float* lse_part = a->lse_partial;
+  const bool direct = a->num_splits == 1 && a->out != nullptr && !a->o_partial;
+  if (direct) {
+    p.emit_partial = 0;
+    p.out = static_cast<uint16_t*>(a->out);
+    p.out_indices = a->out_indices;
+  } else {
+    if (!o_part) {
+      const size_t need = nvfp4_decode_workspace_bytes(a->rows, a->heads_q, a->num_splits);
+      if (!a->workspace || a->workspace_bytes < need)
+        return fail(NVFP4_ERR_INVALID, "decode: num_splits=%d needs a workspace of %zu bytes, got %zu",
+                    a->num_splits, need, a->workspace_bytes);
+      if (!aligned16(a->workspace)) return fail(NVFP4_ERR_INVALID, "decode: workspace must be 16-byte aligned");
+      o_part = static_cast<float*>(a->workspace);
+      lse_part = o_part + (size_t)a->num_splits * a->rows * a->heads_q * 128;
+    }
+    p.emit_partial = 1;
+    p.o_partial = o_part;
+    p.lse_partial = lse_part;
+  }
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int impl = a->impl;
+  if (impl == NVFP4_IMPL_AUTO) impl = nvfp4::decode_sm100_supports(p) ? NVFP4_IMPL_SM100 : NVFP4_IMPL_GENERIC;
+  cudaError_t e;
+  if (impl == NVFP4_IMPL_SM100) {
+    if (!nvfp4::decode_sm100_supports(p))
+      return fail(NVFP4_ERR_UNSUPPORTED, "decode: the tensor-core kernel takes at most 8 query heads per KV head");
+    e = nvfp4::launch_decode_sm100(p, st);
+  } else if (impl == NVFP4_IMPL_GENERIC) {
+    e = nvfp4::launch_decode_generic(p, st);
+  } else {
+    return fail(NVFP4_ERR_INVALID, "decode: unknown impl %d", a->impl);
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "decode launch");
+
+  if (!direct && a->out) {
+    e = nvfp4::launch_lse_merge(o_part, (int64_t)a->rows * a->heads_q * 128, lse_part,
+                                (int64_t)a->rows * a->heads_q, nullptr, nullptr, a->num_splits,
+                                a->rows, a->heads_q, a->out, 0, a->out_indices, nullptr, st);
+    if (e != cudaSuccess) return cuda_fail(e, "lse_merge launch");
+  }
+  return NVFP4_OK;
+}
+
+int nvfp4_lse_merge(const float* o_parts, int64_t o_split_stride, const float* lse_parts,
+                    int64_t lse_split_stride, int num_splits, int rows, int heads_q, void* out,
+                    int out_is_f32, const int32_t* out_indices, float* lse_out, void* stream) {
+  if (rows < 0 || heads_q < 1 || num_splits < 1)
+    return fail(NVFP4_ERR_INVALID, "lse_merge: bad extents (%d rows, %d heads, %d splits)", rows, heads_q, num_splits);
+  if (rows == 0) return NVFP4_OK;
+  if (!o_parts || !lse_parts || (!out && !lse_out)) return fail(NVFP4_ERR_INVALID, "lse_merge: null argument");
+  if (rows > 65535) return fail(NVFP4_ERR_INVALID, "lse_merge: too many rows");
+  cudaError_t e = nvfp4::launch_lse_merge(o_parts, o_split_stride, lse_parts, lse_split_stride, nullptr,
+                                          nullptr, num_splits, rows, heads_q, out, out_is_f32,
+                                          out_indices, lse_out, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "lse_merge launch");
+}
+
+int nvfp4_lse_merge_ptrs(const float* const* o_part_ptrs, const float* const* lse_part_ptrs,
+                         int num_splits, int rows, int heads_q, void* out, int out_is_f32,
+                         const int32_t* out_indices, float* lse_out, void* stream) {
+  if (rows < 0 || heads_q < 1 || num_splits < 1)
+    return fail(NVFP4_ERR_INVALID, "lse_merge_ptrs: bad extents (%d rows, %d heads, %d splits)", rows, heads_q, num_splits);
+  if (rows == 0) return NVFP4_OK;
+  if (!o_part_ptrs || !lse_part_ptrs || (!out && !lse_out))
+    return fail(NVFP4_ERR_INVALID, "lse_merge_ptrs: null argument");
+  if (rows > 65535) return fail(NVFP4_ERR_INVALID, "lse_merge_ptrs: too many rows");
+  cudaError_t e = nvfp4::launch_lse_merge(nullptr, 0, nullptr, 0, o_part_ptrs, lse_part_ptrs, num_splits,
+                                          rows, heads_q, out, out_is_f32, out_indices, lse_out,
+                                          static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "lse_merge_ptrs launch");
+}
+
+}  // extern "C"

@@ -1,0 +1,184 @@
+// Pieces shared by the two decode kernels: work decomposition, the BF16 tail
+// block (CUDA cores), block-wide reductions over the 128 softmax threads and the
+// epilogue.  Thread t of the 128 plays two roles: "kv position t of the current
+// block" while scores are formed, and "output channel d = t" while P.V is
+// accumulated, so neither role needs a transpose of the G x 128 score tile.
+#pragma once
+
+#include "nvfp4_common.cuh"
+#include "nvfp4_kernels.h"
+#include "../../include/nvfp4_b200.h"
+
+namespace nvfp4 {
+
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct TileWork {
+  int row, kvh, split;
+  int first_page, last_page;  // logical FP4 pages [first, last) owned by this split
+  int tail_len;               // BF16 tail tokens owned by this split (0 if none)
+  int tail_id;
+};
+
+__device__ __forceinline__ void set_status(uint32_t* status, uint32_t bit) {
+  if (status) atomicOr(status, bit);
+}
+
+// Resolve what this CTA owns.  Metadata is device-resident and, on the trusted
+// path, unchecked by the host: anything out of range is clamped, flagged in the
+// sticky status word and never turned into an address.
+__device__ __forceinline__ TileWork resolve_work(const DecodeParams& p, int row, int kvh, int split) {
+  TileWork w;
+  w.row = row; w.kvh = kvh; w.split = split;
+  int fp4 = p.seqused_fp4[row];
+  int n = fp4 >> 7;
+  if (fp4 < 0 || (fp4 & 127) || n > p.max_pages) {
+    set_status(p.status, NVFP4_STATUS_BAD_LENGTH);
+    n = fp4 < 0 ? 0 : (n > p.max_pages ? p.max_pages : n);
+  }
+  const int per = (n + p.num_splits - 1) / p.num_splits;
+  w.first_page = min(split * per, n);
+  w.last_page = min((split + 1) * per, n);
+  w.tail_len = 0;
+  w.tail_id = -1;
+  if (split == 0 && p.tail_key != nullptr && p.seqused_tail != nullptr) {
+    int len = p.seqused_tail[row];
+    if (len > 0) {
+      if (len > kPage) { set_status(p.status, NVFP4_STATUS_BAD_LENGTH); len = kPage; }
+      const int id = p.tail_ids[row];
+      if (id < 0 || (int64_t)id >= p.tail_pages) {
+        set_status(p.status, NVFP4_STATUS_BAD_TAIL_ID);
+      } else {
+        w.tail_len = len;
+        w.tail_id = id;
+      }
+    }
+  }
+  return w;
+}
+
+// max over the 128 softmax threads of G per-thread values; red is [4][G] floats.
+// Every one of the 128 threads must call; uses barrier `bar_id` with 128 threads.
+template <int G>
+__device__ __forceinline__ void block_max_128(float (&v)[G], float* red, int tid, int bar_id) {
+  const int warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+  for (int q = 0; q < G; ++q) {
+    const float w = warp_max(v[q]);
+    if (lane == 0) red[warp * G + q] = w;
+  }
+  asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+#pragma unroll
+  for (int q = 0; q < G; ++q)
+    v[q] = fmaxf(fmaxf(red[q], red[G + q]), fmaxf(red[2 * G + q], red[3 * G + q]));
+  asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+}
+
+template <int G>
+__device__ __forceinline__ void block_sum_128(float (&v)[G], float* red, int tid, int bar_id) {
+  const int warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+  for (int q = 0; q < G; ++q) {
+    const float w = warp_sum(v[q]);
+    if (lane == 0) red[warp * G + q] = w;
+  }
+  asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+#pragma unroll
+  for (int q = 0; q < G; ++q) v[q] = (red[q] + red[G + q]) + (red[2 * G + q] + red[3 * G + q]);
+  asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+}
+
+// exp2 of (z - m) with the conventions of the oracle: a masked position
+// (z = -inf) gives 0 even when the running maximum is still -inf.
+__device__ __forceinline__ float exp2_rel(float z, float m) {
+  return (m == -INFINITY) ? 0.f : exp2f(z - m);
+}
+
+// The BF16 tail block.  Seeds the running max m, the per-thread partial sums l
+// and the per-thread output accumulators o (thread = channel).
+//   qb : [G][128] floats, the BF16 query of this KV head's G query heads
+//   pf : [G][128] floats scratch for P
+template <int G>
+__device__ __forceinline__ void tail_block(const DecodeParams& p, const TileWork& w, const float* qb,
+                                           float* pf, float* red, int tid, int bar_id,
+                                           float (&m)[G], float (&l)[G], float (&o)[G]) {
+  const int len = w.tail_len;
+  const int64_t tok0 = (int64_t)w.tail_id * kPage;
+  float z[G];
+#pragma unroll
+  for (int q = 0; q < G; ++q) z[q] = -INFINITY;
+  if (tid < len) {
+    const uint4* krow = reinterpret_cast<const uint4*>(
+        p.tail_key + ((tok0 + tid) * p.heads_kv + w.kvh) * kHeadDim);
+    float acc[G];
+#pragma unroll
+    for (int q = 0; q < G; ++q) acc[q] = 0.f;
+#pragma unroll 4
+    for (int c = 0; c < 16; ++c) {
+      float kf[8];
+      unpack_bf16x8(__ldg(krow + c), kf);
+#pragma unroll
+      for (int q = 0; q < G; ++q) {
+        const float4 qa = *reinterpret_cast<const float4*>(qb + q * kHeadDim + c * 8);
+        const float4 qc = *reinterpret_cast<const float4*>(qb + q * kHeadDim + c * 8 + 4);
+        acc[q] = fmaf(kf[0], qa.x, acc[q]); acc[q] = fmaf(kf[1], qa.y, acc[q]);
+        acc[q] = fmaf(kf[2], qa.z, acc[q]); acc[q] = fmaf(kf[3], qa.w, acc[q]);
+        acc[q] = fmaf(kf[4], qc.x, acc[q]); acc[q] = fmaf(kf[5], qc.y, acc[q]);
+        acc[q] = fmaf(kf[6], qc.z, acc[q]); acc[q] = fmaf(kf[7], qc.w, acc[q]);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < G; ++q) z[q] = acc[q] * p.scale_log2;
+  }
+  float bm[G];
+#pragma unroll
+  for (int q = 0; q < G; ++q) bm[q] = z[q];
+  block_max_128<G>(bm, red, tid, bar_id);
+#pragma unroll
+  for (int q = 0; q < G; ++q) {
+    m[q] = bm[q];
+    const float pe = exp2_rel(z[q], bm[q]);
+    l[q] = pe;
+    // P of the tail meets V as BF16
+    pf[q * kHeadDim + tid] = __bfloat162float(__float2bfloat16_rn(pe));
+  }
+  asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+  // thread = channel d; positions past the tail length are never read, so stale
+  // or non-finite bytes there cannot reach the output.
+  const uint16_t* vcol = p.tail_value + (tok0 * p.heads_kv + w.kvh) * kHeadDim + tid;
+  const int64_t vstride = (int64_t)p.heads_kv * kHeadDim;
+#pragma unroll
+  for (int q = 0; q < G; ++q) o[q] = 0.f;
+#pragma unroll 4
+  for (int t = 0; t < len; ++t) {
+    const float v = bf16_bits_to_f32(__ldg(vcol + t * vstride));
+#pragma unroll
+    for (int q = 0; q < G; ++q) o[q] = fmaf(pf[q * kHeadDim + t], v, o[q]);
+  }
+  asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+}
+
+// Normalise and store.  l holds per-thread partial sums; o per-channel sums.
+template <int G>
+__device__ __forceinline__ void write_output(const DecodeParams& p, const TileWork& w, float* red,
+                                             int tid, int bar_id, const float (&m)[G],
+                                             float (&l)[G], const float (&o)[G]) {
+  block_sum_128<G>(l, red, tid, bar_id);
+#pragma unroll
+  for (int q = 0; q < G; ++q) {
+    const int head = w.kvh * G + q;
+    const float val = l[q] > 0.f ? __fdiv_rn(o[q], l[q]) : 0.f;
+    if (p.emit_partial) {
+      const int64_t idx = ((int64_t)w.split * p.rows + w.row) * p.heads_q + head;
+      p.o_partial[idx * kHeadDim + tid] = val;
+      if (tid == 0)
+        p.lse_partial[idx] = l[q] > 0.f ? (m[q] + log2f(l[q])) * kLn2 : -INFINITY;
+    } else {
+      const int64_t orow = p.out_indices ? (int64_t)p.out_indices[w.row] : (int64_t)w.row;
+      p.out[(orow * p.heads_q + head) * kHeadDim + tid] =
+          __bfloat16_as_ushort(__float2bfloat16_rn(val));
+    }
+  }
+}
+
+}  // namespace nvfp4

@@ -1,0 +1,64 @@
+// LSE merge of split-KV partials: lse = log sum_s exp(lse_s), O = sum_s exp(lse_s - lse) O_s.
+// One CTA of 128 threads (one per channel) per (query head, row); splits are folded in
+// index order, so the result is bitwise reproducible.  The partials may sit at a uniform
+// split stride or behind one pointer per split (buffers of peer GPUs mapped into this
+// process are read with plain loads).
+#include "decode_common.cuh"
+
+namespace nvfp4 {
+
+template <bool kOutF32>
+__global__ void __launch_bounds__(128)
+lse_merge_kernel(const float* __restrict__ o_parts, int64_t o_split_stride,
+                 const float* __restrict__ lse_parts, int64_t lse_split_stride,
+                 const float* const* __restrict__ o_ptrs, const float* const* __restrict__ lse_ptrs,
+                 int num_splits, int rows, int heads_q, void* __restrict__ out,
+                 const int32_t* __restrict__ out_indices, float* __restrict__ lse_out) {
+  const int head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
+  const int64_t idx = (int64_t)row * heads_q + head;
+  float mx = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) {
+    const float* lp = lse_ptrs ? lse_ptrs[s] : lse_parts + s * lse_split_stride;
+    mx = fmaxf(mx, lp[idx]);
+  }
+  float acc = 0.f, tot = 0.f;
+  if (mx != -INFINITY) {
+    for (int s = 0; s < num_splits; ++s) {
+      const float* lp = lse_ptrs ? lse_ptrs[s] : lse_parts + s * lse_split_stride;
+      const float* op = o_ptrs ? o_ptrs[s] : o_parts + s * o_split_stride;
+      const float ls = lp[idx];
+      if (ls == -INFINITY) continue;  // an empty split weighs nothing, whatever its O holds
+      const float wgt = expf(ls - mx);
+      tot += wgt;
+      acc = fmaf(wgt, op[idx * kHeadDim + d], acc);
+    }
+  }
+  const float val = tot > 0.f ? __fdiv_rn(acc, tot) : 0.f;
+  if (out) {
+    const int64_t orow = out_indices ? (int64_t)out_indices[row] : (int64_t)row;
+    const int64_t at = (orow * heads_q + head) * kHeadDim + d;
+    if (kOutF32) static_cast<float*>(out)[at] = val;
+    else static_cast<uint16_t*>(out)[at] = __bfloat16_as_ushort(__float2bfloat16_rn(val));
+  }
+  if (lse_out && d == 0) lse_out[idx] = tot > 0.f ? mx + logf(tot) : -INFINITY;
+}
+
+cudaError_t launch_lse_merge(const float* o_parts, int64_t o_split_stride, const float* lse_parts,
+                             int64_t lse_split_stride, const float* const* o_ptrs,
+                             const float* const* lse_ptrs, int num_splits, int rows, int heads_q,
+                             void* out, int out_is_f32, const int32_t* out_indices,
+                             float* lse_out, cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  dim3 grid(heads_q, rows);
+  if (out_is_f32)
+    lse_merge_kernel<true><<<grid, 128, 0, stream>>>(o_parts, o_split_stride, lse_parts,
+                                                     lse_split_stride, o_ptrs, lse_ptrs, num_splits,
+                                                     rows, heads_q, out, out_indices, lse_out);
+  else
+    lse_merge_kernel<false><<<grid, 128, 0, stream>>>(o_parts, o_split_stride, lse_parts,
+                                                      lse_split_stride, o_ptrs, lse_ptrs, num_splits,
+                                                      rows, heads_q, out, out_indices, lse_out);
+  return cudaGetLastError();
+}
+
+}  // namespace nvfp4

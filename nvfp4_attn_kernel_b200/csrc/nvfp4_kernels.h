@@ -1,0 +1,83 @@
+// Internal launcher declarations shared by the .cu translation units and the C ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace nvfp4 {
+
+cudaError_t launch_quantize_q(const void* q, int64_t row_stride, int64_t head_stride,
+                              const int32_t* row_indices, void* q_fp4, void* q_sf, void* q_padded,
+                              int rows, int heads_q, int heads_kv, cudaStream_t stream);
+
+cudaError_t launch_quantize_k(const void* tokens, int64_t token_stride, const void* key_shift,
+                              void* packed, int64_t packed_pitch, void* sf, int64_t sf_pitch,
+                              const int32_t* src_tokens, const int32_t* dst_pages,
+                              const int64_t* packed_bases, const int64_t* sf_bases, int work,
+                              int layers, int64_t src_layer_stride, int heads_kv,
+                              cudaStream_t stream);
+
+cudaError_t launch_quantize_v(const void* tokens, int64_t token_stride, void* packed,
+                              int64_t packed_pitch, void* sf, int64_t sf_pitch,
+                              const int32_t* src_tokens, const int32_t* dst_pages,
+                              const int64_t* packed_bases, const int64_t* sf_bases, int work,
+                              int layers, int64_t src_layer_stride, int heads_kv,
+                              cudaStream_t stream);
+
+cudaError_t launch_tail_append(const void* key, const void* value, int64_t key_token_stride,
+                               int64_t value_token_stride, const void* key_shift, void* tail_key,
+                               void* tail_value, int64_t tail_slot_stride,
+                               const int32_t* query_start_loc, const int32_t* seq_lens,
+                               const int32_t* seqused_fp4, const int32_t* row_to_slot,
+                               int num_tokens, int num_reqs, int heads_kv, cudaStream_t stream);
+
+cudaError_t launch_tail_reset(void* tail_key, void* tail_value, int64_t layer_stride,
+                              int64_t slot_stride, int layers, const int32_t* query_start_loc,
+                              const int32_t* seq_lens, const int32_t* row_to_slot, int num_reqs,
+                              int heads_kv, cudaStream_t stream);
+
+cudaError_t launch_tail_flush(const void* tail_key, const void* tail_value,
+                              int64_t src_layer_stride, const int32_t* src_tokens,
+                              const int32_t* dst_pages, const int64_t* bases, int64_t k_pitch,
+                              int64_t k_sf_pitch, int64_t v_pitch, int64_t v_sf_pitch, int work,
+                              int layers, int heads_kv, cudaStream_t stream);
+
+// Everything a decode kernel needs, by value.
+struct DecodeParams {
+  const uint8_t* q_fp4;
+  const uint8_t* q_sf;
+  const uint16_t* q_bf16;  // nullable
+  int64_t q_row_stride, q_head_stride;
+  const uint8_t* k_packed; int64_t k_pitch;
+  const uint8_t* k_sf; int64_t k_sf_pitch;
+  const uint8_t* v_packed; int64_t v_pitch;
+  const uint8_t* v_sf; int64_t v_sf_pitch;
+  int64_t num_pages;
+  const int32_t* page_table; int64_t page_table_row_stride; int max_pages;
+  const int32_t* seqused_fp4;
+  const uint16_t* tail_key; const uint16_t* tail_value; int64_t tail_pages;
+  const int32_t* tail_ids; const int32_t* seqused_tail;
+  uint16_t* out; const int32_t* out_indices;  // bf16 out (only when num_splits == 1)
+  float* o_partial; float* lse_partial;       // partial outputs (when emit_partial)
+  int rows, heads_q, heads_kv;
+  float scale_log2;  // softmax_scale * log2(e)
+  int num_splits;
+  int emit_partial;  // 1: write (O normalised fp32, LSE) per split; 0: write bf16 out
+  uint32_t* status;
+};
+
+// CUDA-core kernel: any G = Hq/Hkv in {1,2,4,8,16,32}.
+cudaError_t launch_decode_generic(const DecodeParams& p, cudaStream_t stream);
+
+// tcgen05 kernel: G <= 8.  Returns cudaErrorNotSupported when the shape is outside it.
+cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream);
+bool decode_sm100_supports(const DecodeParams& p);
+
+cudaError_t launch_lse_merge(const float* o_parts, int64_t o_split_stride, const float* lse_parts,
+                             int64_t lse_split_stride, const float* const* o_ptrs,
+                             const float* const* lse_ptrs, int num_splits, int rows, int heads_q,
+                             void* out, int out_is_f32, const int32_t* out_indices,
+                             float* lse_out, cudaStream_t stream);
+
+}  // namespace nvfp4

@@ -1,0 +1,468 @@
+"""Host side of the paged NVFP4 decode: contract checks and the launch.
+
+Mirrors ``decode_fp4`` / ``decode_fp4_split`` / ``split_k_heuristic`` of the
+reference project (``src/nvfp4_decode_kernel/_decode.py:28-86,532-1171``): the
+same tensor contracts are enforced with the same complaints, then the work is
+handed to ``nvfp4_decode`` of the C ABI on torch's current stream.  With
+``trusted_metadata=True`` nothing is read back from the device.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import _lib
+
+PAGE_SIZE = 128
+HEAD_DIM = 128
+
+# NVFP4_IMPL_* of the C ABI; tests flip this to compare the two decode kernels.
+DEFAULT_IMPL = _lib.IMPL_AUTO
+
+
+def split_k_heuristic(rows: int, heads_kv: int, max_pages_per_row: int, *, sms: int) -> int:
+    """Pick a power-of-two split count for a pure-FP4 decode by predicted makespan.
+
+    Model: one CTA per (row, KV head, split); a launch takes
+    ``ceil(ctas / sms)`` scheduling rounds and each round costs the pages one CTA
+    walks plus a fixed pipeline fill of 8 page-times.  A split is accepted only
+    if it beats the unsplit makespan by more than 20 %, and among equals the
+    smallest count wins.  ``max_pages_per_row`` is the page table's width, not
+    the device-side lengths, so callers should size the table to the batch.
+    """
+    if rows < 1 or heads_kv < 1 or max_pages_per_row < 2 or sms < 1:
+        return 1
+    tiles = rows * heads_kv
+    fill = 8
+
+    def cost(splits: int) -> int:
+        return math.ceil(tiles * splits / sms) * (math.ceil(max_pages_per_row / splits) + fill)
+
+    best, best_cost = 1, None
+    for splits in (2, 4, 8, 16, 32):
+        if 2 * splits > max_pages_per_row:
+            break
+        c = cost(splits)
+        if best_cost is None or c < best_cost:
+            best, best_cost = splits, c
+    if best_cost is None or best_cost * 6 >= cost(1) * 5:
+        return 1
+    return best
+
+
+def _need_cuda(tensor: torch.Tensor, name: str, device: torch.device) -> None:
+    if not tensor.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if tensor.device != device:
+        raise ValueError(f"{name} must be on {device}, got {tensor.device}")
+
+
+def _scale_bytes(scales: torch.Tensor, name: str) -> torch.Tensor:
+    if scales.dtype is torch.uint8:
+        return scales
+    if scales.dtype is torch.float8_e4m3fn:
+        return scales.view(torch.uint8)
+    raise ValueError(f"{name} must contain E4M3 scale-factor bytes")
+
+
+def _page_pitch_bytes(pages: torch.Tensor, name: str) -> int:
+    """Dense below the page axis, free (>= dense, 16-byte aligned) page stride."""
+    itemsize = pages.element_size()
+    dense = 1
+    for axis in range(pages.ndim - 1, 0, -1):
+        if pages.stride(axis) != dense:
+            raise ValueError(
+                f"{name} must be densely packed within a page; axis {axis} has "
+                f"stride {pages.stride(axis)}, expected {dense}"
+            )
+        dense *= pages.shape[axis]
+    pitch = pages.stride(0)
+    if pitch < dense or (pitch * itemsize) % 16:
+        raise ValueError(
+            f"{name} needs a page stride of at least {dense} elements, "
+            f"aligned to 16 bytes, got {pitch}"
+        )
+    return pitch * itemsize
+
+
+def _scale_pitch_bytes(scales: torch.Tensor, name: str) -> int:
+    _, _, _, rest_m, _, rest_k, heads = scales.shape
+    head_stride = rest_m * rest_k * 512
+    pitch = scales.stride(0)
+    if scales.stride() != (pitch, 16, 4, rest_k * 512, 1, 512, head_stride):
+        raise ValueError(f"{name} must use the scale layout returned by the K/V quantizer")
+    if pitch < heads * head_stride or pitch % 512:
+        raise ValueError(
+            f"{name} needs a page stride of at least {heads * head_stride} bytes, "
+            f"aligned to 512, got {pitch}"
+        )
+    return pitch
+
+
+def _any(condition: torch.Tensor, message: str) -> None:
+    if bool(torch.any(condition).item()):
+        raise ValueError(message)
+
+
+def decode_fp4(
+    *,
+    query_fp4: torch.Tensor,
+    query_scales: torch.Tensor,
+    query_padded_bf16: torch.Tensor | None,
+    key_pages_fp4: torch.Tensor,
+    key_scales: torch.Tensor,
+    value_pages_fp4: torch.Tensor,
+    value_scales: torch.Tensor,
+    fp4_page_table: torch.Tensor,
+    seqused_fp4: torch.Tensor,
+    residual_key_pages_bf16: torch.Tensor | None = None,
+    residual_value_pages_bf16: torch.Tensor | None = None,
+    residual_page_ids: torch.Tensor | None = None,
+    seqused_residual: torch.Tensor | None = None,
+    has_bf16: torch.Tensor | None = None,
+    softmax_scale: float,
+    out: torch.Tensor | None = None,
+    out_indices: torch.Tensor | None = None,
+    trusted_metadata: bool = False,
+    validate_only: bool = False,
+    num_splits: int = 1,
+    status: torch.Tensor | None = None,
+    _partials: tuple[torch.Tensor, torch.Tensor] | None = None,
+) -> torch.Tensor | None:
+    """Validate every tensor contract and launch the decode on the current stream.
+
+    ``query_padded_bf16`` (``[rows, 128, heads_q, 128]``, row 0 of each tile live)
+    carries the BF16 query that meets the BF16 residual page.
+    """
+    if not torch.cuda.is_available():
+        raise RuntimeError("decode_fp4 requires CUDA")
+    if not math.isfinite(softmax_scale) or softmax_scale <= 0.0:
+        raise ValueError("softmax_scale must be finite and positive")
+    if query_fp4.ndim != 4:
+        raise ValueError("query_fp4 must have shape [rows, 1, heads_q, 64]")
+    device = query_fp4.device
+    _need_cuda(query_fp4, "query_fp4", device)
+    if torch.cuda.get_device_capability(device)[0] != 10:
+        raise RuntimeError("decode_fp4 requires an SM100 CUDA device")
+    fp4_dtype = torch.float4_e2m1fn_x2
+    if query_fp4.dtype is not fp4_dtype or not query_fp4.is_contiguous():
+        raise ValueError("query_fp4 must be contiguous packed E2M1 FP4")
+    rows, query_len, heads_q, packed_dim = query_fp4.shape
+    if rows < 1 or query_len != 1 or packed_dim * 2 != HEAD_DIM:
+        raise ValueError("query_fp4 must have shape [rows, 1, heads_q, 64]")
+
+    for tensor, name in (
+        (key_pages_fp4, "key_pages_fp4"),
+        (value_pages_fp4, "value_pages_fp4"),
+        (query_scales, "query_scales"),
+        (key_scales, "key_scales"),
+        (value_scales, "value_scales"),
+        (fp4_page_table, "fp4_page_table"),
+        (seqused_fp4, "seqused_fp4"),
+    ):
+        _need_cuda(tensor, name, device)
+
+    packed_types = (torch.uint8, fp4_dtype)
+    if (
+        key_pages_fp4.dtype not in packed_types
+        or key_pages_fp4.ndim != 4
+        or key_pages_fp4.shape[1] != PAGE_SIZE
+        or key_pages_fp4.shape[3] * 2 != HEAD_DIM
+    ):
+        raise ValueError("key_pages_fp4 must be packed FP4 with shape [pages, 128, heads_kv, 64]")
+    page_count, _, heads_kv, _ = key_pages_fp4.shape
+    if value_pages_fp4.dtype not in packed_types or tuple(value_pages_fp4.shape) != (
+        page_count, heads_kv, HEAD_DIM, PAGE_SIZE // 2,
+    ):
+        raise ValueError("value_pages_fp4 must be packed FP4 with shape [pages, heads_kv, 128, 64]")
+    k_pitch = _page_pitch_bytes(key_pages_fp4, "key_pages_fp4")
+    v_pitch = _page_pitch_bytes(value_pages_fp4, "value_pages_fp4")
+    if heads_kv < 1 or heads_q % heads_kv:
+        raise ValueError("heads_q must be divisible by heads_kv")
+    group = heads_q // heads_kv
+    if PAGE_SIZE % group:
+        raise ValueError("128 must be divisible by the query-heads-per-KV-head ratio")
+
+    want_q_sf = (32, 4, 1, 4, 2, heads_kv, rows)
+    want_page_sf = (page_count, 32, 4, 1, 4, 2, heads_kv)
+    if tuple(query_scales.shape) != want_q_sf:
+        raise ValueError(f"query_scales must have shape {want_q_sf}")
+    if query_scales.stride() != (16, 4, heads_q * 1024, 1, 512, 1024, heads_q * 1024):
+        raise ValueError("query_scales must use the layout returned by quantize_query")
+    if tuple(key_scales.shape) != want_page_sf:
+        raise ValueError(f"key_scales must have shape {want_page_sf}")
+    if tuple(value_scales.shape) != want_page_sf:
+        raise ValueError(f"value_scales must have shape {want_page_sf}")
+    query_scales = _scale_bytes(query_scales, "query_scales")
+    key_scales = _scale_bytes(key_scales, "key_scales")
+    value_scales = _scale_bytes(value_scales, "value_scales")
+    if query_scales.storage_offset() != 0:
+        raise ValueError("query_scales must start at storage offset zero")
+    k_sf_pitch = _scale_pitch_bytes(key_scales, "key_scales")
+    v_sf_pitch = _scale_pitch_bytes(value_scales, "value_scales")
+
+    if (
+        fp4_page_table.dtype is not torch.int32
+        or fp4_page_table.ndim != 2
+        or fp4_page_table.shape[0] != rows
+        or (fp4_page_table.shape[1] > 1 and fp4_page_table.stride(-1) != 1)
+    ):
+        raise ValueError("fp4_page_table must be row-major INT32 with shape [rows, max_pages]")
+    if (
+        seqused_fp4.dtype is not torch.int32
+        or tuple(seqused_fp4.shape) != (rows,)
+        or not seqused_fp4.is_contiguous()
+    ):
+        raise ValueError("seqused_fp4 must be contiguous INT32 with shape [rows]")
+    max_tokens = fp4_page_table.shape[1] * PAGE_SIZE
+    if not trusted_metadata:
+        _any(
+            (seqused_fp4 < 0) | (seqused_fp4 > max_tokens) | (seqused_fp4 % PAGE_SIZE != 0),
+            f"seqused_fp4 values must be page-aligned and in [0, {max_tokens}]",
+        )
+
+    residual = (residual_key_pages_bf16, residual_value_pages_bf16, residual_page_ids,
+                seqused_residual)
+    has_residual = any(item is not None for item in residual)
+    if has_residual and not all(item is not None for item in residual):
+        raise ValueError(
+            "residual_key_pages_bf16, residual_value_pages_bf16, "
+            "residual_page_ids, and seqused_residual must be provided together"
+        )
+    if has_residual:
+        if query_padded_bf16 is None:
+            raise ValueError(
+                "pre-quantized query with a BF16 residual requires "
+                "query_padded_bf16 support; use the BF16 query path"
+            )
+        _need_cuda(query_padded_bf16, "query_padded_bf16", device)
+        want_padded = (rows, PAGE_SIZE, heads_q, HEAD_DIM)
+        if (
+            query_padded_bf16.dtype is not torch.bfloat16
+            or tuple(query_padded_bf16.shape) != want_padded
+            or not query_padded_bf16.is_contiguous()
+        ):
+            raise ValueError(
+                f"query_padded_bf16 must be contiguous BF16 with shape {want_padded}"
+            )
+        for tensor, name in (
+            (residual_key_pages_bf16, "residual_key_pages_bf16"),
+            (residual_value_pages_bf16, "residual_value_pages_bf16"),
+            (residual_page_ids, "residual_page_ids"),
+            (seqused_residual, "seqused_residual"),
+        ):
+            _need_cuda(tensor, name, device)
+        if residual_key_pages_bf16.ndim != 4:
+            raise ValueError(
+                "residual_key_pages_bf16 must be contiguous BF16 with "
+                "shape [pages, 128, heads_kv, 128]"
+            )
+        residual_pages = residual_key_pages_bf16.shape[0]
+        want_residual = (residual_pages, PAGE_SIZE, heads_kv, HEAD_DIM)
+        if (
+            residual_key_pages_bf16.dtype is not torch.bfloat16
+            or tuple(residual_key_pages_bf16.shape) != want_residual
+            or not residual_key_pages_bf16.is_contiguous()
+        ):
+            raise ValueError(
+                "residual_key_pages_bf16 must be contiguous BF16 with "
+                "shape [pages, 128, heads_kv, 128]"
+            )
+        if (
+            residual_value_pages_bf16.dtype is not torch.bfloat16
+            or tuple(residual_value_pages_bf16.shape) != want_residual
+            or not residual_value_pages_bf16.is_contiguous()
+        ):
+            raise ValueError("residual_value_pages_bf16 must match the residual K cache")
+        for tensor, name in ((residual_page_ids, "residual_page_ids"),
+                             (seqused_residual, "seqused_residual")):
+            if (
+                tensor.dtype is not torch.int32
+                or tuple(tensor.shape) != (rows,)
+                or not tensor.is_contiguous()
+            ):
+                raise ValueError(f"{name} must be contiguous INT32 with shape [rows]")
+        if not trusted_metadata:
+            _any(
+                (residual_page_ids < 0) | (residual_page_ids >= residual_pages),
+                "residual_page_ids contains an out-of-range physical page ID",
+            )
+            _any(
+                (seqused_residual < 0) | (seqused_residual > PAGE_SIZE),
+                "seqused_residual values must be in [0, 128]",
+            )
+        if has_bf16 is not None:
+            _need_cuda(has_bf16, "has_bf16", device)
+            if (
+                has_bf16.dtype is not torch.bool
+                or tuple(has_bf16.shape) != (rows,)
+                or not has_bf16.is_contiguous()
+            ):
+                raise ValueError("has_bf16 must be contiguous BOOL with shape [rows]")
+            if not trusted_metadata:
+                _any(has_bf16 != (seqused_residual > 0),
+                     "has_bf16 must agree with seqused_residual > 0")
+    elif has_bf16 is not None:
+        raise ValueError("has_bf16 requires the BF16 residual cache arguments")
+
+    if out is None and out_indices is not None:
+        raise ValueError("out_indices needs the out it indexes into")
+    if out is not None:
+        _need_cuda(out, "out", device)
+        if (
+            out.dtype is not torch.bfloat16
+            or out.ndim != 3
+            or tuple(out.shape[1:]) != (heads_q, HEAD_DIM)
+            or not out.is_contiguous()
+        ):
+            raise ValueError("out must be contiguous BF16 with shape [output_rows, heads_q, 128]")
+        if out_indices is None:
+            if out.shape[0] < rows:
+                raise ValueError(
+                    f"out needs at least {rows} rows when no out_indices say "
+                    f"where they go, found {out.shape[0]}"
+                )
+        else:
+            _need_cuda(out_indices, "out_indices", device)
+            if (
+                out_indices.dtype is not torch.int32
+                or tuple(out_indices.shape) != (rows,)
+                or not out_indices.is_contiguous()
+            ):
+                raise ValueError("out_indices must be contiguous INT32 with shape [rows]")
+            if not trusted_metadata:
+                _any((out_indices < 0) | (out_indices >= out.shape[0]),
+                     "out_indices contains an out-of-range output row")
+    if status is not None and (
+        status.dtype is not torch.int32 or status.numel() != 1 or status.device != device
+    ):
+        raise ValueError("status must be a one-element INT32 tensor on the query's device")
+
+    if validate_only:
+        return None
+
+    if out is None and _partials is None:
+        out = torch.empty(rows, heads_q, HEAD_DIM, dtype=torch.bfloat16, device=device)
+    workspace = None
+    if num_splits > 1 and _partials is None:
+        need = _lib.load().nvfp4_decode_workspace_bytes(rows, heads_q, num_splits)
+        workspace = torch.empty(need, dtype=torch.uint8, device=device)
+
+    args = _lib.DecodeArgs()
+    args.q_fp4 = query_fp4.data_ptr()
+    args.q_sf = query_scales.data_ptr()
+    if query_padded_bf16 is not None:
+        args.q_bf16 = query_padded_bf16.data_ptr()
+        args.q_bf16_row_stride = query_padded_bf16.stride(0)
+        args.q_bf16_head_stride = query_padded_bf16.stride(2)
+    args.k_packed = key_pages_fp4.data_ptr()
+    args.k_pitch = k_pitch
+    args.k_sf = key_scales.data_ptr()
+    args.k_sf_pitch = k_sf_pitch
+    args.v_packed = value_pages_fp4.data_ptr()
+    args.v_pitch = v_pitch
+    args.v_sf = value_scales.data_ptr()
+    args.v_sf_pitch = v_sf_pitch
+    args.num_pages = page_count
+    args.page_table = fp4_page_table.data_ptr()
+    args.page_table_row_stride = fp4_page_table.stride(0) if rows > 1 else fp4_page_table.shape[1]
+    args.max_pages = fp4_page_table.shape[1]
+    args.seqused_fp4 = seqused_fp4.data_ptr()
+    if has_residual:
+        args.tail_key = residual_key_pages_bf16.data_ptr()
+        args.tail_value = residual_value_pages_bf16.data_ptr()
+        args.tail_pages = residual_key_pages_bf16.shape[0]
+        args.tail_ids = residual_page_ids.data_ptr()
+        args.seqused_tail = seqused_residual.data_ptr()
+    if out is not None:
+        args.out = out.data_ptr()
+    args.out_indices = _lib.ptr(out_indices)
+    if _partials is not None:
+        args.o_partial = _partials[0].data_ptr()
+        args.lse_partial = _partials[1].data_ptr()
+    args.rows = rows
+    args.heads_q = heads_q
+    args.heads_kv = heads_kv
+    args.softmax_scale = softmax_scale
+    args.num_splits = num_splits
+    args.impl = DEFAULT_IMPL
+    if workspace is not None:
+        args.workspace = workspace.data_ptr()
+        args.workspace_bytes = workspace.numel()
+    args.status = _lib.ptr(status)
+    if args.page_table_row_stride < args.max_pages:
+        raise ValueError("fp4_page_table rows overlap")
+    with torch.cuda.device(device):
+        _lib.check(
+            _lib.load().nvfp4_decode(args, torch.cuda.current_stream(device).cuda_stream)
+        )
+    if out is None:
+        return None
+    return out if out_indices is not None else out[:rows]
+
+
+def decode_fp4_split(
+    *,
+    query_fp4: torch.Tensor,
+    query_scales: torch.Tensor,
+    key_pages_fp4: torch.Tensor,
+    key_scales: torch.Tensor,
+    value_pages_fp4: torch.Tensor,
+    value_scales: torch.Tensor,
+    fp4_page_table: torch.Tensor,
+    seqused_fp4: torch.Tensor,
+    softmax_scale: float,
+    num_splits: int,
+    query_padded_bf16: torch.Tensor | None = None,
+    residual_key_pages_bf16: torch.Tensor | None = None,
+    residual_value_pages_bf16: torch.Tensor | None = None,
+    residual_page_ids: torch.Tensor | None = None,
+    seqused_residual: torch.Tensor | None = None,
+    has_bf16: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+    trusted_metadata: bool = False,
+    return_partials: bool = False,
+):
+    """Split-KV decode: split ``s`` owns pages ``[s*ceil(n/S), min((s+1)*ceil(n/S), n))``,
+    the residual belongs to split 0; partials are merged by LSE weight.
+
+    With ``return_partials=True`` the fp32 partials ``([S, rows, 1, heads, 128],
+    [S, rows, heads, 1])`` are returned as well.
+    """
+    common = dict(
+        query_fp4=query_fp4,
+        query_scales=query_scales,
+        query_padded_bf16=query_padded_bf16,
+        key_pages_fp4=key_pages_fp4,
+        key_scales=key_scales,
+        value_pages_fp4=value_pages_fp4,
+        value_scales=value_scales,
+        fp4_page_table=fp4_page_table,
+        seqused_fp4=seqused_fp4,
+        residual_key_pages_bf16=residual_key_pages_bf16,
+        residual_value_pages_bf16=residual_value_pages_bf16,
+        residual_page_ids=residual_page_ids,
+        seqused_residual=seqused_residual,
+        has_bf16=has_bf16,
+        softmax_scale=softmax_scale,
+        out=out,
+        trusted_metadata=trusted_metadata,
+    )
+    if num_splits <= 1 and not return_partials:
+        return decode_fp4(**common)
+    rows, _, heads_q, _ = query_fp4.shape
+    device = query_fp4.device
+    if out is None:
+        out = torch.empty(rows, heads_q, HEAD_DIM, dtype=torch.bfloat16, device=device)
+        common["out"] = out
+    # Every slot is written by the kernel (an empty split stores O = 0, LSE = -inf),
+    # so the workspace needs no fill.
+    o_part = torch.empty(num_splits, rows, 1, heads_q, HEAD_DIM, dtype=torch.float32,
+                         device=device)
+    lse_part = torch.empty(num_splits, rows, heads_q, 1, dtype=torch.float32, device=device)
+    result = decode_fp4(**common, num_splits=num_splits, _partials=(o_part, lse_part))
+    if return_partials:
+        return result, o_part, lse_part
+    return result

@@ -1,0 +1,166 @@
+"""Composition of the public decode entry: query preparation, split dispatch.
+
+Follows ``fp4_decode_impl`` of the reference project
+(``src/nvfp4_decode_kernel/_kernel.py:92-302``), including which combinations
+are refused and with which words.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .interface import RESIDUAL_ROW_TILE
+
+
+def _padded_query(query: torch.Tensor, rows: int, scratch: torch.Tensor | None) -> torch.Tensor:
+    heads, head_dim = query.shape[1], query.shape[2]
+    if scratch is None:
+        return torch.zeros(rows, RESIDUAL_ROW_TILE, heads, head_dim, dtype=torch.bfloat16,
+                           device=query.device)
+    if (
+        scratch.dtype is not torch.bfloat16
+        or scratch.device != query.device
+        or scratch.ndim != 4
+        or scratch.shape[0] < rows
+        or tuple(scratch.shape[1:]) != (RESIDUAL_ROW_TILE, heads, head_dim)
+        or not scratch.is_contiguous()
+    ):
+        raise ValueError(
+            "query_padded_scratch must be a contiguous BF16 tensor on the "
+            f"query's device shaped [at least {rows}, {RESIDUAL_ROW_TILE}, "
+            f"{heads}, {head_dim}]"
+        )
+    return scratch[:rows]
+
+
+def _check_scratch(scratch, name: str, rows: int, trailing: tuple[int, ...],
+                   device: torch.device) -> None:
+    if scratch is None:
+        return
+    if (
+        scratch.dtype is not torch.uint8
+        or scratch.device != device
+        or scratch.ndim != 1 + len(trailing)
+        or scratch.shape[0] < rows
+        or tuple(scratch.shape[1:]) != trailing
+        or not scratch.is_contiguous()
+        or scratch.storage_offset() != 0
+    ):
+        extents = ", ".join(str(e) for e in trailing)
+        raise ValueError(
+            f"{name} must be a contiguous UINT8 tensor on the query's device "
+            f"shaped [at least {rows}, {extents}], starting at storage offset zero"
+        )
+
+
+def fp4_decode_impl(
+    query,
+    key_pages_fp4,
+    key_scales,
+    value_pages_fp4,
+    value_scales,
+    fp4_page_table,
+    seqused_fp4,
+    *,
+    query_fp4=None,
+    query_scales=None,
+    residual_key_pages_bf16=None,
+    residual_value_pages_bf16=None,
+    residual_page_ids=None,
+    seqused_residual=None,
+    has_bf16=None,
+    softmax_scale=None,
+    query_row_indices=None,
+    out=None,
+    out_indices=None,
+    trusted_metadata=False,
+    num_splits=1,
+    query_padded_scratch=None,
+    query_fp4_scratch=None,
+    query_scales_scratch=None,
+):
+    from ._decode import decode_fp4, decode_fp4_split
+    from ._quantize import quantize_query
+
+    if not isinstance(num_splits, int) or num_splits < 1 or num_splits & (num_splits - 1):
+        raise ValueError(f"num_splits must be a positive power of two, got {num_splits!r}")
+
+    bf16_query = query is not None
+    fp4_query = query_fp4 is not None or query_scales is not None
+    if bf16_query == fp4_query:
+        raise ValueError("supply either BF16 query or query_fp4 + query_scales")
+
+    padded = None
+    if bf16_query:
+        if softmax_scale is None:
+            softmax_scale = query.shape[-1] ** -0.5
+        rows = query.shape[0] if query_row_indices is None else query_row_indices.shape[0]
+        if residual_key_pages_bf16 is not None:
+            padded = _padded_query(query, rows, query_padded_scratch)
+        heads, head_dim = query.shape[1], query.shape[2]
+        _check_scratch(query_fp4_scratch, "query_fp4_scratch", rows,
+                       (1, heads, head_dim // 2), query.device)
+        _check_scratch(query_scales_scratch, "query_scales_scratch", rows,
+                       (1, heads, head_dim // 64, 32, 4, 4), query.device)
+        query_fp4, query_scales = quantize_query(
+            query,
+            row_indices=query_row_indices,
+            query_padded_out=padded,
+            heads_kv=key_pages_fp4.shape[2],
+            query_fp4_scratch=query_fp4_scratch,
+            query_scales_scratch=query_scales_scratch,
+        )
+    else:
+        if query_fp4 is None or query_scales is None:
+            raise ValueError("query_fp4 and query_scales must be provided together")
+        if query_row_indices is not None:
+            raise ValueError("query_row_indices applies only to the BF16 query path")
+        for name, scratch in (
+            ("query_padded_scratch", query_padded_scratch),
+            ("query_fp4_scratch", query_fp4_scratch),
+            ("query_scales_scratch", query_scales_scratch),
+        ):
+            if scratch is not None:
+                raise ValueError(f"{name} applies only to the BF16 query path")
+        if softmax_scale is None:
+            softmax_scale = 128 ** -0.5
+
+    residual = (residual_key_pages_bf16, residual_value_pages_bf16, residual_page_ids,
+                seqused_residual)
+    complete = all(item is not None for item in residual)
+    absent = all(item is None for item in residual) and has_bf16 is None
+    splittable = absent or (complete and padded is not None)
+    if num_splits > 1 and not splittable:
+        raise ValueError(
+            "num_splits > 1 needs either no residual argument at all or a "
+            "complete residual on the BF16 query path; this combination "
+            "runs on the single-tile path only"
+        )
+    if num_splits > 1 and out_indices is not None:
+        raise ValueError(
+            "num_splits > 1 cannot be combined with out_indices, because the "
+            "split path's combine writes the batch's rows in order"
+        )
+
+    shared = dict(
+        query_fp4=query_fp4,
+        query_scales=query_scales,
+        query_padded_bf16=padded,
+        key_pages_fp4=key_pages_fp4,
+        key_scales=key_scales,
+        value_pages_fp4=value_pages_fp4,
+        value_scales=value_scales,
+        fp4_page_table=fp4_page_table,
+        seqused_fp4=seqused_fp4,
+        residual_key_pages_bf16=residual_key_pages_bf16,
+        residual_value_pages_bf16=residual_value_pages_bf16,
+        residual_page_ids=residual_page_ids,
+        seqused_residual=seqused_residual,
+        has_bf16=has_bf16,
+        softmax_scale=softmax_scale,
+        out=out,
+        trusted_metadata=trusted_metadata,
+    )
+    if num_splits > 1:
+        return decode_fp4_split(**shared, num_splits=num_splits)
+    return decode_fp4(**shared, out_indices=out_indices)

@@ -1,0 +1,95 @@
+"""CPU tests of the C-ABI boundary: the shared library loads without a GPU,
+exports every function the public header declares, and rejects bad arguments
+before touching the device."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+import nvfp4_attn_kernel_b200._lib as L
+
+ROOT = os.path.dirname(os.path.dirname(__file__))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "nvfp4_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(nvfp4_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = L.load()
+    names = declared_functions()
+    assert len(names) >= 12
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/nvfp4_b200.h but not exported"
+    assert set(names) == set(L.EXPORTS) | {n for n in names if n not in L.EXPORTS}
+    assert set(L.EXPORTS) <= set(names)
+    assert lib.nvfp4_version() >= 100
+
+
+def test_struct_mirror_matches_header_field_order():
+    text = open(os.path.join(ROOT, "include", "nvfp4_b200.h")).read()
+    body = text[text.index("typedef struct nvfp4_decode_args {"):text.index("} nvfp4_decode_args;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = re.findall(r"\b([a-z_0-9]+)\s*;", body)
+    assert fields == [name for name, _ in L.DecodeArgs._fields_]
+
+
+def test_workspace_size():
+    lib = L.load()
+    assert lib.nvfp4_decode_workspace_bytes(32, 32, 1) == 0
+    assert lib.nvfp4_decode_workspace_bytes(4, 32, 8) == 8 * 4 * 32 * 129 * 4
+    assert lib.nvfp4_decode_workspace_bytes(0, 32, 8) == 0
+
+
+def test_argument_errors_are_reported_without_a_device():
+    lib = L.load()
+    assert lib.nvfp4_decode(None, None) == L.ERR_INVALID
+    assert "null argument block" in L.last_error()
+    assert lib.nvfp4_quantize_q(None, 0, 0, None, None, None, None, -1, 32, 8, None) == L.ERR_INVALID
+    with pytest.raises(ValueError, match="non-negative"):
+        L.check(L.ERR_INVALID)
+    args = L.DecodeArgs()
+    args.rows, args.heads_q, args.heads_kv = 1, 24, 8
+    assert lib.nvfp4_decode(ctypes.byref(args), None) == L.ERR_UNSUPPORTED
+    args.heads_q = 32
+    args.softmax_scale = 0.0
+    assert lib.nvfp4_decode(ctypes.byref(args), None) == L.ERR_INVALID
+    assert "softmax_scale" in L.last_error()
+    args.softmax_scale = 0.1
+    args.num_splits = 0
+    assert lib.nvfp4_decode(ctypes.byref(args), None) == L.ERR_INVALID
+    args.num_splits = 1
+    assert lib.nvfp4_decode(ctypes.byref(args), None) == L.ERR_INVALID
+    assert "required pointer" in L.last_error()
+    # zero-sized work is a successful no-op
+    assert lib.nvfp4_quantize_kv_pages(0, None, 0, None, None, 0, None, 0, None, None, None, None,
+                                       0, 1, 0, 8, None) == 0
+    assert lib.nvfp4_lse_merge(None, 0, None, 0, 1, 0, 32, None, 0, None, None, None) == 0
+
+
+def test_host_side_checks_of_the_python_operator():
+    import torch
+
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import fp4_decode
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel._decode import split_k_heuristic
+
+    with pytest.raises(ValueError, match="missing required decode arguments"):
+        fp4_decode(torch.zeros(1, 32, 128, dtype=torch.bfloat16))
+    z = torch.zeros(1)
+    with pytest.raises(ValueError, match="positive power of two"):
+        fp4_decode(z, z, z, z, z, z, z, num_splits=3)
+    with pytest.raises(ValueError, match="either BF16 query"):
+        fp4_decode(None, z, z, z, z, z, z)
+    with pytest.raises(ValueError, match="must be provided together"):
+        fp4_decode(None, z, z, z, z, z, z, query_fp4=z)
+    with pytest.raises(ValueError, match="applies only to the BF16 query path"):
+        fp4_decode(None, z, z, z, z, z, z, query_fp4=z, query_scales=z, query_row_indices=z)
+    # the makespan model: 32 tiles on 148 SMs split, 256 tiles do not
+    assert split_k_heuristic(4, 8, 256, sms=148) == 4
+    assert split_k_heuristic(32, 8, 32, sms=148) == 1
+    assert split_k_heuristic(1, 8, 1, sms=148) == 1
+    assert split_k_heuristic(1, 1, 64, sms=148) == 32

@@ -1,0 +1,299 @@
+"""GPU parity of the decode operator against the numpy oracle (tolerance: max-abs
+2e-2 on BF16 outputs, the bound the project states for this path), the golden
+vectors, and the operator's edge-case contract."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import inputs
+import nvfp4_oracle as O
+from helpers import Problem, bf16_tensor, interleave_vllm, to_np
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-2          # max-abs vs the oracle fed the library's own dequantised bytes
+TOL_E2E = 5e-2      # vs the oracle quantising from BF16 itself (tie rule differs); reference gate
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+IMPLS = ["generic", "sm100"]
+
+
+def _set_impl(name):
+    import nvfp4_attn_kernel_b200._lib as L
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode
+
+    _decode.DEFAULT_IMPL = {"generic": L.IMPL_GENERIC, "sm100": L.IMPL_SM100, "auto": L.IMPL_AUTO}[name]
+
+
+@pytest.fixture(params=IMPLS)
+def impl(request):
+    _skip_if_unsupported(request.param, 8, 2)
+    _set_impl(request.param)
+    yield request.param
+    _set_impl("auto")
+
+
+def _case(name):
+    if name == "config1":
+        return inputs.config1(0)
+    return inputs.attention_case(*inputs.SMALL_CASES[name])
+
+
+def _skip_if_unsupported(impl, heads_q, heads_kv):
+    import nvfp4_attn_kernel_b200._lib as L
+
+    code = {"generic": L.IMPL_GENERIC, "sm100": L.IMPL_SM100}[impl]
+    if not L.load().nvfp4_decode_impl_available(code, heads_q, heads_kv):
+        pytest.skip(f"the {impl} kernel does not take {heads_q}/{heads_kv} heads")
+
+
+@pytest.mark.parametrize("name", list(inputs.SMALL_CASES) + ["config1"])
+def test_decode_matches_oracle(cuda_device, impl, name):
+    case = _case(name)
+    _skip_if_unsupported(impl, case["q"].shape[1], case["k_pages"].shape[2])
+    prob = Problem(case, cuda_device)
+    out = to_np(prob.decode())
+    want = prob.oracle_from_bytes()
+    assert np.isfinite(out).all()
+    assert np.abs(out - want).max() <= TOL, np.abs(out - want).max()
+    gold = np.load(os.path.join(GOLD, "attention.npz"))[name]
+    assert np.abs(out - gold).max() <= TOL_E2E
+    cos = (out * gold).sum() / np.sqrt((out * out).sum() * (gold * gold).sum())
+    assert cos >= 0.99
+
+
+def test_vllm_block_pitch_is_bit_identical(cuda_device, impl):
+    prob = Problem(_case("gqa4_short"), cuda_device)
+    dense = prob.decode()
+    cache, kv, ksv, vv, vsv = interleave_vllm(prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf)
+    assert cache.shape[1] == O.vllm_block_bytes(prob.heads_kv)
+    paged = prob.decode(key_pages_fp4=kv, key_scales=ksv, value_pages_fp4=vv, value_scales=vsv)
+    assert torch.equal(dense, paged)
+
+
+def test_prequantised_query_equals_bf16_query(cuda_device, impl):
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _quantize, fp4_decode
+
+    case = inputs.attention_case(41, 3, 8, 2, (256, 384, 128), 1.0, 0.0)
+    case["seqused_fp4"] = np.array([256, 384, 128], dtype=np.int32)  # page-aligned, no tail
+    prob = Problem(case, cuda_device)
+    common = (prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, prob.page_table, prob.seqused_fp4)
+    a = fp4_decode(prob.q, *common)
+    q_fp4, q_sf = _quantize.quantize_query(prob.q, heads_kv=2)
+    b = fp4_decode(None, *common, query_fp4=q_fp4, query_scales=q_sf)
+    assert torch.equal(a, b)
+
+
+def test_rows_without_keys_and_padding_rows(cuda_device, impl):
+    """CUDA-graph padding rows arrive with both lengths 0 and a tail id of -1; they
+    must write zeros, fault nothing and leave live rows bit-identical."""
+    case = inputs.attention_case(43, 4, 8, 2, (300, 1, 129, 256), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    base = prob.decode()
+    fp4 = prob.seqused_fp4.clone()
+    res = prob.seqused_residual.clone()
+    ids = prob.residual_page_ids.clone()
+    fp4[1], res[1], ids[1] = 0, 0, -1
+    table = prob.page_table.clone()
+    table[1] = -1  # nothing of a dead row may be dereferenced
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode, _quantize
+
+    out = prob.decode(fp4_page_table=table, seqused_fp4=fp4, seqused_residual=res,
+                      residual_page_ids=ids, trusted_metadata=True)
+    assert torch.equal(out[[0, 2, 3]], base[[0, 2, 3]])
+    assert not out[1].any()
+    # zero-length residual contributes exactly nothing: row 3 with its tail cut to 0
+    res2 = prob.seqused_residual.clone()
+    res2[3] = 0
+    out2 = to_np(prob.decode(seqused_residual=res2))
+    want = prob.oracle_from_bytes()
+    c2 = dict(case)
+    c2["seqused_residual"] = to_np(res2)
+    prob2 = Problem(c2, cuda_device)
+    assert np.abs(out2 - prob2.oracle_from_bytes()).max() <= TOL
+    del status, _decode, _quantize, want
+
+
+def test_poisoned_unused_table_columns_are_never_read(cuda_device, impl):
+    case = inputs.attention_case(45, 2, 8, 2, (200, 600), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    base = prob.decode()
+    table = prob.page_table.clone()
+    used = (prob.seqused_fp4 // 128).tolist()
+    for r, n in enumerate(used):
+        table[r, n:] = 0x7FFFFFF0
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode, _quantize
+
+    q_fp4, q_sf = _quantize.quantize_query(prob.q, heads_kv=2)
+    padded = torch.zeros(2, 128, 8, 128, dtype=torch.bfloat16, device=cuda_device)
+    padded[:, 0] = prob.q
+    out = _decode.decode_fp4(
+        query_fp4=q_fp4, query_scales=q_sf, query_padded_bf16=padded,
+        key_pages_fp4=prob.k_fp4, key_scales=prob.k_sf, value_pages_fp4=prob.v_fp4,
+        value_scales=prob.v_sf, fp4_page_table=table, seqused_fp4=prob.seqused_fp4,
+        residual_key_pages_bf16=prob.k_pages, residual_value_pages_bf16=prob.v_pages,
+        residual_page_ids=prob.residual_page_ids, seqused_residual=prob.seqused_residual,
+        softmax_scale=prob.softmax_scale, trusted_metadata=True, status=status)
+    assert torch.equal(out, base)
+    assert int(status.item()) == 0
+    # a bad id INSIDE the used range is skipped and reported, never dereferenced
+    table[1, 0] = 0x7FFFFFF0
+    _decode.decode_fp4(
+        query_fp4=q_fp4, query_scales=q_sf, query_padded_bf16=padded,
+        key_pages_fp4=prob.k_fp4, key_scales=prob.k_sf, value_pages_fp4=prob.v_fp4,
+        value_scales=prob.v_sf, fp4_page_table=table, seqused_fp4=prob.seqused_fp4,
+        residual_key_pages_bf16=prob.k_pages, residual_value_pages_bf16=prob.v_pages,
+        residual_page_ids=prob.residual_page_ids, seqused_residual=prob.seqused_residual,
+        softmax_scale=prob.softmax_scale, trusted_metadata=True, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & 1
+
+
+def test_non_finite_bytes_past_the_tail_length_do_not_reach_the_output(cuda_device, impl):
+    case = inputs.attention_case(47, 2, 8, 2, (200, 130), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    base = prob.decode()
+    k2, v2 = prob.k_pages.clone(), prob.v_pages.clone()
+    for r in range(2):
+        pid = int(case["residual_page_ids"][r])
+        n = int(case["seqused_residual"][r])
+        k2[pid, n:] = float("nan")
+        v2[pid, n:] = float("inf")
+    out = prob.decode(residual_key_pages_bf16=k2, residual_value_pages_bf16=v2)
+    assert torch.equal(out, base)
+
+
+def test_out_buffer_scatter_and_row_indices(cuda_device, impl):
+    case = inputs.attention_case(49, 3, 8, 2, (72 + 256, 127, 384), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    base = prob.decode()
+    out = torch.full((6, 8, 128), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    got = prob.decode(out=out)
+    assert got.data_ptr() == out.data_ptr() and tuple(got.shape) == (3, 8, 128)
+    assert torch.equal(out[:3], base) and (out[3:] == 7.0).all()
+    out.fill_(7.0)
+    idx = torch.tensor([4, 1, 3], dtype=torch.int32, device=cuda_device)
+    got = prob.decode(out=out, out_indices=idx)
+    assert tuple(got.shape) == (6, 8, 128)
+    assert torch.equal(out[[4, 1, 3]], base) and (out[[0, 2, 5]] == 7.0).all()
+    # query_row_indices picks rows out of a wider query
+    wide = torch.zeros(7, 8, 128, dtype=torch.bfloat16, device=cuda_device)
+    wide[[5, 0, 2]] = prob.q
+    rows = torch.tensor([5, 0, 2], dtype=torch.int32, device=cuda_device)
+    assert torch.equal(prob.decode(query=wide, query_row_indices=rows), base)
+
+
+@pytest.mark.parametrize("splits", [2, 4, 8])
+def test_split_kv_matches_unsplit_and_oracle(cuda_device, impl, splits):
+    case = inputs.attention_case(51, 3, 8, 2, (1024 + 17, 128 * 5, 60), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    base = to_np(prob.decode())
+    out = to_np(prob.decode(num_splits=splits))
+    assert np.abs(out - base).max() <= TOL
+    # the oracle run split by split, merged by LSE weight
+    want_parts, want_lse = [], []
+    import helpers
+
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _quantize
+
+    q_fp4, q_sf = _quantize.quantize_query(prob.q, heads_kv=2)
+    storage = q_sf.as_strided((3, 8 * 1024), (8 * 1024, 1))
+    q_dq = O.dequantize_query(to_np(q_fp4), to_np(storage).reshape(3, 1, 8, 2, 32, 4, 4), 2)
+    k_dq = O.dequantize_key_pages(to_np(prob.k_fp4), helpers.scale_bytes(prob.k_sf))
+    v_dq = O.dequantize_value_pages(to_np(prob.v_fp4), helpers.scale_bytes(prob.v_sf))
+    for s in range(splits):
+        o, lse = O.attention_from_dequantized(
+            case["q"], q_dq, k_dq, v_dq, case["page_table"], case["seqused_fp4"],
+            tail_key=case["k_pages"], tail_value=case["v_pages"], tail_ids=case["residual_page_ids"],
+            seqused_residual=case["seqused_residual"], softmax_scale=case["softmax_scale"],
+            page_range=lambda n, s=s: O.split_page_range(n, s, splits), owns_tail=(s == 0),
+            return_lse=True)
+        want_parts.append(o)
+        want_lse.append(lse)
+    want = O.lse_merge(np.stack(want_parts), np.stack(want_lse))
+    assert np.abs(out - want).max() <= TOL
+
+
+def test_split_partials_and_merge_entry_points(cuda_device, impl):
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode, _quantize
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel.split_k_combine import flash_attn_combine
+
+    case = inputs.attention_case(53, 2, 8, 2, (128 * 6, 128 * 2), 1.0, 0.0)
+    case["seqused_fp4"] = np.array([768, 256], dtype=np.int32)
+    prob = Problem(case, cuda_device)
+    q_fp4, q_sf = _quantize.quantize_query(prob.q, heads_kv=2)
+    out, o_part, lse_part = _decode.decode_fp4_split(
+        query_fp4=q_fp4, query_scales=q_sf, key_pages_fp4=prob.k_fp4, key_scales=prob.k_sf,
+        value_pages_fp4=prob.v_fp4, value_scales=prob.v_sf, fp4_page_table=prob.page_table,
+        seqused_fp4=prob.seqused_fp4, softmax_scale=prob.softmax_scale, num_splits=4,
+        return_partials=True)
+    lse = to_np(lse_part)[..., 0]
+    assert np.isneginf(lse[2:, 1]).all()          # row 1 has 2 pages: splits 2, 3 are empty
+    assert np.isfinite(lse[:, 0]).all()
+    assert not to_np(o_part)[2:, 1].any()
+    merged, merged_lse = flash_attn_combine(o_part, lse_part.transpose(-1, -2), out_dtype=torch.bfloat16)
+    assert torch.equal(merged[:, 0], out)
+    want, want_lse = O.lse_merge(to_np(o_part)[:, :, 0], lse, return_lse=True)
+    assert np.abs(to_np(merged)[:, 0] - want).max() <= 1e-2
+    assert np.abs(to_np(merged_lse)[:, 0] - want_lse).max() <= 1e-4
+    f32, _ = flash_attn_combine(o_part, lse_part.transpose(-1, -2), out_dtype=torch.float32,
+                                return_lse=False)
+    assert np.abs(to_np(f32)[:, 0] - want).max() <= 1e-5
+
+
+def test_repeated_calls_are_bitwise_identical(cuda_device, impl):
+    case = inputs.attention_case(55, 18, 8, 1, tuple([513] * 18), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    first = prob.decode()
+    first_split = prob.decode(num_splits=4)
+    for _ in range(8):
+        assert torch.equal(prob.decode(), first)
+        assert torch.equal(prob.decode(num_splits=4), first_split)
+
+
+def test_refusals(cuda_device):
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import fp4_decode
+
+    case = inputs.attention_case(57, 2, 16, 1, (256, 256), 0.3, 0.0)
+    case["seqused_fp4"] = np.array([256, 256], dtype=np.int32)
+    prob = Problem(case, cuda_device)
+    common = (prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, prob.page_table, prob.seqused_fp4)
+    for shape, dtype, complaint in (
+        ((2, 16, 128), torch.float16, "out must be contiguous BF16"),
+        ((1, 16, 128), torch.bfloat16, "out needs at least 2 rows"),
+        ((2, 17, 128), torch.bfloat16, "out must be contiguous BF16"),
+    ):
+        for splits in (1, 2):
+            with pytest.raises(ValueError, match=complaint):
+                fp4_decode(prob.q, *common, out=torch.zeros(shape, dtype=dtype, device=cuda_device),
+                           num_splits=splits)
+    idx = torch.zeros(2, dtype=torch.int32, device=cuda_device)
+    out = torch.zeros(2, 16, 128, dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(ValueError, match="cannot be combined with out_indices"):
+        fp4_decode(prob.q, *common, out=out, out_indices=idx, num_splits=2)
+    with pytest.raises(ValueError, match="complete residual on the BF16 query"):
+        fp4_decode(prob.q, *common, residual_key_pages_bf16=prob.k_pages, num_splits=2)
+    with pytest.raises(ValueError, match="must be provided together"):
+        fp4_decode(prob.q, *common, residual_key_pages_bf16=prob.k_pages)
+    bad = prob.seqused_fp4.clone()
+    bad[0] = 100
+    with pytest.raises(ValueError, match="page-aligned"):
+        fp4_decode(prob.q, prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, prob.page_table, bad)
+    with pytest.raises(ValueError, match="query_scales_scratch"):
+        fp4_decode(prob.q, *common,
+                   query_scales_scratch=torch.zeros(2, 1, 16, 2, 32, 4, 3, dtype=torch.uint8,
+                                                    device=cuda_device))
+    with pytest.raises(ValueError, match="query_padded_scratch"):
+        fp4_decode(prob.q, *common, residual_key_pages_bf16=prob.k_pages,
+                   residual_value_pages_bf16=prob.v_pages, residual_page_ids=prob.residual_page_ids,
+                   seqused_residual=prob.seqused_residual,
+                   query_padded_scratch=torch.zeros(2, 64, 16, 128, dtype=torch.bfloat16,
+                                                    device=cuda_device))
+    with pytest.raises(ValueError, match="layout returned"):
+        fp4_decode(prob.q, prob.k_fp4, prob.k_sf.permute(0, 2, 1, 3, 4, 5, 6).contiguous().permute(
+            0, 2, 1, 3, 4, 5, 6), prob.v_fp4, prob.v_sf, prob.page_table, prob.seqused_fp4)
