@@ -1,5 +1,597 @@
+// Tensor-core decode kernel for sm_100a: block-scaled tcgen05 MMA (kind::mxf4nvf4,
+// E2M1 operands with UE4M3 scales per 16 elements), accumulators in tensor memory,
+// K/V page tiles staged by TMA through a ring of shared-memory stages.
+//
+// One CTA of 192 threads per (split, KV head, row):
+//   warps 0-3  softmax / output threads (one tensor-memory lane each)
+//   warp  4    producer: page-table walk, TMA tile loads, bulk copies of the scale blocks
+//   warp  5    MMA issuer (one elected lane) and owner of the tensor-memory allocation
+//
+// The product is formed transposed so that the G <= 8 query heads of a KV head are the
+// N = 8 side of the MMA and nothing is padded to 128:
+//   S^T[128 kv, 8 q] = K_page[128 kv, 128 d] . Q^T            (A = K tile as it lies in the page)
+//   O^T[128 d , 8 q] = V_page^T[128 d, 128 kv] . P^T          (A = V tile as it lies in the page)
+// Both page layouts are already K-major A operands, and the 512-byte scale atoms of the
+// page format are copied to tensor memory with tcgen05.cp unchanged.
+// Thread t of the 128 is kv position t while S^T is read and channel t while O^T is
+// accumulated, so the running output lives in G registers per thread and O^T is never
+// rescaled in tensor memory: each page's P.V lands in a fresh accumulator and is folded
+// in as o = o * rescale + O_page, exactly the order of the attention oracle.
+//
+// Every device-side wait is bounded; on expiry the CTA raises NVFP4_STATUS_WAIT_TIMEOUT,
+// drains what it has in flight, frees its tensor memory and returns.
+#include <cuda.h>
+
 #include "decode_common.cuh"
+
 namespace nvfp4 {
-bool decode_sm100_supports(const DecodeParams& p) { (void)p; return false; }
-cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream) { (void)p; (void)stream; return cudaErrorNotSupported; }
+
+namespace sm100 {
+
+constexpr int kStages = 4;
+constexpr int kTileBytes = 8192;                                  // 128 rows x 64 B
+constexpr int kStageBytes = 2 * kTileBytes + 2 * kSfBlockBytes;   // K, V, K scales, V scales
+constexpr int kNQ = 8;                                            // MMA N
+constexpr int kTmemCols = 64;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;        // 2 s
+
+// tensor-memory column map (32-bit columns)
+constexpr int kColS = 0;     // 2 x 8 : S^T double buffer
+constexpr int kColO = 16;    // 2 x 8 : per-page O^T double buffer
+constexpr int kColSfQ = 32;  // 8 : 2 k-blocks x 4
+constexpr int kColSfK = 40;
+constexpr int kColSfV = 48;
+constexpr int kColSfP = 56;
+
+struct __align__(1024) Smem {
+  uint8_t stage[kStages][kStageBytes];          // each stage: K tile | V tile | K scales | V scales
+  __align__(1024) uint8_t q_tile[512];          // 8 rows x 64 B, 64-byte swizzle
+  __align__(1024) uint8_t p_tile[2][512];
+  __align__(512) uint8_t q_sf[kSfBlockBytes];
+  __align__(512) uint8_t p_sf[2][kSfBlockBytes];
+  __align__(16) float qb[8 * kHeadDim];         // BF16 query as floats (tail)
+  __align__(16) float pf[8 * kHeadDim];         // P of the tail block
+  float red[2][4 * 8];
+  float red_io[4 * 8];                          // reductions of the tail block and the epilogue
+  volatile int page_ok[kStages];                // 0: the stage stands for a page id that was refused
+  __align__(8) uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t s_full[2], s_free[2], p_full[2], o_full[2], o_free[2];
+  uint64_t q_ready, drain;
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (someone's wait expired).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Smem& sm, uint32_t* status) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  uint32_t spins = 0;
+  while (!mbar_try(bar, parity)) {
+    if (sm.abort_flag) return false;
+    if ((++spins & 1023u) == 0 && global_ns() - t0 > kWaitLimitNs) {
+      sm.abort_flag = 1;
+      set_status(status, NVFP4_STATUS_WAIT_TIMEOUT);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                 "=r"(r[7])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, 64-byte swizzle: rows of 64 bytes, eight-row
+// groups 512 bytes apart (stride byte offset), descriptor version 1, layout type 4.
+__device__ __forceinline__ uint64_t desc_sw64(uint32_t saddr) {
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(512 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)4 << 61);
+}
+// Scale atom for tcgen05.cp 32x128b: 32 rows of 16 bytes, no swizzle, eight-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+
+// Instruction descriptor: E2M1 x E2M1 (format code 1), UE4M3 scales, K-major both, N = 8, M = 128, K = 64.
+constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((kNQ >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t sfa,
+                                         uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void cp_sf(uint32_t tmem_dst, uint32_t saddr) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(desc_sf(saddr))
+               : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// Barrier over the 128 softmax threads that also ANDs a predicate across them.
+__device__ __forceinline__ bool bar_and_128(int bar_id, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "bar.red.and.pred p, %1, 128, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(bar_id), "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
+
+// byte offset of (row, byte column) inside an 8-row, 64-byte-swizzled B tile
+__device__ __forceinline__ int sw64_offset(int row, int byte_col) {
+  return row * 64 + ((((byte_col >> 4) ^ ((row >> 1) & 3))) << 4) + (byte_col & 15);
+}
+
+template <int G>
+__global__ void __launch_bounds__(192, 2)
+decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                    const DecodeParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const TileWork w = resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x);
+  const int n_pages = w.last_page - w.first_page;
+
+  // ---- set-up: barriers, tensor memory, zeroed operand tiles ----
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.s_full[b], 1); mbar_init(&sm.s_free[b], 128);
+      mbar_init(&sm.p_full[b], 128);
+      mbar_init(&sm.o_full[b], 1); mbar_init(&sm.o_free[b], 128);
+    }
+    mbar_init(&sm.q_ready, 128);
+    mbar_init(&sm.drain, 1);
+    sm.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&sm.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // rows G..7 of the N = 8 operands and their scale rows stay zero for the whole kernel
+  for (int i = tid; i < 512 / 16; i += 192) reinterpret_cast<uint4*>(sm.q_tile)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < 2 * 512 / 16; i += 192) reinterpret_cast<uint4*>(sm.p_tile)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < 2 * kSfBlockBytes / 16; i += 192)
+    reinterpret_cast<uint4*>(sm.p_sf)[i] = make_uint4(0, 0, 0, 0);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp < 4) {
+    // =====================  softmax / output threads  =====================
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    // query operand: G packed rows, swizzled; its scale block; the BF16 copy for the tail
+    if (tid < G * 4) {
+      const int q = tid >> 2, c = tid & 3;
+      const uint4 v = *reinterpret_cast<const uint4*>(
+          p.q_fp4 + ((int64_t)w.row * p.heads_q + w.kvh * G + q) * 64 + c * 16);
+      *reinterpret_cast<uint4*>(sm.q_tile + sw64_offset(q, c * 16)) = v;
+    }
+    if (tid >= 64) {
+      reinterpret_cast<uint4*>(sm.q_sf)[tid - 64] = *(reinterpret_cast<const uint4*>(
+          p.q_sf + (int64_t)w.row * p.heads_q * kSfBlockBytes + (int64_t)w.kvh * kSfBlockBytes) + (tid - 64));
+    }
+    if (w.tail_len > 0) {
+      for (int it = tid; it < G * 16; it += 128) {
+        const int q = it >> 4, c = it & 15;
+        float f[8];
+        if (p.q_bf16) {
+          unpack_bf16x8(*reinterpret_cast<const uint4*>(p.q_bf16 + (int64_t)w.row * p.q_row_stride +
+                                                        (int64_t)(w.kvh * G + q) * p.q_head_stride + c * 8), f);
+        } else {
+          // no BF16 query supplied: the tail meets the dequantised NVFP4 query
+          const uint32_t pk = *reinterpret_cast<const uint32_t*>(
+              p.q_fp4 + ((int64_t)w.row * p.heads_q + w.kvh * G + q) * 64 + c * 4);
+          const float sc = e4m3_to_f32(p.q_sf[(int64_t)w.row * p.heads_q * kSfBlockBytes +
+                                              (int64_t)w.kvh * kSfBlockBytes + sf_offset(q, c >> 1)]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = e2m1_to_f32((pk >> (4 * i)) & 15u) * sc;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sm.qb[q * kHeadDim + c * 8 + i] = f[i];
+      }
+    }
+    fence_proxy_async();
+    mbar_arrive(&sm.q_ready);
+
+    float m[G], l[G], o[G], resc_prev[G];
+#pragma unroll
+    for (int q = 0; q < G; ++q) { m[q] = -INFINITY; l[q] = 0.f; o[q] = 0.f; resc_prev[q] = 0.f; }
+    if (w.tail_len > 0) {
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // qb visible
+      tail_block<G>(p, w, sm.qb, sm.pf, sm.red_io, tid, 1, m, l, o);
+    }
+
+    // A thread whose wait expired keeps walking the loop's barrier points with ok = false, so
+    // the 128 threads always leave the loop together.
+    bool alive = true;
+    for (int i = 0; i <= n_pages; ++i) {
+      if (i < n_pages) {
+        const int b = i & 1;
+        bool ok = alive && mbar_wait(&sm.s_full[b], (i >> 1) & 1, sm, p.status);
+        float z[G], resc[G];
+#pragma unroll
+        for (int q = 0; q < G; ++q) z[q] = -INFINITY;
+        if (ok) {
+          tc_fence_after();
+          uint32_t r[8];
+          tmem_ld8(tmem + lane_off + kColS + b * 8, r);
+          tc_fence_before();
+          mbar_arrive(&sm.s_free[b]);
+          if (sm.page_ok[i % kStages]) {
+#pragma unroll
+            for (int q = 0; q < G; ++q) z[q] = __uint_as_float(r[q]) * p.scale_log2;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < G; ++q) {
+          const float wm = warp_max(z[q]);
+          if (lane == 0) sm.red[b][warp * 8 + q] = wm;
+        }
+        if (!bar_and_128(1, ok)) { alive = false; break; }
+        uint32_t word = 0;
+#pragma unroll
+        for (int q = 0; q < G; ++q) {
+          const float bm = fmaxf(fmaxf(sm.red[b][q], sm.red[b][8 + q]),
+                                 fmaxf(sm.red[b][16 + q], sm.red[b][24 + q]));
+          const float mn = fmaxf(m[q], bm);
+          resc[q] = (m[q] == -INFINITY) ? 0.f : exp2f(m[q] - mn);
+          m[q] = mn;
+          const float pe = exp2_rel(z[q], mn);
+          l[q] = fmaf(l[q], resc[q], pe);
+          // NVFP4 P: scale = e4m3(group max / 6), nibble = e2m1(p / scale); a scale that
+          // rounds to zero is raised to the smallest E4M3 subnormal instead of dropping the group
+          uint32_t sb = p_scale_byte(halfwarp_max(pe));
+          sb = sb == 0 ? 1u : sb;
+          const float sc = e4m3_to_f32((uint8_t)sb);
+          word |= f32_to_e2m1(__fdiv_rn(pe, sc)) << (4 * q);
+          if ((lane & 15) == 0) {  // lanes 0 and 16 own one 16-position group each
+            const int g = tid >> 4;
+            sm.p_sf[b][(g >> 2) * 512 + q * 16 + (g & 3)] = (uint8_t)sb;
+          }
+        }
+        // pair kv positions 2j, 2j+1 into one byte (even position in the low nibble)
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, word, 1);
+        if ((lane & 1) == 0) {
+#pragma unroll
+          for (int q = 0; q < G; ++q)
+            sm.p_tile[b][sw64_offset(q, tid >> 1)] =
+                (uint8_t)(((word >> (4 * q)) & 15u) | (((other >> (4 * q)) & 15u) << 4));
+        }
+        fence_proxy_async();
+        mbar_arrive(&sm.p_full[b]);
+        if (i >= 1) {
+          // fold page i-1: o = o * rescale(i-1) + O_page(i-1)
+          const int bj = (i - 1) & 1;
+          if (mbar_wait(&sm.o_full[bj], ((i - 1) >> 1) & 1, sm, p.status)) {
+            tc_fence_after();
+            uint32_t ro[8];
+            tmem_ld8(tmem + lane_off + kColO + bj * 8, ro);
+            tc_fence_before();
+            mbar_arrive(&sm.o_free[bj]);
+#pragma unroll
+            for (int q = 0; q < G; ++q) o[q] = fmaf(o[q], resc_prev[q], __uint_as_float(ro[q]));
+          } else {
+            alive = false;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < G; ++q) resc_prev[q] = resc[q];
+      } else if (n_pages > 0 && alive) {
+        const int bj = (i - 1) & 1;
+        if (mbar_wait(&sm.o_full[bj], ((i - 1) >> 1) & 1, sm, p.status)) {
+          tc_fence_after();
+          uint32_t ro[8];
+          tmem_ld8(tmem + lane_off + kColO + bj * 8, ro);
+          tc_fence_before();
+#pragma unroll
+          for (int q = 0; q < G; ++q) o[q] = fmaf(o[q], resc_prev[q], __uint_as_float(ro[q]));
+        } else {
+          alive = false;
+        }
+      }
+    }
+    if (bar_and_128(1, alive)) write_output<G>(p, w, sm.red_io, tid, 1, m, l, o);
+  } else if (warp == 4) {
+    // =====================  producer  =====================
+    bool alive = true;
+    int issued = 0;
+    int ids = -1;
+    for (int i = 0; i < n_pages && alive; ++i) {
+      if ((i & 31) == 0) {
+        const int idx = w.last_page - 1 - (i + lane);  // pages are walked from the last to the first
+        ids = idx >= w.first_page ? p.page_table[(int64_t)w.row * p.page_table_row_stride + idx] : -1;
+      }
+      int64_t pid = __shfl_sync(0xffffffffu, ids, i & 31);
+      if (pid < 0 || pid >= p.num_pages) {
+        if (lane == 0) set_status(p.status, NVFP4_STATUS_BAD_PAGE_ID);
+        pid = -1;
+      }
+      if (lane == 0) {
+        const int s = i % kStages;
+        alive = mbar_wait(&sm.empty[s], ((i / kStages) & 1) ^ 1, sm, p.status);
+        if (alive) {
+          uint8_t* st = sm.stage[s];
+          sm.page_ok[s] = pid >= 0 ? 1 : 0;
+          if (pid >= 0) {
+            mbar_expect_tx(&sm.full[s], kStageBytes);
+            tma_load_4d(smem_u32(st), &k_map, &sm.full[s], 0, w.kvh, 0, (int)pid);
+            tma_load_4d(smem_u32(st + kTileBytes), &v_map, &sm.full[s], 0, 0, w.kvh, (int)pid);
+            bulk_load(smem_u32(st + 2 * kTileBytes),
+                      p.k_sf + pid * p.k_sf_pitch + (int64_t)w.kvh * kSfBlockBytes, kSfBlockBytes, &sm.full[s]);
+            bulk_load(smem_u32(st + 2 * kTileBytes + kSfBlockBytes),
+                      p.v_sf + pid * p.v_sf_pitch + (int64_t)w.kvh * kSfBlockBytes, kSfBlockBytes, &sm.full[s]);
+          } else {
+            // a page id outside the cache is never turned into an address: the stage gets zero
+            // scales (so both products are zero) and the softmax threads mask its scores
+            for (int j = 0; j < 2 * kSfBlockBytes / 16; ++j)
+              reinterpret_cast<uint4*>(st + 2 * kTileBytes)[j] = make_uint4(0, 0, 0, 0);
+            fence_proxy_async();
+            mbar_arrive(&sm.full[s]);
+          }
+          ++issued;
+        }
+      }
+      alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
+    }
+    (void)issued;
+  } else {
+    // =====================  MMA issuer  =====================
+    if (lane == 0 && n_pages > 0) {
+      bool alive = mbar_wait(&sm.q_ready, 0, sm, p.status);
+      if (alive) {
+        tc_fence_after();
+        cp_sf(tmem + kColSfQ, smem_u32(sm.q_sf));
+        cp_sf(tmem + kColSfQ + 4, smem_u32(sm.q_sf + 512));
+      }
+      const uint64_t q_desc = desc_sw64(smem_u32(sm.q_tile));
+      for (int i = 0; i <= n_pages && alive; ++i) {
+        if (i < n_pages) {
+          const int s = i % kStages, b = i & 1;
+          alive = mbar_wait(&sm.full[s], (i / kStages) & 1, sm, p.status) &&
+                  mbar_wait(&sm.s_free[b], ((i >> 1) & 1) ^ 1, sm, p.status);
+          if (!alive) break;
+          tc_fence_after();
+          const uint32_t st = smem_u32(sm.stage[s]);
+          cp_sf(tmem + kColSfK, st + 2 * kTileBytes);
+          cp_sf(tmem + kColSfK + 4, st + 2 * kTileBytes + 512);
+          const uint64_t k_desc = desc_sw64(st);
+          mma_nvf4(tmem + kColS + b * 8, k_desc, q_desc, tmem + kColSfK, tmem + kColSfQ, 0);
+          mma_nvf4(tmem + kColS + b * 8, k_desc + 2, q_desc + 2, tmem + kColSfK + 4, tmem + kColSfQ + 4, 1);
+          mma_commit(&sm.s_full[b]);
+        }
+        if (i >= 1) {
+          const int j = i - 1, s = j % kStages, b = j & 1;
+          alive = mbar_wait(&sm.p_full[b], (j >> 1) & 1, sm, p.status) &&
+                  mbar_wait(&sm.o_free[b], ((j >> 1) & 1) ^ 1, sm, p.status);
+          if (!alive) break;
+          tc_fence_after();
+          const uint32_t st = smem_u32(sm.stage[s]);
+          cp_sf(tmem + kColSfV, st + 2 * kTileBytes + kSfBlockBytes);
+          cp_sf(tmem + kColSfV + 4, st + 2 * kTileBytes + kSfBlockBytes + 512);
+          cp_sf(tmem + kColSfP, smem_u32(sm.p_sf[b]));
+          cp_sf(tmem + kColSfP + 4, smem_u32(sm.p_sf[b] + 512));
+          const uint64_t v_desc = desc_sw64(st + kTileBytes);
+          const uint64_t p_desc = desc_sw64(smem_u32(sm.p_tile[b]));
+          mma_nvf4(tmem + kColO + b * 8, v_desc, p_desc, tmem + kColSfV, tmem + kColSfP, 0);
+          mma_nvf4(tmem + kColO + b * 8, v_desc + 2, p_desc + 2, tmem + kColSfV + 4, tmem + kColSfP + 4, 1);
+          mma_commit(&sm.o_full[b]);
+          mma_commit(&sm.empty[s]);
+        }
+      }
+      // everything this thread issued must have retired before tensor memory is freed
+      mma_commit(&sm.drain);
+      mbar_wait(&sm.drain, 0, sm, p.status);
+    }
+    __syncwarp();
+  }
+
+  // ---- teardown ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4 && lane == 0 && sm.abort_flag) {
+    // copies still in flight must land before the CTA's shared memory is handed on
+    for (int s = 0; s < kStages; ++s) {
+      const unsigned long long t0 = global_ns();
+      while (!mbar_try(&sm.full[s], 0) && !mbar_try(&sm.full[s], 1) && global_ns() - t0 < 200000000ull) {}
+    }
+  }
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side: tensor maps through the driver entry point (no link-time libcuda)
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+struct MapKey {
+  const void* base; int64_t pitch; int64_t pages; int heads; int which;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && pitch == o.pitch && pages == o.pages && heads == o.heads && which == o.which;
+  }
+};
+struct MapEntry { MapKey key; CUtensorMap map; bool valid; };
+
+// K: bytes [64] x heads x tokens [128] x pages ; V: bytes [64] x channels [128] x heads x pages
+static cudaError_t make_map(int which, const void* base, int64_t pitch, int64_t pages, int heads,
+                            CUtensorMap* out) {
+  thread_local MapEntry cache[8] = {};
+  thread_local int next = 0;
+  const MapKey key{base, pitch, pages, heads, which};
+  for (auto& e : cache)
+    if (e.valid && e.key == key) { *out = e.map; return cudaSuccess; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return cudaErrorNotSupported;
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+  if (which == 0) {
+    dims[0] = 64; dims[1] = heads; dims[2] = 128; dims[3] = pages;
+    strides[0] = 64; strides[1] = (cuuint64_t)heads * 64; strides[2] = pitch;
+    box[0] = 64; box[1] = 1; box[2] = 128; box[3] = 1;
+  } else {
+    dims[0] = 64; dims[1] = 128; dims[2] = heads; dims[3] = pages;
+    strides[0] = 64; strides[1] = 128 * 64; strides[2] = pitch;
+    box[0] = 64; box[1] = 128; box[2] = 1; box[3] = 1;
+  }
+  CUtensorMap map;
+  CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  cache[next] = MapEntry{key, map, true};
+  next = (next + 1) % 8;
+  *out = map;
+  return cudaSuccess;
+}
+
+template <int G>
+static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const CUtensorMap& vm,
+                            cudaStream_t stream) {
+  const size_t smem = sizeof(Smem) + 1024;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    e = cudaFuncSetAttribute(decode_sm100_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  dim3 grid(p.num_splits, p.heads_kv, p.rows);
+  decode_sm100_kernel<G><<<grid, 192, smem, stream>>>(km, vm, p);
+  return cudaGetLastError();
+}
+
+}  // namespace sm100
+
+bool decode_sm100_supports(const DecodeParams& p) {
+  if (p.heads_kv < 1 || p.heads_q % p.heads_kv) return false;
+  const int g = p.heads_q / p.heads_kv;
+  return g == 1 || g == 2 || g == 4 || g == 8;
+}
+
+cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream) {
+  if (p.rows == 0) return cudaSuccess;
+  if (!decode_sm100_supports(p)) return cudaErrorNotSupported;
+  if (p.num_pages < 1 || p.num_pages > 0x7FFFFFFF) return cudaErrorInvalidValue;
+  CUtensorMap km, vm;
+  cudaError_t e = sm100::make_map(0, p.k_packed, p.k_pitch, p.num_pages, p.heads_kv, &km);
+  if (e != cudaSuccess) return e;
+  e = sm100::make_map(1, p.v_packed, p.v_pitch, p.num_pages, p.heads_kv, &vm);
+  if (e != cudaSuccess) return e;
+  switch (p.heads_q / p.heads_kv) {
+    case 1: return sm100::launch_g<1>(p, km, vm, stream);
+    case 2: return sm100::launch_g<2>(p, km, vm, stream);
+    case 4: return sm100::launch_g<4>(p, km, vm, stream);
+    case 8: return sm100::launch_g<8>(p, km, vm, stream);
+    default: return cudaErrorNotSupported;
+  }
+}
+
+}  // namespace nvfp4

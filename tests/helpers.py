@@ -74,8 +74,10 @@ class Problem:
         args.update(kw)
         return fp4_decode(**args)
 
-    def oracle_from_bytes(self, rows=None):
-        """Oracle fed with the library's dequantised Q/K/V bytes."""
+    def oracle_from_bytes(self, rows=None, splits: int = 1):
+        """Oracle fed with the library's dequantised Q/K/V bytes.  With ``splits`` > 1 the
+        oracle runs once per page range (the tail goes with range 0) and the partials are
+        merged by LSE weight, which is what the split path computes."""
         from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _quantize
 
         q_fp4, q_sf = _quantize.quantize_query(self.q, heads_kv=self.heads_kv)
@@ -87,11 +89,21 @@ class Problem:
         v_dq = O.dequantize_value_pages(to_np(self.v_fp4), scale_bytes(self.v_sf))
         c = self.case
         sel = slice(None) if rows is None else rows
-        return O.attention_from_dequantized(
-            c["q"][sel], q_dq[sel], k_dq, v_dq, c["page_table"][sel], c["seqused_fp4"][sel],
+        common = dict(
             tail_key=c["k_pages"], tail_value=c["v_pages"], tail_ids=c["residual_page_ids"][sel],
             seqused_residual=c["seqused_residual"][sel], softmax_scale=c["softmax_scale"],
         )
+        args = (c["q"][sel], q_dq[sel], k_dq, v_dq, c["page_table"][sel], c["seqused_fp4"][sel])
+        if splits == 1:
+            return O.attention_from_dequantized(*args, **common)
+        parts, lses = [], []
+        for s in range(splits):
+            o, lse = O.attention_from_dequantized(
+                *args, **common, page_range=lambda n, s=s: O.split_page_range(n, s, splits),
+                owns_tail=(s == 0), return_lse=True)
+            parts.append(o)
+            lses.append(lse)
+        return O.lse_merge(np.stack(parts), np.stack(lses))
 
 
 def interleave_vllm(k_fp4, k_sf, v_fp4, v_sf):
