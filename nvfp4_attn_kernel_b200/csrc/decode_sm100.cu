@@ -51,7 +51,8 @@ struct __align__(1024) Smem {
   __align__(512) uint8_t p_sf[2][kSfBlockBytes];
   __align__(16) float qb[8 * kHeadDim];         // BF16 query as floats (tail)
   __align__(16) float pf[8 * kHeadDim];         // P of the tail block
-  float red[2][4 * 8];
+  __align__(16) float z[2][8 * kPage];          // scaled scores of the current page, [q][kv position]
+  float resc[2][8];                             // per-page rescale factor of each query head
   float red_io[4 * 8];                          // reductions of the tail block and the epilogue
   volatile int page_ok[kStages];                // 0: the stage stands for a page id that was refused
   __align__(8) uint64_t full[kStages];
@@ -280,12 +281,32 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     fence_proxy_async();
     mbar_arrive(&sm.q_ready);
 
-    float m[G], l[G], o[G], resc_prev[G];
+    // Ownership while a page's scores are processed: softmax warp w owns query heads
+    // q = w, w + 4 (< G) over ALL 128 kv positions, four consecutive positions per lane, so
+    // the block maximum is a warp reduction, a 16-position scale group is four adjacent
+    // lanes and the packed E2M1 bytes of P are formed without any exchange.  While P.V is
+    // folded in, thread t is channel t for every query head.
+    constexpr int QPW = (G + 3) / 4;
+    float o[G];
+    float m_w[QPW], l_w[QPW];
 #pragma unroll
-    for (int q = 0; q < G; ++q) { m[q] = -INFINITY; l[q] = 0.f; o[q] = 0.f; resc_prev[q] = 0.f; }
+    for (int q = 0; q < G; ++q) o[q] = 0.f;
+#pragma unroll
+    for (int k = 0; k < QPW; ++k) { m_w[k] = -INFINITY; l_w[k] = 0.f; }
     if (w.tail_len > 0) {
+      float m[G], l[G];
+#pragma unroll
+      for (int q = 0; q < G; ++q) { m[q] = -INFINITY; l[q] = 0.f; }
       asm volatile("bar.sync 1, 128;" ::: "memory");  // qb visible
       tail_block<G>(p, w, sm.qb, sm.pf, sm.red_io, tid, 1, m, l, o);
+      block_sum_128<G>(l, sm.red_io, tid, 1);
+#pragma unroll
+      for (int k = 0; k < QPW; ++k) {
+        const int q = warp + 4 * k;
+#pragma unroll
+        for (int qq = 0; qq < G; ++qq)
+          if (qq == q) { m_w[k] = m[qq]; l_w[k] = lane == 0 ? l[qq] : 0.f; }
+      }
     }
 
     // A thread whose wait expired keeps walking the loop's barrier points with ok = false, so
@@ -294,90 +315,94 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     for (int i = 0; i <= n_pages; ++i) {
       if (i < n_pages) {
         const int b = i & 1;
-        bool ok = alive && mbar_wait(&sm.s_full[b], (i >> 1) & 1, sm, p.status);
-        float z[G], resc[G];
-#pragma unroll
-        for (int q = 0; q < G; ++q) z[q] = -INFINITY;
+        const bool ok = alive && mbar_wait(&sm.s_full[b], (i >> 1) & 1, sm, p.status);
         if (ok) {
           tc_fence_after();
           uint32_t r[8];
           tmem_ld8(tmem + lane_off + kColS + b * 8, r);
           tc_fence_before();
           mbar_arrive(&sm.s_free[b]);
-          if (sm.page_ok[i % kStages]) {
-#pragma unroll
-            for (int q = 0; q < G; ++q) z[q] = __uint_as_float(r[q]) * p.scale_log2;
-          }
-        }
-#pragma unroll
-        for (int q = 0; q < G; ++q) {
-          const float wm = warp_max(z[q]);
-          if (lane == 0) sm.red[b][warp * 8 + q] = wm;
-        }
-        if (!bar_and_128(1, ok)) { alive = false; break; }
-        uint32_t word = 0;
-#pragma unroll
-        for (int q = 0; q < G; ++q) {
-          const float bm = fmaxf(fmaxf(sm.red[b][q], sm.red[b][8 + q]),
-                                 fmaxf(sm.red[b][16 + q], sm.red[b][24 + q]));
-          const float mn = fmaxf(m[q], bm);
-          resc[q] = (m[q] == -INFINITY) ? 0.f : exp2f(m[q] - mn);
-          m[q] = mn;
-          const float pe = exp2_rel(z[q], mn);
-          l[q] = fmaf(l[q], resc[q], pe);
-          // NVFP4 P: scale = e4m3(group max / 6), nibble = e2m1(p / scale); a scale that
-          // rounds to zero is raised to the smallest E4M3 subnormal instead of dropping the group
-          uint32_t sb = p_scale_byte(halfwarp_max(pe));
-          sb = sb == 0 ? 1u : sb;
-          const float sc = e4m3_to_f32((uint8_t)sb);
-          word |= f32_to_e2m1(__fdiv_rn(pe, sc)) << (4 * q);
-          if ((lane & 15) == 0) {  // lanes 0 and 16 own one 16-position group each
-            const int g = tid >> 4;
-            sm.p_sf[b][(g >> 2) * 512 + q * 16 + (g & 3)] = (uint8_t)sb;
-          }
-        }
-        // pair kv positions 2j, 2j+1 into one byte (even position in the low nibble)
-        const uint32_t other = __shfl_xor_sync(0xffffffffu, word, 1);
-        if ((lane & 1) == 0) {
+          const bool page_ok = sm.page_ok[i % kStages] != 0;
 #pragma unroll
           for (int q = 0; q < G; ++q)
-            sm.p_tile[b][sw64_offset(q, tid >> 1)] =
-                (uint8_t)(((word >> (4 * q)) & 15u) | (((other >> (4 * q)) & 15u) << 4));
+            sm.z[b][q * kPage + tid] = page_ok ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY;
+        }
+        if (!bar_and_128(1, ok)) { alive = false; break; }
+#pragma unroll
+        for (int k = 0; k < QPW; ++k) {
+          const int q = warp + 4 * k;
+          if (q < G) {
+            const float4 zz = *reinterpret_cast<const float4*>(&sm.z[b][q * kPage + 4 * lane]);
+            float gm = fmaxf(fmaxf(zz.x, zz.y), fmaxf(zz.z, zz.w));
+            gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 1));
+            gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 2));   // max of this 16-position group
+            float bm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 4));
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));  // max of the page
+            const float mn = fmaxf(m_w[k], bm);
+            const float resc = (m_w[k] == -INFINITY) ? 0.f : exp2f(m_w[k] - mn);
+            m_w[k] = mn;
+            const float p0 = exp2_rel(zz.x, mn), p1 = exp2_rel(zz.y, mn);
+            const float p2 = exp2_rel(zz.z, mn), p3 = exp2_rel(zz.w, mn);
+            l_w[k] = fmaf(l_w[k], resc, (p0 + p1) + (p2 + p3));
+            // NVFP4 P: scale = e4m3(group max / 6), nibble = e2m1(p / scale); a scale that
+            // rounds to zero is raised to the smallest E4M3 subnormal instead of dropping the group
+            uint32_t sb = p_scale_byte(exp2_rel(gm, mn));
+            sb = sb == 0 ? 1u : sb;
+            const float inv = __fdiv_rn(1.0f, e4m3_to_f32((uint8_t)sb));
+            const uint32_t packed = f32x4_to_e2m1x4(p0 * inv, p1 * inv, p2 * inv, p3 * inv);
+            *reinterpret_cast<uint16_t*>(&sm.p_tile[b][sw64_offset(q, 2 * lane)]) = (uint16_t)packed;
+            if ((lane & 3) == 0) {
+              const int g = lane >> 2;
+              sm.p_sf[b][(g >> 2) * 512 + q * 16 + (g & 3)] = (uint8_t)sb;
+            }
+            if (lane == 0) sm.resc[b][q] = resc;
+          }
         }
         fence_proxy_async();
         mbar_arrive(&sm.p_full[b]);
-        if (i >= 1) {
-          // fold page i-1: o = o * rescale(i-1) + O_page(i-1)
-          const int bj = (i - 1) & 1;
-          if (mbar_wait(&sm.o_full[bj], ((i - 1) >> 1) & 1, sm, p.status)) {
-            tc_fence_after();
-            uint32_t ro[8];
-            tmem_ld8(tmem + lane_off + kColO + bj * 8, ro);
-            tc_fence_before();
-            mbar_arrive(&sm.o_free[bj]);
-#pragma unroll
-            for (int q = 0; q < G; ++q) o[q] = fmaf(o[q], resc_prev[q], __uint_as_float(ro[q]));
-          } else {
-            alive = false;
-          }
-        }
-#pragma unroll
-        for (int q = 0; q < G; ++q) resc_prev[q] = resc[q];
-      } else if (n_pages > 0 && alive) {
-        const int bj = (i - 1) & 1;
-        if (mbar_wait(&sm.o_full[bj], ((i - 1) >> 1) & 1, sm, p.status)) {
+      }
+      if (i >= 1 && alive) {
+        // fold page i-1: o = o * rescale(i-1) + O_page(i-1)
+        const int j = i - 1, bj = j & 1;
+        if (mbar_wait(&sm.o_full[bj], (j >> 1) & 1, sm, p.status)) {
           tc_fence_after();
           uint32_t ro[8];
           tmem_ld8(tmem + lane_off + kColO + bj * 8, ro);
           tc_fence_before();
+          mbar_arrive(&sm.o_free[bj]);
 #pragma unroll
-          for (int q = 0; q < G; ++q) o[q] = fmaf(o[q], resc_prev[q], __uint_as_float(ro[q]));
+          for (int q = 0; q < G; ++q) o[q] = fmaf(o[q], sm.resc[bj][q], __uint_as_float(ro[q]));
         } else {
           alive = false;
         }
       }
     }
-    if (bar_and_128(1, alive)) write_output<G>(p, w, sm.red_io, tid, 1, m, l, o);
+    // ---- epilogue: row sums per query head, normalise, store ----
+#pragma unroll
+    for (int k = 0; k < QPW; ++k) {
+      const int q = warp + 4 * k;
+      if (q < G) {
+        const float ls = warp_sum(l_w[k]);
+        if (lane == 0) { sm.red_io[q] = ls; sm.red_io[8 + q] = m_w[k]; }
+      }
+    }
+    if (bar_and_128(1, alive)) {
+#pragma unroll
+      for (int q = 0; q < G; ++q) {
+        const float lq = sm.red_io[q], mq = sm.red_io[8 + q];
+        const int head = w.kvh * G + q;
+        const float val = lq > 0.f ? __fdiv_rn(o[q], lq) : 0.f;
+        if (p.emit_partial) {
+          const int64_t idx = ((int64_t)w.split * p.rows + w.row) * p.heads_q + head;
+          p.o_partial[idx * kHeadDim + tid] = val;
+          if (tid == 0) p.lse_partial[idx] = lq > 0.f ? (mq + log2f(lq)) * kLn2 : -INFINITY;
+        } else {
+          const int64_t orow = p.out_indices ? (int64_t)p.out_indices[w.row] : (int64_t)w.row;
+          p.out[(orow * p.heads_q + head) * kHeadDim + tid] = __bfloat16_as_ushort(__float2bfloat16_rn(val));
+        }
+      }
+    }
   } else if (warp == 4) {
     // =====================  producer  =====================
     bool alive = true;

@@ -58,6 +58,20 @@ __device__ __forceinline__ uint32_t f32x8_to_e2m1x8(float f0, float f1, float f2
   return r;
 }
 
+// Four floats -> four E2M1 nibbles in the low 16 bits, element i in nibble i.
+__device__ __forceinline__ uint32_t f32x4_to_e2m1x4(float f0, float f1, float f2, float f3) {
+  uint32_t r;
+  asm("{\n\t"
+      ".reg .b8 b0, b1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "mov.b32 %0, {b0, b1, b0, b1};\n\t"
+      "}"
+      : "=r"(r)
+      : "f"(f0), "f"(f1), "f"(f2), "f"(f3));
+  return r & 0xFFFFu;
+}
+
 // One float -> E2M1 nibble (low 4 bits).
 __device__ __forceinline__ uint32_t f32_to_e2m1(float x) {
   uint32_t r;
