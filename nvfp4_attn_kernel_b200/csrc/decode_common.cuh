@@ -94,14 +94,13 @@ __device__ __forceinline__ float exp2_rel(float z, float m) {
   return (m == -INFINITY) ? 0.f : exp2f(z - m);
 }
 
-// The BF16 tail block.  Seeds the running max m, the per-thread partial sums l
-// and the per-thread output accumulators o (thread = channel).
+// The BF16 tail block, first half: thread = kv position.  Seeds the running max m and the
+// per-thread partial sums l, and leaves P (rounded to BF16, as floats) in pf[G][128].
 //   qb : [G][128] floats, the BF16 query of this KV head's G query heads
-//   pf : [G][128] floats scratch for P
 template <int G>
-__device__ __forceinline__ void tail_block(const DecodeParams& p, const TileWork& w, const float* qb,
-                                           float* pf, float* red, int tid, int bar_id,
-                                           float (&m)[G], float (&l)[G], float (&o)[G]) {
+__device__ __forceinline__ void tail_scores(const DecodeParams& p, const TileWork& w, const float* qb,
+                                            float* pf, float* red, int tid, int bar_id,
+                                            float (&m)[G], float (&l)[G]) {
   const int len = w.tail_len;
   const int64_t tok0 = (int64_t)w.tail_id * kPage;
   float z[G];
@@ -142,9 +141,16 @@ __device__ __forceinline__ void tail_block(const DecodeParams& p, const TileWork
     // P of the tail meets V as BF16
     pf[q * kHeadDim + tid] = __bfloat162float(__float2bfloat16_rn(pe));
   }
-  asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
-  // thread = channel d; positions past the tail length are never read, so stale
-  // or non-finite bytes there cannot reach the output.
+}
+
+// Second half: thread = channel d, o[q] = sum_t P[q][t] * V[t][d].  The caller orders the
+// pf writes of tail_scores before this.  Positions past the tail length are never read, so
+// stale or non-finite bytes there cannot reach the output.
+template <int G>
+__device__ __forceinline__ void tail_pv(const DecodeParams& p, const TileWork& w, const float* pf,
+                                        int tid, float (&o)[G]) {
+  const int len = w.tail_len;
+  const int64_t tok0 = (int64_t)w.tail_id * kPage;
   const uint16_t* vcol = p.tail_value + (tok0 * p.heads_kv + w.kvh) * kHeadDim + tid;
   const int64_t vstride = (int64_t)p.heads_kv * kHeadDim;
 #pragma unroll
@@ -155,6 +161,16 @@ __device__ __forceinline__ void tail_block(const DecodeParams& p, const TileWork
 #pragma unroll
     for (int q = 0; q < G; ++q) o[q] = fmaf(pf[q * kHeadDim + t], v, o[q]);
   }
+}
+
+// Both halves on the same 128 threads (the CUDA-core kernel).
+template <int G>
+__device__ __forceinline__ void tail_block(const DecodeParams& p, const TileWork& w, const float* qb,
+                                           float* pf, float* red, int tid, int bar_id,
+                                           float (&m)[G], float (&l)[G], float (&o)[G]) {
+  tail_scores<G>(p, w, qb, pf, red, tid, bar_id, m, l);
+  asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+  tail_pv<G>(p, w, pf, tid, o);
   asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
 }
 

@@ -2,10 +2,12 @@
 // E2M1 operands with UE4M3 scales per 16 elements), accumulators in tensor memory,
 // K/V page tiles staged by TMA through a ring of shared-memory stages.
 //
-// One CTA of 192 threads per (split, KV head, row):
-//   warps 0-3  softmax / output threads (one tensor-memory lane each)
-//   warp  4    producer: page-table walk, TMA tile loads, bulk copies of the scale blocks
-//   warp  5    MMA issuer (one elected lane) and owner of the tensor-memory allocation
+// One CTA of 352 threads per (split, KV head, row):
+//   warps 0-3  score threads: read S^T from tensor memory, online softmax, P -> NVFP4
+//   warps 4-7  output threads: fold each page's O^T into the running output, epilogue
+//   warp  8    producer: page-table walk, TMA tile loads, bulk copies of the scale blocks
+//   warp  9    issuer of S^T = K . Q^T (one elected lane), owner of the tensor-memory allocation
+//   warp 10    issuer of O^T = V^T . P^T (one elected lane)
 //
 // The product is formed transposed so that the G <= 8 query heads of a KV head are the
 // N = 8 side of the MMA and nothing is padded to 128:
@@ -13,20 +15,34 @@
 //   O^T[128 d , 8 q] = V_page^T[128 d, 128 kv] . P^T          (A = V tile as it lies in the page)
 // Both page layouts are already K-major A operands, and the 512-byte scale atoms of the
 // page format are copied to tensor memory with tcgen05.cp unchanged.
-// Thread t of the 128 is kv position t while S^T is read and channel t while O^T is
-// accumulated, so the running output lives in G registers per thread and O^T is never
-// rescaled in tensor memory: each page's P.V lands in a fresh accumulator and is folded
-// in as o = o * rescale + O_page, exactly the order of the attention oracle.
+// An output thread is channel t for every query head, so the running output lives in G
+// registers per thread and O^T is never rescaled in tensor memory: each page's P.V lands
+// in a fresh accumulator and is folded in as o = o * rescale + O_page, exactly the order
+// of the attention oracle.
 //
 // Every device-side wait is bounded; on expiry the CTA raises NVFP4_STATUS_WAIT_TIMEOUT,
 // drains what it has in flight, frees its tensor memory and returns.
 #include <cuda.h>
+#include <cstdlib>
 
 #include "decode_common.cuh"
 
 namespace nvfp4 {
 
 namespace sm100 {
+
+// Developer timeline: with -DNVFP4_TRACE one CTA stamps clock64() at the hand-over points of
+// its three roles into the buffer whose address is in the NVFP4_TRACE_PTR environment variable.
+#ifdef NVFP4_TRACE
+__device__ unsigned long long* g_trace = nullptr;
+#define TRACE(role, iter, ev)                                                              \
+  do {                                                                                     \
+    if (g_trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (iter) < 40)   \
+      g_trace[((role) * 40 + (iter)) * 8 + (ev)] = clock64();                              \
+  } while (0)
+#else
+#define TRACE(role, iter, ev) do {} while (0)
+#endif
 
 constexpr int kStages = 4;
 constexpr int kTileBytes = 8192;                                  // 128 rows x 64 B
@@ -52,13 +68,13 @@ struct __align__(1024) Smem {
   __align__(16) float qb[8 * kHeadDim];         // BF16 query as floats (tail)
   __align__(16) float pf[8 * kHeadDim];         // P of the tail block
   __align__(16) float z[2][8 * kPage];          // scaled scores of the current page, [q][kv position]
-  float resc[2][8];                             // per-page rescale factor of each query head
+  float resc[4][8];                             // ring of per-page rescale factors, [page & 3][q]
   float red_io[4 * 8];                          // reductions of the tail block and the epilogue
   volatile int page_ok[kStages];                // 0: the stage stands for a page id that was refused
   __align__(8) uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t s_full[2], s_free[2], p_full[2], o_full[2], o_free[2];
-  uint64_t q_ready, drain;
+  uint64_t q_ready, drain[2];
   uint32_t tmem_base;
   volatile int abort_flag;
 };
@@ -185,7 +201,25 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "memory");
 }
 
-// Barrier over the 128 softmax threads that also ANDs a predicate across them.
+constexpr int kProducerWarp = 8;
+constexpr int kQkWarp = 9;   // also owns the tensor-memory allocation
+constexpr int kPvWarp = 10;
+
+// Barrier over the 256 score and output threads with an AND of a predicate.
+__device__ __forceinline__ bool bar_and_256(int bar_id, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "bar.red.and.pred p, %1, 256, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(bar_id), "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
+
+// Barrier over the 128 score threads that also ANDs a predicate across them.
 __device__ __forceinline__ bool bar_and_128(int bar_id, bool pred) {
   uint32_t out;
   asm volatile(
@@ -204,15 +238,15 @@ __device__ __forceinline__ int sw64_offset(int row, int byte_col) {
   return row * 64 + ((((byte_col >> 4) ^ ((row >> 1) & 3))) << 4) + (byte_col & 15);
 }
 
+constexpr int kThreads = 352;
+
 template <int G>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(kThreads, 2)
 decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                     const DecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const TileWork w = resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x);
-  const int n_pages = w.last_page - w.first_page;
 
   // ---- set-up: barriers, tensor memory, zeroed operand tiles ----
   if (tid == 0) {
@@ -223,11 +257,12 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       mbar_init(&sm.o_full[b], 1); mbar_init(&sm.o_free[b], 128);
     }
     mbar_init(&sm.q_ready, 128);
-    mbar_init(&sm.drain, 1);
+    mbar_init(&sm.drain[0], 1);
+    mbar_init(&sm.drain[1], 1);
     sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == kQkWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&sm.tmem_base)),
                  "r"(kTmemCols)
@@ -235,17 +270,23 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   // rows G..7 of the N = 8 operands and their scale rows stay zero for the whole kernel
-  for (int i = tid; i < 512 / 16; i += 192) reinterpret_cast<uint4*>(sm.q_tile)[i] = make_uint4(0, 0, 0, 0);
-  for (int i = tid; i < 2 * 512 / 16; i += 192) reinterpret_cast<uint4*>(sm.p_tile)[i] = make_uint4(0, 0, 0, 0);
-  for (int i = tid; i < 2 * kSfBlockBytes / 16; i += 192)
+  for (int i = tid; i < 512 / 16; i += kThreads) reinterpret_cast<uint4*>(sm.q_tile)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < 2 * 512 / 16; i += kThreads) reinterpret_cast<uint4*>(sm.p_tile)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < 2 * kSfBlockBytes / 16; i += kThreads)
     reinterpret_cast<uint4*>(sm.p_sf)[i] = make_uint4(0, 0, 0, 0);
+  const TileWork w = resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x);
+  const int n_pages = w.last_page - w.first_page;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
 
   if (warp < 4) {
-    // =====================  softmax / output threads  =====================
+    // =====================  score threads  =====================
+    // While a page's scores are processed, warp w owns query heads q = w, w + 4 (< G) over
+    // ALL 128 kv positions, four consecutive positions per lane: the page maximum is a warp
+    // reduction, a 16-position scale group is four adjacent lanes and the packed E2M1 bytes
+    // of P are formed without any exchange.
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     // query operand: G packed rows, swizzled; its scale block; the BF16 copy for the tail
     if (tid < G * 4) {
@@ -258,6 +299,13 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       reinterpret_cast<uint4*>(sm.q_sf)[tid - 64] = *(reinterpret_cast<const uint4*>(
           p.q_sf + (int64_t)w.row * p.heads_q * kSfBlockBytes + (int64_t)w.kvh * kSfBlockBytes) + (tid - 64));
     }
+    fence_proxy_async();
+    mbar_arrive(&sm.q_ready);
+
+    constexpr int QPW = (G + 3) / 4;
+    float m_w[QPW], l_w[QPW];
+#pragma unroll
+    for (int k = 0; k < QPW; ++k) { m_w[k] = -INFINITY; l_w[k] = 0.f; }
     if (w.tail_len > 0) {
       for (int it = tid; it < G * 16; it += 128) {
         const int q = it >> 4, c = it & 15;
@@ -277,28 +325,10 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 #pragma unroll
         for (int i = 0; i < 8; ++i) sm.qb[q * kHeadDim + c * 8 + i] = f[i];
       }
-    }
-    fence_proxy_async();
-    mbar_arrive(&sm.q_ready);
-
-    // Ownership while a page's scores are processed: softmax warp w owns query heads
-    // q = w, w + 4 (< G) over ALL 128 kv positions, four consecutive positions per lane, so
-    // the block maximum is a warp reduction, a 16-position scale group is four adjacent
-    // lanes and the packed E2M1 bytes of P are formed without any exchange.  While P.V is
-    // folded in, thread t is channel t for every query head.
-    constexpr int QPW = (G + 3) / 4;
-    float o[G];
-    float m_w[QPW], l_w[QPW];
-#pragma unroll
-    for (int q = 0; q < G; ++q) o[q] = 0.f;
-#pragma unroll
-    for (int k = 0; k < QPW; ++k) { m_w[k] = -INFINITY; l_w[k] = 0.f; }
-    if (w.tail_len > 0) {
       float m[G], l[G];
-#pragma unroll
-      for (int q = 0; q < G; ++q) { m[q] = -INFINITY; l[q] = 0.f; }
       asm volatile("bar.sync 1, 128;" ::: "memory");  // qb visible
-      tail_block<G>(p, w, sm.qb, sm.pf, sm.red_io, tid, 1, m, l, o);
+      tail_scores<G>(p, w, sm.qb, sm.pf, sm.red_io, tid, 1, m, l);
+      asm volatile("bar.sync 2, 256;" ::: "memory");  // P of the tail visible to the output threads
       block_sum_128<G>(l, sm.red_io, tid, 1);
 #pragma unroll
       for (int k = 0; k < QPW; ++k) {
@@ -312,73 +342,68 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     // A thread whose wait expired keeps walking the loop's barrier points with ok = false, so
     // the 128 threads always leave the loop together.
     bool alive = true;
-    for (int i = 0; i <= n_pages; ++i) {
-      if (i < n_pages) {
-        const int b = i & 1;
-        const bool ok = alive && mbar_wait(&sm.s_full[b], (i >> 1) & 1, sm, p.status);
-        if (ok) {
-          tc_fence_after();
-          uint32_t r[8];
-          tmem_ld8(tmem + lane_off + kColS + b * 8, r);
-          tc_fence_before();
-          mbar_arrive(&sm.s_free[b]);
-          const bool page_ok = sm.page_ok[i % kStages] != 0;
+    for (int i = 0; i < n_pages; ++i) {
+      const int b = i & 1;
+      if (tid == 0) TRACE(0, i, 0);
+      const bool ok = alive && mbar_wait(&sm.s_full[b], (i >> 1) & 1, sm, p.status);
+      if (tid == 0) TRACE(0, i, 1);
+      if (ok) {
+        tc_fence_after();
+        uint32_t r[8];
+        tmem_ld8(tmem + lane_off + kColS + b * 8, r);
+        tc_fence_before();
+        mbar_arrive(&sm.s_free[b]);
+        const bool page_ok = sm.page_ok[i % kStages] != 0;
 #pragma unroll
-          for (int q = 0; q < G; ++q)
-            sm.z[b][q * kPage + tid] = page_ok ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY;
-        }
-        if (!bar_and_128(1, ok)) { alive = false; break; }
+        for (int q = 0; q < G; ++q)
+          sm.z[b][q * kPage + tid] = page_ok ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY;
+      }
+      if (tid == 0) TRACE(0, i, 2);
+      if (!bar_and_128(1, ok)) { alive = false; break; }
+      if (tid == 0) TRACE(0, i, 3);
+      // P.V of page i-2 has retired: its P tile, its scale rows and the rescale slot of
+      // page i-4 may be overwritten
+      if (i >= 2 && !mbar_wait(&sm.o_full[b], ((i - 2) >> 1) & 1, sm, p.status)) alive = false;
 #pragma unroll
-        for (int k = 0; k < QPW; ++k) {
-          const int q = warp + 4 * k;
-          if (q < G) {
-            const float4 zz = *reinterpret_cast<const float4*>(&sm.z[b][q * kPage + 4 * lane]);
-            float gm = fmaxf(fmaxf(zz.x, zz.y), fmaxf(zz.z, zz.w));
-            gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 1));
-            gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 2));   // max of this 16-position group
-            float bm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 4));
-            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
-            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));  // max of the page
-            const float mn = fmaxf(m_w[k], bm);
-            const float resc = (m_w[k] == -INFINITY) ? 0.f : exp2f(m_w[k] - mn);
-            m_w[k] = mn;
-            const float p0 = exp2_rel(zz.x, mn), p1 = exp2_rel(zz.y, mn);
-            const float p2 = exp2_rel(zz.z, mn), p3 = exp2_rel(zz.w, mn);
-            l_w[k] = fmaf(l_w[k], resc, (p0 + p1) + (p2 + p3));
-            // NVFP4 P: scale = e4m3(group max / 6), nibble = e2m1(p / scale); a scale that
-            // rounds to zero is raised to the smallest E4M3 subnormal instead of dropping the group
-            uint32_t sb = p_scale_byte(exp2_rel(gm, mn));
-            sb = sb == 0 ? 1u : sb;
-            const float inv = __fdiv_rn(1.0f, e4m3_to_f32((uint8_t)sb));
-            const uint32_t packed = f32x4_to_e2m1x4(p0 * inv, p1 * inv, p2 * inv, p3 * inv);
-            *reinterpret_cast<uint16_t*>(&sm.p_tile[b][sw64_offset(q, 2 * lane)]) = (uint16_t)packed;
-            if ((lane & 3) == 0) {
-              const int g = lane >> 2;
-              sm.p_sf[b][(g >> 2) * 512 + q * 16 + (g & 3)] = (uint8_t)sb;
-            }
-            if (lane == 0) sm.resc[b][q] = resc;
+      for (int k = 0; k < QPW; ++k) {
+        const int q = warp + 4 * k;
+        if (q < G) {
+          const float4 zz = *reinterpret_cast<const float4*>(&sm.z[b][q * kPage + 4 * lane]);
+          float gm = fmaxf(fmaxf(zz.x, zz.y), fmaxf(zz.z, zz.w));
+          gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 1));
+          gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 2));   // max of this 16-position group
+          float bm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 4));
+          bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
+          bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));  // max of the page
+          const float mn = fmaxf(m_w[k], bm);
+          const float resc = (m_w[k] == -INFINITY) ? 0.f : exp2f(m_w[k] - mn);
+          m_w[k] = mn;
+          const float p0 = exp2_rel(zz.x, mn), p1 = exp2_rel(zz.y, mn);
+          const float p2 = exp2_rel(zz.z, mn), p3 = exp2_rel(zz.w, mn);
+          l_w[k] = fmaf(l_w[k], resc, (p0 + p1) + (p2 + p3));
+          // NVFP4 P in the oracle's form: scale = e4m3(group max / 6), nibble = e2m1(p / scale).
+          // A scale that rounds to zero is raised to the smallest E4M3 subnormal instead of
+          // dropping the group.  The two divisions are a multiply by fp32(1/6) and by an
+          // approximate reciprocal; that can move a result only when it sits within an ulp of
+          // a rounding boundary.
+          uint32_t sb = f32_to_e4m3(exp2_rel(gm, mn) * (1.0f / 6.0f));
+          sb = sb == 0 ? 1u : sb;
+          const float inv = __fdividef(1.0f, e4m3_to_f32((uint8_t)sb));
+          const uint32_t packed = f32x4_to_e2m1x4(p0 * inv, p1 * inv, p2 * inv, p3 * inv);
+          *reinterpret_cast<uint16_t*>(&sm.p_tile[b][sw64_offset(q, 2 * lane)]) = (uint16_t)packed;
+          if ((lane & 3) == 0) {
+            const int g = lane >> 2;
+            sm.p_sf[b][(g >> 2) * 512 + q * 16 + (g & 3)] = (uint8_t)sb;
           }
-        }
-        fence_proxy_async();
-        mbar_arrive(&sm.p_full[b]);
-      }
-      if (i >= 1 && alive) {
-        // fold page i-1: o = o * rescale(i-1) + O_page(i-1)
-        const int j = i - 1, bj = j & 1;
-        if (mbar_wait(&sm.o_full[bj], (j >> 1) & 1, sm, p.status)) {
-          tc_fence_after();
-          uint32_t ro[8];
-          tmem_ld8(tmem + lane_off + kColO + bj * 8, ro);
-          tc_fence_before();
-          mbar_arrive(&sm.o_free[bj]);
-#pragma unroll
-          for (int q = 0; q < G; ++q) o[q] = fmaf(o[q], sm.resc[bj][q], __uint_as_float(ro[q]));
-        } else {
-          alive = false;
+          if (lane == 0) sm.resc[i & 3][q] = resc;
         }
       }
+      if (tid == 0) TRACE(0, i, 4);
+      fence_proxy_async();
+      mbar_arrive(&sm.p_full[b]);
+      if (tid == 0) TRACE(0, i, 5);
     }
-    // ---- epilogue: row sums per query head, normalise, store ----
+    // row sums and final maxima of every query head, for the output threads
 #pragma unroll
     for (int k = 0; k < QPW; ++k) {
       const int q = warp + 4 * k;
@@ -387,7 +412,37 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         if (lane == 0) { sm.red_io[q] = ls; sm.red_io[8 + q] = m_w[k]; }
       }
     }
-    if (bar_and_128(1, alive)) {
+    bar_and_256(3, alive);
+  } else if (warp < 8) {
+    // =====================  output threads: thread t = channel t  =====================
+    const int t = tid - 128;
+    const uint32_t lane_off = (uint32_t)((warp - 4) * 32) << 16;
+    float o[G];
+#pragma unroll
+    for (int q = 0; q < G; ++q) o[q] = 0.f;
+    if (w.tail_len > 0) {
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      tail_pv<G>(p, w, sm.pf, t, o);
+    }
+    bool alive = true;
+    for (int j = 0; j < n_pages && alive; ++j) {
+      // fold page j: o = o * rescale(j) + O_page(j)
+      const int bj = j & 1;
+      if (mbar_wait(&sm.o_full[bj], (j >> 1) & 1, sm, p.status)) {
+        if (t == 0) TRACE(0, j, 6);
+        tc_fence_after();
+        uint32_t ro[8];
+        tmem_ld8(tmem + lane_off + kColO + bj * 8, ro);
+        tc_fence_before();
+        mbar_arrive(&sm.o_free[bj]);
+#pragma unroll
+        for (int q = 0; q < G; ++q) o[q] = fmaf(o[q], sm.resc[j & 3][q], __uint_as_float(ro[q]));
+        if (t == 0) TRACE(0, j, 7);
+      } else {
+        alive = false;
+      }
+    }
+    if (bar_and_256(3, alive)) {
 #pragma unroll
       for (int q = 0; q < G; ++q) {
         const float lq = sm.red_io[q], mq = sm.red_io[8 + q];
@@ -395,18 +450,17 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         const float val = lq > 0.f ? __fdiv_rn(o[q], lq) : 0.f;
         if (p.emit_partial) {
           const int64_t idx = ((int64_t)w.split * p.rows + w.row) * p.heads_q + head;
-          p.o_partial[idx * kHeadDim + tid] = val;
-          if (tid == 0) p.lse_partial[idx] = lq > 0.f ? (mq + log2f(lq)) * kLn2 : -INFINITY;
+          p.o_partial[idx * kHeadDim + t] = val;
+          if (t == 0) p.lse_partial[idx] = lq > 0.f ? (mq + log2f(lq)) * kLn2 : -INFINITY;
         } else {
           const int64_t orow = p.out_indices ? (int64_t)p.out_indices[w.row] : (int64_t)w.row;
-          p.out[(orow * p.heads_q + head) * kHeadDim + tid] = __bfloat16_as_ushort(__float2bfloat16_rn(val));
+          p.out[(orow * p.heads_q + head) * kHeadDim + t] = __bfloat16_as_ushort(__float2bfloat16_rn(val));
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == kProducerWarp) {
     // =====================  producer  =====================
     bool alive = true;
-    int issued = 0;
     int ids = -1;
     for (int i = 0; i < n_pages && alive; ++i) {
       if ((i & 31) == 0) {
@@ -420,7 +474,9 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
       if (lane == 0) {
         const int s = i % kStages;
+        TRACE(1, i, 0);
         alive = mbar_wait(&sm.empty[s], ((i / kStages) & 1) ^ 1, sm, p.status);
+        TRACE(1, i, 1);
         if (alive) {
           uint8_t* st = sm.stage[s];
           sm.page_ok[s] = pid >= 0 ? 1 : 0;
@@ -434,20 +490,21 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
                       p.v_sf + pid * p.v_sf_pitch + (int64_t)w.kvh * kSfBlockBytes, kSfBlockBytes, &sm.full[s]);
           } else {
             // a page id outside the cache is never turned into an address: the stage gets zero
-            // scales (so both products are zero) and the softmax threads mask its scores
+            // scales (so both products are zero) and the score threads mask its scores
             for (int j = 0; j < 2 * kSfBlockBytes / 16; ++j)
               reinterpret_cast<uint4*>(st + 2 * kTileBytes)[j] = make_uint4(0, 0, 0, 0);
             fence_proxy_async();
             mbar_arrive(&sm.full[s]);
           }
-          ++issued;
+          TRACE(1, i, 2);
         }
       }
       alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
     }
-    (void)issued;
-  } else {
-    // =====================  MMA issuer  =====================
+  } else if (warp == kQkWarp) {
+    // =====================  MMA issuer 1: S^T = K . Q^T  =====================
+    // Issuing a tcgen05 instruction costs the issuing thread some 60 cycles and a barrier
+    // wait about twice that, so the two products of a page are issued by two threads.
     if (lane == 0 && n_pages > 0) {
       bool alive = mbar_wait(&sm.q_ready, 0, sm, p.status);
       if (alive) {
@@ -456,43 +513,55 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         cp_sf(tmem + kColSfQ + 4, smem_u32(sm.q_sf + 512));
       }
       const uint64_t q_desc = desc_sw64(smem_u32(sm.q_tile));
-      for (int i = 0; i <= n_pages && alive; ++i) {
-        if (i < n_pages) {
-          const int s = i % kStages, b = i & 1;
-          alive = mbar_wait(&sm.full[s], (i / kStages) & 1, sm, p.status) &&
-                  mbar_wait(&sm.s_free[b], ((i >> 1) & 1) ^ 1, sm, p.status);
-          if (!alive) break;
-          tc_fence_after();
-          const uint32_t st = smem_u32(sm.stage[s]);
-          cp_sf(tmem + kColSfK, st + 2 * kTileBytes);
-          cp_sf(tmem + kColSfK + 4, st + 2 * kTileBytes + 512);
-          const uint64_t k_desc = desc_sw64(st);
-          mma_nvf4(tmem + kColS + b * 8, k_desc, q_desc, tmem + kColSfK, tmem + kColSfQ, 0);
-          mma_nvf4(tmem + kColS + b * 8, k_desc + 2, q_desc + 2, tmem + kColSfK + 4, tmem + kColSfQ + 4, 1);
-          mma_commit(&sm.s_full[b]);
-        }
-        if (i >= 1) {
-          const int j = i - 1, s = j % kStages, b = j & 1;
-          alive = mbar_wait(&sm.p_full[b], (j >> 1) & 1, sm, p.status) &&
-                  mbar_wait(&sm.o_free[b], ((j >> 1) & 1) ^ 1, sm, p.status);
-          if (!alive) break;
-          tc_fence_after();
-          const uint32_t st = smem_u32(sm.stage[s]);
-          cp_sf(tmem + kColSfV, st + 2 * kTileBytes + kSfBlockBytes);
-          cp_sf(tmem + kColSfV + 4, st + 2 * kTileBytes + kSfBlockBytes + 512);
-          cp_sf(tmem + kColSfP, smem_u32(sm.p_sf[b]));
-          cp_sf(tmem + kColSfP + 4, smem_u32(sm.p_sf[b] + 512));
-          const uint64_t v_desc = desc_sw64(st + kTileBytes);
-          const uint64_t p_desc = desc_sw64(smem_u32(sm.p_tile[b]));
-          mma_nvf4(tmem + kColO + b * 8, v_desc, p_desc, tmem + kColSfV, tmem + kColSfP, 0);
-          mma_nvf4(tmem + kColO + b * 8, v_desc + 2, p_desc + 2, tmem + kColSfV + 4, tmem + kColSfP + 4, 1);
-          mma_commit(&sm.o_full[b]);
-          mma_commit(&sm.empty[s]);
-        }
+      for (int i = 0; i < n_pages && alive; ++i) {
+        const int s = i % kStages, b = i & 1;
+        alive = mbar_wait(&sm.full[s], (i / kStages) & 1, sm, p.status) &&
+                mbar_wait(&sm.s_free[b], ((i >> 1) & 1) ^ 1, sm, p.status);
+        if (!alive) break;
+        TRACE(2, i, 0);
+        tc_fence_after();
+        const uint32_t st = smem_u32(sm.stage[s]);
+        cp_sf(tmem + kColSfK, st + 2 * kTileBytes);
+        cp_sf(tmem + kColSfK + 4, st + 2 * kTileBytes + 512);
+        const uint64_t k_desc = desc_sw64(st);
+        mma_nvf4(tmem + kColS + b * 8, k_desc, q_desc, tmem + kColSfK, tmem + kColSfQ, 0);
+        mma_nvf4(tmem + kColS + b * 8, k_desc + 2, q_desc + 2, tmem + kColSfK + 4, tmem + kColSfQ + 4, 1);
+        mma_commit(&sm.s_full[b]);
+        TRACE(2, i, 1);
       }
       // everything this thread issued must have retired before tensor memory is freed
-      mma_commit(&sm.drain);
-      mbar_wait(&sm.drain, 0, sm, p.status);
+      mma_commit(&sm.drain[0]);
+      mbar_wait(&sm.drain[0], 0, sm, p.status);
+    }
+    __syncwarp();
+  } else {
+    // =====================  MMA issuer 2: O^T = V^T . P^T  =====================
+    if (lane == 0 && n_pages > 0) {
+      bool alive = true;
+      for (int j = 0; j < n_pages && alive; ++j) {
+        const int s = j % kStages, b = j & 1;
+        // p_full(j) implies that S^T(j) was read, hence that K.Q^T of page j and its scale
+        // copies have retired: the commit below may hand the whole stage back
+        alive = mbar_wait(&sm.p_full[b], (j >> 1) & 1, sm, p.status) &&
+                mbar_wait(&sm.o_free[b], ((j >> 1) & 1) ^ 1, sm, p.status);
+        if (!alive) break;
+        TRACE(2, j, 2);
+        tc_fence_after();
+        const uint32_t st = smem_u32(sm.stage[s]);
+        cp_sf(tmem + kColSfV, st + 2 * kTileBytes + kSfBlockBytes);
+        cp_sf(tmem + kColSfV + 4, st + 2 * kTileBytes + kSfBlockBytes + 512);
+        cp_sf(tmem + kColSfP, smem_u32(sm.p_sf[b]));
+        cp_sf(tmem + kColSfP + 4, smem_u32(sm.p_sf[b] + 512));
+        const uint64_t v_desc = desc_sw64(st + kTileBytes);
+        const uint64_t p_desc = desc_sw64(smem_u32(sm.p_tile[b]));
+        mma_nvf4(tmem + kColO + b * 8, v_desc, p_desc, tmem + kColSfV, tmem + kColSfP, 0);
+        mma_nvf4(tmem + kColO + b * 8, v_desc + 2, p_desc + 2, tmem + kColSfV + 4, tmem + kColSfP + 4, 1);
+        mma_commit(&sm.o_full[b]);
+        mma_commit(&sm.empty[s]);
+        TRACE(2, j, 3);
+      }
+      mma_commit(&sm.drain[1]);
+      mbar_wait(&sm.drain[1], 0, sm, p.status);
     }
     __syncwarp();
   }
@@ -500,7 +569,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   // ---- teardown ----
   tc_fence_before();
   __syncthreads();
-  if (warp == 4 && lane == 0 && sm.abort_flag) {
+  if (warp == kProducerWarp && lane == 0 && sm.abort_flag) {
     // copies still in flight must land before the CTA's shared memory is handed on
     for (int s = 0; s < kStages; ++s) {
       const unsigned long long t0 = global_ns();
@@ -508,7 +577,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     }
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kQkWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
                  : "memory");
@@ -588,8 +657,15 @@ static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const 
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
+#ifdef NVFP4_TRACE
+  {
+    const char* env = getenv("NVFP4_TRACE_PTR");
+    unsigned long long* ptr = env ? reinterpret_cast<unsigned long long*>(strtoull(env, nullptr, 0)) : nullptr;
+    cudaMemcpyToSymbolAsync(g_trace, &ptr, sizeof(ptr), 0, cudaMemcpyHostToDevice, stream);
+  }
+#endif
   dim3 grid(p.num_splits, p.heads_kv, p.rows);
-  decode_sm100_kernel<G><<<grid, 192, smem, stream>>>(km, vm, p);
+  decode_sm100_kernel<G><<<grid, kThreads, smem, stream>>>(km, vm, p);
   return cudaGetLastError();
 }
 
