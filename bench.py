@@ -38,6 +38,18 @@ WORKLOAD = ("uniform batch decode: 32 seq x 4096 ctx, Hq32/Hkv8/D128, page 128, 
             "NVFP4 K/V (key shift applied at write), tail 0, bf16 out, 1 layer")
 
 
+def set_context(ctx: int) -> None:
+    """Re-derive the workload constants for a non-default context length (exploration only)."""
+    global CTX, PAGES_PER_ROW, POOL_PAGES, KV_BYTES, WORKLOAD
+    if ctx % PAGE:
+        raise SystemExit("--ctx must be a multiple of 128")
+    CTX = ctx
+    PAGES_PER_ROW = CTX // PAGE
+    POOL_PAGES = ROWS * PAGES_PER_ROW
+    KV_BYTES = ROWS * CTX * HKV * 144
+    WORKLOAD = WORKLOAD.replace("4096 ctx", f"{ctx} ctx")
+
+
 # --------------------------------------------------------------------------- CPU arm
 def _cpu_row(args):
     """One sequence of the workload through the CPU oracle (quantises Q/K/V itself)."""
@@ -394,9 +406,13 @@ def main() -> None:
     ap.add_argument("--decode-impl", default="auto", choices=["auto", "generic", "sm100"])
     ap.add_argument("--num-splits", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ctx", type=int, default=CTX,
+                    help="context length per sequence (default: the headline workload's 4096)")
     ap.add_argument("--ncu-traffic", type=float, default=None,
                     help="dram bytes per decode launch from an ncu capture (reported as roofline.traffic)")
     args = ap.parse_args()
+    if args.ctx != CTX:
+        set_context(args.ctx)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -44,31 +44,35 @@ __device__ unsigned long long* g_trace = nullptr;
 #define TRACE(role, iter, ev) do {} while (0)
 #endif
 
-constexpr int kStages = 4;
+// Ring depth: as many 18 KB stages as two resident CTAs per SM leave room for.
+template <int G> struct StageCount { static constexpr int value = G <= 4 ? 5 : 4; };
+constexpr int kBatch = 2;                                         // pages handled per hand-over
 constexpr int kTileBytes = 8192;                                  // 128 rows x 64 B
 constexpr int kStageBytes = 2 * kTileBytes + 2 * kSfBlockBytes;   // K, V, K scales, V scales
 constexpr int kNQ = 8;                                            // MMA N
-constexpr int kTmemCols = 64;
+constexpr int kTmemCols = 128;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;        // 2 s
 
-// tensor-memory column map (32-bit columns)
-constexpr int kColS = 0;     // 2 x 8 : S^T double buffer
-constexpr int kColO = 16;    // 2 x 8 : per-page O^T double buffer
-constexpr int kColSfQ = 32;  // 8 : 2 k-blocks x 4
-constexpr int kColSfK = 40;
-constexpr int kColSfV = 48;
-constexpr int kColSfP = 56;
+// tensor-memory column map (32-bit columns); a "set" holds the kBatch pages of one hand-over
+constexpr int kColS = 0;     // 2 sets x 2 pages x 8 : S^T
+constexpr int kColO = 32;    // 2 sets x 2 pages x 8 : per-page O^T
+constexpr int kColSfQ = 64;  // 8 : 2 k-blocks x 4
+constexpr int kColSfK = 72;
+constexpr int kColSfV = 80;
+constexpr int kColSfP = 88;
 
+template <int G>
 struct __align__(1024) Smem {
+  static constexpr int kStages = StageCount<G>::value;
   uint8_t stage[kStages][kStageBytes];          // each stage: K tile | V tile | K scales | V scales
   __align__(1024) uint8_t q_tile[512];          // 8 rows x 64 B, 64-byte swizzle
-  __align__(1024) uint8_t p_tile[2][512];
+  __align__(1024) uint8_t p_tile[2][kBatch][512];
   __align__(512) uint8_t q_sf[kSfBlockBytes];
-  __align__(512) uint8_t p_sf[2][kSfBlockBytes];
-  __align__(16) float qb[8 * kHeadDim];         // BF16 query as floats (tail)
-  __align__(16) float pf[8 * kHeadDim];         // P of the tail block
-  __align__(16) float z[2][8 * kPage];          // scaled scores of the current page, [q][kv position]
-  float resc[4][8];                             // ring of per-page rescale factors, [page & 3][q]
+  __align__(512) uint8_t p_sf[2][kBatch][kSfBlockBytes];
+  __align__(16) float qb[G * kHeadDim];         // BF16 query as floats (tail)
+  __align__(16) float pf[G * kHeadDim];         // P of the tail block
+  __align__(16) float z[2][kBatch][G * kPage];  // scaled scores, [set][page][q][kv position]
+  float resc[8][8];                             // ring of per-page rescale factors, [page & 7][q]
   float red_io[4 * 8];                          // reductions of the tail block and the epilogue
   volatile int page_ok[kStages];                // 0: the stage stands for a page id that was refused
   __align__(8) uint64_t full[kStages];
@@ -115,7 +119,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 
 // Bounded wait.  Returns false when the CTA is aborting (someone's wait expired).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Smem& sm, uint32_t* status) {
+template <class SM>
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, SM& sm, uint32_t* status) {
   if (mbar_try(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   uint32_t spins = 0;
@@ -138,6 +143,16 @@ __device__ __forceinline__ void tc_fence_before() {
 }
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+      "%14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
@@ -240,13 +255,57 @@ __device__ __forceinline__ int sw64_offset(int row, int byte_col) {
 
 constexpr int kThreads = 352;
 
+// One page of scores for one query head, seen by the 32 lanes of its owner warp (four
+// consecutive kv positions per lane): group and page maxima.
+struct PageMax { float group, page; };
+__device__ __forceinline__ PageMax page_max(const float4& z) {
+  float g = fmaxf(fmaxf(z.x, z.y), fmaxf(z.z, z.w));
+  g = fmaxf(g, __shfl_xor_sync(0xffffffffu, g, 1));
+  g = fmaxf(g, __shfl_xor_sync(0xffffffffu, g, 2));   // the 16-position scale group
+  float b = fmaxf(g, __shfl_xor_sync(0xffffffffu, g, 4));
+  b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, 8));
+  b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, 16));
+  return PageMax{g, b};
+}
+
+// exp2 of one page against its running maximum, NVFP4 quantisation of the probabilities in
+// the oracle's form (scale = e4m3(group max / 6), nibble = e2m1(p / scale)), stores of the
+// packed bytes and of the group's scale byte.  A scale that rounds to zero is raised to the
+// smallest E4M3 subnormal instead of dropping the group.  The two divisions are a multiply by
+// fp32(1/6) and by an approximate reciprocal: that can move a result only when it sits within
+// an ulp of a rounding boundary.  Returns the sum of the unquantised probabilities.
+__device__ __forceinline__ float quantize_page(const float4& z, float group_max, float m, uint8_t* p_tile,
+                                               uint8_t* p_sf, int q, int lane) {
+  const float p0 = exp2_rel(z.x, m), p1 = exp2_rel(z.y, m), p2 = exp2_rel(z.z, m), p3 = exp2_rel(z.w, m);
+  uint32_t sb = f32_to_e4m3(exp2_rel(group_max, m) * (1.0f / 6.0f));
+  sb = sb == 0 ? 1u : sb;
+  const float inv = __fdividef(1.0f, e4m3_to_f32((uint8_t)sb));
+  const uint32_t packed = f32x4_to_e2m1x4(p0 * inv, p1 * inv, p2 * inv, p3 * inv);
+  *reinterpret_cast<uint16_t*>(p_tile + sw64_offset(q, 2 * lane)) = (uint16_t)packed;
+  if ((lane & 3) == 0) {
+    const int g = lane >> 2;
+    p_sf[(g >> 2) * 512 + q * 16 + (g & 3)] = (uint8_t)sb;
+  }
+  return (p0 + p1) + (p2 + p3);
+}
+
 template <int G>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                     const DecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
-  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Smem<G>& sm = *reinterpret_cast<Smem<G>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr int kStages = StageCount<G>::value;
+  if (tid == 0) TRACE(1, 39, 0);
+#ifdef NVFP4_TRACE
+  if (tid == 0 && g_trace) {
+    const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    unsigned smid;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    if (cta < 512) { g_trace[1024 + cta * 4] = global_ns(); g_trace[1024 + cta * 4 + 2] = smid; }
+  }
+#endif
 
   // ---- set-up: barriers, tensor memory, zeroed operand tiles ----
   if (tid == 0) {
@@ -271,22 +330,37 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   }
   // rows G..7 of the N = 8 operands and their scale rows stay zero for the whole kernel
   for (int i = tid; i < 512 / 16; i += kThreads) reinterpret_cast<uint4*>(sm.q_tile)[i] = make_uint4(0, 0, 0, 0);
-  for (int i = tid; i < 2 * 512 / 16; i += kThreads) reinterpret_cast<uint4*>(sm.p_tile)[i] = make_uint4(0, 0, 0, 0);
-  for (int i = tid; i < 2 * kSfBlockBytes / 16; i += kThreads)
+  for (int i = tid; i < 2 * kBatch * 512 / 16; i += kThreads)
+    reinterpret_cast<uint4*>(sm.p_tile)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < 2 * kBatch * kSfBlockBytes / 16; i += kThreads)
     reinterpret_cast<uint4*>(sm.p_sf)[i] = make_uint4(0, 0, 0, 0);
   const TileWork w = resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x);
   const int n_pages = w.last_page - w.first_page;
+  const int n_batches = (n_pages + kBatch - 1) / kBatch;
+  if (tid == 0) TRACE(1, 39, 1);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
+  if (tid == 0) TRACE(1, 39, 2);
 
+#ifdef NVFP4_LOADONLY
+  // developer experiment: stream the pages through shared memory and do nothing with them
+  if (warp == kQkWarp && lane == 0) {
+    for (int i = 0; i < n_pages; ++i) {
+      const int s = i % kStages;
+      if (!mbar_wait(&sm.full[s], (i / kStages) & 1, sm, p.status)) break;
+      mbar_arrive(&sm.empty[s]);
+    }
+  }
+  if (warp < 4 || (warp >= 4 && warp < 8) || warp == kQkWarp || warp == kPvWarp) goto teardown;
+#endif
   if (warp < 4) {
     // =====================  score threads  =====================
-    // While a page's scores are processed, warp w owns query heads q = w, w + 4 (< G) over
-    // ALL 128 kv positions, four consecutive positions per lane: the page maximum is a warp
-    // reduction, a 16-position scale group is four adjacent lanes and the packed E2M1 bytes
-    // of P are formed without any exchange.
+    // Pages are handed over in pairs.  While a pair's scores are processed, warp w owns query
+    // heads q = w, w + 4 (< G) over ALL 128 kv positions of each page, four consecutive
+    // positions per lane: the page maximum is a warp reduction, a 16-position scale group is
+    // four adjacent lanes and the packed E2M1 bytes of P are formed without any exchange.
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     // query operand: G packed rows, swizzled; its scale block; the BF16 copy for the tail
     if (tid < G * 4) {
@@ -342,66 +416,59 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     // A thread whose wait expired keeps walking the loop's barrier points with ok = false, so
     // the 128 threads always leave the loop together.
     bool alive = true;
-    for (int i = 0; i < n_pages; ++i) {
-      const int b = i & 1;
-      if (tid == 0) TRACE(0, i, 0);
-      const bool ok = alive && mbar_wait(&sm.s_full[b], (i >> 1) & 1, sm, p.status);
-      if (tid == 0) TRACE(0, i, 1);
+    for (int kb = 0; kb < n_batches; ++kb) {
+      const int set = kb & 1, i0 = kb * kBatch;
+      const bool two = i0 + 1 < n_pages;
+      if (tid == 0) TRACE(0, kb, 0);
+      const bool ok = alive && mbar_wait(&sm.s_full[set], (kb >> 1) & 1, sm, p.status);
+      if (tid == 0) TRACE(0, kb, 1);
       if (ok) {
         tc_fence_after();
-        uint32_t r[8];
-        tmem_ld8(tmem + lane_off + kColS + b * 8, r);
+        uint32_t r[16];
+        tmem_ld16(tmem + lane_off + kColS + set * 16, r);
         tc_fence_before();
-        mbar_arrive(&sm.s_free[b]);
-        const bool page_ok = sm.page_ok[i % kStages] != 0;
+        mbar_arrive(&sm.s_free[set]);
+        const bool ok0 = sm.page_ok[i0 % kStages] != 0;
+        const bool ok1 = two && sm.page_ok[(i0 + 1) % kStages] != 0;
 #pragma unroll
-        for (int q = 0; q < G; ++q)
-          sm.z[b][q * kPage + tid] = page_ok ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY;
+        for (int q = 0; q < G; ++q) {
+          sm.z[set][0][q * kPage + tid] = ok0 ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY;
+          sm.z[set][1][q * kPage + tid] = ok1 ? __uint_as_float(r[8 + q]) * p.scale_log2 : -INFINITY;
+        }
       }
-      if (tid == 0) TRACE(0, i, 2);
+      if (tid == 0) TRACE(0, kb, 2);
       if (!bar_and_128(1, ok)) { alive = false; break; }
-      if (tid == 0) TRACE(0, i, 3);
-      // P.V of page i-2 has retired: its P tile, its scale rows and the rescale slot of
-      // page i-4 may be overwritten
-      if (i >= 2 && !mbar_wait(&sm.o_full[b], ((i - 2) >> 1) & 1, sm, p.status)) alive = false;
+      if (tid == 0) TRACE(0, kb, 3);
+      // P.V of the pair two hand-overs back has retired: its P tiles, their scale rows and the
+      // rescale slots of the pair four hand-overs back may be overwritten
+      if (kb >= 2 && !mbar_wait(&sm.o_full[set], ((kb - 2) >> 1) & 1, sm, p.status)) alive = false;
 #pragma unroll
       for (int k = 0; k < QPW; ++k) {
         const int q = warp + 4 * k;
         if (q < G) {
-          const float4 zz = *reinterpret_cast<const float4*>(&sm.z[b][q * kPage + 4 * lane]);
-          float gm = fmaxf(fmaxf(zz.x, zz.y), fmaxf(zz.z, zz.w));
-          gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 1));
-          gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 2));   // max of this 16-position group
-          float bm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, 4));
-          bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
-          bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));  // max of the page
-          const float mn = fmaxf(m_w[k], bm);
-          const float resc = (m_w[k] == -INFINITY) ? 0.f : exp2f(m_w[k] - mn);
-          m_w[k] = mn;
-          const float p0 = exp2_rel(zz.x, mn), p1 = exp2_rel(zz.y, mn);
-          const float p2 = exp2_rel(zz.z, mn), p3 = exp2_rel(zz.w, mn);
-          l_w[k] = fmaf(l_w[k], resc, (p0 + p1) + (p2 + p3));
-          // NVFP4 P in the oracle's form: scale = e4m3(group max / 6), nibble = e2m1(p / scale).
-          // A scale that rounds to zero is raised to the smallest E4M3 subnormal instead of
-          // dropping the group.  The two divisions are a multiply by fp32(1/6) and by an
-          // approximate reciprocal; that can move a result only when it sits within an ulp of
-          // a rounding boundary.
-          uint32_t sb = f32_to_e4m3(exp2_rel(gm, mn) * (1.0f / 6.0f));
-          sb = sb == 0 ? 1u : sb;
-          const float inv = __fdividef(1.0f, e4m3_to_f32((uint8_t)sb));
-          const uint32_t packed = f32x4_to_e2m1x4(p0 * inv, p1 * inv, p2 * inv, p3 * inv);
-          *reinterpret_cast<uint16_t*>(&sm.p_tile[b][sw64_offset(q, 2 * lane)]) = (uint16_t)packed;
-          if ((lane & 3) == 0) {
-            const int g = lane >> 2;
-            sm.p_sf[b][(g >> 2) * 512 + q * 16 + (g & 3)] = (uint8_t)sb;
+          const float4 za = *reinterpret_cast<const float4*>(&sm.z[set][0][q * kPage + 4 * lane]);
+          const float4 zb = *reinterpret_cast<const float4*>(&sm.z[set][1][q * kPage + 4 * lane]);
+          const PageMax ma = page_max(za), mb = page_max(zb);
+          // the pages are walked in order: the first page of the pair is quantised against the
+          // maximum up to and including itself, the second against the maximum including both
+          const float m1 = fmaxf(m_w[k], ma.page);
+          const float m2 = fmaxf(m1, mb.page);
+          const float ra = (m_w[k] == -INFINITY) ? 0.f : exp2f(m_w[k] - m1);
+          const float rb = (m1 == -INFINITY) ? 0.f : exp2f(m1 - m2);
+          m_w[k] = m2;
+          const float sa = quantize_page(za, ma.group, m1, sm.p_tile[set][0], sm.p_sf[set][0], q, lane);
+          const float sb = quantize_page(zb, mb.group, m2, sm.p_tile[set][1], sm.p_sf[set][1], q, lane);
+          l_w[k] = fmaf(fmaf(l_w[k], ra, sa), rb, sb);
+          if (lane == 0) {
+            sm.resc[i0 & 7][q] = ra;
+            sm.resc[(i0 + 1) & 7][q] = rb;
           }
-          if (lane == 0) sm.resc[i & 3][q] = resc;
         }
       }
-      if (tid == 0) TRACE(0, i, 4);
+      if (tid == 0) TRACE(0, kb, 4);
       fence_proxy_async();
-      mbar_arrive(&sm.p_full[b]);
-      if (tid == 0) TRACE(0, i, 5);
+      mbar_arrive(&sm.p_full[set]);
+      if (tid == 0) TRACE(0, kb, 5);
     }
     // row sums and final maxima of every query head, for the output threads
 #pragma unroll
@@ -413,6 +480,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
     }
     bar_and_256(3, alive);
+    if (tid == 0) TRACE(1, 39, 3);
   } else if (warp < 8) {
     // =====================  output threads: thread t = channel t  =====================
     const int t = tid - 128;
@@ -425,19 +493,23 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       tail_pv<G>(p, w, sm.pf, t, o);
     }
     bool alive = true;
-    for (int j = 0; j < n_pages && alive; ++j) {
-      // fold page j: o = o * rescale(j) + O_page(j)
-      const int bj = j & 1;
-      if (mbar_wait(&sm.o_full[bj], (j >> 1) & 1, sm, p.status)) {
-        if (t == 0) TRACE(0, j, 6);
+    for (int kb = 0; kb < n_batches && alive; ++kb) {
+      // fold the pair: o = o * rescale(j) + O_page(j), page by page
+      const int set = kb & 1, j0 = kb * kBatch;
+      const bool two = j0 + 1 < n_pages;
+      if (mbar_wait(&sm.o_full[set], (kb >> 1) & 1, sm, p.status)) {
+        if (t == 0) TRACE(0, kb, 6);
         tc_fence_after();
-        uint32_t ro[8];
-        tmem_ld8(tmem + lane_off + kColO + bj * 8, ro);
+        uint32_t ro[16];
+        tmem_ld16(tmem + lane_off + kColO + set * 16, ro);
         tc_fence_before();
-        mbar_arrive(&sm.o_free[bj]);
+        mbar_arrive(&sm.o_free[set]);
 #pragma unroll
-        for (int q = 0; q < G; ++q) o[q] = fmaf(o[q], sm.resc[j & 3][q], __uint_as_float(ro[q]));
-        if (t == 0) TRACE(0, j, 7);
+        for (int q = 0; q < G; ++q) {
+          o[q] = fmaf(o[q], sm.resc[j0 & 7][q], __uint_as_float(ro[q]));
+          if (two) o[q] = fmaf(o[q], sm.resc[(j0 + 1) & 7][q], __uint_as_float(ro[8 + q]));
+        }
+        if (t == 0) TRACE(0, kb, 7);
       } else {
         alive = false;
       }
@@ -458,6 +530,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         }
       }
     }
+    if (t == 0) TRACE(1, 39, 4);
   } else if (warp == kProducerWarp) {
     // =====================  producer  =====================
     bool alive = true;
@@ -482,7 +555,11 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
           sm.page_ok[s] = pid >= 0 ? 1 : 0;
           if (pid >= 0) {
             mbar_expect_tx(&sm.full[s], kStageBytes);
+#ifdef NVFP4_DEV_FAKEK
+            tma_load_4d(smem_u32(st), &k_map, &sm.full[s], 0, 0, w.kvh, (int)pid);
+#else
             tma_load_4d(smem_u32(st), &k_map, &sm.full[s], 0, w.kvh, 0, (int)pid);
+#endif
             tma_load_4d(smem_u32(st + kTileBytes), &v_map, &sm.full[s], 0, 0, w.kvh, (int)pid);
             bulk_load(smem_u32(st + 2 * kTileBytes),
                       p.k_sf + pid * p.k_sf_pitch + (int64_t)w.kvh * kSfBlockBytes, kSfBlockBytes, &sm.full[s]);
@@ -513,21 +590,27 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         cp_sf(tmem + kColSfQ + 4, smem_u32(sm.q_sf + 512));
       }
       const uint64_t q_desc = desc_sw64(smem_u32(sm.q_tile));
-      for (int i = 0; i < n_pages && alive; ++i) {
-        const int s = i % kStages, b = i & 1;
-        alive = mbar_wait(&sm.full[s], (i / kStages) & 1, sm, p.status) &&
-                mbar_wait(&sm.s_free[b], ((i >> 1) & 1) ^ 1, sm, p.status);
-        if (!alive) break;
-        TRACE(2, i, 0);
-        tc_fence_after();
-        const uint32_t st = smem_u32(sm.stage[s]);
-        cp_sf(tmem + kColSfK, st + 2 * kTileBytes);
-        cp_sf(tmem + kColSfK + 4, st + 2 * kTileBytes + 512);
-        const uint64_t k_desc = desc_sw64(st);
-        mma_nvf4(tmem + kColS + b * 8, k_desc, q_desc, tmem + kColSfK, tmem + kColSfQ, 0);
-        mma_nvf4(tmem + kColS + b * 8, k_desc + 2, q_desc + 2, tmem + kColSfK + 4, tmem + kColSfQ + 4, 1);
-        mma_commit(&sm.s_full[b]);
-        TRACE(2, i, 1);
+      for (int kb = 0; kb < n_batches && alive; ++kb) {
+        const int set = kb & 1;
+        alive = mbar_wait(&sm.s_free[set], ((kb >> 1) & 1) ^ 1, sm, p.status);
+        for (int u = 0; u < kBatch && alive; ++u) {
+          const int i = kb * kBatch + u;
+          if (i >= n_pages) break;
+          const int s = i % kStages;
+          alive = mbar_wait(&sm.full[s], (i / kStages) & 1, sm, p.status);
+          if (!alive) break;
+          TRACE(2, i, 0);
+          tc_fence_after();
+          const uint32_t st = smem_u32(sm.stage[s]);
+          cp_sf(tmem + kColSfK, st + 2 * kTileBytes);
+          cp_sf(tmem + kColSfK + 4, st + 2 * kTileBytes + 512);
+          const uint64_t k_desc = desc_sw64(st);
+          const uint32_t d = tmem + kColS + set * 16 + u * 8;
+          mma_nvf4(d, k_desc, q_desc, tmem + kColSfK, tmem + kColSfQ, 0);
+          mma_nvf4(d, k_desc + 2, q_desc + 2, tmem + kColSfK + 4, tmem + kColSfQ + 4, 1);
+        }
+        if (alive) mma_commit(&sm.s_full[set]);
+        TRACE(2, kb * kBatch, 1);
       }
       // everything this thread issued must have retired before tensor memory is freed
       mma_commit(&sm.drain[0]);
@@ -538,27 +621,33 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     // =====================  MMA issuer 2: O^T = V^T . P^T  =====================
     if (lane == 0 && n_pages > 0) {
       bool alive = true;
-      for (int j = 0; j < n_pages && alive; ++j) {
-        const int s = j % kStages, b = j & 1;
-        // p_full(j) implies that S^T(j) was read, hence that K.Q^T of page j and its scale
-        // copies have retired: the commit below may hand the whole stage back
-        alive = mbar_wait(&sm.p_full[b], (j >> 1) & 1, sm, p.status) &&
-                mbar_wait(&sm.o_free[b], ((j >> 1) & 1) ^ 1, sm, p.status);
+      for (int kb = 0; kb < n_batches && alive; ++kb) {
+        const int set = kb & 1;
+        // p_full implies that S^T of the pair was read, hence that K.Q^T of both pages and
+        // their scale copies have retired: the commits below may hand the stages back whole
+        alive = mbar_wait(&sm.p_full[set], (kb >> 1) & 1, sm, p.status) &&
+                mbar_wait(&sm.o_free[set], ((kb >> 1) & 1) ^ 1, sm, p.status);
         if (!alive) break;
-        TRACE(2, j, 2);
+        TRACE(2, kb * kBatch, 2);
         tc_fence_after();
-        const uint32_t st = smem_u32(sm.stage[s]);
-        cp_sf(tmem + kColSfV, st + 2 * kTileBytes + kSfBlockBytes);
-        cp_sf(tmem + kColSfV + 4, st + 2 * kTileBytes + kSfBlockBytes + 512);
-        cp_sf(tmem + kColSfP, smem_u32(sm.p_sf[b]));
-        cp_sf(tmem + kColSfP + 4, smem_u32(sm.p_sf[b] + 512));
-        const uint64_t v_desc = desc_sw64(st + kTileBytes);
-        const uint64_t p_desc = desc_sw64(smem_u32(sm.p_tile[b]));
-        mma_nvf4(tmem + kColO + b * 8, v_desc, p_desc, tmem + kColSfV, tmem + kColSfP, 0);
-        mma_nvf4(tmem + kColO + b * 8, v_desc + 2, p_desc + 2, tmem + kColSfV + 4, tmem + kColSfP + 4, 1);
-        mma_commit(&sm.o_full[b]);
-        mma_commit(&sm.empty[s]);
-        TRACE(2, j, 3);
+        for (int u = 0; u < kBatch; ++u) {
+          const int j = kb * kBatch + u;
+          if (j >= n_pages) break;
+          const int s = j % kStages;
+          const uint32_t st = smem_u32(sm.stage[s]);
+          cp_sf(tmem + kColSfV, st + 2 * kTileBytes + kSfBlockBytes);
+          cp_sf(tmem + kColSfV + 4, st + 2 * kTileBytes + kSfBlockBytes + 512);
+          cp_sf(tmem + kColSfP, smem_u32(sm.p_sf[set][u]));
+          cp_sf(tmem + kColSfP + 4, smem_u32(sm.p_sf[set][u] + 512));
+          const uint64_t v_desc = desc_sw64(st + kTileBytes);
+          const uint64_t p_desc = desc_sw64(smem_u32(sm.p_tile[set][u]));
+          const uint32_t d = tmem + kColO + set * 16 + u * 8;
+          mma_nvf4(d, v_desc, p_desc, tmem + kColSfV, tmem + kColSfP, 0);
+          mma_nvf4(d, v_desc + 2, p_desc + 2, tmem + kColSfV + 4, tmem + kColSfP + 4, 1);
+          mma_commit(&sm.empty[s]);
+        }
+        mma_commit(&sm.o_full[set]);
+        TRACE(2, kb * kBatch, 3);
       }
       mma_commit(&sm.drain[1]);
       mbar_wait(&sm.drain[1], 0, sm, p.status);
@@ -566,6 +655,9 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     __syncwarp();
   }
 
+#ifdef NVFP4_LOADONLY
+teardown:
+#endif
   // ---- teardown ----
   tc_fence_before();
   __syncthreads();
@@ -577,6 +669,13 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     }
   }
   __syncthreads();
+  if (tid == 0) TRACE(1, 39, 5);
+#ifdef NVFP4_TRACE
+  if (tid == 0 && g_trace) {
+    const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    if (cta < 512) g_trace[1024 + cta * 4 + 1] = global_ns();
+  }
+#endif
   if (warp == kQkWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
@@ -633,9 +732,18 @@ static cudaError_t make_map(int which, const void* base, int64_t pitch, int64_t 
     strides[0] = 64; strides[1] = 128 * 64; strides[2] = pitch;
     box[0] = 64; box[1] = 128; box[2] = 1; box[3] = 1;
   }
+  CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+#ifdef NVFP4_DEV
+  if (const char* e = getenv("NVFP4_L2PROMO")) promo = (CUtensorMapL2promotion)atoi(e);
+  if (getenv("NVFP4_FAKEK") && which == 0) {  // bandwidth experiment: K read as if it were head-major
+    dims[0] = 64; dims[1] = 128; dims[2] = heads; dims[3] = pages;
+    strides[0] = 64; strides[1] = 128 * 64; strides[2] = pitch;
+    box[0] = 64; box[1] = 128; box[2] = 1; box[3] = 1;
+  }
+#endif
   CUtensorMap map;
   CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, promo,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   cache[next] = MapEntry{key, map, true};
@@ -647,7 +755,7 @@ static cudaError_t make_map(int which, const void* base, int64_t pitch, int64_t 
 template <int G>
 static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const CUtensorMap& vm,
                             cudaStream_t stream) {
-  const size_t smem = sizeof(Smem) + 1024;
+  const size_t smem = sizeof(Smem<G>) + 1024;
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
