@@ -254,6 +254,7 @@ __device__ __forceinline__ int sw64_offset(int row, int byte_col) {
 }
 
 constexpr int kThreads = 352;
+static_assert(kThreads == 352, "the set-up barrier is written for 352 threads");
 
 // One page of scores for one query head, seen by the 32 lanes of its owner warp (four
 // consecutive kv positions per lane): group and page maxima.
@@ -308,8 +309,28 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 #endif
 
   // ---- set-up: barriers, tensor memory, zeroed operand tiles ----
+  // The producer warp prepares its own ring barriers and starts fetching before the CTA-wide
+  // set-up barrier, so the first page tiles are in flight while tensor memory is allocated.
+  int spec[4] = {-1, -1, -1, -1};
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      for (int s = 0; s < kStages; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+      sm.abort_flag = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    // the producer only signals the set-up barrier (it needs nothing the others prepare)
+    asm volatile("bar.arrive 4, %0;" ::"n"(352) : "memory");
+    // Page-table columns are fetched before the row's length is known (the loads run beside
+    // the length's).  Reading a column is harmless even when it lies past the used prefix;
+    // its value is only used, and range-checked, if the length says the column is live.
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = lane + 32 * j;
+      if (col < p.max_pages) spec[j] = __ldg(p.page_table + (int64_t)blockIdx.z * p.page_table_row_stride + col);
+    }
+  }
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.s_full[b], 1); mbar_init(&sm.s_free[b], 128);
       mbar_init(&sm.p_full[b], 128);
@@ -318,7 +339,6 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     mbar_init(&sm.q_ready, 128);
     mbar_init(&sm.drain[0], 1);
     mbar_init(&sm.drain[1], 1);
-    sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kQkWarp) {
@@ -337,11 +357,62 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   const TileWork w = resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x);
   const int n_pages = w.last_page - w.first_page;
   const int n_batches = (n_pages + kBatch - 1) / kBatch;
+
+  // one page of the ring: K tile, V tile and the two scale blocks, or a masked stand-in
+  auto issue_page = [&](int s, int64_t pid) {
+    uint8_t* st = sm.stage[s];
+    sm.page_ok[s] = pid >= 0 ? 1 : 0;
+    if (pid >= 0) {
+      mbar_expect_tx(&sm.full[s], kStageBytes);
+      tma_load_4d(smem_u32(st), &k_map, &sm.full[s], 0, w.kvh, 0, (int)pid);
+      tma_load_4d(smem_u32(st + kTileBytes), &v_map, &sm.full[s], 0, 0, w.kvh, (int)pid);
+      bulk_load(smem_u32(st + 2 * kTileBytes), p.k_sf + pid * p.k_sf_pitch + (int64_t)w.kvh * kSfBlockBytes,
+                kSfBlockBytes, &sm.full[s]);
+      bulk_load(smem_u32(st + 2 * kTileBytes + kSfBlockBytes),
+                p.v_sf + pid * p.v_sf_pitch + (int64_t)w.kvh * kSfBlockBytes, kSfBlockBytes, &sm.full[s]);
+    } else {
+      // a page id outside the cache is never turned into an address: the stage gets zero
+      // scales (so both products are zero) and the score threads mask its scores
+      for (int j = 0; j < 2 * kSfBlockBytes / 16; ++j)
+        reinterpret_cast<uint4*>(st + 2 * kTileBytes)[j] = make_uint4(0, 0, 0, 0);
+      fence_proxy_async();
+      mbar_arrive(&sm.full[s]);
+    }
+  };
+  // ids: lane l of the producer warp holds the page id of walk step 32c + l of the current chunk c
+  int ids = -1, issued = 0;
+  if (warp == kProducerWarp) {
+    // chunk 0 out of the columns fetched ahead; every lane executes the same four shuffles
+    const int idx0 = w.last_page - 1 - lane;  // pages are walked from the last to the first
+    const bool live = idx0 >= w.first_page;
+    const int src = live ? (idx0 & 31) : 0;
+    int v = -1;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int got = __shfl_sync(0xffffffffu, spec[j], src);
+      if (live && (idx0 >> 5) == j) v = got;
+    }
+    if (live && idx0 >= 128) v = p.page_table[(int64_t)w.row * p.page_table_row_stride + idx0];
+    ids = v;
+    const int first = n_pages < kStages ? n_pages : kStages;
+    for (int i = 0; i < first; ++i) {
+      int64_t pid = __shfl_sync(0xffffffffu, ids, i);
+      if (pid < 0 || pid >= p.num_pages) {
+        if (lane == 0) set_status(p.status, NVFP4_STATUS_BAD_PAGE_ID);
+        pid = -1;
+      }
+      if (lane == 0) { TRACE(1, i, 0); TRACE(1, i, 1); issue_page(i, pid); TRACE(1, i, 2); }
+    }
+    issued = first;
+  }
   if (tid == 0) TRACE(1, 39, 1);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = sm.tmem_base;
+  uint32_t tmem = 0;
+  if (warp != kProducerWarp) {
+    tc_fence_before();
+    asm volatile("bar.sync 4, %0;" ::"n"(352) : "memory");
+    tc_fence_after();
+    tmem = sm.tmem_base;
+  }
   if (tid == 0) TRACE(1, 39, 2);
 
 #ifdef NVFP4_LOADONLY
@@ -534,10 +605,9 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   } else if (warp == kProducerWarp) {
     // =====================  producer  =====================
     bool alive = true;
-    int ids = -1;
-    for (int i = 0; i < n_pages && alive; ++i) {
+    for (int i = issued; i < n_pages && alive; ++i) {
       if ((i & 31) == 0) {
-        const int idx = w.last_page - 1 - (i + lane);  // pages are walked from the last to the first
+        const int idx = w.last_page - 1 - (i + lane);
         ids = idx >= w.first_page ? p.page_table[(int64_t)w.row * p.page_table_row_stride + idx] : -1;
       }
       int64_t pid = __shfl_sync(0xffffffffu, ids, i & 31);
@@ -551,28 +621,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         alive = mbar_wait(&sm.empty[s], ((i / kStages) & 1) ^ 1, sm, p.status);
         TRACE(1, i, 1);
         if (alive) {
-          uint8_t* st = sm.stage[s];
-          sm.page_ok[s] = pid >= 0 ? 1 : 0;
-          if (pid >= 0) {
-            mbar_expect_tx(&sm.full[s], kStageBytes);
-#ifdef NVFP4_DEV_FAKEK
-            tma_load_4d(smem_u32(st), &k_map, &sm.full[s], 0, 0, w.kvh, (int)pid);
-#else
-            tma_load_4d(smem_u32(st), &k_map, &sm.full[s], 0, w.kvh, 0, (int)pid);
-#endif
-            tma_load_4d(smem_u32(st + kTileBytes), &v_map, &sm.full[s], 0, 0, w.kvh, (int)pid);
-            bulk_load(smem_u32(st + 2 * kTileBytes),
-                      p.k_sf + pid * p.k_sf_pitch + (int64_t)w.kvh * kSfBlockBytes, kSfBlockBytes, &sm.full[s]);
-            bulk_load(smem_u32(st + 2 * kTileBytes + kSfBlockBytes),
-                      p.v_sf + pid * p.v_sf_pitch + (int64_t)w.kvh * kSfBlockBytes, kSfBlockBytes, &sm.full[s]);
-          } else {
-            // a page id outside the cache is never turned into an address: the stage gets zero
-            // scales (so both products are zero) and the score threads mask its scores
-            for (int j = 0; j < 2 * kSfBlockBytes / 16; ++j)
-              reinterpret_cast<uint4*>(st + 2 * kTileBytes)[j] = make_uint4(0, 0, 0, 0);
-            fence_proxy_async();
-            mbar_arrive(&sm.full[s]);
-          }
+          issue_page(s, pid);
           TRACE(1, i, 2);
         }
       }
