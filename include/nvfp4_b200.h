@@ -219,6 +219,23 @@ int nvfp4_lse_merge_ptrs(const float* const* o_part_ptrs, const float* const* ls
                          int num_splits, int rows, int heads_q, void* out, int out_is_f32,
                          const int32_t* out_indices, float* lse_out, void* stream);
 
+/*
+ * Merge for the cross-GPU KV page-range split (one process per GPU).  Each rank has written
+ * its partial (normalised fp32 O [rows][Hq][128], fp32 LSE [rows][Hq]) into memory every rank
+ * can address (peer-mapped / symmetric allocations).  The call announces "partial of `epoch`
+ * written" in every peer's flag array (flag_ptrs[p][rank] = epoch), waits - at most one second,
+ * then NVFP4_STATUS_WAIT_TIMEOUT is raised and `out` is left untouched - until every peer has
+ * announced the same epoch, and merges by LSE weight with plain loads from the peers' buffers.
+ * Epochs must grow by one per call on every rank; partial buffers should alternate between two
+ * copies so that a fast rank cannot overwrite what a slow one still reads.
+ * The reference has no multi-GPU path; the merge arithmetic is that of flash_attn_combine
+ * (src/nvfp4_decode_kernel/split_k_combine.py:516-554).
+ *   o_part_ptrs / lse_part_ptrs / flag_ptrs: DEVICE arrays of `world` pointers.
+ */
+int nvfp4_peer_merge(const float* const* o_part_ptrs, const float* const* lse_part_ptrs,
+                     int32_t* const* flag_ptrs, int rank, int world, int epoch, int rows, int heads_q,
+                     void* out, int out_is_f32, uint32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

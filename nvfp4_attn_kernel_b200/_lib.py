@@ -31,6 +31,7 @@ EXPORTS = (
     "nvfp4_decode_impl_available",
     "nvfp4_lse_merge",
     "nvfp4_lse_merge_ptrs",
+    "nvfp4_peer_merge",
 )
 
 
@@ -133,6 +134,14 @@ def _declare(lib) -> None:
     ]
 
 
+def _declare_peer(lib) -> None:
+    lib.nvfp4_peer_merge.restype = c_int
+    lib.nvfp4_peer_merge.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+        c_void_p, c_void_p,
+    ]
+
+
 def load():
     """Load the shared library once and return the ctypes handle."""
     global _lib
@@ -145,6 +154,7 @@ def load():
             )
         lib = ctypes.CDLL(LIB_PATH)
         _declare(lib)
+        _declare_peer(lib)
         _lib = lib
     return _lib
 

@@ -62,3 +62,94 @@ cudaError_t launch_lse_merge(const float* o_parts, int64_t o_split_stride, const
 }
 
 }  // namespace nvfp4
+
+// ---------------------------------------------------------------------------
+// Cross-GPU merge for the KV page-range split: every rank has written its partial
+// (normalised O, LSE) into a buffer that all ranks can address.  One launch per
+// rank: announce "my partial of this epoch is written" in every peer's flag array,
+// wait (bounded) until every peer has announced the same, then merge with plain loads
+// from the peers' buffers.  The kernels of the ranks run on different GPUs.
+// ---------------------------------------------------------------------------
+namespace nvfp4 {
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float ld_relaxed_sys(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+constexpr unsigned long long kPeerWaitNs = 1000000000ull;  // 1 s
+
+template <bool kOutF32>
+__global__ void __launch_bounds__(128)
+peer_merge_kernel(const float* const* __restrict__ o_ptrs, const float* const* __restrict__ lse_ptrs,
+                  int* const* __restrict__ flag_ptrs, int rank, int world, int epoch, int rows,
+                  int heads_q, void* __restrict__ out, uint32_t* __restrict__ status) {
+  __shared__ int ready;
+  const int head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && d < world) {
+    __threadfence_system();
+    st_release_sys(flag_ptrs[d] + rank, epoch);
+  }
+  if (d == 0) {
+    const int* mine = flag_ptrs[rank];
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    int ok = 1;
+    for (int w = 0; w < world && ok; ++w) {
+      // epochs only grow; a peer that is already a step ahead has certainly written this one
+      while (ld_acquire_sys(mine + w) - epoch < 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        if (t - t0 > kPeerWaitNs) { ok = 0; break; }
+        __nanosleep(64);
+      }
+    }
+    if (!ok) set_status(status, NVFP4_STATUS_WAIT_TIMEOUT);
+    ready = ok;
+  }
+  __syncthreads();
+  if (!ready) return;  // the output is left untouched and the status word says why
+  const int64_t idx = (int64_t)row * heads_q + head;
+  float mx = -INFINITY;
+  for (int s = 0; s < world; ++s) mx = fmaxf(mx, ld_relaxed_sys(lse_ptrs[s] + idx));
+  float acc = 0.f, tot = 0.f;
+  if (mx != -INFINITY) {
+    for (int s = 0; s < world; ++s) {
+      const float ls = ld_relaxed_sys(lse_ptrs[s] + idx);
+      if (ls == -INFINITY) continue;
+      const float wgt = expf(ls - mx);
+      tot += wgt;
+      acc = fmaf(wgt, ld_relaxed_sys(o_ptrs[s] + idx * kHeadDim + d), acc);
+    }
+  }
+  const float val = tot > 0.f ? __fdiv_rn(acc, tot) : 0.f;
+  const int64_t at = idx * kHeadDim + d;
+  if (kOutF32) static_cast<float*>(out)[at] = val;
+  else static_cast<uint16_t*>(out)[at] = __bfloat16_as_ushort(__float2bfloat16_rn(val));
+}
+
+cudaError_t launch_peer_merge(const float* const* o_ptrs, const float* const* lse_ptrs,
+                              int* const* flag_ptrs, int rank, int world, int epoch, int rows,
+                              int heads_q, void* out, int out_is_f32, uint32_t* status,
+                              cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  dim3 grid(heads_q, rows);
+  if (out_is_f32)
+    peer_merge_kernel<true><<<grid, 128, 0, stream>>>(o_ptrs, lse_ptrs, flag_ptrs, rank, world, epoch,
+                                                      rows, heads_q, out, status);
+  else
+    peer_merge_kernel<false><<<grid, 128, 0, stream>>>(o_ptrs, lse_ptrs, flag_ptrs, rank, world, epoch,
+                                                       rows, heads_q, out, status);
+  return cudaGetLastError();
+}
+
+}  // namespace nvfp4

@@ -1,0 +1,111 @@
+"""GPU tests of the cross-GPU page-range split.  The two-rank cases need two GPUs (they are
+skipped on a single-GPU box); the expired-wait case runs on one GPU."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+import inputs
+from helpers import Problem, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+def test_peer_merge_wait_expires_with_a_status_and_leaves_out_untouched(cuda_device):
+    """Failure detection without a fault: rank 1 never announces, the wait gives up after its
+    bound, the status word says so and the output buffer is not written."""
+    import nvfp4_attn_kernel_b200._lib as L
+
+    lib = L.load()
+    rows, hq = 2, 8
+    o = torch.zeros(2, rows, hq, 128, dtype=torch.float32, device=cuda_device)
+    lse = torch.zeros(2, rows, hq, dtype=torch.float32, device=cuda_device)
+    flags = torch.zeros(2, 2, dtype=torch.int32, device=cuda_device)  # [owner][announcer]
+    tab = lambda t: torch.tensor([t[0].data_ptr(), t[1].data_ptr()], dtype=torch.int64, device=cuda_device)
+    o_tab, lse_tab, flag_tab = tab(o), tab(lse), tab(flags)
+    out = torch.full((rows, hq, 128), 3.0, dtype=torch.bfloat16, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    stream = torch.cuda.current_stream().cuda_stream
+    L.check(lib.nvfp4_peer_merge(o_tab.data_ptr(), lse_tab.data_ptr(), flag_tab.data_ptr(), 0, 2, 1,
+                                 rows, hq, out.data_ptr(), 0, status.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert int(status.item()) & L.STATUS_WAIT_TIMEOUT
+    assert (out == 3.0).all()
+    assert int(flags[0, 0]) == 1 and int(flags[1, 0]) == 1 and int(flags[0, 1]) == 0
+    # the context is still usable, and once the missing announcement is there the merge runs
+    flags[0, 1] = 1
+    status.zero_()
+    L.check(lib.nvfp4_peer_merge(o_tab.data_ptr(), lse_tab.data_ptr(), flag_tab.data_ptr(), 0, 2, 1,
+                                 rows, hq, out.data_ptr(), 0, status.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and (out == 0.0).all()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, exchange, result):
+    import torch.distributed as dist
+
+    from nvfp4_attn_kernel_b200 import sharding
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode, _quantize
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        case = inputs.attention_case(71, 4, 32, 8, (128 * 9 + 33, 128 * 4, 128 * 16 + 128, 77), 1.0, 0.0)
+        prob = Problem(case, device)   # every rank holds the whole cache here; it only READS its range
+        rows = 4
+        grp = sharding.PageRangeGroup(dist.group.WORLD, rows, 32, device, exchange=exchange)
+        local, lseq = sharding.local_page_table(prob.page_table, prob.seqused_fp4, rank, world)
+        tail = {}
+        if rank == 0:
+            tail = dict(residual_key_pages_bf16=prob.k_pages, residual_value_pages_bf16=prob.v_pages,
+                        residual_page_ids=prob.residual_page_ids, seqused_residual=prob.seqused_residual)
+        out = torch.zeros(rows, 32, 128, dtype=torch.bfloat16, device=device)
+        outs = []
+        for step in range(3):   # three steps exercise the alternating partial copies and the epochs
+            sharding.decode_page_range(grp, prob.q, prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, local, lseq,
+                                       out=out, softmax_scale=prob.softmax_scale, **tail)
+            outs.append(out.clone())
+        torch.cuda.synchronize()
+        assert int(grp.status.item()) == 0
+        # single-GPU split decode of the same problem: same partials, same merge order
+        want = prob.decode(num_splits=world)
+        same = all(torch.equal(o, want) for o in outs)
+        err = float((outs[-1].float() - torch.from_numpy(prob.oracle_from_bytes(splits=world)).to(device)).abs().max())
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (same, err))
+        if rank == 0:
+            result.put(gathered)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("exchange", ["peer", "nccl"])
+def test_page_range_split_over_two_gpus(cuda_device, exchange):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, exchange, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    for same, err in result.get(timeout=10):
+        assert same          # bit-identical to the one-GPU split path
+        assert err <= 2e-2   # and within the parity bound of the split oracle
