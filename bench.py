@@ -176,11 +176,15 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
-def build_pools(device):
-    """Two disjoint page pools in the vLLM block layout, filled by the library's quantisers."""
+def build_pools(device, rows=None, pages_per_row=None, num_pools=None):
+    """Disjoint page pools in the vLLM block layout, filled by the library's quantisers."""
     import torch
 
     from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import quantize_kv_kernel as qkv
+
+    ROWS_, PAGES_PER_ROW_ = rows or ROWS, pages_per_row or PAGES_PER_ROW
+    POOL_PAGES_ = ROWS_ * PAGES_PER_ROW_
+    NUM_POOLS_ = num_pools or NUM_POOLS
 
     block = 2 * (PAGE * HKV * 64 + HKV * 1024)
     o1 = PAGE * HKV * 64
@@ -189,17 +193,19 @@ def build_pools(device):
     pools = []
     gen = torch.Generator(device=device)
     gen.manual_seed(1234)
-    for _ in range(NUM_POOLS):
-        cache = torch.empty(POOL_PAGES, block, dtype=torch.uint8, device=device)
+    for _ in range(NUM_POOLS_):
+        cache = torch.empty(POOL_PAGES_, block, dtype=torch.uint8, device=device)
         flat = cache.view(-1)
-        kview = flat.as_strided((POOL_PAGES, PAGE, HKV, 64), (block, HKV * 64, 64, 1), 0)
-        vview = flat.as_strided((POOL_PAGES, HKV, D, 64), (block, D * 64, 64, 1), o2)
-        ksf = qkv.scale_view(flat, POOL_PAGES, HKV, block, o1)
-        vsf = qkv.scale_view(flat, POOL_PAGES, HKV, block, o3)
-        chunk = 128
+        kview = flat.as_strided((POOL_PAGES_, PAGE, HKV, 64), (block, HKV * 64, 64, 1), 0)
+        vview = flat.as_strided((POOL_PAGES_, HKV, D, 64), (block, D * 64, 64, 1), o2)
+        ksf = qkv.scale_view(flat, POOL_PAGES_, HKV, block, o1)
+        vsf = qkv.scale_view(flat, POOL_PAGES_, HKV, block, o3)
+        chunk = min(128, POOL_PAGES_)
+        while POOL_PAGES_ % chunk:
+            chunk -= 1
         offset = torch.randn(HKV, D, device=device, generator=gen) * 2.0
         shift = None
-        for lo in range(0, POOL_PAGES, chunk):
+        for lo in range(0, POOL_PAGES_, chunk):
             k = (torch.randn(chunk * PAGE, HKV, D, device=device, generator=gen) + offset).to(torch.bfloat16)
             v = torch.randn(chunk * PAGE, HKV, D, device=device, generator=gen).to(torch.bfloat16)
             if shift is None:
@@ -208,8 +214,8 @@ def build_pools(device):
             dst = torch.arange(lo, lo + chunk, dtype=torch.int32, device=device)
             qkv.quantize_key_tokens_into(k, kview, ksf, src, dst, key_shift=shift)
             qkv.quantize_value_tokens_into(v, vview, vsf, src, dst)
-        table = torch.randperm(POOL_PAGES, device=device, generator=gen).to(torch.int32).reshape(
-            ROWS, PAGES_PER_ROW)
+        table = torch.randperm(POOL_PAGES_, device=device, generator=gen).to(torch.int32).reshape(
+            ROWS_, PAGES_PER_ROW_)
         pools.append(dict(cache=cache, k=kview, ksf=ksf, v=vview, vsf=vsf, table=table, block=block))
     return pools
 
@@ -397,6 +403,131 @@ def run_gpu(args) -> None:
         dist.destroy_process_group()
 
 
+def run_long_context(args) -> None:
+    """Long-context workload: 4 sequences x 32768 context, the KV pages of every sequence split
+    by page range over the ranks (rank r holds only its pages), partial results merged over
+    NVLink.  Strong scaling: the total work is fixed as the number of GPUs grows."""
+    import torch
+    import torch.distributed as dist
+
+    import nvfp4_attn_kernel_b200._lib as L
+    from nvfp4_attn_kernel_b200 import sharding
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode, _quantize
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel._decode import split_k_heuristic
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=device)
+    rows, ctx = 4, 32768
+    pages = ctx // PAGE
+    if pages % world:
+        raise SystemExit("the page count must divide over the ranks")
+    local_pages = pages // world
+    kv_bytes = rows * ctx * HKV * 144
+    per_pool = rows * local_pages * 147456
+    num_pools = max(2, -(-2 * 132 * 2 ** 20 // per_pool))   # together well past the 126 MB L2
+    num_pools += num_pools & 1                               # the partial copies alternate in pairs
+    pools = build_pools(device, rows, local_pages, num_pools)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(7)                                       # the same query on every rank
+    q = torch.randn(rows, HQ, D, device=device, generator=gen).to(torch.bfloat16)
+    out = torch.zeros(rows, HQ, D, dtype=torch.bfloat16, device=device)
+    seq = torch.full((rows,), local_pages * PAGE, dtype=torch.int32, device=device)
+    q_fp4_s = torch.zeros(rows, 1, HQ, 64, dtype=torch.uint8, device=device)
+    q_sf_s = torch.zeros(rows, 1, HQ, 2, 32, 4, 4, dtype=torch.uint8, device=device)
+    splits = args.num_splits if args.num_splits > 1 else split_k_heuristic(rows, HKV, local_pages, sms=148)
+    grp = sharding.PageRangeGroup(dist.group.WORLD, rows, HQ, device, args.exchange) if world > 1 else None
+
+    def step(i):
+        pool = pools[i % num_pools]
+        q_fp4, q_sf = _quantize.quantize_query(q, heads_kv=HKV, query_fp4_scratch=q_fp4_s,
+                                               query_scales_scratch=q_sf_s)
+        common = dict(query_fp4=q_fp4, query_scales=q_sf, query_padded_bf16=None,
+                      key_pages_fp4=pool["k"], key_scales=pool["ksf"], value_pages_fp4=pool["v"],
+                      value_scales=pool["vsf"], fp4_page_table=pool["table"], seqused_fp4=seq,
+                      softmax_scale=D ** -0.5, trusted_metadata=True)
+        if grp is None:
+            _decode.decode_fp4_split(**{k: v for k, v in common.items() if k != "query_padded_bf16"},
+                                     num_splits=splits, out=out)
+        else:
+            _decode.decode_fp4(**common, _partials=grp.partial_buffers())
+            grp.merge(out)
+
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream())
+    workspace_warm = 2 * num_pools
+    with torch.cuda.stream(side):
+        for i in range(workspace_warm):
+            step(i)
+    side.synchronize()
+    if world > 1:
+        dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(num_pools):
+            step(i)
+    reps = max(1, args.steps // num_pools)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(1, args.warmup // num_pools)):
+        graph.replay()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    done = reps * num_pools
+    ms_step = ms / done
+    status = int(grp.status.item()) if grp is not None else 0
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except (OSError, ValueError):
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        per_gpu = kv_bytes / world / (ms_step * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": METRIC, "value": rows / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": done, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
+            "config": {
+                "workload": "long-context split-KV: 4 seq x 32768 ctx, Hq32/Hkv8/D128, KV pages of every "
+                            "sequence partitioned by page range over the GPUs, partial (O, LSE) merged over NVLink",
+                "exchange": args.exchange if world > 1 else f"one GPU, num_splits={splits}",
+                "l2": f"{num_pools} rotating page pools per GPU, {per_pool / 1e6:.0f} MB each",
+                "timing": "CUDA-graph replay (Q quantise + decode + merge per step), CUDA events, max over ranks",
+            },
+            "hbm_gbs_per_gpu": per_gpu,
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
+                         "frac": per_gpu / peak, "peak_source": "measured" if peaks else "fallback",
+                         "traffic": None},
+            "cpu_baseline": None, "e2e": None,
+            "gpu_launches": done * (3 if world > 1 else 3),
+            "clocks": clocks, "device_status_word": status,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -408,6 +539,10 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ctx", type=int, default=CTX,
                     help="context length per sequence (default: the headline workload's 4096)")
+    ap.add_argument("--workload", default="batch", choices=["batch", "long-context"],
+                    help="batch: the headline uniform batch (default); long-context: 4 x 32768 split "
+                         "by page range over the GPUs")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--ncu-traffic", type=float, default=None,
                     help="dram bytes per decode launch from an ncu capture (reported as roofline.traffic)")
     args = ap.parse_args()
@@ -415,6 +550,8 @@ def main() -> None:
         set_context(args.ctx)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "long-context":
+        run_long_context(args)
     else:
         run_gpu(args)
 

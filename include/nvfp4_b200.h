@@ -227,14 +227,17 @@ int nvfp4_lse_merge_ptrs(const float* const* o_part_ptrs, const float* const* ls
  * then NVFP4_STATUS_WAIT_TIMEOUT is raised and `out` is left untouched - until every peer has
  * announced the same epoch, and merges by LSE weight with plain loads from the peers' buffers.
  * Epochs must grow by one per call on every rank; partial buffers should alternate between two
- * copies so that a fast rank cannot overwrite what a slow one still reads.
+ * copies so that a fast rank cannot overwrite what a slow one still reads.  With epoch_state
+ * (two zero-initialised int32 in device memory, private to the rank) the epoch is kept on the
+ * device - the call uses epoch_state[0] + 1 and advances it - so that the launch can be
+ * replayed from a CUDA graph; `epoch` is then ignored.
  * The reference has no multi-GPU path; the merge arithmetic is that of flash_attn_combine
  * (src/nvfp4_decode_kernel/split_k_combine.py:516-554).
  *   o_part_ptrs / lse_part_ptrs / flag_ptrs: DEVICE arrays of `world` pointers.
  */
 int nvfp4_peer_merge(const float* const* o_part_ptrs, const float* const* lse_part_ptrs,
-                     int32_t* const* flag_ptrs, int rank, int world, int epoch, int rows, int heads_q,
-                     void* out, int out_is_f32, uint32_t* status, void* stream);
+                     int32_t* const* flag_ptrs, int rank, int world, int epoch, int32_t* epoch_state,
+                     int rows, int heads_q, void* out, int out_is_f32, uint32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -137,7 +137,7 @@ def _declare(lib) -> None:
 def _declare_peer(lib) -> None:
     lib.nvfp4_peer_merge.restype = c_int
     lib.nvfp4_peer_merge.argtypes = [
-        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
         c_void_p, c_void_p,
     ]
 

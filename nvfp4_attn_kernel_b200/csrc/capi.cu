@@ -338,8 +338,8 @@ int nvfp4_lse_merge_ptrs(const float* const* o_part_ptrs, const float* const* ls
 }
 
 int nvfp4_peer_merge(const float* const* o_part_ptrs, const float* const* lse_part_ptrs,
-                     int32_t* const* flag_ptrs, int rank, int world, int epoch, int rows, int heads_q,
-                     void* out, int out_is_f32, uint32_t* status, void* stream) {
+                     int32_t* const* flag_ptrs, int rank, int world, int epoch, int32_t* epoch_state,
+                     int rows, int heads_q, void* out, int out_is_f32, uint32_t* status, void* stream) {
   if (world < 1 || world > 128 || rank < 0 || rank >= world)
     return fail(NVFP4_ERR_INVALID, "peer_merge: rank %d of %d is out of range (at most 128 ranks)", rank, world);
   if (rows < 0 || heads_q < 1) return fail(NVFP4_ERR_INVALID, "peer_merge: bad extents");
@@ -347,8 +347,8 @@ int nvfp4_peer_merge(const float* const* o_part_ptrs, const float* const* lse_pa
   if (!o_part_ptrs || !lse_part_ptrs || !flag_ptrs || !out)
     return fail(NVFP4_ERR_INVALID, "peer_merge: null argument");
   if (rows > 65535) return fail(NVFP4_ERR_INVALID, "peer_merge: too many rows");
-  cudaError_t e = nvfp4::launch_peer_merge(o_part_ptrs, lse_part_ptrs, flag_ptrs, rank, world, epoch, rows,
-                                           heads_q, out, out_is_f32, status,
+  cudaError_t e = nvfp4::launch_peer_merge(o_part_ptrs, lse_part_ptrs, flag_ptrs, rank, world, epoch,
+                                           epoch_state, rows, heads_q, out, out_is_f32, status,
                                            static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "peer_merge launch");
 }

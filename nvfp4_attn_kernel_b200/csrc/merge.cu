@@ -91,10 +91,14 @@ constexpr unsigned long long kPeerWaitNs = 1000000000ull;  // 1 s
 template <bool kOutF32>
 __global__ void __launch_bounds__(128)
 peer_merge_kernel(const float* const* __restrict__ o_ptrs, const float* const* __restrict__ lse_ptrs,
-                  int* const* __restrict__ flag_ptrs, int rank, int world, int epoch, int rows,
-                  int heads_q, void* __restrict__ out, uint32_t* __restrict__ status) {
+                  int* const* __restrict__ flag_ptrs, int rank, int world, int epoch_arg,
+                  int* __restrict__ epoch_state, int rows, int heads_q, void* __restrict__ out,
+                  uint32_t* __restrict__ status) {
   __shared__ int ready;
   const int head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
+  // With a device-resident epoch (graph replay) every block reads it before any block can
+  // advance it: the block that finishes last does that.
+  const int epoch = epoch_state ? *reinterpret_cast<volatile int*>(epoch_state) + 1 : epoch_arg;
   if (blockIdx.x == 0 && blockIdx.y == 0 && d < world) {
     __threadfence_system();
     st_release_sys(flag_ptrs[d] + rank, epoch);
@@ -117,6 +121,14 @@ peer_merge_kernel(const float* const* __restrict__ o_ptrs, const float* const* _
     ready = ok;
   }
   __syncthreads();
+  if (epoch_state && d == 0) {
+    const int blocks = gridDim.x * gridDim.y;
+    if (atomicAdd(epoch_state + 1, 1) == blocks - 1) {
+      epoch_state[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile int*>(epoch_state) = epoch;
+    }
+  }
   if (!ready) return;  // the output is left untouched and the status word says why
   const int64_t idx = (int64_t)row * heads_q + head;
   float mx = -INFINITY;
@@ -138,17 +150,17 @@ peer_merge_kernel(const float* const* __restrict__ o_ptrs, const float* const* _
 }
 
 cudaError_t launch_peer_merge(const float* const* o_ptrs, const float* const* lse_ptrs,
-                              int* const* flag_ptrs, int rank, int world, int epoch, int rows,
-                              int heads_q, void* out, int out_is_f32, uint32_t* status,
-                              cudaStream_t stream) {
+                              int* const* flag_ptrs, int rank, int world, int epoch,
+                              int* epoch_state, int rows, int heads_q, void* out, int out_is_f32,
+                              uint32_t* status, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   dim3 grid(heads_q, rows);
   if (out_is_f32)
     peer_merge_kernel<true><<<grid, 128, 0, stream>>>(o_ptrs, lse_ptrs, flag_ptrs, rank, world, epoch,
-                                                      rows, heads_q, out, status);
+                                                      epoch_state, rows, heads_q, out, status);
   else
     peer_merge_kernel<false><<<grid, 128, 0, stream>>>(o_ptrs, lse_ptrs, flag_ptrs, rank, world, epoch,
-                                                       rows, heads_q, out, status);
+                                                       epoch_state, rows, heads_q, out, status);
   return cudaGetLastError();
 }
 

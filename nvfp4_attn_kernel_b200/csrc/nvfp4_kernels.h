@@ -81,8 +81,8 @@ cudaError_t launch_lse_merge(const float* o_parts, int64_t o_split_stride, const
                              float* lse_out, cudaStream_t stream);
 
 cudaError_t launch_peer_merge(const float* const* o_ptrs, const float* const* lse_ptrs,
-                              int* const* flag_ptrs, int rank, int world, int epoch, int rows,
-                              int heads_q, void* out, int out_is_f32, uint32_t* status,
-                              cudaStream_t stream);
+                              int* const* flag_ptrs, int rank, int world, int epoch,
+                              int* epoch_state, int rows, int heads_q, void* out, int out_is_f32,
+                              uint32_t* status, cudaStream_t stream);
 
 }  // namespace nvfp4

@@ -86,6 +86,7 @@ class PageRangeGroup:
         self.rows, self.heads_q, self.device, self.exchange = rows, heads_q, device, exchange
         self.epoch = 0
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._epoch_state = torch.zeros(2, dtype=torch.int32, device=device)  # device-resident epoch
         self._o_elems = rows * heads_q * HEAD_DIM
         self._lse_elems = rows * heads_q
         per_copy = self._o_elems + self._lse_elems
@@ -138,8 +139,8 @@ class PageRangeGroup:
             with torch.cuda.device(self.device):
                 _lib.check(lib.nvfp4_peer_merge(
                     o_tab.data_ptr(), lse_tab.data_ptr(), self._flags.data_ptr(), self.rank,
-                    self.world, self.epoch, self.rows, self.heads_q, out.data_ptr(), f32,
-                    self.status.data_ptr(), stream))
+                    self.world, self.epoch, self._epoch_state.data_ptr(), self.rows, self.heads_q,
+                    out.data_ptr(), f32, self.status.data_ptr(), stream))
         else:
             import torch.distributed as dist
 

@@ -30,7 +30,7 @@ def test_peer_merge_wait_expires_with_a_status_and_leaves_out_untouched(cuda_dev
     status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
     stream = torch.cuda.current_stream().cuda_stream
     L.check(lib.nvfp4_peer_merge(o_tab.data_ptr(), lse_tab.data_ptr(), flag_tab.data_ptr(), 0, 2, 1,
-                                 rows, hq, out.data_ptr(), 0, status.data_ptr(), stream))
+                                 None, rows, hq, out.data_ptr(), 0, status.data_ptr(), stream))
     torch.cuda.synchronize()
     assert int(status.item()) & L.STATUS_WAIT_TIMEOUT
     assert (out == 3.0).all()
@@ -39,7 +39,7 @@ def test_peer_merge_wait_expires_with_a_status_and_leaves_out_untouched(cuda_dev
     flags[0, 1] = 1
     status.zero_()
     L.check(lib.nvfp4_peer_merge(o_tab.data_ptr(), lse_tab.data_ptr(), flag_tab.data_ptr(), 0, 2, 1,
-                                 rows, hq, out.data_ptr(), 0, status.data_ptr(), stream))
+                                 None, rows, hq, out.data_ptr(), 0, status.data_ptr(), stream))
     torch.cuda.synchronize()
     assert int(status.item()) == 0 and (out == 0.0).all()
 
