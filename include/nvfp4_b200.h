@@ -220,6 +220,32 @@ int nvfp4_lse_merge_ptrs(const float* const* o_part_ptrs, const float* const* ls
                          const int32_t* out_indices, float* lse_out, void* stream);
 
 /*
+ * Split-KV decode for callers that cannot allocate.  No counterpart in the reference project
+ * (its split path allocates and fills its partial buffers on every call,
+ * src/nvfp4_decode_kernel/_decode.py:1051-1065).
+ *
+ * Meant for an engine that has handed every free byte of HBM to its KV cache after a memory
+ * profiling pass, or that must not take the device-wide synchronisation an allocation implies in
+ * the middle of a decode step: the per-split partial results go into a fixed array of
+ * NVFP4_STATIC_WORKSPACE_BYTES that is part of the library image (every GPU that loads the
+ * library holds it until the process exits).  The call itself never allocates or frees.
+ *
+ *  - args as for nvfp4_decode with num_splits >= 2 and out != NULL; workspace, workspace_bytes,
+ *    o_partial and lse_partial are ignored / must be NULL.
+ *  - rows * heads_q * num_splits * 516 bytes must fit the array, otherwise NVFP4_ERR_INVALID with
+ *    a message (nvfp4_decode_split_static_error()) that names both sizes.
+ *  - The first call on a device looks the array's address up (with that device current); make
+ *    that first call before any stream capture.
+ *  - All calls on a device share the one array: two calls whose kernels may overlap on the GPU
+ *    (different streams, no ordering) race on it.  Nothing in it needs clearing between calls -
+ *    every slot that the merge reads is written by the decode kernel of the same call.
+ */
+#define NVFP4_STATIC_WORKSPACE_BYTES (8u << 20)
+int nvfp4_decode_split_static(const nvfp4_decode_args* args, void* stream);
+size_t nvfp4_static_workspace_bytes(void);
+const char* nvfp4_decode_split_static_error(void);
+
+/*
  * Merge for the cross-GPU KV page-range split (one process per GPU).  Each rank has written
  * its partial (normalised fp32 O [rows][Hq][128], fp32 LSE [rows][Hq]) into memory every rank
  * can address (peer-mapped / symmetric allocations).  The call announces "partial of `epoch`

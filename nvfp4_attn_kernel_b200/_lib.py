@@ -32,6 +32,9 @@ EXPORTS = (
     "nvfp4_lse_merge",
     "nvfp4_lse_merge_ptrs",
     "nvfp4_peer_merge",
+    "nvfp4_decode_split_static",
+    "nvfp4_static_workspace_bytes",
+    "nvfp4_decode_split_static_error",
 )
 
 
@@ -142,6 +145,15 @@ def _declare_peer(lib) -> None:
     ]
 
 
+def _declare_static(lib) -> None:
+    lib.nvfp4_decode_split_static.restype = c_int
+    lib.nvfp4_decode_split_static.argtypes = [ctypes.POINTER(DecodeArgs), c_void_p]
+    lib.nvfp4_static_workspace_bytes.restype = c_size_t
+    lib.nvfp4_static_workspace_bytes.argtypes = []
+    lib.nvfp4_decode_split_static_error.restype = c_char_p
+    lib.nvfp4_decode_split_static_error.argtypes = []
+
+
 def load():
     """Load the shared library once and return the ctypes handle."""
     global _lib
@@ -155,6 +167,7 @@ def load():
         lib = ctypes.CDLL(LIB_PATH)
         _declare(lib)
         _declare_peer(lib)
+        _declare_static(lib)
         _lib = lib
     return _lib
 

@@ -16,7 +16,8 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_NAME = "libnvfp4_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
 
-SOURCES = ["capi.cu", "quantize.cu", "decode_generic.cu", "decode_sm100.cu", "merge.cu"]
+SOURCES = ["capi.cu", "quantize.cu", "decode_generic.cu", "decode_sm100.cu", "merge.cu",
+           "decode_static_ws.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
