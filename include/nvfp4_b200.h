@@ -220,6 +220,36 @@ int nvfp4_lse_merge_ptrs(const float* const* o_part_ptrs, const float* const* ls
                          const int32_t* out_indices, float* lse_out, void* stream);
 
 /*
+ * Slot control plane: one step of the BF16 tail-slot table, entirely on the device (one CTA).
+ * ref: _control_kernel / ControlPlane.prepare, src/nvfp4_vllm/control.py:114-334,447-511.
+ * A row is a request iff seq_len > 0 and block_table[row][0] != 0 (the null block).  Rows keep
+ * the slot keyed on their first block; new rows take the unclaimed slot that was seen longest
+ * ago.  Outputs (all of width num_slots): row_to_slot (-1 = none), seqused_fp4 =
+ * ((seq-1)/128)*128, seqused_residual = seq - seqused_fp4, promotion_source_tokens = slot*128,
+ * promotion_pages = block_table[row][seq/128 - 1] when seq is a multiple of 128, else -1;
+ * token_to_slot has num_actual_tokens entries.  error_code is a sticky OR of:
+ * 1 prompt split across steps, 2 row with history matched no slot, 4 matched slot's length does
+ * not continue, 8 no free slot, 16 two live rows share a block, 32 promotion column out of range.
+ * slot_keys start at -1, slot_last_seq at -1, slot_last_seen (int64) at -1, step (int64) at 0.
+ */
+int nvfp4_control_step(const int32_t* block_table, int64_t block_table_stride, int block_table_columns,
+                       const int32_t* seq_lens, const int32_t* query_start_loc, int32_t* slot_keys,
+                       int32_t* slot_last_seq, int64_t* slot_last_seen, int64_t* step, int32_t* row_to_slot,
+                       int32_t* token_to_slot, int32_t* seqused_fp4, int32_t* seqused_residual,
+                       int32_t* promotion_source_tokens, int32_t* promotion_pages, int32_t* error_code,
+                       int num_reqs, int num_actual_tokens, int num_slots, void* stream);
+
+/*
+ * Page work table of a step: for row r and page column c < columns_per_row,
+ * source_tokens[r*columns+c] = query_start_loc[r] + 128*c and destination_pages[...] =
+ * block_table[r][c] if the row is a fresh prefill (more than one query token, owns a slot) and
+ * c < seqused_fp4[r]/128, else -1.  ref: _work_table_kernel, src/nvfp4_vllm/write.py:30-76.
+ */
+int nvfp4_work_table(const int32_t* query_start_loc, const int32_t* seqused_fp4, const int32_t* row_to_slot,
+                     const int32_t* block_table, int64_t block_table_stride, int32_t* source_tokens,
+                     int32_t* destination_pages, int num_reqs, int columns_per_row, void* stream);
+
+/*
  * Split-KV decode for callers that cannot allocate.  No counterpart in the reference project
  * (its split path allocates and fills its partial buffers on every call,
  * src/nvfp4_decode_kernel/_decode.py:1051-1065).

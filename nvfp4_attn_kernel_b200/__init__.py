@@ -16,13 +16,38 @@ names (``nvfp4_decode_kernel``, ``nvfp4_vllm``).
 from __future__ import annotations
 
 import importlib
+import importlib.abc
+import importlib.util
 import sys
 
 __version__ = "0.1.0"
 
+_ALIASES = ("nvfp4_decode_kernel", "nvfp4_vllm")
+
+
+class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
+    """Resolves ``nvfp4_vllm.x`` to the one module object of ``<this package>.nvfp4_vllm.x`` so
+    that a submodule is never executed twice under two names."""
+
+    def find_spec(self, fullname, path=None, target=None):
+        if fullname.partition(".")[0] not in _ALIASES:
+            return None
+        return importlib.util.spec_from_loader(fullname, self)
+
+    def create_module(self, spec):
+        module = importlib.import_module(f"{__name__}.{spec.name}")
+        self._real_spec = module.__spec__   # the import machinery is about to overwrite it
+        return module
+
+    def exec_module(self, module):
+        # already executed under its real name; keep the spec its relative imports rely on
+        module.__spec__ = self._real_spec
+
 
 def install_aliases() -> None:
-    """Make ``import nvfp4_decode_kernel`` / ``import nvfp4_vllm`` resolve here."""
-    for name in ("nvfp4_decode_kernel", "nvfp4_vllm"):
-        if name not in sys.modules:
-            sys.modules[name] = importlib.import_module(f"{__name__}.{name}")
+    """Make ``import nvfp4_decode_kernel`` / ``import nvfp4_vllm`` (and their submodules)
+    resolve here."""
+    if not any(isinstance(finder, _AliasFinder) for finder in sys.meta_path):
+        sys.meta_path.insert(0, _AliasFinder())
+    for name in _ALIASES:
+        importlib.import_module(name)

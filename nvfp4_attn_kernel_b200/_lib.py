@@ -32,6 +32,8 @@ EXPORTS = (
     "nvfp4_lse_merge",
     "nvfp4_lse_merge_ptrs",
     "nvfp4_peer_merge",
+    "nvfp4_control_step",
+    "nvfp4_work_table",
     "nvfp4_decode_split_static",
     "nvfp4_static_workspace_bytes",
     "nvfp4_decode_split_static_error",
@@ -145,6 +147,14 @@ def _declare_peer(lib) -> None:
     ]
 
 
+def _declare_control(lib) -> None:
+    lib.nvfp4_control_step.restype = c_int
+    lib.nvfp4_control_step.argtypes = [c_void_p, c_int64, c_int] + [c_void_p] * 13 + [c_int, c_int, c_int, c_void_p]
+    lib.nvfp4_work_table.restype = c_int
+    lib.nvfp4_work_table.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                     c_int, c_int, c_void_p]
+
+
 def _declare_static(lib) -> None:
     lib.nvfp4_decode_split_static.restype = c_int
     lib.nvfp4_decode_split_static.argtypes = [ctypes.POINTER(DecodeArgs), c_void_p]
@@ -168,6 +178,7 @@ def load():
         _declare(lib)
         _declare_peer(lib)
         _declare_static(lib)
+        _declare_control(lib)
         _lib = lib
     return _lib
 

@@ -337,6 +337,44 @@ int nvfp4_lse_merge_ptrs(const float* const* o_part_ptrs, const float* const* ls
   return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "lse_merge_ptrs launch");
 }
 
+int nvfp4_control_step(const int32_t* block_table, int64_t block_table_stride, int block_table_columns,
+                       const int32_t* seq_lens, const int32_t* query_start_loc, int32_t* slot_keys,
+                       int32_t* slot_last_seq, int64_t* slot_last_seen, int64_t* step, int32_t* row_to_slot,
+                       int32_t* token_to_slot, int32_t* seqused_fp4, int32_t* seqused_residual,
+                       int32_t* promotion_source_tokens, int32_t* promotion_pages, int32_t* error_code,
+                       int num_reqs, int num_actual_tokens, int num_slots, void* stream) {
+  if (num_slots < 1 || num_slots > 128)
+    return fail(NVFP4_ERR_INVALID, "control_step: the slot table holds 1 to 128 slots, got %d", num_slots);
+  if (num_reqs < 0 || num_reqs > num_slots)
+    return fail(NVFP4_ERR_INVALID, "control_step: %d rows exceeds the %d tail slots", num_reqs, num_slots);
+  if (num_actual_tokens < 0 || block_table_columns < 1)
+    return fail(NVFP4_ERR_INVALID, "control_step: bad extents");
+  if (!block_table || !seq_lens || !query_start_loc || !slot_keys || !slot_last_seq || !slot_last_seen ||
+      !step || !row_to_slot || !token_to_slot || !seqused_fp4 || !seqused_residual ||
+      !promotion_source_tokens || !promotion_pages || !error_code)
+    return fail(NVFP4_ERR_INVALID, "control_step: null argument");
+  nvfp4::ControlArgs a{block_table, block_table_stride, block_table_columns, seq_lens, query_start_loc,
+                       slot_keys, slot_last_seq, slot_last_seen, step, row_to_slot, token_to_slot,
+                       seqused_fp4, seqused_residual, promotion_source_tokens, promotion_pages, error_code,
+                       num_reqs, num_actual_tokens, num_slots};
+  cudaError_t e = nvfp4::launch_control(a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "control_step launch");
+}
+
+int nvfp4_work_table(const int32_t* query_start_loc, const int32_t* seqused_fp4, const int32_t* row_to_slot,
+                     const int32_t* block_table, int64_t block_table_stride, int32_t* source_tokens,
+                     int32_t* destination_pages, int num_reqs, int columns_per_row, void* stream) {
+  if (num_reqs < 0 || columns_per_row < 0 || num_reqs > 65535)
+    return fail(NVFP4_ERR_INVALID, "work_table: bad extents");
+  if (num_reqs == 0 || columns_per_row == 0) return NVFP4_OK;
+  if (!query_start_loc || !seqused_fp4 || !row_to_slot || !block_table || !source_tokens || !destination_pages)
+    return fail(NVFP4_ERR_INVALID, "work_table: null argument");
+  cudaError_t e = nvfp4::launch_work_table(query_start_loc, seqused_fp4, row_to_slot, block_table,
+                                           block_table_stride, source_tokens, destination_pages, num_reqs,
+                                           columns_per_row, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "work_table launch");
+}
+
 int nvfp4_peer_merge(const float* const* o_part_ptrs, const float* const* lse_part_ptrs,
                      int32_t* const* flag_ptrs, int rank, int world, int epoch, int32_t* epoch_state,
                      int rows, int heads_q, void* out, int out_is_f32, uint32_t* status, void* stream) {

@@ -80,6 +80,23 @@ cudaError_t launch_lse_merge(const float* o_parts, int64_t o_split_stride, const
                              void* out, int out_is_f32, const int32_t* out_indices,
                              float* lse_out, cudaStream_t stream);
 
+// Slot control plane (one CTA) and the page work table.
+struct ControlArgs {
+  const int32_t* block_table; int64_t block_table_stride; int block_table_columns;
+  const int32_t* seq_lens; const int32_t* query_start_loc;
+  int32_t* slot_keys; int32_t* slot_last_seq; int64_t* slot_last_seen; int64_t* step;
+  int32_t* row_to_slot; int32_t* token_to_slot; int32_t* seqused_fp4; int32_t* seqused_residual;
+  int32_t* promotion_source_tokens; int32_t* promotion_pages; int32_t* error_code;
+  int num_reqs, num_actual_tokens, num_slots;
+};
+
+cudaError_t launch_control(const ControlArgs& a, cudaStream_t stream);
+cudaError_t launch_work_table(const int32_t* query_start_loc, const int32_t* seqused_fp4,
+                              const int32_t* row_to_slot, const int32_t* block_table,
+                              int64_t block_table_stride, int32_t* source_tokens,
+                              int32_t* destination_pages, int num_reqs, int columns_per_row,
+                              cudaStream_t stream);
+
 cudaError_t launch_peer_merge(const float* const* o_ptrs, const float* const* lse_ptrs,
                               int* const* flag_ptrs, int rank, int world, int epoch,
                               int* epoch_state, int rows, int heads_q, void* out, int out_is_f32,

@@ -1,0 +1,161 @@
+"""GPU state that one model's NVFP4 attention layers share for their whole lifetime: the BF16
+tail of every layer, the carved views of each layer's block array, the query scratch, the
+key-shift vector and its measurement, and the layer-order check.
+
+Counterpart of the reference project's ``src/nvfp4_vllm/runtime.py`` (``load_key_shift`` :39-86,
+``LayerRuntime`` :89-337).  Everything is allocated once, in the first forward pass (vLLM's
+profile run), so the KV cache is sized around it and no decode step allocates.
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+
+from ..nvfp4_decode_kernel import RESIDUAL_ROW_TILE
+from . import layout
+
+PAGE_SIZE = 128
+# Path of a safetensors file with one tensor ``key_shift`` [layers, kv_heads, head_dim].
+KEY_SHIFT_ENV = "NVFP4_KEY_SHIFT"
+
+
+def load_key_shift(num_layers: int, num_kv_heads: int, head_dim: int, device, dtype):
+    """The per-channel constant subtracted from post-RoPE K on its way into the cache, or None.
+
+    Scores become ``q.k - q.mu`` and ``q.mu`` is the same for every key of a query, so softmax
+    is unchanged as long as EVERY stored key is shifted; the constant only shrinks the block
+    scales.  Held in the cache's dtype so the subtraction is a single BF16 operation.
+    """
+    path = os.environ.get(KEY_SHIFT_ENV)
+    if not path:
+        return None
+    from safetensors.torch import load_file
+
+    tensors = load_file(path)
+    if "key_shift" not in tensors:
+        raise ValueError(f"{path} has no 'key_shift' tensor, found {sorted(tensors)}")
+    shift = tensors["key_shift"]
+    expected = (num_layers, num_kv_heads, head_dim)
+    if tuple(shift.shape) != expected:
+        raise ValueError(
+            f"{path} holds a key_shift of {tuple(shift.shape)}, this model needs {expected}"
+        )
+    return shift.to(device=device, dtype=dtype).contiguous()
+
+
+class LayerRuntime:
+    """Tail buffers, cache views and query scratch of one model."""
+
+    def __init__(self, *, num_layers: int, num_slots: int, num_heads: int, num_kv_heads: int,
+                 head_dim: int, device) -> None:
+        self.num_layers = num_layers
+        self.num_kv_heads = num_kv_heads
+        self.head_dim = head_dim
+        self.key_shift_enabled = True
+        self.key_shift_sum: torch.Tensor | None = None   # set only while measuring
+        self.key_shift_tokens = 0
+
+        # zeroed, because attention may read a whole tail page and masked positions must be finite
+        shape = (num_layers, num_slots, PAGE_SIZE, num_kv_heads, head_dim)
+        self.tail_key = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+        self.tail_value = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+        self.key_shift = load_key_shift(num_layers, num_kv_heads, head_dim, device,
+                                        self.tail_key.dtype)
+        # the same storage as one run of tokens: layer l, slot s starts at (l*slots + s)*128
+        self.tail_key_tokens = self.tail_key.view(-1, num_kv_heads, head_dim)
+        self.tail_value_tokens = self.tail_value.view(-1, num_kv_heads, head_dim)
+
+        # zeroed once and never again (the contract fp4_decode states for caller-owned scratch)
+        self.query_padded = torch.zeros(num_slots, RESIDUAL_ROW_TILE, num_heads, head_dim,
+                                        dtype=torch.bfloat16, device=device)
+        self.query_fp4 = torch.zeros(num_slots, 1, num_heads, head_dim // 2, dtype=torch.uint8,
+                                     device=device)
+        self.query_scales = torch.zeros(num_slots, 1, num_heads, head_dim // 64, 32, 4, 4,
+                                        dtype=torch.uint8, device=device)
+        self._views: dict[int, tuple[torch.Tensor, ...]] = {}
+        self._by_layer: dict[int, tuple[torch.Tensor, ...]] = {}
+        self._bases: torch.Tensor | None = None
+        self._expected_layer = 0
+
+    @property
+    def tail_bytes(self) -> int:
+        return 2 * self.tail_key.numel() * self.tail_key.element_size()
+
+    @property
+    def active_key_shift(self) -> torch.Tensor | None:
+        """What the write path should subtract, or None to store K as it is."""
+        return self.key_shift if self.key_shift_enabled else None
+
+    def set_key_shift_enabled(self, enabled: bool) -> None:
+        """Turn the shift on or off; only valid between requests (cached keys keep the setting
+        they were written under)."""
+        if enabled and self.key_shift is None:
+            raise ValueError(
+                "no shift has been loaded or measured, so there is nothing to enable"
+            )
+        self.key_shift_enabled = enabled
+
+    def begin_key_shift_measurement(self) -> None:
+        """Measure the K mean instead of removing it, until told to stop."""
+        self.key_shift = None
+        self.key_shift_sum = torch.zeros(self.num_layers, self.num_kv_heads, self.head_dim,
+                                         dtype=torch.float64, device=self.tail_key.device)
+        self.key_shift_tokens = 0
+
+    def finish_key_shift_measurement(self) -> torch.Tensor:
+        """Freeze what was measured (fp64 mean, rounded once to the cache dtype) and apply it."""
+        if self.key_shift_sum is None or self.key_shift_tokens == 0:
+            raise ValueError(
+                "no tokens were measured, so there is no mean to subtract; "
+                "begin_key_shift_measurement must precede a forward pass"
+            )
+        self.key_shift = (self.key_shift_sum / self.key_shift_tokens).to(self.tail_key.dtype)
+        self.key_shift_enabled = True
+        self.key_shift_sum = None
+        self.key_shift_tokens = 0
+        return self.key_shift
+
+    def views(self, layer_index: int, kv_cache: torch.Tensor) -> tuple[torch.Tensor, ...]:
+        """The four NVFP4 regions of one layer's block array (cached by the array's address)."""
+        key = kv_cache.data_ptr()
+        carved = self._views.get(key)
+        if carved is None:
+            carved = layout.carve(kv_cache, self.num_kv_heads, self.head_dim)
+            self._views[key] = carved
+        if self._by_layer.get(layer_index) is not carved:
+            self._by_layer[layer_index] = carved
+            self._bases = None
+        return carved
+
+    @property
+    def destination_bases(self) -> torch.Tensor:
+        """int64 ``[4, layers]``: where each layer's K packed, K scales, V packed, V scales start."""
+        if self._bases is None:
+            missing = [i for i in range(self.num_layers) if i not in self._by_layer]
+            if missing:
+                raise ValueError(
+                    f"layers {missing} have not written their KV cache, so "
+                    "promotion has no address to send their pages to"
+                )
+            self._bases = torch.tensor(
+                [[self._by_layer[layer][region].data_ptr() for layer in range(self.num_layers)]
+                 for region in range(4)],
+                dtype=torch.int64, device=self.tail_key.device)
+        return self._bases
+
+    def layer_regions(self, layer_index: int) -> tuple[torch.Tensor, ...]:
+        return self._by_layer[layer_index]
+
+    def expect_layer(self, layer_index: int) -> None:
+        """Refuse a step whose layers do not run in index order (the flush fires after the
+        highest index and must come after every layer wrote its share of the boundary token)."""
+        if layer_index != self._expected_layer:
+            expected = self._expected_layer
+            self._expected_layer = (layer_index + 1) % self.num_layers
+            raise ValueError(
+                f"layer {layer_index} ran where layer {expected} was expected; "
+                "promotion assumes layers run in index order"
+            )
+        self._expected_layer = (layer_index + 1) % self.num_layers

@@ -1,0 +1,87 @@
+"""Placing a step's K/V into the NVFP4 pages and the BF16 tail.
+
+Same functions and arguments as the reference project's ``src/nvfp4_vllm/write.py``
+(``reset_new_request_tails`` :182-215, ``PageWorkTable`` :218-277, ``write_kv`` :280-337).
+Every decision is taken on the device; launch shapes come from host integers only.
+``write_kv`` additionally takes ``key_shift``: the per-channel shift is then subtracted inside
+the page quantiser and the tail copy instead of by a separate ``torch.sub``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ..nvfp4_decode_kernel.quantize_kv_kernel import (
+    quantize_key_tokens_into,
+    quantize_value_tokens_into,
+)
+
+PAGE_SIZE = 128
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def reset_new_request_tails(*, tail_key: torch.Tensor, tail_value: torch.Tensor,
+                            query_start_loc: torch.Tensor, seq_lens: torch.Tensor,
+                            row_to_slot: torch.Tensor) -> None:
+    """Zero every layer's tail page of the rows that start a request this step
+    (``seq_len <= query_len``).  ``tail_*``: ``[layers, slots, 128, heads, head_dim]``."""
+    layers, _, _, heads, _ = tail_key.shape
+    with torch.cuda.device(tail_key.device):
+        _lib.check(_lib.load().nvfp4_tail_reset(
+            tail_key.data_ptr(), tail_value.data_ptr(), tail_key.stride(0), tail_key.stride(1),
+            layers, query_start_loc.data_ptr(), seq_lens.data_ptr(), row_to_slot.data_ptr(),
+            seq_lens.shape[0], heads, _stream(tail_key.device)))
+
+
+class PageWorkTable:
+    """Which full pages this step must quantise: a dense rows x columns rectangle, -1 = none."""
+
+    def __init__(self, *, max_num_seqs: int, max_num_batched_tokens: int, device) -> None:
+        self.max_num_seqs = max_num_seqs
+        self.max_columns = max_num_batched_tokens // PAGE_SIZE + 1
+        capacity = max_num_seqs * self.max_columns
+        self.source_tokens = torch.empty(capacity, dtype=torch.int32, device=device)
+        self.destination_pages = torch.full((capacity,), -1, dtype=torch.int32, device=device)
+
+    def build(self, *, query_start_loc: torch.Tensor, seqused_fp4: torch.Tensor,
+              row_to_slot: torch.Tensor, block_table: torch.Tensor, num_reqs: int,
+              max_query_len: int) -> tuple[torch.Tensor, torch.Tensor]:
+        if max_query_len <= 1:   # a pure decode step brings no full page
+            return self.source_tokens[:0], self.destination_pages[:0]
+        columns = min(max_query_len // PAGE_SIZE + 1, self.max_columns, block_table.shape[1])
+        items = num_reqs * columns
+        with torch.cuda.device(block_table.device):
+            _lib.check(_lib.load().nvfp4_work_table(
+                query_start_loc.data_ptr(), seqused_fp4.data_ptr(), row_to_slot.data_ptr(),
+                block_table.data_ptr(), block_table.stride(0), self.source_tokens.data_ptr(),
+                self.destination_pages.data_ptr(), num_reqs, columns, _stream(block_table.device)))
+        return self.source_tokens[:items], self.destination_pages[:items]
+
+
+def write_kv(*, key: torch.Tensor, value: torch.Tensor, key_pages_fp4: torch.Tensor,
+             key_scales: torch.Tensor, value_pages_fp4: torch.Tensor, value_scales: torch.Tensor,
+             tail_key: torch.Tensor, tail_value: torch.Tensor, source_tokens: torch.Tensor,
+             destination_pages: torch.Tensor, query_start_loc: torch.Tensor,
+             seq_lens: torch.Tensor, seqused_fp4: torch.Tensor, row_to_slot: torch.Tensor,
+             num_actual_tokens: int, key_shift: torch.Tensor | None = None) -> None:
+    """One layer's K/V of this step: full pages quantised into their blocks, the rest copied
+    to the row's tail slot.  ``tail_*`` is this layer's ``[slots, 128, heads, head_dim]``."""
+    key = key[:num_actual_tokens]
+    value = value[:num_actual_tokens]
+    if destination_pages.numel():
+        quantize_key_tokens_into(key, key_pages_fp4, key_scales, source_tokens, destination_pages,
+                                 key_shift=key_shift)
+        quantize_value_tokens_into(value, value_pages_fp4, value_scales, source_tokens,
+                                   destination_pages)
+    heads = tail_key.shape[2]
+    with torch.cuda.device(key.device):
+        _lib.check(_lib.load().nvfp4_tail_append(
+            key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0),
+            _lib.ptr(key_shift), tail_key.data_ptr(), tail_value.data_ptr(), tail_key.stride(0),
+            query_start_loc.data_ptr(), seq_lens.data_ptr(), seqused_fp4.data_ptr(),
+            row_to_slot.data_ptr(), num_actual_tokens, seq_lens.shape[0], heads,
+            _stream(key.device)))

@@ -581,3 +581,103 @@ def lse_merge(o_parts, lse_parts, return_lse: bool = False):
             lse = np.where(tot > 0, m_safe + np.log(tot), -np.inf).astype(np.float32)
         return out, lse
     return out
+
+
+# --------------------------------------------------------------------------
+# slot control plane, written out the long way
+# (tests/e2e/test_control.py:107-221 restates src/nvfp4_vllm/control.py:114-334)
+# --------------------------------------------------------------------------
+
+class SlotTable:
+    """Serial restatement of the tail-slot control plane.
+
+    A row is a request iff its length is positive and its first block is not the null block
+    (0).  A row keeps the slot keyed on its first block; a new row takes the unclaimed slot
+    seen longest ago (ties: lowest index).  Error flags accumulate in ``errors``.
+    """
+
+    FREE, NULL_BLOCK, INACTIVE = -1, 0, -1
+    E_CONT_PREFILL, E_SLOT_LOST, E_STALE, E_NO_FREE, E_DUP, E_PROMO = 1, 2, 4, 8, 16, 32
+
+    def __init__(self, num_slots: int):
+        self.n = num_slots
+        self.keys = [self.FREE] * num_slots
+        self.last_seq = [-1] * num_slots
+        self.last_seen = [-1] * num_slots
+        self.step = 0
+        self.errors = 0
+
+    def prepare(self, block_table, seq_lens, query_lens):
+        self.step += 1
+        rows = len(seq_lens)
+        key = [int(block_table[r][0]) for r in range(rows)]
+        live = [seq_lens[r] > 0 and key[r] != self.NULL_BLOCK for r in range(rows)]
+        slot_of = [self.INACTIVE] * rows
+        taken = set()
+        seen = set()
+        for r in range(rows):
+            if live[r]:
+                if key[r] in seen:
+                    self.errors |= self.E_DUP
+                seen.add(key[r])
+        for r in range(rows):
+            if not live[r]:
+                continue
+            computed = seq_lens[r] - query_lens[r]
+            if query_lens[r] > 1 and computed > 0:
+                self.errors |= self.E_CONT_PREFILL
+            for s in range(self.n):
+                if self.keys[s] == key[r]:
+                    slot_of[r] = s
+                    taken.add(s)
+                    if computed > 0 and self.last_seq[s] != computed:
+                        self.errors |= self.E_STALE
+                    break
+        for r in range(rows):
+            if not live[r] or slot_of[r] != self.INACTIVE:
+                continue
+            if seq_lens[r] - query_lens[r] > 0:
+                self.errors |= self.E_SLOT_LOST
+            free = [s for s in range(self.n) if s not in taken]
+            if not free:
+                self.errors |= self.E_NO_FREE
+                continue
+            victim = min(free, key=lambda s: (self.last_seen[s], s))
+            slot_of[r] = victim
+            taken.add(victim)
+        written = set()
+        for r, s in enumerate(slot_of):
+            if s == self.INACTIVE or s in written:
+                continue
+            written.add(s)
+            self.keys[s], self.last_seq[s], self.last_seen[s] = key[r], seq_lens[r], self.step
+        fp4 = [((seq_lens[r] - 1) // PAGE) * PAGE if live[r] else 0 for r in range(rows)]
+        residual = [seq_lens[r] - fp4[r] if live[r] else 0 for r in range(rows)]
+        token_to_slot = [slot_of[r] if live[r] else 0 for r in range(rows) for _ in range(query_lens[r])]
+        sources, pages = [0] * self.n, [-1] * self.n
+        for r in range(rows):
+            if not live[r]:
+                continue
+            sources[r] = slot_of[r] * PAGE
+            if seq_lens[r] % PAGE:
+                continue
+            column = seq_lens[r] // PAGE - 1
+            if column >= len(block_table[r]):
+                self.errors |= self.E_PROMO
+                continue
+            pages[r] = int(block_table[r][column])
+        return dict(row_to_slot=slot_of, token_to_slot=token_to_slot, seqused_fp4=fp4,
+                    seqused_residual=residual, promotion_source_tokens=sources,
+                    promotion_pages=pages, error_code=self.errors)
+
+
+def work_table(query_start_loc, seqused_fp4, row_to_slot, block_table, columns):
+    """Page work table of a step (write.py:30-76)."""
+    src, dst = [], []
+    for r in range(len(seqused_fp4)):
+        start, end = query_start_loc[r], query_start_loc[r + 1]
+        writes = (end - start > 1) and row_to_slot[r] >= 0
+        for c in range(columns):
+            src.append(start + c * PAGE)
+            dst.append(int(block_table[r][c]) if writes and c < seqused_fp4[r] // PAGE else -1)
+    return src, dst
