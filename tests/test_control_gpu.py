@@ -72,7 +72,11 @@ def test_scripted_lifecycle(cuda_device):
     assert int(plane.error_code.item()) == 0 and (plane.slot_keys == -1).all()
 
 
-def test_randomised_scheduler(cuda_device):
+@pytest.mark.parametrize("sit_out", [0.0, 0.1])
+def test_randomised_scheduler(cuda_device, sit_out):
+    """``sit_out`` > 0 lets a running request miss steps; its slot may then be handed to a
+    newcomer, which both sides must flag identically (a served engine never does this: vLLM
+    schedules every running request every step)."""
     from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane
 
     rng = np.random.default_rng(0xC7)
@@ -87,7 +91,7 @@ def test_randomised_scheduler(cuda_device):
         while len(running) < SLOTS and rng.random() < 0.3:
             running[next_block] = 0
             next_block += 1
-        batch = [k for k in running if rng.random() < 0.9]
+        batch = [k for k in running if rng.random() >= sit_out]
         rng.shuffle(batch)
         if not batch:
             continue
@@ -119,13 +123,15 @@ def test_randomised_scheduler(cuda_device):
             columns = min(max(qlen) // 128 + 1, wt.max_columns, COLUMNS)
             wsrc, wdst = O.work_table(qsl.tolist(), got["seqused_fp4"], got["row_to_slot"], table, columns)
             assert src.tolist() == wsrc and dst.tolist() == wdst
-    assert ref.errors == 0 and int(plane.error_code.item()) == 0
+    assert int(plane.error_code.item()) == ref.errors
+    if sit_out == 0.0:
+        assert ref.errors == 0
 
 
 def test_error_flags(cuda_device):
     from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane
 
-    plane = ControlPlane(max_num_seqs=4, max_num_batched_tokens=64, device=cuda_device)
+    plane = ControlPlane(max_num_seqs=4, max_num_batched_tokens=512, device=cuda_device)
     ref = O.SlotTable(4)
     cases = [
         ([[5, 1], [5, 2]], [10, 20], [10, 20]),      # two live rows share a block
