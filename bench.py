@@ -5,8 +5,8 @@
     python bench.py --impl reference --gpus N --steps K ...   # the CPU oracle path
 
 One "step" is one decode step of one attention layer over the whole batch:
-Q quantisation + split-KV paged decode (the LSE merge is part of the decode call
-when it splits).  The workload is the uniform batch-decode configuration:
+Q quantisation + split-KV paged decode, ONE launch (the decode kernel quantises the
+BF16 query itself; the LSE merge is a second launch of the same call when it splits).  The workload is the uniform batch-decode configuration:
 32 sequences x 4096 context, 32 query heads / 8 KV heads / head_dim 128,
 128-token pages, key shift applied when the pages were written, no BF16 tail.
 
@@ -271,12 +271,20 @@ def run_gpu(args) -> None:
         return a
 
     dargs = [decode_args(p) for p in pools]
+    # the step as a caller runs it: ONE launch that takes the BF16 query and quantises it inside
+    fused = [decode_args(p) for p in pools]
+    for a in fused:
+        a.q_fp4, a.q_sf = None, None
+        a.q_bf16, a.q_bf16_row_stride, a.q_bf16_head_stride = q.data_ptr(), q.stride(0), q.stride(1)
+    L.check(lib.nvfp4_quantize_q(q.data_ptr(), q.stride(0), q.stride(1), None, q_fp4.data_ptr(),
+                                 q_sf.data_ptr(), None, ROWS, HQ, HKV,
+                                 torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
 
     def step(i, stream, with_q=True):
-        if with_q:
-            L.check(lib.nvfp4_quantize_q(q.data_ptr(), q.stride(0), q.stride(1), None, q_fp4.data_ptr(),
-                                         q_sf.data_ptr(), None, ROWS, HQ, HKV, stream))
-        L.check(lib.nvfp4_decode(ctypes.byref(dargs[i % NUM_POOLS]), stream))
+        """with_q: BF16 query in, quantised inside the decode launch; else the query was
+        quantised beforehand and the launch only streams the pages."""
+        L.check(lib.nvfp4_decode(ctypes.byref((fused if with_q else dargs)[i % NUM_POOLS]), stream))
 
     def timed_graph(with_q, steps, warmup):
         """Capture NUM_POOLS steps into a CUDA graph, replay, time with events on its stream."""
@@ -370,7 +378,7 @@ def run_gpu(args) -> None:
             res = cpu_path(1, 0)
             cpu = {"value": res["value"], "unit": UNIT, "cores": res["cores"], "kind": "port",
                    "sample": res["sample"]}
-        launches_per_step = 2 + (1 if splits > 1 else 0)
+        launches_per_step = 1 + (1 if splits > 1 else 0)   # decode (query quantised inside) [+ merge]
         line = {
             "metric": METRIC, "value": world * ROWS / (ms_step * 1e-3), "unit": UNIT,
             "n_gpus": world, "steps": done, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -467,16 +475,25 @@ def run_long_context(args) -> None:
     side.synchronize()
     if world > 1:
         dist.barrier()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
-        for i in range(num_pools):
-            step(i)
+    # The NCCL exchange is timed with plain launches: a run that captured the all-gather into
+    # the graph next to the hand-launched kernels did not finish on two GPUs.
+    use_graph = grp is None or args.exchange == "peer"
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(num_pools):
+                step(i)
+        one_round = graph.replay
+    else:
+        def one_round():
+            for i in range(num_pools):
+                step(i)
     reps = max(1, args.steps // num_pools)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     for _ in range(max(1, args.warmup // num_pools)):
-        graph.replay()
+        one_round()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -484,7 +501,7 @@ def run_long_context(args) -> None:
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(reps):
-        graph.replay()
+        one_round()
     end.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(end)
@@ -514,7 +531,8 @@ def run_long_context(args) -> None:
                             "sequence partitioned by page range over the GPUs, partial (O, LSE) merged over NVLink",
                 "exchange": args.exchange if world > 1 else f"one GPU, num_splits={splits}",
                 "l2": f"{num_pools} rotating page pools per GPU, {per_pool / 1e6:.0f} MB each",
-                "timing": "CUDA-graph replay (Q quantise + decode + merge per step), CUDA events, max over ranks",
+                "timing": ("CUDA-graph replay" if use_graph else "plain launches")
+                          + " (Q quantise + decode + merge per step), CUDA events, max over ranks",
             },
             "hbm_gbs_per_gpu": per_gpu,
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",

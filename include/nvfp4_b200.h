@@ -143,7 +143,11 @@ typedef struct nvfp4_decode_args {
   /* query */
   const void* q_fp4;          /* [rows][1][Hq][64] */
   const void* q_sf;           /* [rows][Hq*1024] */
-  const void* q_bf16;         /* nullable: bf16 query used against the BF16 tail */
+  const void* q_bf16;         /* nullable: bf16 query used against the BF16 tail.  With q_fp4 and q_sf
+                                 both NULL it is required, and the decode kernel quantises the rows
+                                 itself with the arithmetic of nvfp4_quantize_q (bit-identical result,
+                                 one launch instead of two): row r, head h at
+                                 q_bf16 + r*row_stride + h*head_stride, 128 contiguous channels */
   int64_t q_bf16_row_stride;  /* elements */
   int64_t q_bf16_head_stride; /* elements */
   /* NVFP4 pages */

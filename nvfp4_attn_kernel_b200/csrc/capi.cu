@@ -204,9 +204,12 @@ int nvfp4_decode(const nvfp4_decode_args* a, void* stream) {
     return fail(NVFP4_ERR_INVALID, "softmax_scale must be finite and positive");
   if (a->num_splits < 1 || a->num_splits > 1024)
     return fail(NVFP4_ERR_INVALID, "num_splits must be in [1, 1024], got %d", a->num_splits);
-  if (!a->q_fp4 || !a->q_sf || !a->k_packed || !a->k_sf || !a->v_packed || !a->v_sf || !a->page_table ||
-      !a->seqused_fp4)
+  if (!a->k_packed || !a->k_sf || !a->v_packed || !a->v_sf || !a->page_table || !a->seqused_fp4)
     return fail(NVFP4_ERR_INVALID, "decode: a required pointer is null");
+  const bool fused_query = !a->q_fp4 && !a->q_sf;
+  if (fused_query ? !a->q_bf16 : (!a->q_fp4 || !a->q_sf))
+    return fail(NVFP4_ERR_INVALID,
+                "decode: give q_fp4 and q_sf together, or neither and a BF16 query to quantise in the kernel");
   if (a->rows > 65535 || a->heads_kv > 65535)
     return fail(NVFP4_ERR_INVALID, "decode: rows and heads_kv are limited to 65535");
   const int64_t dense_packed = (int64_t)128 * a->heads_kv * 64, dense_sf = (int64_t)a->heads_kv * 1024;
@@ -216,7 +219,7 @@ int nvfp4_decode(const nvfp4_decode_args* a, void* stream) {
   if (a->k_sf_pitch < dense_sf || a->v_sf_pitch < dense_sf || (a->k_sf_pitch % 16) || (a->v_sf_pitch % 16))
     return fail(NVFP4_ERR_INVALID, "decode: scale page pitch must be >= %lld bytes and 16-byte aligned",
                 (long long)dense_sf);
-  if (!aligned16(a->q_fp4) || !aligned16(a->q_sf) || !aligned16(a->k_packed) || !aligned16(a->k_sf) ||
+  if ((!fused_query && (!aligned16(a->q_fp4) || !aligned16(a->q_sf))) || !aligned16(a->k_packed) || !aligned16(a->k_sf) ||
       !aligned16(a->v_packed) || !aligned16(a->v_sf))
     return fail(NVFP4_ERR_INVALID, "decode: query and page regions must be 16-byte aligned");
   if (a->max_pages < 0 || a->page_table_row_stride < a->max_pages || a->num_pages < 0)

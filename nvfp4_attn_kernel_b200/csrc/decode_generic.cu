@@ -41,9 +41,22 @@ __global__ void __launch_bounds__(128) decode_generic_kernel(const DecodeParams 
   for (int it = tid; it < G * 8; it += 128) {
     const int q = it >> 3, g = it & 7;
     const int head = w.kvh * G + q;
-    const uint2 pk = *reinterpret_cast<const uint2*>(p.q_fp4 + ((int64_t)w.row * p.heads_q + head) * 64 + g * 8);
-    const float sc = e4m3_to_f32(p.q_sf[(int64_t)w.row * p.heads_q * kSfBlockBytes +
-                                        (int64_t)w.kvh * kSfBlockBytes + sf_offset(q, g)]);
+    uint2 pk;
+    float sc;
+    if (p.q_fp4) {
+      pk = *reinterpret_cast<const uint2*>(p.q_fp4 + ((int64_t)w.row * p.heads_q + head) * 64 + g * 8);
+      sc = e4m3_to_f32(p.q_sf[(int64_t)w.row * p.heads_q * kSfBlockBytes +
+                              (int64_t)w.kvh * kSfBlockBytes + sf_offset(q, g)]);
+    } else {
+      // no quantised query was supplied: quantise the BF16 group here (stand-alone quantiser's arithmetic)
+      const uint16_t* qsrc = p.q_bf16 + (int64_t)w.row * p.q_row_stride + (int64_t)head * p.q_head_stride + g * 16;
+      float x[16];
+      unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(qsrc)), x);
+      unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(qsrc) + 1), x + 8);
+      uint8_t sf;
+      quantize_group16(x, pk.x, pk.y, sf);
+      sc = e4m3_to_f32(sf);
+    }
     float v[16];
     decode16(pk, v);
 #pragma unroll

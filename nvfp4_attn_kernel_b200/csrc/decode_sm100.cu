@@ -341,7 +341,10 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     mbar_init(&sm.drain[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == kQkWarp) {
+#ifndef NVFP4_LO
+#define NVFP4_LO 0
+#endif
+  if (warp == kQkWarp && !(NVFP4_LO & 1)) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&sm.tmem_base)),
                  "r"(kTmemCols)
@@ -354,6 +357,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     reinterpret_cast<uint4*>(sm.p_tile)[i] = make_uint4(0, 0, 0, 0);
   for (int i = tid; i < 2 * kBatch * kSfBlockBytes / 16; i += kThreads)
     reinterpret_cast<uint4*>(sm.p_sf)[i] = make_uint4(0, 0, 0, 0);
+  if (!p.q_fp4)
+    for (int i = tid; i < kSfBlockBytes / 16; i += kThreads) reinterpret_cast<uint4*>(sm.q_sf)[i] = make_uint4(0, 0, 0, 0);
   const TileWork w = resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x);
   const int n_pages = w.last_page - w.first_page;
   const int n_batches = (n_pages + kBatch - 1) / kBatch;
@@ -364,8 +369,17 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     sm.page_ok[s] = pid >= 0 ? 1 : 0;
     if (pid >= 0) {
       mbar_expect_tx(&sm.full[s], kStageBytes);
+#if NVFP4_LO & 12
+      bulk_load(smem_u32(st), p.k_packed + pid * p.k_pitch + (int64_t)w.kvh * kTileBytes, kTileBytes, &sm.full[s]);
+#else
       tma_load_4d(smem_u32(st), &k_map, &sm.full[s], 0, w.kvh, 0, (int)pid);
+#endif
+#if NVFP4_LO & 20
+      bulk_load(smem_u32(st + kTileBytes), p.v_packed + pid * p.v_pitch + (int64_t)w.kvh * kTileBytes, kTileBytes,
+                &sm.full[s]);
+#else
       tma_load_4d(smem_u32(st + kTileBytes), &v_map, &sm.full[s], 0, 0, w.kvh, (int)pid);
+#endif
       bulk_load(smem_u32(st + 2 * kTileBytes), p.k_sf + pid * p.k_sf_pitch + (int64_t)w.kvh * kSfBlockBytes,
                 kSfBlockBytes, &sm.full[s]);
       bulk_load(smem_u32(st + 2 * kTileBytes + kSfBlockBytes),
@@ -417,7 +431,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 
 #ifdef NVFP4_LOADONLY
   // developer experiment: stream the pages through shared memory and do nothing with them
-  if (warp == kQkWarp && lane == 0) {
+  if (warp == kQkWarp && lane == 0 && !(NVFP4_LO & 2)) {
     for (int i = 0; i < n_pages; ++i) {
       const int s = i % kStages;
       if (!mbar_wait(&sm.full[s], (i / kStages) & 1, sm, p.status)) break;
@@ -434,15 +448,32 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     // four adjacent lanes and the packed E2M1 bytes of P are formed without any exchange.
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     // query operand: G packed rows, swizzled; its scale block; the BF16 copy for the tail
-    if (tid < G * 4) {
-      const int q = tid >> 2, c = tid & 3;
-      const uint4 v = *reinterpret_cast<const uint4*>(
-          p.q_fp4 + ((int64_t)w.row * p.heads_q + w.kvh * G + q) * 64 + c * 16);
-      *reinterpret_cast<uint4*>(sm.q_tile + sw64_offset(q, c * 16)) = v;
-    }
-    if (tid >= 64) {
-      reinterpret_cast<uint4*>(sm.q_sf)[tid - 64] = *(reinterpret_cast<const uint4*>(
-          p.q_sf + (int64_t)w.row * p.heads_q * kSfBlockBytes + (int64_t)w.kvh * kSfBlockBytes) + (tid - 64));
+    if (p.q_fp4) {
+      if (tid < G * 4) {
+        const int q = tid >> 2, c = tid & 3;
+        const uint4 v = *reinterpret_cast<const uint4*>(
+            p.q_fp4 + ((int64_t)w.row * p.heads_q + w.kvh * G + q) * 64 + c * 16);
+        *reinterpret_cast<uint4*>(sm.q_tile + sw64_offset(q, c * 16)) = v;
+      }
+      if (tid >= 64) {
+        reinterpret_cast<uint4*>(sm.q_sf)[tid - 64] = *(reinterpret_cast<const uint4*>(
+            p.q_sf + (int64_t)w.row * p.heads_q * kSfBlockBytes + (int64_t)w.kvh * kSfBlockBytes) + (tid - 64));
+      }
+    } else if (tid < G * 8) {
+      // no quantised query was supplied: quantise the BF16 rows of this KV head here, one
+      // 16-channel group per thread, with the arithmetic of the stand-alone query quantiser
+      // (the scale block was zeroed during set-up)
+      const int q = tid >> 3, g = tid & 7;
+      const uint16_t* src = p.q_bf16 + (int64_t)w.row * p.q_row_stride +
+                            (int64_t)(w.kvh * G + q) * p.q_head_stride + g * 16;
+      float x[16];
+      unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(src)), x);
+      unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(src) + 1), x + 8);
+      uint32_t lo, hi;
+      uint8_t sf;
+      quantize_group16(x, lo, hi, sf);
+      *reinterpret_cast<uint2*>(sm.q_tile + sw64_offset(q, g * 8)) = make_uint2(lo, hi);
+      sm.q_sf[sf_offset(q, g)] = sf;
     }
     fence_proxy_async();
     mbar_arrive(&sm.q_ready);
@@ -618,7 +649,11 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       if (lane == 0) {
         const int s = i % kStages;
         TRACE(1, i, 0);
+#if NVFP4_LO & 2
+        alive = mbar_wait(&sm.full[s], ((i / kStages) & 1) ^ 1, sm, p.status);
+#else
         alive = mbar_wait(&sm.empty[s], ((i / kStages) & 1) ^ 1, sm, p.status);
+#endif
         TRACE(1, i, 1);
         if (alive) {
           issue_page(s, pid);
@@ -627,6 +662,11 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
       alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
     }
+#if NVFP4_LO & 2
+    if (lane == 0)
+      for (int i = (n_pages > kStages ? n_pages - kStages : 0); i < n_pages; ++i)
+        mbar_wait(&sm.full[i % kStages], (i / kStages) & 1, sm, p.status);
+#endif
   } else if (warp == kQkWarp) {
     // =====================  MMA issuer 1: S^T = K . Q^T  =====================
     // Issuing a tcgen05 instruction costs the issuing thread some 60 cycles and a barrier
@@ -725,7 +765,7 @@ teardown:
     if (cta < 512) g_trace[1024 + cta * 4 + 1] = global_ns();
   }
 #endif
-  if (warp == kQkWarp) {
+  if (warp == kQkWarp && !(NVFP4_LO & 1)) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
                  : "memory");

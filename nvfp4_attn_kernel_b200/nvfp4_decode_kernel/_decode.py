@@ -108,9 +108,10 @@ def _any(condition: torch.Tensor, message: str) -> None:
 
 def decode_fp4(
     *,
-    query_fp4: torch.Tensor,
-    query_scales: torch.Tensor,
+    query_fp4: torch.Tensor | None,
+    query_scales: torch.Tensor | None,
     query_padded_bf16: torch.Tensor | None,
+    query_bf16: torch.Tensor | None = None,
     key_pages_fp4: torch.Tensor,
     key_scales: torch.Tensor,
     value_pages_fp4: torch.Tensor,
@@ -135,28 +136,61 @@ def decode_fp4(
 
     ``query_padded_bf16`` (``[rows, 128, heads_q, 128]``, row 0 of each tile live)
     carries the BF16 query that meets the BF16 residual page.
+
+    With ``query_fp4`` and ``query_scales`` both None and ``query_bf16`` (BF16
+    ``[rows, heads_q, 128]``, unit stride along the channels) given, the decode kernel
+    quantises the query itself with the query quantiser's arithmetic: one launch instead of
+    two, no scratch, and the same ``query_bf16`` meets the residual page.
     """
     if not torch.cuda.is_available():
         raise RuntimeError("decode_fp4 requires CUDA")
     if not math.isfinite(softmax_scale) or softmax_scale <= 0.0:
         raise ValueError("softmax_scale must be finite and positive")
-    if query_fp4.ndim != 4:
-        raise ValueError("query_fp4 must have shape [rows, 1, heads_q, 64]")
-    device = query_fp4.device
-    _need_cuda(query_fp4, "query_fp4", device)
+    fused_query = query_fp4 is None and query_scales is None
+    fp4_dtype = torch.float4_e2m1fn_x2
+    if fused_query:
+        if query_bf16 is None:
+            raise ValueError("give query_fp4 + query_scales, or query_bf16 to quantise in the kernel")
+        if (
+            query_bf16.dtype is not torch.bfloat16
+            or query_bf16.ndim != 3
+            or query_bf16.shape[0] < 1
+            or query_bf16.shape[2] != HEAD_DIM
+            or query_bf16.stride(2) != 1
+            or query_bf16.stride(0) % 8
+            or query_bf16.stride(1) % 8
+            or query_bf16.data_ptr() % 16
+        ):
+            raise ValueError(
+                "query_bf16 must be BF16 [rows, heads_q, 128] with unit channel stride and "
+                "16-byte aligned rows"
+            )
+        if query_padded_bf16 is not None:
+            raise ValueError("query_padded_bf16 belongs to the pre-quantised query path")
+        device = query_bf16.device
+        _need_cuda(query_bf16, "query_bf16", device)
+        rows, heads_q, _ = query_bf16.shape
+    else:
+        if query_fp4 is None or query_scales is None:
+            raise ValueError("query_fp4 and query_scales must be provided together")
+        if query_bf16 is not None:
+            raise ValueError("query_bf16 is only read when the kernel quantises the query")
+        if query_fp4.ndim != 4:
+            raise ValueError("query_fp4 must have shape [rows, 1, heads_q, 64]")
+        device = query_fp4.device
+        _need_cuda(query_fp4, "query_fp4", device)
+        if query_fp4.dtype is not fp4_dtype or not query_fp4.is_contiguous():
+            raise ValueError("query_fp4 must be contiguous packed E2M1 FP4")
+        rows, query_len, heads_q, packed_dim = query_fp4.shape
+        if rows < 1 or query_len != 1 or packed_dim * 2 != HEAD_DIM:
+            raise ValueError("query_fp4 must have shape [rows, 1, heads_q, 64]")
     if torch.cuda.get_device_capability(device)[0] != 10:
         raise RuntimeError("decode_fp4 requires an SM100 CUDA device")
-    fp4_dtype = torch.float4_e2m1fn_x2
-    if query_fp4.dtype is not fp4_dtype or not query_fp4.is_contiguous():
-        raise ValueError("query_fp4 must be contiguous packed E2M1 FP4")
-    rows, query_len, heads_q, packed_dim = query_fp4.shape
-    if rows < 1 or query_len != 1 or packed_dim * 2 != HEAD_DIM:
-        raise ValueError("query_fp4 must have shape [rows, 1, heads_q, 64]")
 
     for tensor, name in (
         (key_pages_fp4, "key_pages_fp4"),
         (value_pages_fp4, "value_pages_fp4"),
-        (query_scales, "query_scales"),
+        *(() if fused_query else ((query_scales, "query_scales"),)),
         (key_scales, "key_scales"),
         (value_scales, "value_scales"),
         (fp4_page_table, "fp4_page_table"),
@@ -187,19 +221,21 @@ def decode_fp4(
 
     want_q_sf = (32, 4, 1, 4, 2, heads_kv, rows)
     want_page_sf = (page_count, 32, 4, 1, 4, 2, heads_kv)
-    if tuple(query_scales.shape) != want_q_sf:
-        raise ValueError(f"query_scales must have shape {want_q_sf}")
-    if query_scales.stride() != (16, 4, heads_q * 1024, 1, 512, 1024, heads_q * 1024):
-        raise ValueError("query_scales must use the layout returned by quantize_query")
+    if not fused_query:
+        if tuple(query_scales.shape) != want_q_sf:
+            raise ValueError(f"query_scales must have shape {want_q_sf}")
+        if query_scales.stride() != (16, 4, heads_q * 1024, 1, 512, 1024, heads_q * 1024):
+            raise ValueError("query_scales must use the layout returned by quantize_query")
     if tuple(key_scales.shape) != want_page_sf:
         raise ValueError(f"key_scales must have shape {want_page_sf}")
     if tuple(value_scales.shape) != want_page_sf:
         raise ValueError(f"value_scales must have shape {want_page_sf}")
-    query_scales = _scale_bytes(query_scales, "query_scales")
     key_scales = _scale_bytes(key_scales, "key_scales")
     value_scales = _scale_bytes(value_scales, "value_scales")
-    if query_scales.storage_offset() != 0:
-        raise ValueError("query_scales must start at storage offset zero")
+    if not fused_query:
+        query_scales = _scale_bytes(query_scales, "query_scales")
+        if query_scales.storage_offset() != 0:
+            raise ValueError("query_scales must start at storage offset zero")
     k_sf_pitch = _scale_pitch_bytes(key_scales, "key_scales")
     v_sf_pitch = _scale_pitch_bytes(value_scales, "value_scales")
 
@@ -232,21 +268,22 @@ def decode_fp4(
             "residual_page_ids, and seqused_residual must be provided together"
         )
     if has_residual:
-        if query_padded_bf16 is None:
-            raise ValueError(
-                "pre-quantized query with a BF16 residual requires "
-                "query_padded_bf16 support; use the BF16 query path"
-            )
-        _need_cuda(query_padded_bf16, "query_padded_bf16", device)
-        want_padded = (rows, PAGE_SIZE, heads_q, HEAD_DIM)
-        if (
-            query_padded_bf16.dtype is not torch.bfloat16
-            or tuple(query_padded_bf16.shape) != want_padded
-            or not query_padded_bf16.is_contiguous()
-        ):
-            raise ValueError(
-                f"query_padded_bf16 must be contiguous BF16 with shape {want_padded}"
-            )
+        if not fused_query:
+            if query_padded_bf16 is None:
+                raise ValueError(
+                    "pre-quantized query with a BF16 residual requires "
+                    "query_padded_bf16 support; use the BF16 query path"
+                )
+            _need_cuda(query_padded_bf16, "query_padded_bf16", device)
+            want_padded = (rows, PAGE_SIZE, heads_q, HEAD_DIM)
+            if (
+                query_padded_bf16.dtype is not torch.bfloat16
+                or tuple(query_padded_bf16.shape) != want_padded
+                or not query_padded_bf16.is_contiguous()
+            ):
+                raise ValueError(
+                    f"query_padded_bf16 must be contiguous BF16 with shape {want_padded}"
+                )
         for tensor, name in (
             (residual_key_pages_bf16, "residual_key_pages_bf16"),
             (residual_value_pages_bf16, "residual_value_pages_bf16"),
@@ -351,8 +388,13 @@ def decode_fp4(
         workspace = torch.empty(need, dtype=torch.uint8, device=device)
 
     args = _lib.DecodeArgs()
-    args.q_fp4 = query_fp4.data_ptr()
-    args.q_sf = query_scales.data_ptr()
+    if fused_query:
+        args.q_bf16 = query_bf16.data_ptr()
+        args.q_bf16_row_stride = query_bf16.stride(0)
+        args.q_bf16_head_stride = query_bf16.stride(1)
+    else:
+        args.q_fp4 = query_fp4.data_ptr()
+        args.q_sf = query_scales.data_ptr()
     if query_padded_bf16 is not None:
         args.q_bf16 = query_padded_bf16.data_ptr()
         args.q_bf16_row_stride = query_padded_bf16.stride(0)
@@ -405,8 +447,8 @@ def decode_fp4(
 
 def decode_fp4_split(
     *,
-    query_fp4: torch.Tensor,
-    query_scales: torch.Tensor,
+    query_fp4: torch.Tensor | None,
+    query_scales: torch.Tensor | None,
     key_pages_fp4: torch.Tensor,
     key_scales: torch.Tensor,
     value_pages_fp4: torch.Tensor,
@@ -416,6 +458,7 @@ def decode_fp4_split(
     softmax_scale: float,
     num_splits: int,
     query_padded_bf16: torch.Tensor | None = None,
+    query_bf16: torch.Tensor | None = None,
     residual_key_pages_bf16: torch.Tensor | None = None,
     residual_value_pages_bf16: torch.Tensor | None = None,
     residual_page_ids: torch.Tensor | None = None,
@@ -435,6 +478,7 @@ def decode_fp4_split(
         query_fp4=query_fp4,
         query_scales=query_scales,
         query_padded_bf16=query_padded_bf16,
+        query_bf16=query_bf16,
         key_pages_fp4=key_pages_fp4,
         key_scales=key_scales,
         value_pages_fp4=value_pages_fp4,
@@ -452,8 +496,12 @@ def decode_fp4_split(
     )
     if num_splits <= 1 and not return_partials:
         return decode_fp4(**common)
-    rows, _, heads_q, _ = query_fp4.shape
-    device = query_fp4.device
+    if query_fp4 is not None:
+        rows, _, heads_q, _ = query_fp4.shape
+        device = query_fp4.device
+    else:
+        rows, heads_q, _ = query_bf16.shape
+        device = query_bf16.device
     if out is None:
         out = torch.empty(rows, heads_q, HEAD_DIM, dtype=torch.bfloat16, device=device)
         common["out"] = out

@@ -53,6 +53,26 @@ def _check_scratch(scratch, name: str, rows: int, trailing: tuple[int, ...],
         )
 
 
+# When the BF16 query can be read in place (no row gather, unit channel stride, 16-byte aligned
+# rows) the decode kernel quantises it itself: one launch per call instead of two.  The result
+# is bit-identical to quantising first (same arithmetic); False forces the two-launch form.
+FUSE_QUERY_QUANT = True
+
+
+def _kernel_can_quantise(query: torch.Tensor) -> bool:
+    return (
+        query.dtype is torch.bfloat16
+        and query.is_cuda
+        and query.ndim == 3
+        and query.shape[0] >= 1
+        and query.shape[2] == 128
+        and query.stride(2) == 1
+        and query.stride(0) % 8 == 0
+        and query.stride(1) % 8 == 0
+        and query.data_ptr() % 16 == 0
+    )
+
+
 def fp4_decode_impl(
     query,
     key_pages_fp4,
@@ -95,21 +115,29 @@ def fp4_decode_impl(
         if softmax_scale is None:
             softmax_scale = query.shape[-1] ** -0.5
         rows = query.shape[0] if query_row_indices is None else query_row_indices.shape[0]
+        fused = FUSE_QUERY_QUANT and query_row_indices is None and _kernel_can_quantise(query)
         if residual_key_pages_bf16 is not None:
-            padded = _padded_query(query, rows, query_padded_scratch)
+            # validated either way; only the two-launch form writes into it
+            padded = _padded_query(query, rows, query_padded_scratch) \
+                if not fused or query_padded_scratch is not None else None
         heads, head_dim = query.shape[1], query.shape[2]
         _check_scratch(query_fp4_scratch, "query_fp4_scratch", rows,
                        (1, heads, head_dim // 2), query.device)
         _check_scratch(query_scales_scratch, "query_scales_scratch", rows,
                        (1, heads, head_dim // 64, 32, 4, 4), query.device)
-        query_fp4, query_scales = quantize_query(
-            query,
-            row_indices=query_row_indices,
-            query_padded_out=padded,
-            heads_kv=key_pages_fp4.shape[2],
-            query_fp4_scratch=query_fp4_scratch,
-            query_scales_scratch=query_scales_scratch,
-        )
+        if fused:
+            # the decode kernel quantises the rows itself; the scratch tensors stay untouched
+            query_bf16, padded_for_kernel = query, None
+        else:
+            query_fp4, query_scales = quantize_query(
+                query,
+                row_indices=query_row_indices,
+                query_padded_out=padded,
+                heads_kv=key_pages_fp4.shape[2],
+                query_fp4_scratch=query_fp4_scratch,
+                query_scales_scratch=query_scales_scratch,
+            )
+            query_bf16, padded_for_kernel = None, padded
     else:
         if query_fp4 is None or query_scales is None:
             raise ValueError("query_fp4 and query_scales must be provided together")
@@ -124,12 +152,13 @@ def fp4_decode_impl(
                 raise ValueError(f"{name} applies only to the BF16 query path")
         if softmax_scale is None:
             softmax_scale = 128 ** -0.5
+        query_bf16, padded_for_kernel = None, None
 
     residual = (residual_key_pages_bf16, residual_value_pages_bf16, residual_page_ids,
                 seqused_residual)
     complete = all(item is not None for item in residual)
     absent = all(item is None for item in residual) and has_bf16 is None
-    splittable = absent or (complete and padded is not None)
+    splittable = absent or (complete and bf16_query)
     if num_splits > 1 and not splittable:
         raise ValueError(
             "num_splits > 1 needs either no residual argument at all or a "
@@ -145,7 +174,8 @@ def fp4_decode_impl(
     shared = dict(
         query_fp4=query_fp4,
         query_scales=query_scales,
-        query_padded_bf16=padded,
+        query_padded_bf16=padded_for_kernel,
+        query_bf16=query_bf16,
         key_pages_fp4=key_pages_fp4,
         key_scales=key_scales,
         value_pages_fp4=value_pages_fp4,

@@ -286,3 +286,30 @@ def test_refusals(cuda_device):
     with pytest.raises(ValueError, match="layout returned"):
         fp4_decode(prob.q, prob.k_fp4, prob.k_sf.permute(0, 2, 1, 3, 4, 5, 6).contiguous().permute(
             0, 2, 1, 3, 4, 5, 6), prob.v_fp4, prob.v_sf, prob.page_table, prob.seqused_fp4)
+
+
+@pytest.mark.parametrize("heads", [(4, 4), (4, 2), (8, 2), (16, 2), (32, 2)])
+def test_in_kernel_query_quantisation_is_bit_identical(cuda_device, impl, heads):
+    """A BF16 query the kernel can read in place is quantised inside the decode launch; the
+    result must equal the two-launch form (query quantiser, then decode) bit for bit, with a
+    BF16 tail, with a query that is a strided slice of a wider projection, and when split."""
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _kernel
+
+    heads_q, heads_kv = heads
+    _skip_if_unsupported(impl, heads_q, heads_kv)
+    case = inputs.attention_case(57, 3, heads_q, heads_kv, (300, 129, 640), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    wide = torch.zeros(3, heads_q + 2 * heads_kv, 128, dtype=torch.bfloat16, device=cuda_device)
+    wide[:, :heads_q] = prob.q
+    sliced = wide[:, :heads_q]                       # row stride wider than heads_q * 128
+    assert not sliced.is_contiguous()
+    for kw in ({}, {"num_splits": 2}):
+        fused = prob.decode(query=sliced, **kw)
+        fused_dense = prob.decode(**kw)
+        _kernel.FUSE_QUERY_QUANT = False
+        try:
+            two_launch = prob.decode(**kw)
+        finally:
+            _kernel.FUSE_QUERY_QUANT = True
+        assert torch.equal(fused, two_launch)
+        assert torch.equal(fused_dense, two_launch)
