@@ -2,12 +2,18 @@
 // E2M1 operands with UE4M3 scales per 16 elements), accumulators in tensor memory,
 // K/V page tiles staged by TMA through a ring of shared-memory stages.
 //
-// One CTA of 352 threads per (split, KV head, row):
+// One CTA of 384 threads per (split, KV head, row):
 //   warps 0-3  score threads: read S^T from tensor memory, online softmax, P -> NVFP4
 //   warps 4-7  output threads: fold each page's O^T into the running output, epilogue
-//   warp  8    producer: page-table walk, TMA tile loads, bulk copies of the scale blocks
+//   warp  8    K producer: page-table walk, TMA loads of the K tiles, bulk copies of their scales
 //   warp  9    issuer of S^T = K . Q^T (one elected lane), owner of the tensor-memory allocation
 //   warp 10    issuer of O^T = V^T . P^T (one elected lane)
+//   warp 11    V producer: the same walk for the V tiles and their scales
+//
+// K and V travel through separate rings.  A K slot is handed back as soon as K . Q^T of its
+// page has retired, a V slot only after V^T . P^T, two hand-overs later: with one ring a page's
+// K would sit in shared memory for all of that time, and the bytes in flight per CTA (which,
+// over the memory latency, set the rate a CTA can stream at) would shrink by as much.
 //
 // The product is formed transposed so that the G <= 8 query heads of a KV head are the
 // N = 8 side of the MMA and nothing is padded to 128:
@@ -44,11 +50,18 @@ __device__ unsigned long long* g_trace = nullptr;
 #define TRACE(role, iter, ev) do {} while (0)
 #endif
 
-// Ring depth: as many 18 KB stages as two resident CTAs per SM leave room for.
-template <int G> struct StageCount { static constexpr int value = G <= 4 ? 5 : 4; };
+// Ring depths: as many 9 KB slots as two resident CTAs per SM leave room for.  V slots are
+// held about two pages longer than K slots, so the V ring is that much deeper.
+#ifdef NVFP4_KS
+template <int G> struct KSlots { static constexpr int value = NVFP4_KS; };
+template <int G> struct VSlots { static constexpr int value = NVFP4_VS; };
+#else
+template <int G> struct KSlots { static constexpr int value = G <= 4 ? 4 : 3; };
+template <int G> struct VSlots { static constexpr int value = G <= 4 ? 6 : 5; };
+#endif
 constexpr int kBatch = 2;                                         // pages handled per hand-over
 constexpr int kTileBytes = 8192;                                  // 128 rows x 64 B
-constexpr int kStageBytes = 2 * kTileBytes + 2 * kSfBlockBytes;   // K, V, K scales, V scales
+constexpr int kSlotBytes = kTileBytes + kSfBlockBytes;            // a tile and its scale block
 constexpr int kNQ = 8;                                            // MMA N
 constexpr int kTmemCols = 128;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;        // 2 s
@@ -57,14 +70,15 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull;        // 2 s
 constexpr int kColS = 0;     // 2 sets x 2 pages x 8 : S^T
 constexpr int kColO = 32;    // 2 sets x 2 pages x 8 : per-page O^T
 constexpr int kColSfQ = 64;  // 8 : 2 k-blocks x 4
-constexpr int kColSfK = 72;
-constexpr int kColSfV = 80;
-constexpr int kColSfP = 88;
+constexpr int kColSfK = 72;  // 8
+constexpr int kColSfP = 80;  // 8
+constexpr int kColSfV = 96;  // 2 sets x 2 pages x 8 : copied as soon as the V slot has landed
 
 template <int G>
 struct __align__(1024) Smem {
-  static constexpr int kStages = StageCount<G>::value;
-  uint8_t stage[kStages][kStageBytes];          // each stage: K tile | V tile | K scales | V scales
+  static constexpr int kKS = KSlots<G>::value, kVS = VSlots<G>::value;
+  uint8_t k_slot[kKS][kSlotBytes];              // K tile | K scales
+  uint8_t v_slot[kVS][kSlotBytes];              // V tile | V scales
   __align__(1024) uint8_t q_tile[512];          // 8 rows x 64 B, 64-byte swizzle
   __align__(1024) uint8_t p_tile[2][kBatch][512];
   __align__(512) uint8_t q_sf[kSfBlockBytes];
@@ -74,9 +88,9 @@ struct __align__(1024) Smem {
   __align__(16) float z[2][kBatch][G * kPage];  // scaled scores, [set][page][q][kv position]
   float resc[8][8];                             // ring of per-page rescale factors, [page & 7][q]
   float red_io[4 * 8];                          // reductions of the tail block and the epilogue
-  volatile int page_ok[kStages];                // 0: the stage stands for a page id that was refused
-  __align__(8) uint64_t full[kStages];
-  uint64_t empty[kStages];
+  volatile int page_ok[kKS];                    // 0: the slot stands for a page id that was refused
+  __align__(8) uint64_t k_full[kKS];
+  uint64_t k_empty[kKS], v_full[kVS], v_empty[kVS];
   uint64_t s_full[2], s_free[2], p_full[2], o_full[2], o_free[2];
   uint64_t q_ready, drain[2];
   uint32_t tmem_base;
@@ -216,9 +230,14 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "memory");
 }
 
-constexpr int kProducerWarp = 8;
+#ifndef NVFP4_PLANES
+#define NVFP4_PLANES 2
+#endif
+constexpr int kProducerLanes = NVFP4_PLANES;   // lanes of a producer warp that issue loads
+constexpr int kKProducerWarp = 8;
 constexpr int kQkWarp = 9;   // also owns the tensor-memory allocation
 constexpr int kPvWarp = 10;
+constexpr int kVProducerWarp = 11;
 
 // Barrier over the 256 score and output threads with an AND of a predicate.
 __device__ __forceinline__ bool bar_and_256(int bar_id, bool pred) {
@@ -253,8 +272,8 @@ __device__ __forceinline__ int sw64_offset(int row, int byte_col) {
   return row * 64 + ((((byte_col >> 4) ^ ((row >> 1) & 3))) << 4) + (byte_col & 15);
 }
 
-constexpr int kThreads = 352;
-static_assert(kThreads == 352, "the set-up barrier is written for 352 threads");
+constexpr int kThreads = 384;
+static_assert(kThreads == 384, "the set-up barrier is written for 384 threads");
 
 // One page of scores for one query head, seen by the 32 lanes of its owner warp (four
 // consecutive kv positions per lane): group and page maxima.
@@ -297,7 +316,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   Smem<G>& sm = *reinterpret_cast<Smem<G>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  constexpr int kStages = StageCount<G>::value;
+  constexpr int kKS = KSlots<G>::value, kVS = VSlots<G>::value;
   if (tid == 0) TRACE(1, 39, 0);
 #ifdef NVFP4_TRACE
   if (tid == 0 && g_trace) {
@@ -309,18 +328,25 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 #endif
 
   // ---- set-up: barriers, tensor memory, zeroed operand tiles ----
-  // The producer warp prepares its own ring barriers and starts fetching before the CTA-wide
+  // Each producer warp prepares its own ring barriers and starts fetching before the CTA-wide
   // set-up barrier, so the first page tiles are in flight while tensor memory is allocated.
+  const bool is_k_producer = warp == kKProducerWarp, is_v_producer = warp == kVProducerWarp;
+  const bool is_producer = is_k_producer || is_v_producer;
   int spec[4] = {-1, -1, -1, -1};
-  if (warp == kProducerWarp) {
+  if (is_producer) {
     if (lane == 0) {
-      for (int s = 0; s < kStages; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-      sm.abort_flag = 0;
+      if (is_k_producer) {
+        for (int s = 0; s < kKS; ++s) { mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1); }
+        sm.abort_flag = 0;
+      } else {
+        for (int s = 0; s < kVS; ++s) { mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1); }
+        sm.abort_flag = 0;   // both producers clear it: either may be the first to wait
+      }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
-    // the producer only signals the set-up barrier (it needs nothing the others prepare)
-    asm volatile("bar.arrive 4, %0;" ::"n"(352) : "memory");
+    // a producer only signals the set-up barrier (it needs nothing the others prepare)
+    asm volatile("bar.arrive 4, %0;" ::"n"(kThreads) : "memory");
     // Page-table columns are fetched before the row's length is known (the loads run beside
     // the length's).  Reading a column is harmless even when it lies past the used prefix;
     // its value is only used, and range-checked, if the length says the column is live.
@@ -341,10 +367,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     mbar_init(&sm.drain[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-#ifndef NVFP4_LO
-#define NVFP4_LO 0
-#endif
-  if (warp == kQkWarp && !(NVFP4_LO & 1)) {
+  if (warp == kQkWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&sm.tmem_base)),
                  "r"(kTmemCols)
@@ -352,50 +375,50 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   // rows G..7 of the N = 8 operands and their scale rows stay zero for the whole kernel
-  for (int i = tid; i < 512 / 16; i += kThreads) reinterpret_cast<uint4*>(sm.q_tile)[i] = make_uint4(0, 0, 0, 0);
-  for (int i = tid; i < 2 * kBatch * 512 / 16; i += kThreads)
-    reinterpret_cast<uint4*>(sm.p_tile)[i] = make_uint4(0, 0, 0, 0);
-  for (int i = tid; i < 2 * kBatch * kSfBlockBytes / 16; i += kThreads)
-    reinterpret_cast<uint4*>(sm.p_sf)[i] = make_uint4(0, 0, 0, 0);
-  if (!p.q_fp4)
-    for (int i = tid; i < kSfBlockBytes / 16; i += kThreads) reinterpret_cast<uint4*>(sm.q_sf)[i] = make_uint4(0, 0, 0, 0);
+  if (!is_producer) {
+    constexpr int kWorkers = kThreads - 64;
+    const int wt = tid < kKProducerWarp * 32 ? tid : tid - 32;   // warps 0-7, 9, 10 -> 0..319
+    for (int i = wt; i < 512 / 16; i += kWorkers) reinterpret_cast<uint4*>(sm.q_tile)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = wt; i < 2 * kBatch * 512 / 16; i += kWorkers)
+      reinterpret_cast<uint4*>(sm.p_tile)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = wt; i < 2 * kBatch * kSfBlockBytes / 16; i += kWorkers)
+      reinterpret_cast<uint4*>(sm.p_sf)[i] = make_uint4(0, 0, 0, 0);
+    if (!p.q_fp4)
+      for (int i = wt; i < kSfBlockBytes / 16; i += kWorkers) reinterpret_cast<uint4*>(sm.q_sf)[i] = make_uint4(0, 0, 0, 0);
+  }
   const TileWork w = resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x);
   const int n_pages = w.last_page - w.first_page;
   const int n_batches = (n_pages + kBatch - 1) / kBatch;
 
-  // one page of the ring: K tile, V tile and the two scale blocks, or a masked stand-in
-  auto issue_page = [&](int s, int64_t pid) {
-    uint8_t* st = sm.stage[s];
-    sm.page_ok[s] = pid >= 0 ? 1 : 0;
+  // one slot of a ring: the K (or V) tile of a page and its scale block, or a masked stand-in
+  auto issue_slot = [&](bool is_k, int s, int64_t pid) {
+    uint8_t* st = is_k ? sm.k_slot[s] : sm.v_slot[s];
+    uint64_t* bar = is_k ? &sm.k_full[s] : &sm.v_full[s];
+    if (is_k) sm.page_ok[s] = pid >= 0 ? 1 : 0;
     if (pid >= 0) {
-      mbar_expect_tx(&sm.full[s], kStageBytes);
-#if NVFP4_LO & 12
-      bulk_load(smem_u32(st), p.k_packed + pid * p.k_pitch + (int64_t)w.kvh * kTileBytes, kTileBytes, &sm.full[s]);
-#else
-      tma_load_4d(smem_u32(st), &k_map, &sm.full[s], 0, w.kvh, 0, (int)pid);
-#endif
-#if NVFP4_LO & 20
-      bulk_load(smem_u32(st + kTileBytes), p.v_packed + pid * p.v_pitch + (int64_t)w.kvh * kTileBytes, kTileBytes,
-                &sm.full[s]);
-#else
-      tma_load_4d(smem_u32(st + kTileBytes), &v_map, &sm.full[s], 0, 0, w.kvh, (int)pid);
-#endif
-      bulk_load(smem_u32(st + 2 * kTileBytes), p.k_sf + pid * p.k_sf_pitch + (int64_t)w.kvh * kSfBlockBytes,
-                kSfBlockBytes, &sm.full[s]);
-      bulk_load(smem_u32(st + 2 * kTileBytes + kSfBlockBytes),
-                p.v_sf + pid * p.v_sf_pitch + (int64_t)w.kvh * kSfBlockBytes, kSfBlockBytes, &sm.full[s]);
+      mbar_expect_tx(bar, kSlotBytes);
+      if (is_k) {
+        tma_load_4d(smem_u32(st), &k_map, bar, 0, w.kvh, 0, (int)pid);
+        bulk_load(smem_u32(st + kTileBytes), p.k_sf + pid * p.k_sf_pitch + (int64_t)w.kvh * kSfBlockBytes,
+                  kSfBlockBytes, bar);
+      } else {
+        tma_load_4d(smem_u32(st), &v_map, bar, 0, 0, w.kvh, (int)pid);
+        bulk_load(smem_u32(st + kTileBytes), p.v_sf + pid * p.v_sf_pitch + (int64_t)w.kvh * kSfBlockBytes,
+                  kSfBlockBytes, bar);
+      }
     } else {
-      // a page id outside the cache is never turned into an address: the stage gets zero
-      // scales (so both products are zero) and the score threads mask its scores
-      for (int j = 0; j < 2 * kSfBlockBytes / 16; ++j)
-        reinterpret_cast<uint4*>(st + 2 * kTileBytes)[j] = make_uint4(0, 0, 0, 0);
+      // a page id outside the cache is never turned into an address: the slot gets zero
+      // scales (so its product is zero) and the score threads mask its scores
+      for (int j = 0; j < kSfBlockBytes / 16; ++j)
+        reinterpret_cast<uint4*>(st + kTileBytes)[j] = make_uint4(0, 0, 0, 0);
       fence_proxy_async();
-      mbar_arrive(&sm.full[s]);
+      mbar_arrive(bar);
     }
   };
-  // ids: lane l of the producer warp holds the page id of walk step 32c + l of the current chunk c
+  // ids: lane l of a producer warp holds the page id of walk step 32c + l of the current chunk c
   int ids = -1, issued = 0;
-  if (warp == kProducerWarp) {
+  if (is_producer) {
+    const int slots = is_k_producer ? kKS : kVS;
     // chunk 0 out of the columns fetched ahead; every lane executes the same four shuffles
     const int idx0 = w.last_page - 1 - lane;  // pages are walked from the last to the first
     const bool live = idx0 >= w.first_page;
@@ -408,38 +431,31 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     }
     if (live && idx0 >= 128) v = p.page_table[(int64_t)w.row * p.page_table_row_stride + idx0];
     ids = v;
-    const int first = n_pages < kStages ? n_pages : kStages;
+    const int first = n_pages < slots ? n_pages : slots;
     for (int i = 0; i < first; ++i) {
       int64_t pid = __shfl_sync(0xffffffffu, ids, i);
       if (pid < 0 || pid >= p.num_pages) {
-        if (lane == 0) set_status(p.status, NVFP4_STATUS_BAD_PAGE_ID);
+        if (lane == 0 && is_k_producer) set_status(p.status, NVFP4_STATUS_BAD_PAGE_ID);
         pid = -1;
       }
-      if (lane == 0) { TRACE(1, i, 0); TRACE(1, i, 1); issue_page(i, pid); TRACE(1, i, 2); }
+      if (lane == 0) {
+        if (is_k_producer) { TRACE(1, i, 0); TRACE(1, i, 1); }
+        issue_slot(is_k_producer, i, pid);
+        if (is_k_producer) TRACE(1, i, 2);
+      }
     }
     issued = first;
   }
   if (tid == 0) TRACE(1, 39, 1);
   uint32_t tmem = 0;
-  if (warp != kProducerWarp) {
+  if (!is_producer) {
     tc_fence_before();
-    asm volatile("bar.sync 4, %0;" ::"n"(352) : "memory");
+    asm volatile("bar.sync 4, %0;" ::"n"(kThreads) : "memory");
     tc_fence_after();
     tmem = sm.tmem_base;
   }
   if (tid == 0) TRACE(1, 39, 2);
 
-#ifdef NVFP4_LOADONLY
-  // developer experiment: stream the pages through shared memory and do nothing with them
-  if (warp == kQkWarp && lane == 0 && !(NVFP4_LO & 2)) {
-    for (int i = 0; i < n_pages; ++i) {
-      const int s = i % kStages;
-      if (!mbar_wait(&sm.full[s], (i / kStages) & 1, sm, p.status)) break;
-      mbar_arrive(&sm.empty[s]);
-    }
-  }
-  if (warp < 4 || (warp >= 4 && warp < 8) || warp == kQkWarp || warp == kPvWarp) goto teardown;
-#endif
   if (warp < 4) {
     // =====================  score threads  =====================
     // Pages are handed over in pairs.  While a pair's scores are processed, warp w owns query
@@ -530,8 +546,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         tmem_ld16(tmem + lane_off + kColS + set * 16, r);
         tc_fence_before();
         mbar_arrive(&sm.s_free[set]);
-        const bool ok0 = sm.page_ok[i0 % kStages] != 0;
-        const bool ok1 = two && sm.page_ok[(i0 + 1) % kStages] != 0;
+        const bool ok0 = sm.page_ok[i0 % kKS] != 0;
+        const bool ok1 = two && sm.page_ok[(i0 + 1) % kKS] != 0;
 #pragma unroll
         for (int q = 0; q < G; ++q) {
           sm.z[set][0][q * kPage + tid] = ok0 ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY;
@@ -633,40 +649,34 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
     }
     if (t == 0) TRACE(1, 39, 4);
-  } else if (warp == kProducerWarp) {
-    // =====================  producer  =====================
-    bool alive = true;
-    for (int i = issued; i < n_pages && alive; ++i) {
-      if ((i & 31) == 0) {
-        const int idx = w.last_page - 1 - (i + lane);
-        ids = idx >= w.first_page ? p.page_table[(int64_t)w.row * p.page_table_row_stride + idx] : -1;
-      }
-      int64_t pid = __shfl_sync(0xffffffffu, ids, i & 31);
-      if (pid < 0 || pid >= p.num_pages) {
-        if (lane == 0) set_status(p.status, NVFP4_STATUS_BAD_PAGE_ID);
-        pid = -1;
-      }
-      if (lane == 0) {
-        const int s = i % kStages;
-        TRACE(1, i, 0);
-#if NVFP4_LO & 2
-        alive = mbar_wait(&sm.full[s], ((i / kStages) & 1) ^ 1, sm, p.status);
-#else
-        alive = mbar_wait(&sm.empty[s], ((i / kStages) & 1) ^ 1, sm, p.status);
-#endif
-        TRACE(1, i, 1);
-        if (alive) {
-          issue_page(s, pid);
-          TRACE(1, i, 2);
+  } else if (is_producer) {
+    // =====================  producers (K ring: warp 8, V ring: warp 11)  =====================
+    // Issuing a tile load, a scale-block copy and their byte count costs one thread some 500
+    // cycles a page, close to the time a page may take overall.  kProducerLanes lanes therefore
+    // take consecutive pages and issue side by side; each reads its own page-table entries, one
+    // step ahead of their use.
+    if (lane < kProducerLanes) {
+      const int slots = is_k_producer ? kKS : kVS;
+      const int32_t* table = p.page_table + (int64_t)w.row * p.page_table_row_stride;
+      int i = issued + lane;
+      int64_t next = i < n_pages ? table[w.last_page - 1 - i] : -1;
+      for (; i < n_pages; i += kProducerLanes) {
+        int64_t pid = next;
+        if (i + kProducerLanes < n_pages) next = table[w.last_page - 1 - (i + kProducerLanes)];
+        if (pid < 0 || pid >= p.num_pages) {
+          if (is_k_producer) set_status(p.status, NVFP4_STATUS_BAD_PAGE_ID);
+          pid = -1;
         }
+        const int s = i % slots;
+        uint64_t* freed = is_k_producer ? &sm.k_empty[s] : &sm.v_empty[s];
+        if (is_k_producer && lane == 0) TRACE(1, i, 0);
+        if (!mbar_wait(freed, ((i / slots) & 1) ^ 1, sm, p.status)) break;
+        if (is_k_producer && lane == 0) TRACE(1, i, 1);
+        issue_slot(is_k_producer, s, pid);
+        if (is_k_producer && lane == 0) TRACE(1, i, 2);
       }
-      alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
     }
-#if NVFP4_LO & 2
-    if (lane == 0)
-      for (int i = (n_pages > kStages ? n_pages - kStages : 0); i < n_pages; ++i)
-        mbar_wait(&sm.full[i % kStages], (i / kStages) & 1, sm, p.status);
-#endif
+    __syncwarp();
   } else if (warp == kQkWarp) {
     // =====================  MMA issuer 1: S^T = K . Q^T  =====================
     // Issuing a tcgen05 instruction costs the issuing thread some 60 cycles and a barrier
@@ -685,18 +695,19 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         for (int u = 0; u < kBatch && alive; ++u) {
           const int i = kb * kBatch + u;
           if (i >= n_pages) break;
-          const int s = i % kStages;
-          alive = mbar_wait(&sm.full[s], (i / kStages) & 1, sm, p.status);
+          const int s = i % kKS;
+          alive = mbar_wait(&sm.k_full[s], (i / kKS) & 1, sm, p.status);
           if (!alive) break;
           TRACE(2, i, 0);
           tc_fence_after();
-          const uint32_t st = smem_u32(sm.stage[s]);
-          cp_sf(tmem + kColSfK, st + 2 * kTileBytes);
-          cp_sf(tmem + kColSfK + 4, st + 2 * kTileBytes + 512);
+          const uint32_t st = smem_u32(sm.k_slot[s]);
+          cp_sf(tmem + kColSfK, st + kTileBytes);
+          cp_sf(tmem + kColSfK + 4, st + kTileBytes + 512);
           const uint64_t k_desc = desc_sw64(st);
           const uint32_t d = tmem + kColS + set * 16 + u * 8;
           mma_nvf4(d, k_desc, q_desc, tmem + kColSfK, tmem + kColSfQ, 0);
           mma_nvf4(d, k_desc + 2, q_desc + 2, tmem + kColSfK + 4, tmem + kColSfQ + 4, 1);
+          mma_commit(&sm.k_empty[s]);   // the K slot goes back once this page's product has retired
         }
         if (alive) mma_commit(&sm.s_full[set]);
         TRACE(2, kb * kBatch, 1);
@@ -706,15 +717,28 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       mbar_wait(&sm.drain[0], 0, sm, p.status);
     }
     __syncwarp();
-  } else {
+  } else if (warp == kPvWarp) {
     // =====================  MMA issuer 2: O^T = V^T . P^T  =====================
     if (lane == 0 && n_pages > 0) {
       bool alive = true;
       for (int kb = 0; kb < n_batches && alive; ++kb) {
         const int set = kb & 1;
-        // p_full implies that S^T of the pair was read, hence that K.Q^T of both pages and
-        // their scale copies have retired: the commits below may hand the stages back whole
-        alive = mbar_wait(&sm.p_full[set], (kb >> 1) & 1, sm, p.status) &&
+        // The V slots of a pair land long before its probabilities are ready: their scale
+        // blocks go to tensor memory now (columns of their own per page of the pair), which
+        // keeps four copies off the path between P being ready and O^T being done.
+        for (int u = 0; u < kBatch && alive; ++u) {
+          const int j = kb * kBatch + u;
+          if (j >= n_pages) break;
+          const int s = j % kVS;
+          alive = mbar_wait(&sm.v_full[s], (j / kVS) & 1, sm, p.status);
+          if (!alive) break;
+          tc_fence_after();
+          const uint32_t st = smem_u32(sm.v_slot[s]);
+          const uint32_t c = tmem + kColSfV + (set * kBatch + u) * 8;
+          cp_sf(c, st + kTileBytes);
+          cp_sf(c + 4, st + kTileBytes + 512);
+        }
+        alive = alive && mbar_wait(&sm.p_full[set], (kb >> 1) & 1, sm, p.status) &&
                 mbar_wait(&sm.o_free[set], ((kb >> 1) & 1) ^ 1, sm, p.status);
         if (!alive) break;
         TRACE(2, kb * kBatch, 2);
@@ -722,18 +746,16 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         for (int u = 0; u < kBatch; ++u) {
           const int j = kb * kBatch + u;
           if (j >= n_pages) break;
-          const int s = j % kStages;
-          const uint32_t st = smem_u32(sm.stage[s]);
-          cp_sf(tmem + kColSfV, st + 2 * kTileBytes + kSfBlockBytes);
-          cp_sf(tmem + kColSfV + 4, st + 2 * kTileBytes + kSfBlockBytes + 512);
+          const int s = j % kVS;
+          const uint32_t c = tmem + kColSfV + (set * kBatch + u) * 8;
           cp_sf(tmem + kColSfP, smem_u32(sm.p_sf[set][u]));
           cp_sf(tmem + kColSfP + 4, smem_u32(sm.p_sf[set][u] + 512));
-          const uint64_t v_desc = desc_sw64(st + kTileBytes);
+          const uint64_t v_desc = desc_sw64(smem_u32(sm.v_slot[s]));
           const uint64_t p_desc = desc_sw64(smem_u32(sm.p_tile[set][u]));
           const uint32_t d = tmem + kColO + set * 16 + u * 8;
-          mma_nvf4(d, v_desc, p_desc, tmem + kColSfV, tmem + kColSfP, 0);
-          mma_nvf4(d, v_desc + 2, p_desc + 2, tmem + kColSfV + 4, tmem + kColSfP + 4, 1);
-          mma_commit(&sm.empty[s]);
+          mma_nvf4(d, v_desc, p_desc, c, tmem + kColSfP, 0);
+          mma_nvf4(d, v_desc + 2, p_desc + 2, c + 4, tmem + kColSfP + 4, 1);
+          mma_commit(&sm.v_empty[s]);   // the V slot goes back once this page's product has retired
         }
         mma_commit(&sm.o_full[set]);
         TRACE(2, kb * kBatch, 3);
@@ -744,17 +766,16 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     __syncwarp();
   }
 
-#ifdef NVFP4_LOADONLY
-teardown:
-#endif
   // ---- teardown ----
   tc_fence_before();
   __syncthreads();
-  if (warp == kProducerWarp && lane == 0 && sm.abort_flag) {
+  if (is_producer && lane == 0 && sm.abort_flag) {
     // copies still in flight must land before the CTA's shared memory is handed on
-    for (int s = 0; s < kStages; ++s) {
+    const int slots = is_k_producer ? kKS : kVS;
+    for (int s = 0; s < slots; ++s) {
+      uint64_t* bar = is_k_producer ? &sm.k_full[s] : &sm.v_full[s];
       const unsigned long long t0 = global_ns();
-      while (!mbar_try(&sm.full[s], 0) && !mbar_try(&sm.full[s], 1) && global_ns() - t0 < 200000000ull) {}
+      while (!mbar_try(bar, 0) && !mbar_try(bar, 1) && global_ns() - t0 < 200000000ull) {}
     }
   }
   __syncthreads();
@@ -765,7 +786,7 @@ teardown:
     if (cta < 512) g_trace[1024 + cta * 4 + 1] = global_ns();
   }
 #endif
-  if (warp == kQkWarp && !(NVFP4_LO & 1)) {
+  if (warp == kQkWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
                  : "memory");
