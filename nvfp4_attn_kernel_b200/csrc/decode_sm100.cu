@@ -52,13 +52,8 @@ __device__ unsigned long long* g_trace = nullptr;
 
 // Ring depths: as many 9 KB slots as two resident CTAs per SM leave room for.  V slots are
 // held about two pages longer than K slots, so the V ring is that much deeper.
-#ifdef NVFP4_KS
-template <int G> struct KSlots { static constexpr int value = NVFP4_KS; };
-template <int G> struct VSlots { static constexpr int value = NVFP4_VS; };
-#else
 template <int G> struct KSlots { static constexpr int value = G <= 4 ? 4 : 3; };
 template <int G> struct VSlots { static constexpr int value = G <= 4 ? 6 : 5; };
-#endif
 constexpr int kBatch = 2;                                         // pages handled per hand-over
 constexpr int kTileBytes = 8192;                                  // 128 rows x 64 B
 constexpr int kSlotBytes = kTileBytes + kSfBlockBytes;            // a tile and its scale block
@@ -88,7 +83,7 @@ struct __align__(1024) Smem {
   __align__(16) float z[2][kBatch][G * kPage];  // scaled scores, [set][page][q][kv position]
   float resc[8][8];                             // ring of per-page rescale factors, [page & 7][q]
   float red_io[4 * 8];                          // reductions of the tail block and the epilogue
-  volatile int page_ok[kKS];                    // 0: the slot stands for a page id that was refused
+  volatile int page_ok[32];                     // [walk step & 31] 0: the page id was refused
   __align__(8) uint64_t k_full[kKS];
   uint64_t k_empty[kKS], v_full[kVS], v_empty[kVS];
   uint64_t s_full[2], s_free[2], p_full[2], o_full[2], o_free[2];
@@ -230,10 +225,7 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "memory");
 }
 
-#ifndef NVFP4_PLANES
-#define NVFP4_PLANES 2
-#endif
-constexpr int kProducerLanes = NVFP4_PLANES;   // lanes of a producer warp that issue loads
+constexpr int kProducerLanes = 1;   // lanes of a producer warp that issue loads (more measured no faster)
 constexpr int kKProducerWarp = 8;
 constexpr int kQkWarp = 9;   // also owns the tensor-memory allocation
 constexpr int kPvWarp = 10;
@@ -391,10 +383,10 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   const int n_batches = (n_pages + kBatch - 1) / kBatch;
 
   // one slot of a ring: the K (or V) tile of a page and its scale block, or a masked stand-in
-  auto issue_slot = [&](bool is_k, int s, int64_t pid) {
+  auto issue_slot = [&](bool is_k, int s, int step, int64_t pid) {
     uint8_t* st = is_k ? sm.k_slot[s] : sm.v_slot[s];
     uint64_t* bar = is_k ? &sm.k_full[s] : &sm.v_full[s];
-    if (is_k) sm.page_ok[s] = pid >= 0 ? 1 : 0;
+    if (is_k) sm.page_ok[step & 31] = pid >= 0 ? 1 : 0;   // by walk step: a K slot is reused before its scores are read
     if (pid >= 0) {
       mbar_expect_tx(bar, kSlotBytes);
       if (is_k) {
@@ -440,7 +432,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
       if (lane == 0) {
         if (is_k_producer) { TRACE(1, i, 0); TRACE(1, i, 1); }
-        issue_slot(is_k_producer, i, pid);
+        issue_slot(is_k_producer, i, i, pid);
         if (is_k_producer) TRACE(1, i, 2);
       }
     }
@@ -546,8 +538,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         tmem_ld16(tmem + lane_off + kColS + set * 16, r);
         tc_fence_before();
         mbar_arrive(&sm.s_free[set]);
-        const bool ok0 = sm.page_ok[i0 % kKS] != 0;
-        const bool ok1 = two && sm.page_ok[(i0 + 1) % kKS] != 0;
+        const bool ok0 = sm.page_ok[i0 & 31] != 0;
+        const bool ok1 = two && sm.page_ok[(i0 + 1) & 31] != 0;
 #pragma unroll
         for (int q = 0; q < G; ++q) {
           sm.z[set][0][q * kPage + tid] = ok0 ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY;
@@ -651,10 +643,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     if (t == 0) TRACE(1, 39, 4);
   } else if (is_producer) {
     // =====================  producers (K ring: warp 8, V ring: warp 11)  =====================
-    // Issuing a tile load, a scale-block copy and their byte count costs one thread some 500
-    // cycles a page, close to the time a page may take overall.  kProducerLanes lanes therefore
-    // take consecutive pages and issue side by side; each reads its own page-table entries, one
-    // step ahead of their use.
+    // An issuing lane takes every kProducerLanes-th page and reads its own page-table entries,
+    // one step ahead of their use.
     if (lane < kProducerLanes) {
       const int slots = is_k_producer ? kKS : kVS;
       const int32_t* table = p.page_table + (int64_t)w.row * p.page_table_row_stride;
@@ -672,7 +662,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         if (is_k_producer && lane == 0) TRACE(1, i, 0);
         if (!mbar_wait(freed, ((i / slots) & 1) ^ 1, sm, p.status)) break;
         if (is_k_producer && lane == 0) TRACE(1, i, 1);
-        issue_slot(is_k_producer, s, pid);
+        issue_slot(is_k_producer, s, i, pid);
         if (is_k_producer && lane == 0) TRACE(1, i, 2);
       }
     }

@@ -313,3 +313,44 @@ def test_in_kernel_query_quantisation_is_bit_identical(cuda_device, impl, heads)
             _kernel.FUSE_QUERY_QUANT = True
         assert torch.equal(fused, two_launch)
         assert torch.equal(fused_dense, two_launch)
+
+
+def test_refused_page_ids_are_masked_and_reported(cuda_device, impl):
+    """A page id outside the cache (possible only with ``trusted_metadata``) is never turned
+    into an address: the page contributes nothing, the rest of the row is exact, and the device
+    status word reports it.  Rows are long enough for every ring slot to be reused."""
+    import nvfp4_attn_kernel_b200._lib as L
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode
+
+    case = inputs.attention_case(63, 3, 8, 2, (12 * 128, 9 * 128 + 40, 5 * 128), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    table = case["page_table"].copy()
+    pages = prob.k_fp4.shape[0]
+    bad = {0: [3, 4, 10], 1: [0, 8], 2: [2]}           # logical pages whose ids are corrupted
+    for row, cols in bad.items():
+        for n, col in enumerate(cols):
+            table[row, col] = pages + 7 if n % 2 == 0 else -3
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    got = _decode.decode_fp4(
+        query_fp4=None, query_scales=None, query_padded_bf16=None, query_bf16=prob.q,
+        key_pages_fp4=prob.k_fp4, key_scales=prob.k_sf, value_pages_fp4=prob.v_fp4,
+        value_scales=prob.v_sf, fp4_page_table=torch.from_numpy(table).to(cuda_device),
+        seqused_fp4=prob.seqused_fp4, residual_key_pages_bf16=prob.k_pages,
+        residual_value_pages_bf16=prob.v_pages, residual_page_ids=prob.residual_page_ids,
+        seqused_residual=prob.seqused_residual, softmax_scale=prob.softmax_scale,
+        trusted_metadata=True, status=status)
+    assert int(status.item()) & L.STATUS_BAD_PAGE_ID
+    # the oracle sees the same rows with the corrupted pages taken out of the walk
+    clean = dict(case)
+    clean["page_table"] = case["page_table"].copy()
+    clean["seqused_fp4"] = case["seqused_fp4"].copy()
+    for row, cols in bad.items():
+        n = int(case["seqused_fp4"][row]) // 128
+        keep = [c for c in range(n) if c not in cols]
+        clean["page_table"][row, :len(keep)] = case["page_table"][row, keep]
+        clean["seqused_fp4"][row] = len(keep) * 128
+    prob.case = clean
+    want = prob.oracle_from_bytes()
+    got = to_np(got)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= TOL, np.abs(got - want).max()
