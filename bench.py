@@ -32,6 +32,9 @@ PAGES_PER_ROW = CTX // PAGE
 POOL_PAGES = ROWS * PAGES_PER_ROW          # 1024 pages = 151 MB of NVFP4 K+V per pool
 NUM_POOLS = 2                              # alternate so that L2 (126 MB) cannot hold a step's KV
 KV_BYTES = ROWS * CTX * HKV * 144          # algorithmic bytes of one step (144 B per token-head)
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch of the default workload, from
+# the capture summarised in profiles/decode_sm100_kernel__batch32x4096__ncu_full.md
+NCU_TRAFFIC_BYTES = 151_337_984 + 6_474_496
 METRIC = "decode_attn_tokens_per_s"
 UNIT = "tokens/s"
 WORKLOAD = ("uniform batch decode: 32 seq x 4096 ctx, Hq32/Hkv8/D128, page 128, "
@@ -329,6 +332,31 @@ def run_gpu(args) -> None:
     clocks = sampler.stop() if rank == 0 else None
     kernel_s = ms_k / done_k * 1e-3
 
+    # the floor on this GPU: a launch that only reads the step's bytes, same pools, same timing
+    def read_floor(steps, warmup):
+        sink = torch.zeros(1, dtype=torch.int32, device=device)
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(NUM_POOLS):
+                cache = pools[i]["cache"]
+                L.check(lib.nvfp4_probe_hbm_read(cache.data_ptr(), cache.numel(), sink.data_ptr(),
+                                                 torch.cuda.current_stream().cuda_stream))
+        reps = max(1, steps // NUM_POOLS)
+        for _ in range(max(1, warmup // NUM_POOLS)):
+            graph.replay()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(reps):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / (reps * NUM_POOLS) * 1e-3
+
+    floor_s = read_floor(min(args.steps, 400), args.warmup)
+
     # end to end through the public operator with host buffers
     q_host = q.cpu().pin_memory()
     out_host = torch.empty_like(out, device="cpu").pin_memory()
@@ -397,7 +425,11 @@ def run_gpu(args) -> None:
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
                          "peak_source": "measured" if peaks else "fallback",
-                         "traffic": args.ncu_traffic},
+                         "traffic": args.ncu_traffic if args.ncu_traffic is not None else (
+                             NCU_TRAFFIC_BYTES if (CTX == 4096 and splits == 1 and args.decode_impl != "generic")
+                             else None),
+                         "read_only_launch_us": floor_s * 1e6,
+                         "kernel_over_read_only_launch": kernel_s / floor_s},
             "cpu_baseline": cpu,
             "e2e": {"value": world * ROWS * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,

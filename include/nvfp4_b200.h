@@ -254,6 +254,16 @@ int nvfp4_work_table(const int32_t* query_start_loc, const int32_t* seqused_fp4,
                      int32_t* destination_pages, int num_reqs, int columns_per_row, void* stream);
 
 /*
+ * Measurement aid, no counterpart in the reference project: one launch that reads
+ * [ptr, ptr + bytes) once with plain 16-byte loads from every SM and discards the data.
+ * Its duration over the page pools of a decode step is the floor for any launch that has to
+ * touch those bytes on this GPU; bench.py reports it beside the decode kernel's duration.
+ * sink: nullable device word (written only in the practically impossible case that the
+ * checksum of the data equals a constant; it keeps the loads alive).
+ */
+int nvfp4_probe_hbm_read(const void* ptr, size_t bytes, uint32_t* sink, void* stream);
+
+/*
  * Split-KV decode for callers that cannot allocate.  No counterpart in the reference project
  * (its split path allocates and fills its partial buffers on every call,
  * src/nvfp4_decode_kernel/_decode.py:1051-1065).

@@ -364,6 +364,13 @@ int nvfp4_control_step(const int32_t* block_table, int64_t block_table_stride, i
   return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "control_step launch");
 }
 
+int nvfp4_probe_hbm_read(const void* ptr, size_t bytes, uint32_t* sink, void* stream) {
+  if (!ptr && bytes) return fail(NVFP4_ERR_INVALID, "probe_hbm_read: null range");
+  if (!aligned16(ptr)) return fail(NVFP4_ERR_INVALID, "probe_hbm_read: the range must be 16-byte aligned");
+  cudaError_t e = nvfp4::launch_read_probe(ptr, bytes, sink, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "probe_hbm_read launch");
+}
+
 int nvfp4_work_table(const int32_t* query_start_loc, const int32_t* seqused_fp4, const int32_t* row_to_slot,
                      const int32_t* block_table, int64_t block_table_stride, int32_t* source_tokens,
                      int32_t* destination_pages, int num_reqs, int columns_per_row, void* stream) {
