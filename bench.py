@@ -143,7 +143,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -480,20 +480,24 @@ def run_long_context(args) -> None:
     seq = torch.full((rows,), local_pages * PAGE, dtype=torch.int32, device=device)
     q_fp4_s = torch.zeros(rows, 1, HQ, 64, dtype=torch.uint8, device=device)
     q_sf_s = torch.zeros(rows, 1, HQ, 2, 32, 4, 4, dtype=torch.uint8, device=device)
-    splits = args.num_splits if args.num_splits > 1 else split_k_heuristic(rows, HKV, local_pages, sms=148)
+    # the kernel keeps two CTAs on an SM, so there are twice as many CTA slots as SMs
+    slots = 2 * torch.cuda.get_device_properties(device).multi_processor_count
+    splits = args.num_splits if args.num_splits > 1 else split_k_heuristic(rows, HKV, local_pages, sms=slots)
     grp = sharding.PageRangeGroup(dist.group.WORLD, rows, HQ, device, args.exchange) if world > 1 else None
 
     def step(i):
         pool = pools[i % num_pools]
-        q_fp4, q_sf = _quantize.quantize_query(q, heads_kv=HKV, query_fp4_scratch=q_fp4_s,
-                                               query_scales_scratch=q_sf_s)
-        common = dict(query_fp4=q_fp4, query_scales=q_sf, query_padded_bf16=None,
+        common = dict(query_fp4=None, query_scales=None, query_padded_bf16=None, query_bf16=q,
                       key_pages_fp4=pool["k"], key_scales=pool["ksf"], value_pages_fp4=pool["v"],
                       value_scales=pool["vsf"], fp4_page_table=pool["table"], seqused_fp4=seq,
                       softmax_scale=D ** -0.5, trusted_metadata=True)
         if grp is None:
             _decode.decode_fp4_split(**{k: v for k, v in common.items() if k != "query_padded_bf16"},
                                      num_splits=splits, out=out)
+        elif splits > 1:
+            _decode.decode_fp4(**common, num_splits=splits, _partials=grp.local_split_buffers(splits))
+            grp.fold_local_splits(splits)
+            grp.merge(out)
         else:
             _decode.decode_fp4(**common, _partials=grp.partial_buffers())
             grp.merge(out)
@@ -561,17 +565,18 @@ def run_long_context(args) -> None:
             "config": {
                 "workload": "long-context split-KV: 4 seq x 32768 ctx, Hq32/Hkv8/D128, KV pages of every "
                             "sequence partitioned by page range over the GPUs, partial (O, LSE) merged over NVLink",
-                "exchange": args.exchange if world > 1 else f"one GPU, num_splits={splits}",
+                "exchange": (f"{args.exchange}, {splits} local splits per GPU" if world > 1
+                             else f"one GPU, num_splits={splits}"),
                 "l2": f"{num_pools} rotating page pools per GPU, {per_pool / 1e6:.0f} MB each",
                 "timing": ("CUDA-graph replay" if use_graph else "plain launches")
-                          + " (Q quantise + decode + merge per step), CUDA events, max over ranks",
+                          + " (decode with the query quantised inside + merge(s) per step), CUDA events, max over ranks",
             },
             "hbm_gbs_per_gpu": per_gpu,
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                          "frac": per_gpu / peak, "peak_source": "measured" if peaks else "fallback",
                          "traffic": None},
             "cpu_baseline": None, "e2e": None,
-            "gpu_launches": done * (3 if world > 1 else 3),
+            "gpu_launches": done * ((2 if splits > 1 else 1) + (1 if world > 1 else 0)),
             "clocks": clocks, "device_status_word": status,
         }), flush=True)
     if world > 1:

@@ -116,6 +116,30 @@ class PageRangeGroup:
             self._buf = torch.zeros(per_copy, dtype=torch.float32, device=device)
             self._gathered = torch.empty(self.world * per_copy, dtype=torch.float32, device=device)
 
+    def local_split_buffers(self, splits: int):
+        """fp32 scratch for ``splits`` local partials of a rank's own page range (allocated once
+        per split count): ``([S, rows, 1, Hq, 128], [S, rows, Hq, 1])``."""
+        cache = self.__dict__.setdefault("_local", {})
+        if splits not in cache:
+            cache[splits] = (
+                torch.empty(splits, self.rows, 1, self.heads_q, HEAD_DIM, dtype=torch.float32,
+                            device=self.device),
+                torch.empty(splits, self.rows, self.heads_q, 1, dtype=torch.float32,
+                            device=self.device),
+            )
+        return cache[splits]
+
+    def fold_local_splits(self, splits: int) -> None:
+        """Merge the local partials by LSE weight into this rank's partial for the NEXT
+        ``merge`` call (normalised fp32 O and its LSE: the same form, one level up)."""
+        o_loc, lse_loc = self.local_split_buffers(splits)
+        o, lse = self.partial_buffers()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.load().nvfp4_lse_merge(
+                o_loc.data_ptr(), o_loc.stride(0), lse_loc.data_ptr(), lse_loc.stride(0), splits,
+                self.rows, self.heads_q, o.data_ptr(), 1, None, lse.data_ptr(),
+                torch.cuda.current_stream(self.device).cuda_stream))
+
     def partial_buffers(self):
         """(o_partial [1, rows, 1, Hq, 128], lse_partial [1, rows, Hq, 1]) for the NEXT merge call."""
         copy = (self.epoch + 1) & 1 if self.exchange == "peer" else 0
@@ -159,28 +183,30 @@ def decode_page_range(ranges: PageRangeGroup, query: torch.Tensor, key_pages_fp4
                       local_seqused_fp4: torch.Tensor, *, out: torch.Tensor, softmax_scale=None,
                       residual_key_pages_bf16=None, residual_value_pages_bf16=None,
                       residual_page_ids=None, seqused_residual=None,
-                      trusted_metadata: bool = True) -> torch.Tensor:
+                      trusted_metadata: bool = True, local_splits: int = 1) -> torch.Tensor:
     """One decode step under the page-range split: local partial decode, exchange, merge.
 
     Every rank passes the SAME query rows, its own pages and its local table
     (:func:`local_page_table`); the residual arguments are given on rank 0 only.
+    ``local_splits`` > 1 cuts a rank's own page range once more (few rows over a long context
+    would otherwise leave most SMs idle); the local partials are merged on the rank first.
     """
-    from .nvfp4_decode_kernel import _decode, _quantize
+    from .nvfp4_decode_kernel import _decode
 
     rows, heads_q, head_dim = query.shape
     heads_kv = key_pages_fp4.shape[2]
     if softmax_scale is None:
         softmax_scale = head_dim ** -0.5
-    padded = None
-    if residual_key_pages_bf16 is not None:
-        padded = torch.zeros(rows, PAGE, heads_q, head_dim, dtype=torch.bfloat16, device=query.device)
-    q_fp4, q_sf = _quantize.quantize_query(query, heads_kv=heads_kv, query_padded_out=padded)
+    partials = ranges.partial_buffers() if local_splits <= 1 else ranges.local_split_buffers(local_splits)
+    # the decode kernel quantises the BF16 query itself: one launch
     _decode.decode_fp4(
-        query_fp4=q_fp4, query_scales=q_sf, query_padded_bf16=padded,
+        query_fp4=None, query_scales=None, query_padded_bf16=None, query_bf16=query,
         key_pages_fp4=key_pages_fp4, key_scales=key_scales, value_pages_fp4=value_pages_fp4,
         value_scales=value_scales, fp4_page_table=local_table, seqused_fp4=local_seqused_fp4,
         residual_key_pages_bf16=residual_key_pages_bf16,
         residual_value_pages_bf16=residual_value_pages_bf16, residual_page_ids=residual_page_ids,
         seqused_residual=seqused_residual, softmax_scale=softmax_scale,
-        trusted_metadata=trusted_metadata, _partials=ranges.partial_buffers())
+        trusted_metadata=trusted_metadata, num_splits=max(1, local_splits), _partials=partials)
+    if local_splits > 1:
+        ranges.fold_local_splits(local_splits)
     return ranges.merge(out)

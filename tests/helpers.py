@@ -96,11 +96,13 @@ class Problem:
         args = (c["q"][sel], q_dq[sel], k_dq, v_dq, c["page_table"][sel], c["seqused_fp4"][sel])
         if splits == 1:
             return O.attention_from_dequantized(*args, **common)
+        # an int means the split rule itself; a list gives (page_range function, owns_tail) pieces
+        pieces = splits if isinstance(splits, list) else [
+            ((lambda n, s=s: O.split_page_range(n, s, splits)), s == 0) for s in range(splits)]
         parts, lses = [], []
-        for s in range(splits):
+        for page_range, owns_tail in pieces:
             o, lse = O.attention_from_dequantized(
-                *args, **common, page_range=lambda n, s=s: O.split_page_range(n, s, splits),
-                owns_tail=(s == 0), return_lse=True)
+                *args, **common, page_range=page_range, owns_tail=owns_tail, return_lse=True)
             parts.append(o)
             lses.append(lse)
         return O.lse_merge(np.stack(parts), np.stack(lses))

@@ -9,6 +9,7 @@ import pytest
 import torch
 
 import inputs
+import nvfp4_oracle as O
 from helpers import Problem, to_np
 
 pytestmark = pytest.mark.gpu
@@ -82,6 +83,22 @@ def _rank_main(rank, world, port, exchange, result):
         want = prob.decode(num_splits=world)
         same = all(torch.equal(o, want) for o in outs)
         err = float((outs[-1].float() - torch.from_numpy(prob.oracle_from_bytes(splits=world)).to(device)).abs().max())
+        # the same with every rank's own range cut once more and folded on the rank first
+        sharding.decode_page_range(grp, prob.q, prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, local, lseq,
+                                   out=out, softmax_scale=prob.softmax_scale, local_splits=2, **tail)
+        torch.cuda.synchronize()
+        assert int(grp.status.item()) == 0
+
+        def nested(r, s):
+            def page_range(n):
+                first, last = O.split_page_range(n, r, world)
+                lo, hi = O.split_page_range(last - first, s, 2)
+                return first + lo, first + hi
+            return page_range
+
+        pieces = [(nested(r, s), r == 0 and s == 0) for r in range(world) for s in range(2)]
+        want_nested = torch.from_numpy(prob.oracle_from_bytes(splits=pieces)).to(device)
+        err = max(err, float((out.float() - want_nested).abs().max()))
         gathered = [None] * world
         dist.all_gather_object(gathered, (same, err))
         if rank == 0:
