@@ -496,8 +496,11 @@ def run_long_context(args) -> None:
                                      num_splits=splits, out=out)
         elif splits > 1:
             _decode.decode_fp4(**common, num_splits=splits, _partials=grp.local_split_buffers(splits))
-            grp.fold_local_splits(splits)
-            grp.merge(out)
+            if args.exchange == "push":
+                grp.merge(out, splits)          # folds the local splits in the same launch
+            else:
+                grp.fold_local_splits(splits)
+                grp.merge(out)
         else:
             _decode.decode_fp4(**common, _partials=grp.partial_buffers())
             grp.merge(out)
@@ -513,7 +516,7 @@ def run_long_context(args) -> None:
         dist.barrier()
     # The NCCL exchange is timed with plain launches: a run that captured the all-gather into
     # the graph next to the hand-launched kernels did not finish on two GPUs.
-    use_graph = grp is None or args.exchange == "peer"
+    use_graph = grp is None or args.exchange != "nccl"
     if use_graph:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
@@ -576,7 +579,8 @@ def run_long_context(args) -> None:
                          "frac": per_gpu / peak, "peak_source": "measured" if peaks else "fallback",
                          "traffic": None},
             "cpu_baseline": None, "e2e": None,
-            "gpu_launches": done * ((2 if splits > 1 else 1) + (1 if world > 1 else 0)),
+            "gpu_launches": done * (2 if world == 1 or args.exchange == "push"
+                                    else (2 if splits > 1 else 1) + (2 if args.exchange == "nccl" else 1)),
             "clocks": clocks, "device_status_word": status,
         }), flush=True)
     if world > 1:
@@ -597,7 +601,7 @@ def main() -> None:
     ap.add_argument("--workload", default="batch", choices=["batch", "long-context"],
                     help="batch: the headline uniform batch (default); long-context: 4 x 32768 split "
                          "by page range over the GPUs")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"])
+    ap.add_argument("--exchange", default="push", choices=["push", "peer", "nccl"])
     ap.add_argument("--ncu-traffic", type=float, default=None,
                     help="dram bytes per decode launch from an ncu capture (reported as roofline.traffic)")
     args = ap.parse_args()

@@ -254,6 +254,28 @@ int nvfp4_work_table(const int32_t* query_start_loc, const int32_t* seqused_fp4,
                      int32_t* destination_pages, int num_reqs, int columns_per_row, void* stream);
 
 /*
+ * Cross-GPU page-range split, push form: ONE launch per rank after the decode.  No counterpart
+ * in the reference project (it has no multi-GPU code); the partial format and the merge are those
+ * of its split path (fp4_decode_kernel.py:5186-5196, split_k_combine.py:694-768).
+ * The CTA of (query head, row) folds this rank's local_splits partials
+ *   o_local   fp32 [S][rows][Hq][128] (split stride in elements), lse_local fp32 [S][rows][Hq],
+ * stores the result into its slot of every peer's inbox (remote stores only), announces it in the
+ * peer's flag array, waits (bounded, 1 s; NVFP4_STATUS_WAIT_TIMEOUT and out untouched on expiry)
+ * for the peers' pushes of the same (head, row), and merges in rank order out of its own inbox.
+ *   inbox_ptrs DEVICE array [world] of each rank's inbox as this process addresses it:
+ *              float [2][world][rows*Hq][132] (nvfp4_push_merge_inbox_floats), zero-filled once
+ *   flag_ptrs  DEVICE array [world] of each rank's flags: int32 [world][rows*Hq], zero-filled once
+ *   epoch      1, 2, 3, ... per call, the same on every rank; with epoch_state != NULL (two device
+ *              ints, zero-filled once) the kernel keeps the count itself, for CUDA-graph replay
+ * The ranks' kernels must run on different GPUs.
+ */
+int nvfp4_push_merge(const float* o_local, int64_t o_split_stride, const float* lse_local,
+                     int64_t lse_split_stride, int local_splits, float* const* inbox_ptrs,
+                     int32_t* const* flag_ptrs, int rank, int world, int epoch, int32_t* epoch_state,
+                     int rows, int heads_q, void* out, int out_is_f32, uint32_t* status, void* stream);
+size_t nvfp4_push_merge_inbox_floats(int world, int rows, int heads_q);
+
+/*
  * Measurement aid, no counterpart in the reference project: one launch that reads
  * [ptr, ptr + bytes) once with plain 16-byte loads from every SM and discards the data.
  * Its duration over the page pools of a decode step is the floor for any launch that has to

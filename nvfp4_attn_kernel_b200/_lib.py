@@ -35,6 +35,8 @@ EXPORTS = (
     "nvfp4_control_step",
     "nvfp4_work_table",
     "nvfp4_probe_hbm_read",
+    "nvfp4_push_merge",
+    "nvfp4_push_merge_inbox_floats",
     "nvfp4_decode_split_static",
     "nvfp4_static_workspace_bytes",
     "nvfp4_decode_split_static_error",
@@ -151,6 +153,11 @@ def _declare_peer(lib) -> None:
 def _declare_control(lib) -> None:
     lib.nvfp4_control_step.restype = c_int
     lib.nvfp4_control_step.argtypes = [c_void_p, c_int64, c_int] + [c_void_p] * 13 + [c_int, c_int, c_int, c_void_p]
+    lib.nvfp4_push_merge.restype = c_int
+    lib.nvfp4_push_merge.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int,
+                                     c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]
+    lib.nvfp4_push_merge_inbox_floats.restype = c_size_t
+    lib.nvfp4_push_merge_inbox_floats.argtypes = [c_int, c_int, c_int]
     lib.nvfp4_probe_hbm_read.restype = c_int
     lib.nvfp4_probe_hbm_read.argtypes = [c_void_p, c_size_t, c_void_p, c_void_p]
     lib.nvfp4_work_table.restype = c_int

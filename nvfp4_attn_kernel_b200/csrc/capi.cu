@@ -401,4 +401,26 @@ int nvfp4_peer_merge(const float* const* o_part_ptrs, const float* const* lse_pa
   return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "peer_merge launch");
 }
 
+int nvfp4_push_merge(const float* o_local, int64_t o_split_stride, const float* lse_local,
+                     int64_t lse_split_stride, int local_splits, float* const* inbox_ptrs,
+                     int32_t* const* flag_ptrs, int rank, int world, int epoch, int32_t* epoch_state,
+                     int rows, int heads_q, void* out, int out_is_f32, uint32_t* status, void* stream) {
+  if (world < 1 || world > 128 || rank < 0 || rank >= world)
+    return fail(NVFP4_ERR_INVALID, "push_merge: rank %d of %d is out of range (at most 128 ranks)", rank, world);
+  if (rows < 0 || heads_q < 1 || local_splits < 1) return fail(NVFP4_ERR_INVALID, "push_merge: bad extents");
+  if (rows == 0) return NVFP4_OK;
+  if (!o_local || !lse_local || !inbox_ptrs || !flag_ptrs || !out)
+    return fail(NVFP4_ERR_INVALID, "push_merge: null argument");
+  if (rows > 65535) return fail(NVFP4_ERR_INVALID, "push_merge: too many rows");
+  cudaError_t e = nvfp4::launch_push_merge(o_local, o_split_stride, lse_local, lse_split_stride, local_splits,
+                                           inbox_ptrs, flag_ptrs, rank, world, epoch, epoch_state, rows,
+                                           heads_q, out, out_is_f32, status, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "push_merge launch");
+}
+
+size_t nvfp4_push_merge_inbox_floats(int world, int rows, int heads_q) {
+  if (world < 1 || rows < 0 || heads_q < 1) return 0;
+  return (size_t)2 * world * rows * heads_q * 132;
+}
+
 }  // extern "C"

@@ -165,3 +165,137 @@ cudaError_t launch_peer_merge(const float* const* o_ptrs, const float* const* ls
 }
 
 }  // namespace nvfp4
+
+// ---------------------------------------------------------------------------
+// Push exchange for the KV page-range split, ONE launch per rank after the decode:
+// the CTA of (query head, row) folds this rank's local split partials, stores the result
+// into the matching slot of every peer's inbox (posted remote stores, nothing is loaded over
+// NVLink), announces it per (head, row), waits (bounded) for the peers' announcements of the
+// same (head, row) only, and merges out of its own memory.  CTAs of different (head, row) never
+// wait for one another, so a late rank delays only the pairs it has not pushed yet.
+//   inbox of a rank : float [2 copies][world sources][rows * heads_q][kInboxStride]
+//                     (128 channels of normalised O, then the LSE); copies alternate by epoch
+//   flags of a rank : int   [world sources][rows * heads_q], the epoch of the latest push
+// ---------------------------------------------------------------------------
+namespace nvfp4 {
+
+constexpr int kInboxStride = 132;
+
+__device__ __forceinline__ void st_relaxed_sys(float* p, float v) {
+  asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+
+template <bool kOutF32>
+__global__ void __launch_bounds__(128)
+push_merge_kernel(const float* __restrict__ o_local, int64_t o_split_stride,
+                  const float* __restrict__ lse_local, int64_t lse_split_stride, int local_splits,
+                  float* const* __restrict__ inbox_ptrs, int* const* __restrict__ flag_ptrs, int rank,
+                  int world, int epoch_arg, int* __restrict__ epoch_state, int rows, int heads_q,
+                  void* __restrict__ out, uint32_t* __restrict__ status) {
+  __shared__ int ready;
+  const int head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
+  const int64_t idx = (int64_t)row * heads_q + head;
+  const int64_t pairs = (int64_t)rows * heads_q;
+  // With a device-resident epoch (graph replay) every block reads it before any block can
+  // advance it: the block that finishes last does that.
+  const int epoch = epoch_state ? *reinterpret_cast<volatile int*>(epoch_state) + 1 : epoch_arg;
+  if (d == 0) ready = 1;
+
+  // fold this rank's local splits (index order, the arithmetic of lse_merge_kernel)
+  float mx = -INFINITY;
+  for (int s = 0; s < local_splits; ++s) mx = fmaxf(mx, lse_local[s * lse_split_stride + idx]);
+  float acc = 0.f, tot = 0.f;
+  if (mx != -INFINITY) {
+    for (int s = 0; s < local_splits; ++s) {
+      const float ls = lse_local[s * lse_split_stride + idx];
+      if (ls == -INFINITY) continue;
+      const float wgt = expf(ls - mx);
+      tot += wgt;
+      acc = fmaf(wgt, o_local[s * o_split_stride + idx * kHeadDim + d], acc);
+    }
+  }
+  const float my_o = tot > 0.f ? __fdiv_rn(acc, tot) : 0.f;
+  const float my_lse = tot > 0.f ? mx + logf(tot) : -INFINITY;
+
+  // push to every peer's inbox, then announce
+  const int64_t copy_elems = (int64_t)world * pairs * kInboxStride;
+  const int64_t slot = ((epoch & 1) * copy_elems) + ((int64_t)rank * pairs + idx) * kInboxStride;
+  for (int w = 0; w < world; ++w) {
+    if (w == rank) continue;
+    float* dst = inbox_ptrs[w] + slot;
+    st_relaxed_sys(dst + d, my_o);
+    if (d == 0) st_relaxed_sys(dst + kHeadDim, my_lse);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (d < world && d != rank) st_release_sys(flag_ptrs[d] + (int64_t)rank * pairs + idx, epoch);
+
+  // wait for the peers' pushes of this (head, row): thread w watches source w
+  if (d < world && d != rank) {
+    const int* flag = flag_ptrs[rank] + (int64_t)d * pairs + idx;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    // epochs only grow; a peer that is already a step ahead has certainly pushed this one
+    while (ld_acquire_sys(flag) - epoch < 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+      if (t - t0 > kPeerWaitNs) {
+        set_status(status, NVFP4_STATUS_WAIT_TIMEOUT);
+        ready = 0;
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  __syncthreads();
+  if (epoch_state && d == 0) {
+    const int blocks = gridDim.x * gridDim.y;
+    if (atomicAdd(epoch_state + 1, 1) == blocks - 1) {
+      epoch_state[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile int*>(epoch_state) = epoch;
+    }
+  }
+  if (!ready) return;  // the output is left untouched and the status word says why
+
+  // merge in source order (identical on every rank), own partial out of registers
+  const float* mine = inbox_ptrs[rank] + (epoch & 1) * copy_elems;
+  float gm = -INFINITY;
+  for (int s = 0; s < world; ++s)
+    gm = fmaxf(gm, s == rank ? my_lse : ld_relaxed_sys(mine + ((int64_t)s * pairs + idx) * kInboxStride + kHeadDim));
+  float a2 = 0.f, t2 = 0.f;
+  if (gm != -INFINITY) {
+    for (int s = 0; s < world; ++s) {
+      const float* src = mine + ((int64_t)s * pairs + idx) * kInboxStride;
+      const float ls = s == rank ? my_lse : ld_relaxed_sys(src + kHeadDim);
+      if (ls == -INFINITY) continue;
+      const float wgt = expf(ls - gm);
+      t2 += wgt;
+      a2 = fmaf(wgt, s == rank ? my_o : ld_relaxed_sys(src + d), a2);
+    }
+  }
+  const float val = t2 > 0.f ? __fdiv_rn(a2, t2) : 0.f;
+  const int64_t at = idx * kHeadDim + d;
+  if (kOutF32) static_cast<float*>(out)[at] = val;
+  else static_cast<uint16_t*>(out)[at] = __bfloat16_as_ushort(__float2bfloat16_rn(val));
+}
+
+cudaError_t launch_push_merge(const float* o_local, int64_t o_split_stride, const float* lse_local,
+                              int64_t lse_split_stride, int local_splits, float* const* inbox_ptrs,
+                              int* const* flag_ptrs, int rank, int world, int epoch, int* epoch_state,
+                              int rows, int heads_q, void* out, int out_is_f32, uint32_t* status,
+                              cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  dim3 grid(heads_q, rows);
+  if (out_is_f32)
+    push_merge_kernel<true><<<grid, 128, 0, stream>>>(o_local, o_split_stride, lse_local, lse_split_stride,
+                                                      local_splits, inbox_ptrs, flag_ptrs, rank, world, epoch,
+                                                      epoch_state, rows, heads_q, out, status);
+  else
+    push_merge_kernel<false><<<grid, 128, 0, stream>>>(o_local, o_split_stride, lse_local, lse_split_stride,
+                                                       local_splits, inbox_ptrs, flag_ptrs, rank, world, epoch,
+                                                       epoch_state, rows, heads_q, out, status);
+  return cudaGetLastError();
+}
+
+}  // namespace nvfp4

@@ -102,6 +102,12 @@ cudaError_t launch_peer_merge(const float* const* o_ptrs, const float* const* ls
                               int* epoch_state, int rows, int heads_q, void* out, int out_is_f32,
                               uint32_t* status, cudaStream_t stream);
 
+cudaError_t launch_push_merge(const float* o_local, int64_t o_split_stride, const float* lse_local,
+                              int64_t lse_split_stride, int local_splits, float* const* inbox_ptrs,
+                              int* const* flag_ptrs, int rank, int world, int epoch, int* epoch_state,
+                              int rows, int heads_q, void* out, int out_is_f32, uint32_t* status,
+                              cudaStream_t stream);
+
 // Reads [ptr, ptr + bytes) once with plain loads and discards it (bandwidth floor of a launch).
 cudaError_t launch_read_probe(const void* ptr, size_t bytes, unsigned* sink, cudaStream_t stream);
 

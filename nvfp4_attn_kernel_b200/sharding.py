@@ -8,9 +8,12 @@ Three ways, as the path allows:
   ``page_range(n, r, world)`` of every row and the BF16 tail goes with rank 0.
   Each rank runs the decode in partial mode on its own pages and the partials
   ``(normalised O fp32, natural-log LSE)`` are merged by LSE weight.
-  :class:`PageRangeGroup` does the exchange either with peer loads out of
-  symmetric memory (one launch per rank: announce, bounded wait, merge) or with
-  an NCCL all-gather followed by the local merge kernel.
+  :class:`PageRangeGroup` does the exchange in one of three ways: ``"push"`` (one
+  launch per rank that folds the rank's local splits, stores the result into every
+  peer's inbox in symmetric memory, and merges out of its own inbox once the peers'
+  stores for the same (head, row) have arrived), ``"peer"`` (announce, bounded wait,
+  merge with loads from the peers' buffers) or ``"nccl"`` (all-gather, then the local
+  merge kernel).
 
 The reference project has no multi-GPU code; the page-range rule and the partial
 format are those of its intra-GPU split path
@@ -69,17 +72,20 @@ def local_page_table(page_table: torch.Tensor, seqused_fp4: torch.Tensor, rank: 
 class PageRangeGroup:
     """Exchange + merge of per-rank partial results for the KV page-range split.
 
-    ``exchange="peer"``: partials live in symmetric memory that every rank of the group has
-    mapped; ``merge`` is ONE kernel launch per rank (``nvfp4_peer_merge``).  Two copies of the
-    partial buffer alternate per call so that a fast rank cannot overwrite what a slow rank is
-    still reading.  ``exchange="nccl"``: partials are all-gathered, then merged locally.
+    ``exchange="push"``: every rank owns an inbox in symmetric memory; ``merge`` is ONE kernel
+    launch per rank (``nvfp4_push_merge``) that also folds the rank's local splits, and nothing
+    is loaded over NVLink.  ``exchange="peer"``: partials live in symmetric memory that every
+    rank of the group has mapped; ``merge`` is one launch per rank (``nvfp4_peer_merge``) that
+    loads from the peers.  In both, two copies of the exchanged data alternate per call so that
+    a fast rank cannot overwrite what a slow rank is still reading.  ``exchange="nccl"``:
+    partials are all-gathered, then merged locally.
     """
 
     def __init__(self, group, rows: int, heads_q: int, device: torch.device, exchange: str = "peer"):
         import torch.distributed as dist
 
-        if exchange not in ("peer", "nccl"):
-            raise ValueError("exchange must be 'peer' or 'nccl'")
+        if exchange not in ("push", "peer", "nccl"):
+            raise ValueError("exchange must be 'push', 'peer' or 'nccl'")
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -90,7 +96,23 @@ class PageRangeGroup:
         self._o_elems = rows * heads_q * HEAD_DIM
         self._lse_elems = rows * heads_q
         per_copy = self._o_elems + self._lse_elems
-        if exchange == "peer":
+        if exchange == "push":
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+
+            inbox = int(_lib.load().nvfp4_push_merge_inbox_floats(self.world, rows, heads_q))
+            flag_words = self.world * rows * heads_q
+            self._buf = symm.empty(inbox + flag_words, dtype=torch.float32, device=device)
+            self._buf.zero_()
+            torch.cuda.synchronize(device)
+            self._hdl = symm.rendezvous(self._buf, group)
+            bases = [int(p) for p in self._hdl.buffer_ptrs]
+            self._inboxes = torch.tensor(bases, dtype=torch.int64, device=device)
+            self._flags = torch.tensor([b + 4 * inbox for b in bases], dtype=torch.int64, device=device)
+            # this rank's own partial never crosses NVLink: a plain local buffer
+            self._own = torch.zeros(per_copy, dtype=torch.float32, device=device)
+            dist.barrier(group)
+        elif exchange == "peer":
             # plain peer loads only; no switch-side (multi-destination) objects are needed or used
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             import torch.distributed._symmetric_memory as symm
@@ -145,12 +167,15 @@ class PageRangeGroup:
         copy = (self.epoch + 1) & 1 if self.exchange == "peer" else 0
         per_copy = self._o_elems + self._lse_elems
         base = copy * per_copy
-        o = self._buf[base:base + self._o_elems].view(1, self.rows, 1, self.heads_q, HEAD_DIM)
-        lse = self._buf[base + self._o_elems:base + per_copy].view(1, self.rows, self.heads_q, 1)
+        buf = self._own if self.exchange == "push" else self._buf
+        o = buf[base:base + self._o_elems].view(1, self.rows, 1, self.heads_q, HEAD_DIM)
+        lse = buf[base + self._o_elems:base + per_copy].view(1, self.rows, self.heads_q, 1)
         return o, lse
 
-    def merge(self, out: torch.Tensor) -> torch.Tensor:
-        """Merge every rank's partial (written into ``partial_buffers()``) into ``out``."""
+    def merge(self, out: torch.Tensor, local_splits: int = 1) -> torch.Tensor:
+        """Merge every rank's partial (written into ``partial_buffers()``) into ``out``.  With
+        ``exchange="push"`` and ``local_splits`` > 1 the rank's partials are taken from
+        ``local_split_buffers(local_splits)`` and folded inside the same launch."""
         if out.dtype not in (torch.bfloat16, torch.float32) or not out.is_contiguous() or \
                 tuple(out.shape) != (self.rows, self.heads_q, HEAD_DIM):
             raise ValueError("out must be contiguous BF16/FP32 with shape [rows, heads_q, 128]")
@@ -158,7 +183,16 @@ class PageRangeGroup:
         stream = torch.cuda.current_stream(self.device).cuda_stream
         f32 = 1 if out.dtype is torch.float32 else 0
         self.epoch += 1
-        if self.exchange == "peer":
+        if self.exchange == "push":
+            o_loc, lse_loc = (self.partial_buffers() if local_splits <= 1
+                              else self.local_split_buffers(local_splits))
+            with torch.cuda.device(self.device):
+                _lib.check(lib.nvfp4_push_merge(
+                    o_loc.data_ptr(), o_loc.stride(0), lse_loc.data_ptr(), lse_loc.stride(0),
+                    max(1, local_splits), self._inboxes.data_ptr(), self._flags.data_ptr(), self.rank,
+                    self.world, self.epoch, self._epoch_state.data_ptr(), self.rows, self.heads_q,
+                    out.data_ptr(), f32, self.status.data_ptr(), stream))
+        elif self.exchange == "peer":
             o_tab, lse_tab = self._ptr_tables[self.epoch & 1]
             with torch.cuda.device(self.device):
                 _lib.check(lib.nvfp4_peer_merge(
@@ -207,6 +241,8 @@ def decode_page_range(ranges: PageRangeGroup, query: torch.Tensor, key_pages_fp4
         residual_value_pages_bf16=residual_value_pages_bf16, residual_page_ids=residual_page_ids,
         seqused_residual=seqused_residual, softmax_scale=softmax_scale,
         trusted_metadata=trusted_metadata, num_splits=max(1, local_splits), _partials=partials)
+    if ranges.exchange == "push":
+        return ranges.merge(out, local_splits)   # folds the local splits in the same launch
     if local_splits > 1:
         ranges.fold_local_splits(local_splits)
     return ranges.merge(out)

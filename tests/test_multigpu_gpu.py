@@ -45,6 +45,61 @@ def test_peer_merge_wait_expires_with_a_status_and_leaves_out_untouched(cuda_dev
     assert int(status.item()) == 0 and (out == 0.0).all()
 
 
+def test_push_merge_wait_expires_then_completes(cuda_device):
+    """The push exchange on one GPU with a peer that never pushes: the wait of every (head, row)
+    gives up after its bound with a status, ``out`` stays untouched and this rank's own pushes and
+    announcements have landed in the (stand-in) peer's inbox.  After the peer's data and flags are
+    put there by hand the same call merges both partials."""
+    import nvfp4_attn_kernel_b200._lib as L
+    import nvfp4_oracle as O
+
+    lib = L.load()
+    rows, hq, world = 2, 8, 2
+    pairs = rows * hq
+    rng = np.random.default_rng(3)
+    inbox_floats = int(lib.nvfp4_push_merge_inbox_floats(world, rows, hq))
+    assert inbox_floats == 2 * world * pairs * 132
+    inbox = [torch.zeros(inbox_floats, dtype=torch.float32, device=cuda_device) for _ in range(world)]
+    flags = [torch.zeros(world * pairs, dtype=torch.int32, device=cuda_device) for _ in range(world)]
+    table = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=cuda_device)
+    inbox_tab, flag_tab = table(inbox), table(flags)
+    splits = 3
+    o_loc = torch.from_numpy(rng.standard_normal((splits, rows, hq, 128)).astype(np.float32)).to(cuda_device)
+    lse_loc = torch.from_numpy(rng.standard_normal((splits, rows, hq)).astype(np.float32)).to(cuda_device)
+    lse_loc[1, 0, 3] = float("-inf")
+    out = torch.full((rows, hq, 128), 3.0, dtype=torch.bfloat16, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        L.check(lib.nvfp4_push_merge(o_loc.data_ptr(), o_loc.stride(0), lse_loc.data_ptr(), lse_loc.stride(0),
+                                     splits, inbox_tab.data_ptr(), flag_tab.data_ptr(), 0, world, 1, None,
+                                     rows, hq, out.data_ptr(), 0, status.data_ptr(), stream))
+        torch.cuda.synchronize()
+
+    call()
+    assert int(status.item()) & L.STATUS_WAIT_TIMEOUT
+    assert (out == 3.0).all()
+    # rank 0's fold, as pushed into rank 1's inbox: copy 1 (epoch 1), source 0
+    mine_o, mine_lse = O.lse_merge(to_np(o_loc), to_np(lse_loc), return_lse=True)
+    slot = inbox[1].view(2, world, pairs, 132)[1, 0]
+    assert np.allclose(to_np(slot[:, :128]).reshape(rows, hq, 128), mine_o, atol=1e-5)
+    assert np.allclose(to_np(slot[:, 128]).reshape(rows, hq), mine_lse, atol=1e-5)
+    assert (flags[1][:pairs] == 1).all() and (flags[1][pairs:] == 0).all()
+    # now the peer's push arrives
+    peer_o = rng.standard_normal((rows, hq, 128)).astype(np.float32)
+    peer_lse = rng.standard_normal((rows, hq)).astype(np.float32)
+    mine = inbox[0].view(2, world, pairs, 132)
+    mine[1, 1, :, :128] = torch.from_numpy(peer_o.reshape(pairs, 128)).to(cuda_device)
+    mine[1, 1, :, 128] = torch.from_numpy(peer_lse.reshape(pairs)).to(cuda_device)
+    flags[0][pairs:] = 1
+    status.zero_()
+    call()
+    assert int(status.item()) == 0
+    want = O.lse_merge(np.stack([mine_o, peer_o]), np.stack([mine_lse, peer_lse]))
+    assert np.abs(to_np(out) - want).max() <= 1e-2   # bf16 output
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -108,7 +163,7 @@ def _rank_main(rank, world, port, exchange, result):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["peer", "nccl"])
+@pytest.mark.parametrize("exchange", ["push", "peer", "nccl"])
 def test_page_range_split_over_two_gpus(cuda_device, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
