@@ -483,7 +483,8 @@ def run_long_context(args) -> None:
     # the kernel keeps two CTAs on an SM, so there are twice as many CTA slots as SMs
     slots = 2 * torch.cuda.get_device_properties(device).multi_processor_count
     splits = args.num_splits if args.num_splits > 1 else split_k_heuristic(rows, HKV, local_pages, sms=slots)
-    grp = sharding.PageRangeGroup(dist.group.WORLD, rows, HQ, device, args.exchange) if world > 1 else None
+    grp = (sharding.PageRangeGroup(dist.group.WORLD, rows, HQ, device, args.exchange, heads_kv=HKV)
+           if world > 1 else None)
 
     def step(i):
         pool = pools[i % num_pools]
@@ -494,6 +495,10 @@ def run_long_context(args) -> None:
         if grp is None:
             _decode.decode_fp4_split(**{k: v for k, v in common.items() if k != "query_padded_bf16"},
                                      num_splits=splits, out=out)
+        elif args.exchange == "fused":
+            # decode, fold of the local splits, push, wait and merge: ONE launch
+            parts = grp.local_split_buffers(splits) if splits > 1 else grp.partial_buffers()
+            _decode.decode_fp4(**common, num_splits=splits, _partials=parts, _exchange=grp.exchange_args(out))
         elif splits > 1:
             _decode.decode_fp4(**common, num_splits=splits, _partials=grp.local_split_buffers(splits))
             if args.exchange == "push":
@@ -579,7 +584,8 @@ def run_long_context(args) -> None:
                          "frac": per_gpu / peak, "peak_source": "measured" if peaks else "fallback",
                          "traffic": None},
             "cpu_baseline": None, "e2e": None,
-            "gpu_launches": done * (2 if world == 1 or args.exchange == "push"
+            "gpu_launches": done * (1 if world > 1 and args.exchange == "fused"
+                                    else 2 if world == 1 or args.exchange == "push"
                                     else (2 if splits > 1 else 1) + (2 if args.exchange == "nccl" else 1)),
             "clocks": clocks, "device_status_word": status,
         }), flush=True)
@@ -601,7 +607,7 @@ def main() -> None:
     ap.add_argument("--workload", default="batch", choices=["batch", "long-context"],
                     help="batch: the headline uniform batch (default); long-context: 4 x 32768 split "
                          "by page range over the GPUs")
-    ap.add_argument("--exchange", default="push", choices=["push", "peer", "nccl"])
+    ap.add_argument("--exchange", default="fused", choices=["fused", "push", "peer", "nccl"])
     ap.add_argument("--ncu-traffic", type=float, default=None,
                     help="dram bytes per decode launch from an ncu capture (reported as roofline.traffic)")
     args = ap.parse_args()

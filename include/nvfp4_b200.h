@@ -276,6 +276,31 @@ int nvfp4_push_merge(const float* o_local, int64_t o_split_stride, const float* 
 size_t nvfp4_push_merge_inbox_floats(int world, int rows, int heads_q);
 
 /*
+ * Decode and cross-GPU page-range exchange in ONE launch per rank (tensor-core kernel only).
+ * No counterpart in the reference project.  The decode runs in partial mode with
+ * args->num_splits local splits (args->o_partial / lse_partial: this rank's scratch,
+ * [S][rows][Hq][128] and [S][rows][Hq]; args->out must be NULL).  The CTA that stores the last
+ * split partial of a (row, KV head) tile folds the tile's splits, pushes the result into every
+ * peer's inbox, announces it, waits (bounded, 1 s) for the peers' pushes of that tile and writes
+ * the merged rows to x->out: tiles that finish early are exchanged while others still stream.
+ * Inbox, flags and epoch_state are those of nvfp4_push_merge (the two entry points produce the
+ * same bits); tile_counters: device int32 [rows * heads_kv], zero-filled once.
+ * world * (heads_q / heads_kv) <= 128.  The ranks' kernels must run on different GPUs.
+ */
+typedef struct nvfp4_exchange_args {
+  float* const* inbox_ptrs;   /* DEVICE array [world] */
+  int32_t* const* flag_ptrs;  /* DEVICE array [world] */
+  int32_t* epoch_state;       /* two device ints, zero-filled once */
+  int32_t* tile_counters;     /* device ints [rows * heads_kv], zero-filled once */
+  void* out;                  /* [rows][Hq][128] bf16 (out_is_f32 = 0) or fp32 (1) */
+  int32_t out_is_f32;
+  int32_t rank;
+  int32_t world;
+} nvfp4_exchange_args;
+
+int nvfp4_decode_exchange(const nvfp4_decode_args* args, const nvfp4_exchange_args* x, void* stream);
+
+/*
  * Measurement aid, no counterpart in the reference project: one launch that reads
  * [ptr, ptr + bytes) once with plain 16-byte loads from every SM and discards the data.
  * Its duration over the page pools of a decode step is the floor for any launch that has to

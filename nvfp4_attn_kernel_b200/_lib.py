@@ -36,6 +36,7 @@ EXPORTS = (
     "nvfp4_work_table",
     "nvfp4_probe_hbm_read",
     "nvfp4_push_merge",
+    "nvfp4_decode_exchange",
     "nvfp4_push_merge_inbox_floats",
     "nvfp4_decode_split_static",
     "nvfp4_static_workspace_bytes",
@@ -150,9 +151,26 @@ def _declare_peer(lib) -> None:
     ]
 
 
+class ExchangeArgs(ctypes.Structure):
+    """Mirror of ``struct nvfp4_exchange_args``."""
+
+    _fields_ = [
+        ("inbox_ptrs", c_void_p),
+        ("flag_ptrs", c_void_p),
+        ("epoch_state", c_void_p),
+        ("tile_counters", c_void_p),
+        ("out", c_void_p),
+        ("out_is_f32", c_int32),
+        ("rank", c_int32),
+        ("world", c_int32),
+    ]
+
+
 def _declare_control(lib) -> None:
     lib.nvfp4_control_step.restype = c_int
     lib.nvfp4_control_step.argtypes = [c_void_p, c_int64, c_int] + [c_void_p] * 13 + [c_int, c_int, c_int, c_void_p]
+    lib.nvfp4_decode_exchange.restype = c_int
+    lib.nvfp4_decode_exchange.argtypes = [ctypes.POINTER(DecodeArgs), ctypes.POINTER(ExchangeArgs), c_void_p]
     lib.nvfp4_push_merge.restype = c_int
     lib.nvfp4_push_merge.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int,
                                      c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]

@@ -192,7 +192,26 @@ int nvfp4_decode_impl_available(int impl, int heads_q, int heads_kv) {
   return 0;
 }
 
-int nvfp4_decode(const nvfp4_decode_args* a, void* stream) {
+static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x, void* stream);
+
+int nvfp4_decode(const nvfp4_decode_args* a, void* stream) { return decode_call(a, nullptr, stream); }
+
+int nvfp4_decode_exchange(const nvfp4_decode_args* a, const nvfp4_exchange_args* x, void* stream) {
+  if (!x) return fail(NVFP4_ERR_INVALID, "decode_exchange: null exchange block");
+  if (!a) return fail(NVFP4_ERR_INVALID, "decode: null argument block");
+  if (x->world < 1 || x->world > 16 || x->rank < 0 || x->rank >= x->world)
+    return fail(NVFP4_ERR_INVALID, "decode_exchange: rank %d of %d is out of range (at most 16 ranks)", x->rank,
+                x->world);
+  if (!x->inbox_ptrs || !x->flag_ptrs || !x->epoch_state || !x->tile_counters || !x->out)
+    return fail(NVFP4_ERR_INVALID, "decode_exchange: null argument");
+  if (a->out || !a->o_partial || !a->lse_partial)
+    return fail(NVFP4_ERR_INVALID,
+                "decode_exchange: the merged rows go to the exchange block's out; give o_partial and "
+                "lse_partial for the local splits and leave args.out null");
+  return decode_call(a, x, stream);
+}
+
+static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x, void* stream) {
   if (!a) return fail(NVFP4_ERR_INVALID, "decode: null argument block");
   if (a->rows < 0) return fail(NVFP4_ERR_INVALID, "decode: negative row count");
   if (a->rows == 0) return NVFP4_OK;
@@ -290,6 +309,22 @@ int nvfp4_decode(const nvfp4_decode_args* a, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int impl = a->impl;
   if (impl == NVFP4_IMPL_AUTO) impl = nvfp4::decode_sm100_supports(p) ? NVFP4_IMPL_SM100 : NVFP4_IMPL_GENERIC;
+  if (x) {
+    if (impl != NVFP4_IMPL_SM100 || !nvfp4::decode_sm100_supports(p))
+      return fail(NVFP4_ERR_UNSUPPORTED, "decode_exchange: only the tensor-core kernel carries the exchange");
+    if (a->num_splits > 256)
+      return fail(NVFP4_ERR_UNSUPPORTED, "decode_exchange: at most 256 local splits");
+    if (x->world * (a->heads_q / a->heads_kv) > 128)
+      return fail(NVFP4_ERR_UNSUPPORTED, "decode_exchange: world * (heads_q / heads_kv) must not exceed 128");
+    p.xchg_inbox = x->inbox_ptrs;
+    p.xchg_flags = x->flag_ptrs;
+    p.xchg_epoch_state = x->epoch_state;
+    p.xchg_counters = x->tile_counters;
+    p.xchg_out = x->out;
+    p.xchg_out_f32 = x->out_is_f32;
+    p.xchg_rank = x->rank;
+    p.xchg_world = x->world;
+  }
   cudaError_t e;
   if (impl == NVFP4_IMPL_SM100) {
     if (!nvfp4::decode_sm100_supports(p))

@@ -20,6 +20,26 @@ struct TileWork {
   int tail_id;
 };
 
+// ---- system-scope accesses for data and flags that peer GPUs write or read ----
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float ld_relaxed_sys(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys(float* p, float v) {
+  asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+constexpr unsigned long long kPeerWaitNs = 1000000000ull;  // bound of every wait on a peer GPU: 1 s
+constexpr int kInboxStride = 132;  // floats per (source, row, head) slot of an inbox: 128 channels, LSE, padding
+
 __device__ __forceinline__ void set_status(uint32_t* status, uint32_t bit) {
   if (status) atomicOr(status, bit);
 }

@@ -90,6 +90,7 @@ struct __align__(1024) Smem {
   uint64_t q_ready, drain[2];
   uint32_t tmem_base;
   volatile int abort_flag;
+  volatile int xchg_last, xchg_ready;           // hand-overs among the output threads during the exchange
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -299,6 +300,158 @@ __device__ __forceinline__ float quantize_page(const float4& z, float group_max,
     p_sf[(g >> 2) * 512 + q * 16 + (g & 3)] = (uint8_t)sb;
   }
   return (p0 + p1) + (p2 + p3);
+}
+
+// Cross-GPU exchange of a finished (row, KV head) tile, run by the 128 output threads (thread t
+// is channel t) of the CTA that stored the tile's last split partial.  Local splits are folded in
+// index order; the result goes into this tile's slots of every peer's inbox with posted remote
+// stores, then one flag per (peer, head); the wait (bounded) is for the peers' flags of the same
+// heads only; the merge reads this GPU's own inbox, in rank order, like push_merge_kernel.
+template <int G, class SM>
+__device__ __forceinline__ void exchange_tile(const DecodeParams& p, const TileWork& w, SM& sm, int t,
+                                              bool stored, int epoch) {
+  const int tiles = p.rows * p.heads_kv, tile = w.row * p.heads_kv + w.kvh;
+  __threadfence();   // this CTA's partial is visible before its arrival is counted
+  asm volatile("bar.sync 6, 128;" ::: "memory");
+  if (t == 0) {
+    sm.xchg_last = stored && atomicAdd(p.xchg_counters + tile, 1) == p.num_splits - 1;
+    sm.xchg_ready = 1;
+  }
+  asm volatile("bar.sync 6, 128;" ::: "memory");
+  if (!sm.xchg_last) return;
+  __threadfence();
+  if (t == 0) p.xchg_counters[tile] = 0;   // ready for the next launch
+  const int rank = p.xchg_rank, world = p.xchg_world;
+  const int64_t pairs = (int64_t)p.rows * p.heads_q;
+  const int64_t copy_elems = (int64_t)world * pairs * kInboxStride;
+  const int64_t idx0 = (int64_t)w.row * p.heads_q + w.kvh * G;   // first of the tile's G (row, head) pairs
+
+  // The splits' LSEs are the same for all 128 threads: each thread fetches one of them into
+  // shared memory (one round trip for all), and the partial outputs are loaded a batch at a
+  // time (all heads, CH splits) so that their latencies overlap.  The accumulation itself runs
+  // in split order with the arithmetic of lse_merge_kernel.
+  constexpr int CH = G >= 8 ? 2 : 4;
+  float* lse_sh = &sm.z[0][0][0];   // the score buffer is idle by now; room for 128 values and more
+  const int n_lse = p.num_splits * G;
+  for (int i = t; i < n_lse; i += 128)
+    lse_sh[i] = __ldcg(p.lse_partial + (i / G) * pairs + idx0 + (i % G));
+  asm volatile("bar.sync 6, 128;" ::: "memory");
+  float my_o[G], my_lse[G], mx[G], acc[G], tot[G];
+#pragma unroll
+  for (int q = 0; q < G; ++q) { mx[q] = -INFINITY; acc[q] = 0.f; tot[q] = 0.f; }
+  for (int s = 0; s < p.num_splits; ++s)
+#pragma unroll
+    for (int q = 0; q < G; ++q) mx[q] = fmaxf(mx[q], lse_sh[s * G + q]);
+  for (int s0 = 0; s0 < p.num_splits; s0 += CH) {
+    float ov[G][CH];
+#pragma unroll
+    for (int q = 0; q < G; ++q)
+#pragma unroll
+      for (int j = 0; j < CH; ++j)
+        ov[q][j] = s0 + j < p.num_splits ? __ldcg(p.o_partial + ((s0 + j) * pairs + idx0 + q) * kHeadDim + t) : 0.f;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+      if (s0 + j >= p.num_splits) break;
+#pragma unroll
+      for (int q = 0; q < G; ++q) {
+        const float ls = lse_sh[(s0 + j) * G + q];
+        if (ls == -INFINITY) continue;   // an empty split weighs nothing, whatever its O holds
+        const float wgt = expf(ls - mx[q]);
+        tot[q] += wgt;
+        acc[q] = fmaf(wgt, ov[q][j], acc[q]);
+      }
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < G; ++q) {
+    my_o[q] = tot[q] > 0.f ? __fdiv_rn(acc[q], tot[q]) : 0.f;
+    my_lse[q] = tot[q] > 0.f ? mx[q] + logf(tot[q]) : -INFINITY;
+  }
+  const int64_t slot0 = (epoch & 1) * copy_elems + ((int64_t)rank * pairs + idx0) * kInboxStride;
+  for (int peer = 0; peer < world; ++peer) {
+    if (peer == rank) continue;
+    float* dst = p.xchg_inbox[peer] + slot0;
+#pragma unroll
+    for (int q = 0; q < G; ++q) {
+      st_relaxed_sys(dst + q * kInboxStride + t, my_o[q]);
+      if (t == 0) st_relaxed_sys(dst + q * kInboxStride + kHeadDim, my_lse[q]);
+    }
+  }
+  asm volatile("bar.sync 6, 128;" ::: "memory");
+  // thread j < world * G looks after (peer j / G, head j % G): announce, then wait for its push.
+  // The release at system scope is cumulative over what the barrier ordered before it, so the
+  // 128 threads' stores above are visible to whoever acquires the flag.
+  const int peer = t / G, q_mine = t % G;
+  if (peer < world && peer != rank) {
+    st_release_sys(p.xchg_flags[peer] + (int64_t)rank * pairs + idx0 + q_mine, epoch);
+    const int* flag = p.xchg_flags[rank] + (int64_t)peer * pairs + idx0 + q_mine;
+    const unsigned long long t0 = sm100::global_ns();
+    // epochs only grow; a peer that is already a step ahead has certainly pushed this one
+    while (ld_acquire_sys(flag) - epoch < 0) {
+      if (sm100::global_ns() - t0 > kPeerWaitNs) {
+        set_status(p.status, NVFP4_STATUS_WAIT_TIMEOUT);
+        sm.xchg_ready = 0;
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  asm volatile("bar.sync 6, 128;" ::: "memory");
+  if (sm.xchg_ready) {   // else the output is left untouched and the status word says why
+    const float* mine = p.xchg_inbox[rank] + (epoch & 1) * copy_elems;
+    float gm[G], a2[G], t2[G];
+#pragma unroll
+    for (int q = 0; q < G; ++q) { gm[q] = -INFINITY; a2[q] = 0.f; t2[q] = 0.f; }
+    for (int s0 = 0; s0 < world; s0 += CH) {
+      float ls[G][CH];
+#pragma unroll
+      for (int q = 0; q < G; ++q)
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int s = s0 + j;
+          ls[q][j] = s >= world ? -INFINITY
+                     : s == rank ? my_lse[q]
+                                 : ld_relaxed_sys(mine + ((int64_t)s * pairs + idx0 + q) * kInboxStride + kHeadDim);
+        }
+#pragma unroll
+      for (int q = 0; q < G; ++q)
+#pragma unroll
+        for (int j = 0; j < CH; ++j) gm[q] = fmaxf(gm[q], ls[q][j]);
+    }
+    for (int s0 = 0; s0 < world; s0 += CH) {
+      float ls[G][CH], ov[G][CH];
+#pragma unroll
+      for (int q = 0; q < G; ++q)
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int s = s0 + j;
+          const float* src = mine + ((int64_t)s * pairs + idx0 + q) * kInboxStride;
+          ls[q][j] = s >= world ? -INFINITY : s == rank ? my_lse[q] : ld_relaxed_sys(src + kHeadDim);
+          ov[q][j] = s >= world ? 0.f : s == rank ? my_o[q] : ld_relaxed_sys(src + t);
+        }
+#pragma unroll
+      for (int q = 0; q < G; ++q)
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          if (ls[q][j] == -INFINITY) continue;
+          const float wgt = expf(ls[q][j] - gm[q]);
+          t2[q] += wgt;
+          a2[q] = fmaf(wgt, ov[q][j], a2[q]);
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < G; ++q) {
+      const float val = t2[q] > 0.f ? __fdiv_rn(a2[q], t2[q]) : 0.f;
+      const int64_t at = (idx0 + q) * kHeadDim + t;
+      if (p.xchg_out_f32) static_cast<float*>(p.xchg_out)[at] = val;
+      else static_cast<uint16_t*>(p.xchg_out)[at] = __bfloat16_as_ushort(__float2bfloat16_rn(val));
+    }
+  }
+  if (t == 0 && atomicAdd(p.xchg_epoch_state + 1, 1) == tiles - 1) {
+    p.xchg_epoch_state[1] = 0;
+    __threadfence();
+    *reinterpret_cast<volatile int*>(p.xchg_epoch_state) = epoch;
+  }
 }
 
 template <int G>
@@ -595,6 +748,9 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     // =====================  output threads: thread t = channel t  =====================
     const int t = tid - 128;
     const uint32_t lane_off = (uint32_t)((warp - 4) * 32) << 16;
+    // the epoch of this launch's exchange: read now, long before the last tile of the launch
+    // advances it (no CTA of the next launch can run before that)
+    const int xchg_epoch = p.xchg_inbox ? *reinterpret_cast<volatile int*>(p.xchg_epoch_state) + 1 : 0;
     float o[G];
 #pragma unroll
     for (int q = 0; q < G; ++q) o[q] = 0.f;
@@ -624,7 +780,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         alive = false;
       }
     }
-    if (bar_and_256(3, alive)) {
+    const bool stored = bar_and_256(3, alive);
+    if (stored) {
 #pragma unroll
       for (int q = 0; q < G; ++q) {
         const float lq = sm.red_io[q], mq = sm.red_io[8 + q];
@@ -640,6 +797,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         }
       }
     }
+    if (p.xchg_inbox) exchange_tile<G>(p, w, sm, t, stored, xchg_epoch);
     if (t == 0) TRACE(1, 39, 4);
   } else if (is_producer) {
     // =====================  producers (K ring: warp 8, V ring: warp 11)  =====================

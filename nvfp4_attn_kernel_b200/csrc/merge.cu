@@ -72,21 +72,7 @@ cudaError_t launch_lse_merge(const float* o_parts, int64_t o_split_stride, const
 // ---------------------------------------------------------------------------
 namespace nvfp4 {
 
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ float ld_relaxed_sys(const float* p) {
-  float v;
-  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
 
-constexpr unsigned long long kPeerWaitNs = 1000000000ull;  // 1 s
 
 template <bool kOutF32>
 __global__ void __launch_bounds__(128)
@@ -179,11 +165,7 @@ cudaError_t launch_peer_merge(const float* const* o_ptrs, const float* const* ls
 // ---------------------------------------------------------------------------
 namespace nvfp4 {
 
-constexpr int kInboxStride = 132;
 
-__device__ __forceinline__ void st_relaxed_sys(float* p, float v) {
-  asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
-}
 
 template <bool kOutF32>
 __global__ void __launch_bounds__(128)

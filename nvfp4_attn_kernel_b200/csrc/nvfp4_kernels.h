@@ -65,6 +65,15 @@ struct DecodeParams {
   int num_splits;
   int emit_partial;  // 1: write (O normalised fp32, LSE) per split; 0: write bf16 out
   uint32_t* status;
+  // Cross-GPU page-range exchange done by the decode kernel itself (xchg_inbox null: off).
+  // The CTA that completes a (row, KV head) tile last folds its splits, pushes the result into
+  // every peer's inbox, waits for the peers' pushes of the same tile and writes the merged rows.
+  float* const* xchg_inbox;   // device array [world]: each rank's inbox, see nvfp4_push_merge
+  int* const* xchg_flags;     // device array [world]: each rank's flags
+  int* xchg_epoch_state;      // two device ints, zero-filled once: the epoch, finished tiles
+  int* xchg_counters;         // device ints [rows * heads_kv], zero-filled once: arrivals per tile
+  void* xchg_out;             // [rows][heads_q][128] bf16 or fp32
+  int xchg_out_f32, xchg_rank, xchg_world;
 };
 
 // CUDA-core kernel: any G = Hq/Hkv in {1,2,4,8,16,32}.

@@ -131,6 +131,7 @@ def decode_fp4(
     num_splits: int = 1,
     status: torch.Tensor | None = None,
     _partials: tuple[torch.Tensor, torch.Tensor] | None = None,
+    _exchange=None,
 ) -> torch.Tensor | None:
     """Validate every tensor contract and launch the decode on the current stream.
 
@@ -437,9 +438,11 @@ def decode_fp4(
     if args.page_table_row_stride < args.max_pages:
         raise ValueError("fp4_page_table rows overlap")
     with torch.cuda.device(device):
-        _lib.check(
-            _lib.load().nvfp4_decode(args, torch.cuda.current_stream(device).cuda_stream)
-        )
+        stream = torch.cuda.current_stream(device).cuda_stream
+        if _exchange is not None:   # an _lib.ExchangeArgs: decode and cross-GPU exchange in one launch
+            _lib.check(_lib.load().nvfp4_decode_exchange(args, _exchange, stream))
+        else:
+            _lib.check(_lib.load().nvfp4_decode(args, stream))
     if out is None:
         return None
     return out if out_indices is not None else out[:rows]

@@ -8,7 +8,9 @@ Three ways, as the path allows:
   ``page_range(n, r, world)`` of every row and the BF16 tail goes with rank 0.
   Each rank runs the decode in partial mode on its own pages and the partials
   ``(normalised O fp32, natural-log LSE)`` are merged by LSE weight.
-  :class:`PageRangeGroup` does the exchange in one of three ways: ``"push"`` (one
+  :class:`PageRangeGroup` does the exchange in one of four ways: ``"fused"`` (the
+  decode kernel itself pushes and merges every (row, KV head) tile as soon as the
+  tile's last split is done: one launch per rank and step), ``"push"`` (one
   launch per rank that folds the rank's local splits, stores the result into every
   peer's inbox in symmetric memory, and merges out of its own inbox once the peers'
   stores for the same (head, row) have arrived), ``"peer"`` (announce, bounded wait,
@@ -72,7 +74,9 @@ def local_page_table(page_table: torch.Tensor, seqused_fp4: torch.Tensor, rank: 
 class PageRangeGroup:
     """Exchange + merge of per-rank partial results for the KV page-range split.
 
-    ``exchange="push"``: every rank owns an inbox in symmetric memory; ``merge`` is ONE kernel
+    ``exchange="fused"``: as "push", but done by the decode kernel for each (row, KV head)
+    tile as it completes (``nvfp4_decode_exchange``); needs ``heads_kv`` and the tensor-core
+    kernel.  ``exchange="push"``: every rank owns an inbox in symmetric memory; ``merge`` is ONE kernel
     launch per rank (``nvfp4_push_merge``) that also folds the rank's local splits, and nothing
     is loaded over NVLink.  ``exchange="peer"``: partials live in symmetric memory that every
     rank of the group has mapped; ``merge`` is one launch per rank (``nvfp4_peer_merge``) that
@@ -81,11 +85,14 @@ class PageRangeGroup:
     partials are all-gathered, then merged locally.
     """
 
-    def __init__(self, group, rows: int, heads_q: int, device: torch.device, exchange: str = "peer"):
+    def __init__(self, group, rows: int, heads_q: int, device: torch.device, exchange: str = "peer",
+                 heads_kv: int | None = None):
         import torch.distributed as dist
 
-        if exchange not in ("push", "peer", "nccl"):
-            raise ValueError("exchange must be 'push', 'peer' or 'nccl'")
+        if exchange not in ("fused", "push", "peer", "nccl"):
+            raise ValueError("exchange must be 'fused', 'push', 'peer' or 'nccl'")
+        if exchange == "fused" and not heads_kv:
+            raise ValueError("the fused exchange counts arrivals per (row, KV head): pass heads_kv")
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -96,7 +103,9 @@ class PageRangeGroup:
         self._o_elems = rows * heads_q * HEAD_DIM
         self._lse_elems = rows * heads_q
         per_copy = self._o_elems + self._lse_elems
-        if exchange == "push":
+        if exchange in ("push", "fused"):
+            if exchange == "fused":
+                self._tile_counters = torch.zeros(rows * heads_kv, dtype=torch.int32, device=device)
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             import torch.distributed._symmetric_memory as symm
 
@@ -167,10 +176,29 @@ class PageRangeGroup:
         copy = (self.epoch + 1) & 1 if self.exchange == "peer" else 0
         per_copy = self._o_elems + self._lse_elems
         base = copy * per_copy
-        buf = self._own if self.exchange == "push" else self._buf
+        buf = self._own if self.exchange in ("push", "fused") else self._buf
         o = buf[base:base + self._o_elems].view(1, self.rows, 1, self.heads_q, HEAD_DIM)
         lse = buf[base + self._o_elems:base + per_copy].view(1, self.rows, self.heads_q, 1)
         return o, lse
+
+    def exchange_args(self, out: torch.Tensor):
+        """The exchange block for ``nvfp4_decode_exchange`` writing the merged rows to ``out``;
+        counts as this step's merge (the epoch advances)."""
+        if self.exchange != "fused":
+            raise ValueError("exchange_args belongs to exchange='fused'")
+        if out.dtype not in (torch.bfloat16, torch.float32) or not out.is_contiguous() or \
+                tuple(out.shape) != (self.rows, self.heads_q, HEAD_DIM):
+            raise ValueError("out must be contiguous BF16/FP32 with shape [rows, heads_q, 128]")
+        self.epoch += 1
+        x = _lib.ExchangeArgs()
+        x.inbox_ptrs = self._inboxes.data_ptr()
+        x.flag_ptrs = self._flags.data_ptr()
+        x.epoch_state = self._epoch_state.data_ptr()
+        x.tile_counters = self._tile_counters.data_ptr()
+        x.out = out.data_ptr()
+        x.out_is_f32 = 1 if out.dtype is torch.float32 else 0
+        x.rank, x.world = self.rank, self.world
+        return x
 
     def merge(self, out: torch.Tensor, local_splits: int = 1) -> torch.Tensor:
         """Merge every rank's partial (written into ``partial_buffers()``) into ``out``.  With
@@ -182,6 +210,8 @@ class PageRangeGroup:
         lib = _lib.load()
         stream = torch.cuda.current_stream(self.device).cuda_stream
         f32 = 1 if out.dtype is torch.float32 else 0
+        if self.exchange == "fused":
+            raise ValueError("with exchange='fused' the decode launch merges; there is no separate merge")
         self.epoch += 1
         if self.exchange == "push":
             o_loc, lse_loc = (self.partial_buffers() if local_splits <= 1
@@ -232,6 +262,7 @@ def decode_page_range(ranges: PageRangeGroup, query: torch.Tensor, key_pages_fp4
     if softmax_scale is None:
         softmax_scale = head_dim ** -0.5
     partials = ranges.partial_buffers() if local_splits <= 1 else ranges.local_split_buffers(local_splits)
+    fused = ranges.exchange == "fused"
     # the decode kernel quantises the BF16 query itself: one launch
     _decode.decode_fp4(
         query_fp4=None, query_scales=None, query_padded_bf16=None, query_bf16=query,
@@ -240,7 +271,10 @@ def decode_page_range(ranges: PageRangeGroup, query: torch.Tensor, key_pages_fp4
         residual_key_pages_bf16=residual_key_pages_bf16,
         residual_value_pages_bf16=residual_value_pages_bf16, residual_page_ids=residual_page_ids,
         seqused_residual=seqused_residual, softmax_scale=softmax_scale,
-        trusted_metadata=trusted_metadata, num_splits=max(1, local_splits), _partials=partials)
+        trusted_metadata=trusted_metadata, num_splits=max(1, local_splits), _partials=partials,
+        _exchange=ranges.exchange_args(out) if fused else None)
+    if fused:
+        return out
     if ranges.exchange == "push":
         return ranges.merge(out, local_splits)   # folds the local splits in the same launch
     if local_splits > 1:

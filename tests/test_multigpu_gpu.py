@@ -120,7 +120,7 @@ def _rank_main(rank, world, port, exchange, result):
         case = inputs.attention_case(71, 4, 32, 8, (128 * 9 + 33, 128 * 4, 128 * 16 + 128, 77), 1.0, 0.0)
         prob = Problem(case, device)   # every rank holds the whole cache here; it only READS its range
         rows = 4
-        grp = sharding.PageRangeGroup(dist.group.WORLD, rows, 32, device, exchange=exchange)
+        grp = sharding.PageRangeGroup(dist.group.WORLD, rows, 32, device, exchange=exchange, heads_kv=8)
         local, lseq = sharding.local_page_table(prob.page_table, prob.seqused_fp4, rank, world)
         tail = {}
         if rank == 0:
@@ -163,7 +163,7 @@ def _rank_main(rank, world, port, exchange, result):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["push", "peer", "nccl"])
+@pytest.mark.parametrize("exchange", ["fused", "push", "peer", "nccl"])
 def test_page_range_split_over_two_gpus(cuda_device, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
