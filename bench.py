@@ -276,9 +276,13 @@ def run_gpu(args) -> None:
     dargs = [decode_args(p) for p in pools]
     # the step as a caller runs it: ONE launch that takes the BF16 query and quantises it inside
     fused = [decode_args(p) for p in pools]
+    pdl = bool(args.pdl and splits == 1 and args.decode_impl != "generic")
     for a in fused:
         a.q_fp4, a.q_sf = None, None
         a.q_bf16, a.q_bf16_row_stride, a.q_bf16_head_stride = q.data_ptr(), q.stride(0), q.stride(1)
+        # consecutive steps are chained with programmatic stream serialization: a launch's set-up
+        # and first page loads overlap the previous launch's drain (the pages are not its output)
+        a.flags = L.DECODE_PROGRAMMATIC_LAUNCH if pdl else 0
     L.check(lib.nvfp4_quantize_q(q.data_ptr(), q.stride(0), q.stride(1), None, q_fp4.data_ptr(),
                                  q_sf.data_ptr(), None, ROWS, HQ, HKV,
                                  torch.cuda.current_stream().cuda_stream))
@@ -417,6 +421,10 @@ def run_gpu(args) -> None:
                 "l2": f"{NUM_POOLS} rotating page pools of {KV_BYTES / 1e6:.0f} MB each (> 126 MB L2), "
                       "alternated every step",
                 "timing": "CUDA-graph replay, CUDA events on the replay stream, max over ranks",
+                "step": "one decode launch (BF16 query quantised inside)"
+                        + (", launches chained with programmatic stream serialization" if pdl else "")
+                        + "; decode_kernel_us / roofline: the same kernel with a pre-quantised query, "
+                          "plain launches",
                 "decode_impl": args.decode_impl, "num_splits": splits,
                 "sharding": "independent batch of 32 sequences per GPU, no collective",
             },
@@ -608,6 +616,9 @@ def main() -> None:
                     help="batch: the headline uniform batch (default); long-context: 4 x 32768 split "
                          "by page range over the GPUs")
     ap.add_argument("--exchange", default="fused", choices=["fused", "push", "peer", "nccl"])
+    ap.add_argument("--pdl", action=argparse.BooleanOptionalAction, default=True,
+                    help="launch the decode with programmatic stream serialization: a launch's set-up "
+                         "and first page loads overlap the previous launch's drain")
     ap.add_argument("--ncu-traffic", type=float, default=None,
                     help="dram bytes per decode launch from an ncu capture (reported as roofline.traffic)")
     args = ap.parse_args()

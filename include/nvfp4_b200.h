@@ -186,7 +186,20 @@ typedef struct nvfp4_decode_args {
   void* workspace;
   size_t workspace_bytes;
   uint32_t* status;              /* nullable sticky device status word */
+  uint32_t flags;                /* NVFP4_DECODE_* bits, 0 for the plain call */
 } nvfp4_decode_args;
+
+/*
+ * NVFP4_DECODE_PROGRAMMATIC_LAUNCH (tensor-core kernel, no counterpart in the reference): the
+ * launch carries the programmatic-stream-serialization attribute, so its CTAs may start while the
+ * previous kernel in the stream is still draining.  Page tiles, scale blocks, the page table and
+ * the lengths are then read BEFORE that kernel has completed: they must not be written by it
+ * (in a decode step they are not: sealed pages and the step's metadata were written earlier).
+ * The query, the BF16 tail and every output are touched only after the previous kernel has
+ * completed and its writes are visible (griddepcontrol.wait); only then are this launch's own
+ * dependents released, so the rule holds along a chain of such launches.
+ */
+#define NVFP4_DECODE_PROGRAMMATIC_LAUNCH 1u
 
 /*
  * With out != NULL the merged bf16 result is written (for num_splits > 1 the

@@ -14,6 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libnvfp4_b200.so")
 
 IMPL_AUTO, IMPL_GENERIC, IMPL_SM100 = 0, 1, 2
+DECODE_PROGRAMMATIC_LAUNCH = 1
 STATUS_BAD_PAGE_ID, STATUS_BAD_TAIL_ID, STATUS_WAIT_TIMEOUT, STATUS_BAD_LENGTH = 1, 2, 4, 8
 ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED = 1, 2, 3
 
@@ -84,6 +85,7 @@ class DecodeArgs(ctypes.Structure):
         ("workspace", c_void_p),
         ("workspace_bytes", c_size_t),
         ("status", c_void_p),
+        ("flags", ctypes.c_uint32),
     ]
 
 

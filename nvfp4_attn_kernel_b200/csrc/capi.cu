@@ -283,6 +283,9 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.num_splits = a->num_splits;
   p.status = a->status;
+  if (a->flags & ~NVFP4_DECODE_PROGRAMMATIC_LAUNCH)
+    return fail(NVFP4_ERR_INVALID, "decode: unknown flag bits %#x", a->flags);
+  p.pdl = (a->flags & NVFP4_DECODE_PROGRAMMATIC_LAUNCH) ? 1 : 0;
 
   float* o_part = a->o_partial;
   float* lse_part = a->lse_partial;
@@ -309,6 +312,9 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int impl = a->impl;
   if (impl == NVFP4_IMPL_AUTO) impl = nvfp4::decode_sm100_supports(p) ? NVFP4_IMPL_SM100 : NVFP4_IMPL_GENERIC;
+  if (p.pdl && (impl != NVFP4_IMPL_SM100 || x))
+    return fail(NVFP4_ERR_UNSUPPORTED,
+                "decode: programmatic launch is carried by the plain tensor-core decode only");
   if (x) {
     if (impl != NVFP4_IMPL_SM100 || !nvfp4::decode_sm100_supports(p))
       return fail(NVFP4_ERR_UNSUPPORTED, "decode_exchange: only the tensor-core kernel carries the exchange");

@@ -608,6 +608,13 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     // positions per lane: the page maximum is a warp reduction, a 16-position scale group is
     // four adjacent lanes and the packed E2M1 bytes of P are formed without any exchange.
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    // Under a programmatic launch everything up to here, and the producers' and issuers' work,
+    // may run while the previous kernel drains.  The query and the tail may be that kernel's
+    // output: wait for it, and only then let this launch's own dependents go.
+    if (p.pdl) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (tid == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     // query operand: G packed rows, swizzled; its scale block; the BF16 copy for the tail
     if (p.q_fp4) {
       if (tid < G * 4) {
@@ -751,6 +758,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     // the epoch of this launch's exchange: read now, long before the last tile of the launch
     // advances it (no CTA of the next launch can run before that)
     const int xchg_epoch = p.xchg_inbox ? *reinterpret_cast<volatile int*>(p.xchg_epoch_state) + 1 : 0;
+    if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");   // before the tail is read or anything is stored
     float o[G];
 #pragma unroll
     for (int q = 0; q < G; ++q) o[q] = 0.f;
@@ -1031,6 +1039,19 @@ static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const 
   }
 #endif
   dim3 grid(p.num_splits, p.heads_kv, p.rows);
+  if (p.pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, decode_sm100_kernel<G>, km, vm, p);
+  }
   decode_sm100_kernel<G><<<grid, kThreads, smem, stream>>>(km, vm, p);
   return cudaGetLastError();
 }

@@ -74,6 +74,7 @@ struct DecodeParams {
   int* xchg_counters;         // device ints [rows * heads_kv], zero-filled once: arrivals per tile
   void* xchg_out;             // [rows][heads_q][128] bf16 or fp32
   int xchg_out_f32, xchg_rank, xchg_world;
+  int pdl;                    // 1: launched with programmatic stream serialization (tensor-core kernel)
 };
 
 // CUDA-core kernel: any G = Hq/Hkv in {1,2,4,8,16,32}.

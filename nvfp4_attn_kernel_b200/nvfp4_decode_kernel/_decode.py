@@ -132,6 +132,8 @@ def decode_fp4(
     status: torch.Tensor | None = None,
     _partials: tuple[torch.Tensor, torch.Tensor] | None = None,
     _exchange=None,
+    programmatic_launch: bool = False,
+    _plan_sink: list | None = None,
 ) -> torch.Tensor | None:
     """Validate every tensor contract and launch the decode on the current stream.
 
@@ -435,6 +437,10 @@ def decode_fp4(
         args.workspace = workspace.data_ptr()
         args.workspace_bytes = workspace.numel()
     args.status = _lib.ptr(status)
+    if programmatic_launch:
+        # CTAs may start while the previous kernel in the stream drains; pages, scales, table and
+        # lengths must not be that kernel's output (query, tail and outputs may be)
+        args.flags = _lib.DECODE_PROGRAMMATIC_LAUNCH
     if args.page_table_row_stride < args.max_pages:
         raise ValueError("fp4_page_table rows overlap")
     with torch.cuda.device(device):
@@ -443,6 +449,9 @@ def decode_fp4(
             _lib.check(_lib.load().nvfp4_decode_exchange(args, _exchange, stream))
         else:
             _lib.check(_lib.load().nvfp4_decode(args, stream))
+    if _plan_sink is not None:
+        # the filled argument block of a call that passed every check, for callers that repeat it
+        _plan_sink.append((args, rows, heads_q, device))
     if out is None:
         return None
     return out if out_indices is not None else out[:rows]

@@ -59,6 +59,44 @@ def _check_scratch(scratch, name: str, rows: int, trailing: tuple[int, ...],
 FUSE_QUERY_QUANT = True
 
 
+# A serving loop repeats the same call (same tensors, same shapes) every step and layer.  With
+# ``trusted_metadata`` nothing about a call depends on device values, so a call whose tensors
+# all have the address, dtype, shape and strides of one that already passed every check would
+# pass them again: its filled argument block is kept and launched directly.  False turns the
+# cache off (every call is then validated from scratch).
+CACHE_CALL_PLANS = True
+_PLANS: dict = {}
+_MAX_PLANS = 256
+
+
+def _decode_module():
+    from . import _decode
+
+    return _decode
+
+
+def _sig(t):
+    return None if t is None else (t.data_ptr(), t.dtype, t.shape, t.stride())
+
+
+def _launch_plan(plan, out):
+    from .. import _lib
+
+    args, rows, heads_q, device, caller_out, scattered = plan
+    if not caller_out:
+        out = torch.empty(rows, heads_q, 128, dtype=torch.bfloat16, device=device)
+        args = type(args).from_buffer_copy(args)   # the cached block is never written to
+        args.out = out.data_ptr()
+    index = device.index
+    stream = torch._C._cuda_getCurrentRawStream(index)
+    if torch.cuda.current_device() == index:
+        _lib.check(_lib.load().nvfp4_decode(args, stream))
+    else:
+        with torch.cuda.device(index):
+            _lib.check(_lib.load().nvfp4_decode(args, stream))
+    return out if scattered else out[:rows]
+
+
 def _kernel_can_quantise(query: torch.Tensor) -> bool:
     return (
         query.dtype is torch.bfloat16
@@ -104,6 +142,20 @@ def fp4_decode_impl(
 
     if not isinstance(num_splits, int) or num_splits < 1 or num_splits & (num_splits - 1):
         raise ValueError(f"num_splits must be a positive power of two, got {num_splits!r}")
+
+    plan_key = None
+    if CACHE_CALL_PLANS and trusted_metadata and num_splits == 1 and query_row_indices is None:
+        plan_key = (
+            _sig(query), _sig(key_pages_fp4), _sig(key_scales), _sig(value_pages_fp4), _sig(value_scales),
+            _sig(fp4_page_table), _sig(seqused_fp4), _sig(query_fp4), _sig(query_scales),
+            _sig(residual_key_pages_bf16), _sig(residual_value_pages_bf16), _sig(residual_page_ids),
+            _sig(seqused_residual), _sig(has_bf16), _sig(out), _sig(out_indices),
+            _sig(query_padded_scratch), _sig(query_fp4_scratch), _sig(query_scales_scratch),
+            softmax_scale, FUSE_QUERY_QUANT, _decode_module().DEFAULT_IMPL,
+        )
+        plan = _PLANS.get(plan_key)
+        if plan is not None:
+            return _launch_plan(plan, out)
 
     bf16_query = query is not None
     fp4_query = query_fp4 is not None or query_scales is not None
@@ -193,4 +245,13 @@ def fp4_decode_impl(
     )
     if num_splits > 1:
         return decode_fp4_split(**shared, num_splits=num_splits)
-    return decode_fp4(**shared, out_indices=out_indices)
+    # a call that is ONE launch (query quantised in the kernel, or quantised by the caller) can
+    # be repeated from its argument block
+    sink = [] if plan_key is not None and (query_bf16 is not None or not bf16_query) else None
+    result = decode_fp4(**shared, out_indices=out_indices, _plan_sink=sink)
+    if sink:
+        args, rows, heads_q, device = sink[0]
+        if len(_PLANS) >= _MAX_PLANS:
+            _PLANS.clear()
+        _PLANS[plan_key] = (args, rows, heads_q, device, out is not None, out_indices is not None)
+    return result

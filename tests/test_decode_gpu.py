@@ -354,3 +354,65 @@ def test_refused_page_ids_are_masked_and_reported(cuda_device, impl):
     got = to_np(got)
     assert np.isfinite(got).all()
     assert np.abs(got - want).max() <= TOL, np.abs(got - want).max()
+
+
+def test_programmatic_launch_chain_is_bit_identical(cuda_device):
+    """Back-to-back decode launches with programmatic stream serialization (a launch's CTAs may
+    start while the previous launch drains) give the bits of plain launches, also when each
+    launch's query is produced by the kernel right before it."""
+    import nvfp4_attn_kernel_b200._lib as L
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode
+
+    if not L.load().nvfp4_decode_impl_available(L.IMPL_SM100, 8, 2):
+        pytest.skip("needs the tensor-core kernel")
+    case = inputs.attention_case(81, 6, 8, 2, (1500, 700, 128 * 20, 90, 128 * 7 + 5, 300), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+
+    def run(pdl):
+        outs = []
+        q = prob.q.clone()
+        for step in range(6):
+            out = _decode.decode_fp4(
+                query_fp4=None, query_scales=None, query_padded_bf16=None, query_bf16=q,
+                key_pages_fp4=prob.k_fp4, key_scales=prob.k_sf, value_pages_fp4=prob.v_fp4,
+                value_scales=prob.v_sf, fp4_page_table=prob.page_table, seqused_fp4=prob.seqused_fp4,
+                residual_key_pages_bf16=prob.k_pages, residual_value_pages_bf16=prob.v_pages,
+                residual_page_ids=prob.residual_page_ids, seqused_residual=prob.seqused_residual,
+                softmax_scale=prob.softmax_scale, trusted_metadata=True, programmatic_launch=pdl)
+            outs.append(out)
+            q = out * 3.0 + prob.q      # the next launch's query depends on this launch's output
+        torch.cuda.synchronize()
+        return outs
+
+    plain, chained = run(False), run(True)
+    for a, b in zip(plain, chained):
+        assert torch.equal(a, b)
+
+
+def test_repeated_trusted_calls_reuse_their_argument_block(cuda_device, impl):
+    """A trusted call whose tensors have the address, dtype, shape and strides of an earlier one
+    is launched from that call's argument block; anything that differs is validated afresh."""
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _kernel, fp4_decode
+
+    prob = Problem(_case("gqa4_short"), cuda_device)
+    _kernel._PLANS.clear()
+    first = prob.decode(trusted_metadata=True)
+    assert len(_kernel._PLANS) == 1
+    again = prob.decode(trusted_metadata=True)
+    assert len(_kernel._PLANS) == 1 and torch.equal(first, again) and again.data_ptr() != first.data_ptr()
+    out = torch.zeros_like(first)
+    into = prob.decode(trusted_metadata=True, out=out)
+    assert len(_kernel._PLANS) == 2 and into.data_ptr() == out.data_ptr() and torch.equal(into, first)
+    out.zero_()
+    prob.decode(trusted_metadata=True, out=out)
+    assert torch.equal(out, first)
+    # untrusted calls are never cached, and a bad argument is still refused after a cached good one
+    prob.decode()
+    assert len(_kernel._PLANS) == 2
+    with pytest.raises(ValueError):
+        prob.decode(trusted_metadata=True, seqused_fp4=prob.seqused_fp4.to(torch.int64))
+    _kernel.CACHE_CALL_PLANS = False
+    try:
+        assert torch.equal(prob.decode(trusted_metadata=True), first)
+    finally:
+        _kernel.CACHE_CALL_PLANS = True
