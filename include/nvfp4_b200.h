@@ -187,6 +187,19 @@ typedef struct nvfp4_decode_args {
   size_t workspace_bytes;
   uint32_t* status;              /* nullable sticky device status word */
   uint32_t flags;                /* NVFP4_DECODE_* bits, 0 for the plain call */
+  /* Fused tail append for one-token rows (all NULL/0: the tail was appended beforehand, as the
+   * reference does with write_kv, src/nvfp4_vllm/write.py:280-337).  With append_key and
+   * append_value given, row r's own token (token r of both, bf16 [rows][Hkv][128] at the token
+   * strides) is stored at position seqused_tail[r] - 1 of tail page tail_ids[r] by the CTA that
+   * owns the row's tail (key_shift, nullable bf16 [Hkv][128], subtracted from the key with one
+   * BF16 subtract) and meets the query from the source.  seqused_tail counts the token; the tail
+   * buffers are written; rows with seqused_tail 0 or a refused tail id append nothing.  The bytes
+   * of the tail and of the output equal nvfp4_tail_append followed by the plain call. */
+  const void* append_key;
+  const void* append_value;
+  int64_t append_key_token_stride;   /* elements */
+  int64_t append_value_token_stride; /* elements */
+  const void* key_shift;
 } nvfp4_decode_args;
 
 /*

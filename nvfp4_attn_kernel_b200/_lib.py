@@ -86,6 +86,11 @@ class DecodeArgs(ctypes.Structure):
         ("workspace_bytes", c_size_t),
         ("status", c_void_p),
         ("flags", ctypes.c_uint32),
+        ("append_key", c_void_p),
+        ("append_value", c_void_p),
+        ("append_key_token_stride", c_int64),
+        ("append_value_token_stride", c_int64),
+        ("key_shift", c_void_p),
     ]
 
 

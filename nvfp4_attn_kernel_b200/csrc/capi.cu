@@ -286,6 +286,25 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   if (a->flags & ~NVFP4_DECODE_PROGRAMMATIC_LAUNCH)
     return fail(NVFP4_ERR_INVALID, "decode: unknown flag bits %#x", a->flags);
   p.pdl = (a->flags & NVFP4_DECODE_PROGRAMMATIC_LAUNCH) ? 1 : 0;
+  if ((a->append_key == nullptr) != (a->append_value == nullptr))
+    return fail(NVFP4_ERR_INVALID, "decode: append_key and append_value go together");
+  if (a->append_key) {
+    if (!all_tail)
+      return fail(NVFP4_ERR_INVALID, "decode: the fused tail append needs the tail arguments");
+    if (!aligned16(a->append_key) || !aligned16(a->append_value) || (a->key_shift && !aligned16(a->key_shift)) ||
+        (a->append_key_token_stride % 8) || (a->append_value_token_stride % 8) ||
+        a->append_key_token_stride < (int64_t)a->heads_kv * 128 ||
+        a->append_value_token_stride < (int64_t)a->heads_kv * 128)
+      return fail(NVFP4_ERR_INVALID,
+                  "decode: the appended tokens must be 16-byte aligned [rows][heads_kv][128] BF16 rows");
+    p.append_key = static_cast<const uint16_t*>(a->append_key);
+    p.append_value = static_cast<const uint16_t*>(a->append_value);
+    p.append_key_stride = a->append_key_token_stride;
+    p.append_value_stride = a->append_value_token_stride;
+    p.key_shift = static_cast<const uint16_t*>(a->key_shift);
+  } else if (a->key_shift) {
+    return fail(NVFP4_ERR_INVALID, "decode: key_shift is only read by the fused tail append");
+  }
 
   float* o_part = a->o_partial;
   float* lse_part = a->lse_partial;

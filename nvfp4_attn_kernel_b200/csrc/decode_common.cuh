@@ -129,13 +129,41 @@ __device__ __forceinline__ void tail_scores(const DecodeParams& p, const TileWor
   if (tid < len) {
     const uint4* krow = reinterpret_cast<const uint4*>(
         p.tail_key + ((tok0 + tid) * p.heads_kv + w.kvh) * kHeadDim);
+    // the step's own token sits at the tail's last position: it comes from the source (one BF16
+    // subtract of the key shift, as the tail copy does it) and is stored for the steps to come
+    const bool fresh = p.append_key != nullptr && tid == len - 1;
+    const uint4* ksrc = fresh ? reinterpret_cast<const uint4*>(p.append_key + (int64_t)w.row * p.append_key_stride +
+                                                               (int64_t)w.kvh * kHeadDim)
+                              : nullptr;
+    const uint4* shift = fresh && p.key_shift
+                             ? reinterpret_cast<const uint4*>(p.key_shift + (int64_t)w.kvh * kHeadDim)
+                             : nullptr;
     float acc[G];
 #pragma unroll
     for (int q = 0; q < G; ++q) acc[q] = 0.f;
 #pragma unroll 4
     for (int c = 0; c < 16; ++c) {
       float kf[8];
-      unpack_bf16x8(__ldg(krow + c), kf);
+      if (fresh) {
+        uint4 k = __ldg(ksrc + c);
+        if (p.key_shift) {
+          float x[8], y[8];
+          unpack_bf16x8(k, x);
+          unpack_bf16x8(__ldg(shift + c), y);
+          uint32_t pk[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat16 a = __float2bfloat16_rn(x[2 * i] - y[2 * i]);
+            const __nv_bfloat16 b = __float2bfloat16_rn(x[2 * i + 1] - y[2 * i + 1]);
+            pk[i] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+          }
+          k = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+        const_cast<uint4*>(krow)[c] = k;
+        unpack_bf16x8(k, kf);
+      } else {
+        unpack_bf16x8(__ldg(krow + c), kf);
+      }
 #pragma unroll
       for (int q = 0; q < G; ++q) {
         const float4 qa = *reinterpret_cast<const float4*>(qb + q * kHeadDim + c * 8);
@@ -175,11 +203,21 @@ __device__ __forceinline__ void tail_pv(const DecodeParams& p, const TileWork& w
   const int64_t vstride = (int64_t)p.heads_kv * kHeadDim;
 #pragma unroll
   for (int q = 0; q < G; ++q) o[q] = 0.f;
+  // with the step's own token given, the last position comes from the source and is stored
+  const int stored = p.append_value != nullptr ? len - 1 : len;
 #pragma unroll 4
-  for (int t = 0; t < len; ++t) {
+  for (int t = 0; t < stored; ++t) {
     const float v = bf16_bits_to_f32(__ldg(vcol + t * vstride));
 #pragma unroll
     for (int q = 0; q < G; ++q) o[q] = fmaf(pf[q * kHeadDim + t], v, o[q]);
+  }
+  if (stored < len) {
+    const uint16_t bits = __ldg(p.append_value + (int64_t)w.row * p.append_value_stride +
+                                (int64_t)w.kvh * kHeadDim + tid);
+    const_cast<uint16_t*>(vcol)[stored * vstride] = bits;
+    const float v = bf16_bits_to_f32(bits);
+#pragma unroll
+    for (int q = 0; q < G; ++q) o[q] = fmaf(pf[q * kHeadDim + stored], v, o[q]);
   }
 }
 

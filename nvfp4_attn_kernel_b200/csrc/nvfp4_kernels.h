@@ -75,6 +75,12 @@ struct DecodeParams {
   void* xchg_out;             // [rows][heads_q][128] bf16 or fp32
   int xchg_out_f32, xchg_rank, xchg_world;
   int pdl;                    // 1: launched with programmatic stream serialization (tensor-core kernel)
+  // The step's own K/V token of every row (decode rows bring exactly one), null: the tail was
+  // appended beforehand.  The CTA that owns a row's tail stores the token at tail position
+  // seqused_tail - 1 (key shifted) and uses it from the source.
+  const uint16_t* append_key; const uint16_t* append_value;   // bf16 [rows][heads_kv][128], token strides below
+  int64_t append_key_stride, append_value_stride;             // elements
+  const uint16_t* key_shift;                                   // nullable bf16 [heads_kv][128]
 };
 
 // CUDA-core kernel: any G = Hq/Hkv in {1,2,4,8,16,32}.

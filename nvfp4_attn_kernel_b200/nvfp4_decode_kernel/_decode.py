@@ -134,11 +134,19 @@ def decode_fp4(
     _exchange=None,
     programmatic_launch: bool = False,
     _plan_sink: list | None = None,
+    append_key: torch.Tensor | None = None,
+    append_value: torch.Tensor | None = None,
+    key_shift: torch.Tensor | None = None,
 ) -> torch.Tensor | None:
     """Validate every tensor contract and launch the decode on the current stream.
 
     ``query_padded_bf16`` (``[rows, 128, heads_q, 128]``, row 0 of each tile live)
     carries the BF16 query that meets the BF16 residual page.
+
+    ``append_key`` / ``append_value`` (BF16 ``[rows, heads_kv, 128]``, the step's own token of
+    every row) fuse the tail append of one-token rows into the launch: the token is stored at
+    position ``seqused_residual - 1`` of the row's residual page (``key_shift``, BF16
+    ``[heads_kv, 128]``, subtracted from the key first) and the residual caches are written.
 
     With ``query_fp4`` and ``query_scales`` both None and ``query_bf16`` (BF16
     ``[rows, heads_q, 128]``, unit stride along the channels) given, the decode kernel
@@ -379,6 +387,35 @@ def decode_fp4(
         status.dtype is not torch.int32 or status.numel() != 1 or status.device != device
     ):
         raise ValueError("status must be a one-element INT32 tensor on the query's device")
+    if (append_key is None) != (append_value is None):
+        raise ValueError("append_key and append_value must be provided together")
+    if append_key is not None:
+        if not has_residual:
+            raise ValueError("the fused tail append needs the BF16 residual cache arguments")
+        for tensor, name in ((append_key, "append_key"), (append_value, "append_value")):
+            _need_cuda(tensor, name, device)
+            if (
+                tensor.dtype is not torch.bfloat16
+                or tuple(tensor.shape) != (rows, heads_kv, HEAD_DIM)
+                or tensor.stride(2) != 1
+                or tensor.stride(1) != HEAD_DIM
+                or tensor.stride(0) % 8
+                or tensor.data_ptr() % 16
+            ):
+                raise ValueError(
+                    f"{name} must be BF16 [rows, heads_kv, 128] with contiguous tokens' heads and "
+                    "16-byte aligned rows"
+                )
+        if key_shift is not None:
+            _need_cuda(key_shift, "key_shift", device)
+            if (
+                key_shift.dtype is not torch.bfloat16
+                or tuple(key_shift.shape) != (heads_kv, HEAD_DIM)
+                or not key_shift.is_contiguous()
+            ):
+                raise ValueError("key_shift must be contiguous BF16 with shape [heads_kv, 128]")
+    elif key_shift is not None:
+        raise ValueError("key_shift is only read together with append_key / append_value")
 
     if validate_only:
         return None
@@ -437,6 +474,12 @@ def decode_fp4(
         args.workspace = workspace.data_ptr()
         args.workspace_bytes = workspace.numel()
     args.status = _lib.ptr(status)
+    if append_key is not None:
+        args.append_key = append_key.data_ptr()
+        args.append_value = append_value.data_ptr()
+        args.append_key_token_stride = append_key.stride(0)
+        args.append_value_token_stride = append_value.stride(0)
+        args.key_shift = _lib.ptr(key_shift)
     if programmatic_launch:
         # CTAs may start while the previous kernel in the stream drains; pages, scales, table and
         # lengths must not be that kernel's output (query, tail and outputs may be)

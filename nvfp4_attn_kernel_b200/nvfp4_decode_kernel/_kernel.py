@@ -136,6 +136,9 @@ def fp4_decode_impl(
     query_padded_scratch=None,
     query_fp4_scratch=None,
     query_scales_scratch=None,
+    append_key=None,
+    append_value=None,
+    key_shift=None,
 ):
     from ._decode import decode_fp4, decode_fp4_split
     from ._quantize import quantize_query
@@ -151,6 +154,7 @@ def fp4_decode_impl(
             _sig(residual_key_pages_bf16), _sig(residual_value_pages_bf16), _sig(residual_page_ids),
             _sig(seqused_residual), _sig(has_bf16), _sig(out), _sig(out_indices),
             _sig(query_padded_scratch), _sig(query_fp4_scratch), _sig(query_scales_scratch),
+            _sig(append_key), _sig(append_value), _sig(key_shift),
             softmax_scale, FUSE_QUERY_QUANT, _decode_module().DEFAULT_IMPL,
         )
         plan = _PLANS.get(plan_key)
@@ -243,6 +247,10 @@ def fp4_decode_impl(
         out=out,
         trusted_metadata=trusted_metadata,
     )
+    if append_key is not None or append_value is not None or key_shift is not None:
+        if num_splits > 1:
+            raise ValueError("the fused tail append runs on the single-tile path only")
+        shared.update(append_key=append_key, append_value=append_value, key_shift=key_shift)
     if num_splits > 1:
         return decode_fp4_split(**shared, num_splits=num_splits)
     # a call that is ONE launch (query quantised in the kernel, or quantised by the caller) can

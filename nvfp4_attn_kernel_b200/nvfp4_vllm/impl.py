@@ -23,6 +23,11 @@ from .runtime import LayerRuntime
 from .write import reset_new_request_tails, write_kv
 
 
+# A step of one-token rows only (pure decode) needs no page quantisation, and its tail copy can
+# ride in the decode launch: False keeps the reference's separate write_kv launch.
+FUSE_TAIL_APPEND = True
+
+
 class NVFP4Impl(FlashAttentionImpl):
     def __init__(self, *args, **kwargs) -> None:
         config = get_current_vllm_config()
@@ -38,6 +43,7 @@ class NVFP4Impl(FlashAttentionImpl):
             self.num_slots = config.scheduler_config.max_num_seqs
         self.runtime: LayerRuntime | None = None
         self.layer_index = 0
+        self._fused_kv = None   # (key, value, shift) of a pure decode step, appended by the decode launch
 
     def _bind_runtime(self, device: torch.device) -> None:
         """Create the model's shared state once (in the profile run, so that vLLM subtracts it
@@ -82,6 +88,14 @@ class NVFP4Impl(FlashAttentionImpl):
         elif runtime.active_key_shift is not None:
             shift = runtime.active_key_shift[self.layer_index]
         key_fp4, key_sf, value_fp4, value_sf = runtime.views(self.layer_index, kv_cache)
+        rows = metadata.decode_prefix_rows
+        self._fused_kv = None
+        if (FUSE_TAIL_APPEND and rows and metadata.decode_prefix_tokens == metadata.num_actual_tokens
+                and key.shape[0] >= rows and value.shape[0] >= rows):
+            # one-token rows only: nothing to quantise, and the decode launch stores each row's
+            # token itself (rows padded in for a CUDA graph have an empty tail and store nothing)
+            self._fused_kv = (key[:rows], value[:rows], shift)
+            return
         write_kv(key=key, value=value, key_pages_fp4=key_fp4, key_scales=key_sf,
                  value_pages_fp4=value_fp4, value_scales=value_sf,
                  tail_key=runtime.tail_key[self.layer_index],
@@ -131,7 +145,14 @@ class NVFP4Impl(FlashAttentionImpl):
             softmax_scale=self.scale,
             trusted_metadata=True,   # produced on the device this same step; never read back
             query_padded_scratch=runtime.query_padded, query_fp4_scratch=runtime.query_fp4,
-            query_scales_scratch=runtime.query_scales, out=output[:rows])
+            query_scales_scratch=runtime.query_scales, out=output[:rows], **self._take_fused_kv())
+
+    def _take_fused_kv(self) -> dict:
+        fused, self._fused_kv = self._fused_kv, None
+        if fused is None:
+            return {}
+        key, value, shift = fused
+        return dict(append_key=key, append_value=value, key_shift=shift)
 
     def _prefill(self, tokens, query, key, value, attn_metadata, output) -> None:
         starts = attn_metadata.prefill_query_start_loc

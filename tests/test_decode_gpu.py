@@ -416,3 +416,55 @@ def test_repeated_trusted_calls_reuse_their_argument_block(cuda_device, impl):
         assert torch.equal(prob.decode(trusted_metadata=True), first)
     finally:
         _kernel.CACHE_CALL_PLANS = True
+
+
+@pytest.mark.parametrize("with_shift", [False, True])
+def test_fused_tail_append_equals_append_then_decode(cuda_device, impl, with_shift):
+    """One-token rows may hand their step's K/V to the decode launch: the tail pages and the
+    output must come out bit-identical to the tail-append kernel followed by the plain call.
+    Includes a row whose token fills its tail page, a row whose tail holds only that token and a
+    padding row (empty tail, tail id -1) that must not be touched."""
+    import nvfp4_attn_kernel_b200._lib as L
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import fp4_decode
+
+    heads_q, heads_kv = 8, 2
+    case = inputs.attention_case(91, 5, heads_q, heads_kv, (128 * 3 + 50, 128 * 2, 1, 128 * 5 + 128, 300), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    rows = 5
+    rng = np.random.default_rng(92)
+    seq_tail = case["seqused_residual"].copy()
+    seq_tail[4] = 0                                       # a padding row: no keys in the tail
+    tail_ids = case["residual_page_ids"].copy()
+    tail_ids[4] = -1
+    seq_fp4 = case["seqused_fp4"].copy()
+    seq_fp4[4] = 0
+    key = bf16_tensor(rng.standard_normal((rows, heads_kv, 128)).astype(np.float32) + 1.5, cuda_device)
+    value = bf16_tensor(rng.standard_normal((rows, heads_kv, 128)).astype(np.float32), cuda_device)
+    shift = bf16_tensor(rng.standard_normal((heads_kv, 128)).astype(np.float32), cuda_device) if with_shift else None
+    t = lambda a: torch.from_numpy(a).to(cuda_device)
+    common = dict(fp4_page_table=prob.page_table, seqused_fp4=t(seq_fp4), residual_page_ids=t(tail_ids),
+                  seqused_residual=t(seq_tail), softmax_scale=prob.softmax_scale, trusted_metadata=True)
+
+    def run(fused):
+        tail_k, tail_v = prob.k_pages.clone(), prob.v_pages.clone()
+        extra = {}
+        if fused:
+            extra = dict(append_key=key, append_value=value, key_shift=shift)
+        else:
+            starts = torch.arange(rows + 1, dtype=torch.int32, device=cuda_device)
+            seq_lens = t((seq_fp4 + seq_tail).astype(np.int32))
+            L.check(L.load().nvfp4_tail_append(
+                key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0), L.ptr(shift),
+                tail_k.data_ptr(), tail_v.data_ptr(), tail_k.stride(0), starts.data_ptr(), seq_lens.data_ptr(),
+                common["seqused_fp4"].data_ptr(), common["residual_page_ids"].data_ptr(), rows, rows, heads_kv,
+                torch.cuda.current_stream().cuda_stream))
+        out = fp4_decode(prob.q, prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf,
+                         residual_key_pages_bf16=tail_k, residual_value_pages_bf16=tail_v, **common, **extra)
+        torch.cuda.synchronize()
+        return out, tail_k, tail_v
+
+    want, want_k, want_v = run(False)
+    got, got_k, got_v = run(True)
+    assert torch.equal(got_k, want_k) and torch.equal(got_v, want_v)
+    assert not torch.equal(want_k, prob.k_pages)          # something was appended
+    assert torch.equal(got, want)

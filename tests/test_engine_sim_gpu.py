@@ -60,7 +60,8 @@ def oracle_row(request, layer, query, shift, scale):
         seqused_residual=np.array([rest], np.int32), softmax_scale=scale)[0]
 
 
-def test_serving_loop(cuda_device):
+@pytest.mark.parametrize("fuse_append", [False, True])
+def test_serving_loop(cuda_device, fuse_append):
     from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import fp4_decode
     from nvfp4_attn_kernel_b200.nvfp4_vllm import layout, promote
     from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane
@@ -120,13 +121,19 @@ def test_serving_loop(cuda_device):
                                         row_to_slot=out.row_to_slot)
             runtime.expect_layer(layer)
             k_fp4, k_sf, v_fp4, v_sf = runtime.views(layer, caches[layer])
-            write_kv(key=bf16_tensor(key, dev), value=bf16_tensor(value, dev), key_pages_fp4=k_fp4,
-                     key_scales=k_sf, value_pages_fp4=v_fp4, value_scales=v_sf,
-                     tail_key=runtime.tail_key[layer], tail_value=runtime.tail_value[layer],
-                     source_tokens=sources, destination_pages=pages,
-                     query_start_loc=query_start_loc, seq_lens=seq_lens,
-                     seqused_fp4=out.seqused_fp4, row_to_slot=out.row_to_slot,
-                     num_actual_tokens=tokens, key_shift=runtime.active_key_shift[layer])
+            # a step of one-token rows only may leave its tail copy to the decode launch
+            fused = fuse_append and decode_rows == len(batch)
+            key_dev, value_dev = bf16_tensor(key, dev), bf16_tensor(value, dev)
+            extra = dict(append_key=key_dev, append_value=value_dev,
+                         key_shift=runtime.active_key_shift[layer]) if fused else {}
+            if not fused:
+                write_kv(key=key_dev, value=value_dev, key_pages_fp4=k_fp4,
+                         key_scales=k_sf, value_pages_fp4=v_fp4, value_scales=v_sf,
+                         tail_key=runtime.tail_key[layer], tail_value=runtime.tail_value[layer],
+                         source_tokens=sources, destination_pages=pages,
+                         query_start_loc=query_start_loc, seq_lens=seq_lens,
+                         seqused_fp4=out.seqused_fp4, row_to_slot=out.row_to_slot,
+                         num_actual_tokens=tokens, key_shift=runtime.active_key_shift[layer])
             if decode_rows:
                 got = fp4_decode(
                     query=bf16_tensor(query[:decode_rows], dev), key_pages_fp4=k_fp4,
@@ -138,7 +145,7 @@ def test_serving_loop(cuda_device):
                     residual_page_ids=out.row_to_slot[:decode_rows],
                     seqused_residual=out.seqused_residual[:decode_rows], softmax_scale=scale,
                     trusted_metadata=True, query_padded_scratch=runtime.query_padded,
-                    query_fp4_scratch=runtime.query_fp4, query_scales_scratch=runtime.query_scales)
+                    query_fp4_scratch=runtime.query_fp4, query_scales_scratch=runtime.query_scales, **extra)
                 got = to_np(got)
                 for row in range(decode_rows):
                     want = oracle_row(batch[row], layer, query[row], shift_np[layer], scale)
