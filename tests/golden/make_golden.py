@@ -67,7 +67,9 @@ def run_attention(mod, case):
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <checkout of the reference project>")
+    root = sys.argv[1]
     ref_values, mod = load_reference(root)
     torch.set_num_threads(os.cpu_count() or 1)
 
