@@ -115,6 +115,22 @@ int nvfp4_tail_append(const void* key, const void* value, int64_t key_token_stri
                       int num_reqs, int heads_kv, void* stream);
 
 /*
+ * One layer's K/V of a step in ONE launch: every full page of this step's prompts quantised
+ * into its block (work table: src_tokens / dst_pages, -1 = skip; key shift fused) and every other
+ * token copied to its row's tail slot (key shift fused).  Replaces the three launches of
+ * write_kv, src/nvfp4_vllm/write.py:280-337 (two page quantisers + the tail copy) and the
+ * torch.sub of impl.py:152.  Arguments as in nvfp4_quantize_kv_pages and nvfp4_tail_append;
+ * work = 0 (a step without a full page) needs no page regions.
+ */
+int nvfp4_write_kv(const void* key, const void* value, int64_t key_token_stride, int64_t value_token_stride,
+                   const void* key_shift_bf16, void* k_packed, int64_t k_pitch, void* k_sf, int64_t k_sf_pitch,
+                   void* v_packed, int64_t v_pitch, void* v_sf, int64_t v_sf_pitch, const int32_t* src_tokens,
+                   const int32_t* dst_pages, int work, void* tail_key, void* tail_value,
+                   int64_t tail_slot_stride, const int32_t* query_start_loc, const int32_t* seq_lens,
+                   const int32_t* seqused_fp4, const int32_t* row_to_slot, int num_tokens, int num_reqs,
+                   int heads_kv, void* stream);
+
+/*
  * Zero the tail page (all layers) of every row that starts a request this step
  * (seq_len <= query_len).  ref: reset_new_request_tails, write.py:133-215.
  */

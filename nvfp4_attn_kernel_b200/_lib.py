@@ -36,6 +36,7 @@ EXPORTS = (
     "nvfp4_control_step",
     "nvfp4_work_table",
     "nvfp4_probe_hbm_read",
+    "nvfp4_write_kv",
     "nvfp4_push_merge",
     "nvfp4_decode_exchange",
     "nvfp4_push_merge_inbox_floats",
@@ -183,6 +184,11 @@ def _declare_control(lib) -> None:
                                      c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]
     lib.nvfp4_push_merge_inbox_floats.restype = c_size_t
     lib.nvfp4_push_merge_inbox_floats.argtypes = [c_int, c_int, c_int]
+    lib.nvfp4_write_kv.restype = c_int
+    lib.nvfp4_write_kv.argtypes = ([c_void_p, c_void_p, c_int64, c_int64, c_void_p]
+                                   + [c_void_p, c_int64] * 4 + [c_void_p, c_void_p, c_int]
+                                   + [c_void_p, c_void_p, c_int64] + [c_void_p] * 4
+                                   + [c_int, c_int, c_int, c_void_p])
     lib.nvfp4_probe_hbm_read.restype = c_int
     lib.nvfp4_probe_hbm_read.argtypes = [c_void_p, c_size_t, c_void_p, c_void_p]
     lib.nvfp4_work_table.restype = c_int

@@ -133,6 +133,41 @@ int nvfp4_tail_append(const void* key, const void* value, int64_t key_token_stri
   return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "tail_append launch");
 }
 
+int nvfp4_write_kv(const void* key, const void* value, int64_t key_token_stride, int64_t value_token_stride,
+                   const void* key_shift_bf16, void* k_packed, int64_t k_pitch, void* k_sf, int64_t k_sf_pitch,
+                   void* v_packed, int64_t v_pitch, void* v_sf, int64_t v_sf_pitch, const int32_t* src_tokens,
+                   const int32_t* dst_pages, int work, void* tail_key, void* tail_value,
+                   int64_t tail_slot_stride, const int32_t* query_start_loc, const int32_t* seq_lens,
+                   const int32_t* seqused_fp4, const int32_t* row_to_slot, int num_tokens, int num_reqs,
+                   int heads_kv, void* stream) {
+  if (num_tokens < 0 || num_reqs < 0 || work < 0) return fail(NVFP4_ERR_INVALID, "write_kv: negative count");
+  if (num_tokens == 0 || num_reqs == 0) return NVFP4_OK;
+  if (!key || !value || !tail_key || !tail_value || !query_start_loc || !seq_lens || !seqused_fp4 || !row_to_slot)
+    return fail(NVFP4_ERR_INVALID, "write_kv: null argument");
+  if (heads_kv < 1 || heads_kv > 65535 - 4) return fail(NVFP4_ERR_INVALID, "write_kv: bad heads_kv");
+  if (work > 65535) return fail(NVFP4_ERR_INVALID, "write_kv: at most 65535 page-work items");
+  const int64_t width = (int64_t)heads_kv * 128;
+  if (key_token_stride < width || value_token_stride < width || (key_token_stride % 8) ||
+      (value_token_stride % 8) || tail_slot_stride < 128 * width || !aligned16(key) || !aligned16(value) ||
+      !aligned16(tail_key) || !aligned16(tail_value) || (key_shift_bf16 && !aligned16(key_shift_bf16)))
+    return fail(NVFP4_ERR_INVALID, "write_kv: strides must cover a token and keep 16-byte alignment");
+  if (work > 0) {
+    if (!k_packed || !k_sf || !v_packed || !v_sf || !src_tokens || !dst_pages)
+      return fail(NVFP4_ERR_INVALID, "write_kv: page work needs the page regions and the work table");
+    const int64_t dense_packed = 128 * (int64_t)heads_kv * 64, dense_sf = (int64_t)heads_kv * 1024;
+    if (k_pitch < dense_packed || v_pitch < dense_packed || k_sf_pitch < dense_sf || v_sf_pitch < dense_sf ||
+        (k_pitch % 16) || (v_pitch % 16) || (k_sf_pitch % 16) || (v_sf_pitch % 16) || !aligned16(k_packed) ||
+        !aligned16(k_sf) || !aligned16(v_packed) || !aligned16(v_sf))
+      return fail(NVFP4_ERR_INVALID, "write_kv: page pitches must cover a dense page and keep 16-byte alignment");
+  }
+  cudaError_t e = nvfp4::launch_write_kv(key, value, key_token_stride, value_token_stride, key_shift_bf16,
+                                         k_packed, k_pitch, k_sf, k_sf_pitch, v_packed, v_pitch, v_sf,
+                                         v_sf_pitch, src_tokens, dst_pages, work, tail_key, tail_value,
+                                         tail_slot_stride, query_start_loc, seq_lens, seqused_fp4, row_to_slot,
+                                         num_tokens, num_reqs, heads_kv, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "write_kv launch");
+}
+
 int nvfp4_tail_reset(void* tail_key, void* tail_value, int64_t tail_layer_stride,
                      int64_t tail_slot_stride, int layers, const int32_t* query_start_loc,
                      const int32_t* seq_lens, const int32_t* row_to_slot, int num_reqs, int heads_kv,

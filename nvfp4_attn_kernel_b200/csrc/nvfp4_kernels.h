@@ -32,6 +32,16 @@ cudaError_t launch_tail_append(const void* key, const void* value, int64_t key_t
                                const int32_t* seqused_fp4, const int32_t* row_to_slot,
                                int num_tokens, int num_reqs, int heads_kv, cudaStream_t stream);
 
+cudaError_t launch_write_kv(const void* key, const void* value, int64_t key_token_stride,
+                            int64_t value_token_stride, const void* key_shift, void* k_packed,
+                            int64_t k_pitch, void* k_sf, int64_t k_sf_pitch, void* v_packed,
+                            int64_t v_pitch, void* v_sf, int64_t v_sf_pitch, const int32_t* src_tokens,
+                            const int32_t* dst_pages, int work, void* tail_key, void* tail_value,
+                            int64_t tail_slot_stride, const int32_t* query_start_loc,
+                            const int32_t* seq_lens, const int32_t* seqused_fp4,
+                            const int32_t* row_to_slot, int num_tokens, int num_reqs, int heads_kv,
+                            cudaStream_t stream);
+
 cudaError_t launch_tail_reset(void* tail_key, void* tail_value, int64_t layer_stride,
                               int64_t slot_stride, int layers, const int32_t* query_start_loc,
                               const int32_t* seq_lens, const int32_t* row_to_slot, int num_reqs,

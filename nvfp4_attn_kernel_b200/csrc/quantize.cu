@@ -208,15 +208,14 @@ tail_flush_kernel(const __nv_bfloat16* __restrict__ tail_key, const __nv_bfloat1
 // ---------------------------------------------------------------------------
 // Tail append: one block per token, 16 bytes per thread and tensor.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128)
-tail_append_kernel(const __nv_bfloat16* __restrict__ key, const __nv_bfloat16* __restrict__ value,
-                   int64_t key_token_stride, int64_t value_token_stride,
-                   const __nv_bfloat16* __restrict__ key_shift, __nv_bfloat16* __restrict__ tail_key,
-                   __nv_bfloat16* __restrict__ tail_value, int64_t tail_slot_stride,
-                   const int32_t* __restrict__ query_start_loc, const int32_t* __restrict__ seq_lens,
-                   const int32_t* __restrict__ seqused_fp4, const int32_t* __restrict__ row_to_slot,
-                   int num_reqs, int heads_kv) {
-  const int token = blockIdx.x;
+__device__ __forceinline__ void
+tail_append_token(int token, const __nv_bfloat16* __restrict__ key, const __nv_bfloat16* __restrict__ value,
+                  int64_t key_token_stride, int64_t value_token_stride,
+                  const __nv_bfloat16* __restrict__ key_shift, __nv_bfloat16* __restrict__ tail_key,
+                  __nv_bfloat16* __restrict__ tail_value, int64_t tail_slot_stride,
+                  const int32_t* __restrict__ query_start_loc, const int32_t* __restrict__ seq_lens,
+                  const int32_t* __restrict__ seqused_fp4, const int32_t* __restrict__ row_to_slot,
+                  int num_reqs, int heads_kv) {
   // the row that owns this token = number of row ends at or before it
   int row = 0;
   for (int r = 0; r < num_reqs; ++r) row += (query_start_loc[r + 1] <= token) ? 1 : 0;
@@ -246,6 +245,56 @@ tail_append_kernel(const __nv_bfloat16* __restrict__ key, const __nv_bfloat16* _
     *reinterpret_cast<uint4*>(tail_value + dst + c) =
         *reinterpret_cast<const uint4*>(value + (int64_t)token * value_token_stride + c);
   }
+}
+
+__global__ void __launch_bounds__(128)
+tail_append_kernel(const __nv_bfloat16* __restrict__ key, const __nv_bfloat16* __restrict__ value,
+                   int64_t key_token_stride, int64_t value_token_stride,
+                   const __nv_bfloat16* __restrict__ key_shift, __nv_bfloat16* __restrict__ tail_key,
+                   __nv_bfloat16* __restrict__ tail_value, int64_t tail_slot_stride,
+                   const int32_t* __restrict__ query_start_loc, const int32_t* __restrict__ seq_lens,
+                   const int32_t* __restrict__ seqused_fp4, const int32_t* __restrict__ row_to_slot,
+                   int num_reqs, int heads_kv) {
+  tail_append_token(blockIdx.x, key, value, key_token_stride, value_token_stride, key_shift, tail_key,
+                    tail_value, tail_slot_stride, query_start_loc, seq_lens, seqused_fp4, row_to_slot,
+                    num_reqs, heads_kv);
+}
+
+// One layer's K/V of a step in ONE launch: full pages quantised into their blocks (key shift
+// fused), every other token copied to its row's tail slot.
+// grid (4 + heads_kv + tail blocks, max(work, 1)): x < 4 quantises a K token chunk of page-work
+// item y, the next heads_kv blocks one V head of it, the rest take one token each.
+struct WriteKvArgs {
+  const __nv_bfloat16* key; const __nv_bfloat16* value;
+  int64_t key_token_stride, value_token_stride;
+  const __nv_bfloat16* key_shift;
+  uint8_t* k_packed; int64_t k_pitch; uint8_t* k_sf; int64_t k_sf_pitch;
+  uint8_t* v_packed; int64_t v_pitch; uint8_t* v_sf; int64_t v_sf_pitch;
+  const int32_t* src_tokens; const int32_t* dst_pages; int work;
+  __nv_bfloat16* tail_key; __nv_bfloat16* tail_value; int64_t tail_slot_stride;
+  const int32_t* query_start_loc; const int32_t* seq_lens; const int32_t* seqused_fp4;
+  const int32_t* row_to_slot;
+  int num_tokens, num_reqs, heads_kv;
+};
+
+__global__ void __launch_bounds__(256) write_kv_kernel(const WriteKvArgs a) {
+  __shared__ VSmem sm;
+  const int role = blockIdx.x;
+  if (role < 4 + a.heads_kv) {
+    if ((int)blockIdx.y >= a.work) return;
+    if (role < 4)
+      quantize_k_block(role, a.key, a.key_token_stride, a.key_shift, a.k_packed, a.k_pitch, a.k_sf,
+                       a.k_sf_pitch, a.src_tokens, a.dst_pages, nullptr, nullptr, 0, a.heads_kv);
+    else
+      quantize_v_block(sm, role - 4, a.value, a.value_token_stride, a.v_packed, a.v_pitch, a.v_sf,
+                       a.v_sf_pitch, a.src_tokens, a.dst_pages, nullptr, nullptr, 0, a.heads_kv);
+    return;
+  }
+  const int token = (role - 4 - a.heads_kv) * gridDim.y + blockIdx.y;
+  if (token >= a.num_tokens) return;
+  tail_append_token(token, a.key, a.value, a.key_token_stride, a.value_token_stride, a.key_shift,
+                    a.tail_key, a.tail_value, a.tail_slot_stride, a.query_start_loc, a.seq_lens,
+                    a.seqused_fp4, a.row_to_slot, a.num_reqs, a.heads_kv);
 }
 
 // ---------------------------------------------------------------------------
@@ -327,6 +376,37 @@ cudaError_t launch_tail_append(const void* key, const void* value, int64_t key_t
       key_token_stride, value_token_stride, static_cast<const __nv_bfloat16*>(key_shift),
       static_cast<__nv_bfloat16*>(tail_key), static_cast<__nv_bfloat16*>(tail_value),
       tail_slot_stride, query_start_loc, seq_lens, seqused_fp4, row_to_slot, num_reqs, heads_kv);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_write_kv(const void* key, const void* value, int64_t key_token_stride,
+                            int64_t value_token_stride, const void* key_shift, void* k_packed,
+                            int64_t k_pitch, void* k_sf, int64_t k_sf_pitch, void* v_packed,
+                            int64_t v_pitch, void* v_sf, int64_t v_sf_pitch, const int32_t* src_tokens,
+                            const int32_t* dst_pages, int work, void* tail_key, void* tail_value,
+                            int64_t tail_slot_stride, const int32_t* query_start_loc,
+                            const int32_t* seq_lens, const int32_t* seqused_fp4,
+                            const int32_t* row_to_slot, int num_tokens, int num_reqs, int heads_kv,
+                            cudaStream_t stream) {
+  if (num_tokens == 0) return cudaSuccess;
+  WriteKvArgs a;
+  a.key = static_cast<const __nv_bfloat16*>(key); a.value = static_cast<const __nv_bfloat16*>(value);
+  a.key_token_stride = key_token_stride; a.value_token_stride = value_token_stride;
+  a.key_shift = static_cast<const __nv_bfloat16*>(key_shift);
+  a.k_packed = static_cast<uint8_t*>(k_packed); a.k_pitch = k_pitch;
+  a.k_sf = static_cast<uint8_t*>(k_sf); a.k_sf_pitch = k_sf_pitch;
+  a.v_packed = static_cast<uint8_t*>(v_packed); a.v_pitch = v_pitch;
+  a.v_sf = static_cast<uint8_t*>(v_sf); a.v_sf_pitch = v_sf_pitch;
+  a.src_tokens = src_tokens; a.dst_pages = dst_pages; a.work = work;
+  a.tail_key = static_cast<__nv_bfloat16*>(tail_key); a.tail_value = static_cast<__nv_bfloat16*>(tail_value);
+  a.tail_slot_stride = tail_slot_stride;
+  a.query_start_loc = query_start_loc; a.seq_lens = seq_lens; a.seqused_fp4 = seqused_fp4;
+  a.row_to_slot = row_to_slot;
+  a.num_tokens = num_tokens; a.num_reqs = num_reqs; a.heads_kv = heads_kv;
+  const int rows_y = work > 0 ? work : 1;
+  const int tail_blocks = (num_tokens + rows_y - 1) / rows_y;
+  dim3 grid(4 + heads_kv + tail_blocks, rows_y);
+  write_kv_kernel<<<grid, 256, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

@@ -12,11 +12,6 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ..nvfp4_decode_kernel.quantize_kv_kernel import (
-    quantize_key_tokens_into,
-    quantize_value_tokens_into,
-)
-
 PAGE_SIZE = 128
 
 
@@ -69,19 +64,31 @@ def write_kv(*, key: torch.Tensor, value: torch.Tensor, key_pages_fp4: torch.Ten
              seq_lens: torch.Tensor, seqused_fp4: torch.Tensor, row_to_slot: torch.Tensor,
              num_actual_tokens: int, key_shift: torch.Tensor | None = None) -> None:
     """One layer's K/V of this step: full pages quantised into their blocks, the rest copied
-    to the row's tail slot.  ``tail_*`` is this layer's ``[slots, 128, heads, head_dim]``."""
+    to the row's tail slot.  ``tail_*`` is this layer's ``[slots, 128, heads, head_dim]``.
+    ONE launch (``nvfp4_write_kv``) where the reference issues two page quantisers and a tail
+    copy."""
     key = key[:num_actual_tokens]
     value = value[:num_actual_tokens]
-    if destination_pages.numel():
-        quantize_key_tokens_into(key, key_pages_fp4, key_scales, source_tokens, destination_pages,
-                                 key_shift=key_shift)
-        quantize_value_tokens_into(value, value_pages_fp4, value_scales, source_tokens,
-                                   destination_pages)
+    work = destination_pages.numel()
     heads = tail_key.shape[2]
+    if key.dtype is not torch.bfloat16 or value.dtype is not torch.bfloat16:
+        raise ValueError("key and value must be BF16")
+    if key.ndim != 3 or key.stride(2) != 1 or key.stride(1) != key.shape[2] or \
+            value.ndim != 3 or value.stride(2) != 1 or value.stride(1) != value.shape[2]:
+        raise ValueError("key and value must be [tokens, heads, head_dim] with contiguous tokens")
+    if work:
+        if source_tokens.numel() != work:
+            raise ValueError("source_tokens and destination_pages must have the same length")
+        k_pitch = key_pages_fp4.stride(0) * key_pages_fp4.element_size()
+        v_pitch = value_pages_fp4.stride(0) * value_pages_fp4.element_size()
+        regions = (key_pages_fp4.data_ptr(), k_pitch, key_scales.data_ptr(), key_scales.stride(0),
+                   value_pages_fp4.data_ptr(), v_pitch, value_scales.data_ptr(), value_scales.stride(0),
+                   source_tokens.data_ptr(), destination_pages.data_ptr())
+    else:
+        regions = (None, 0, None, 0, None, 0, None, 0, None, None)
     with torch.cuda.device(key.device):
-        _lib.check(_lib.load().nvfp4_tail_append(
-            key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0),
-            _lib.ptr(key_shift), tail_key.data_ptr(), tail_value.data_ptr(), tail_key.stride(0),
+        _lib.check(_lib.load().nvfp4_write_kv(
+            key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0), _lib.ptr(key_shift),
+            *regions, work, tail_key.data_ptr(), tail_value.data_ptr(), tail_key.stride(0),
             query_start_loc.data_ptr(), seq_lens.data_ptr(), seqused_fp4.data_ptr(),
-            row_to_slot.data_ptr(), num_actual_tokens, seq_lens.shape[0], heads,
-            _stream(key.device)))
+            row_to_slot.data_ptr(), num_actual_tokens, seq_lens.shape[0], heads, _stream(key.device)))

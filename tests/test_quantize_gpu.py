@@ -229,3 +229,82 @@ def test_tail_append_reset_flush(cuda_device):
     qkv.quantize_value_tokens_into(tv[0].reshape(-1, heads, 128), vview,
                                    qkv.scale_view(flat, blocks, heads, pitch, o3), src_tok, dst)
     assert torch.equal(c2[1], caches[0][1])
+
+
+@pytest.mark.parametrize("with_pages", [True, False])
+def test_write_kv_single_launch_equals_the_three_launches(cuda_device, with_pages):
+    """``nvfp4_write_kv`` (page quantisers + tail copy in one launch) against the separate
+    K quantiser, V quantiser and tail append: identical blocks and identical tails.  The step mixes
+    a 300-token prompt (two full pages + 44 tail tokens), a 128-token prompt (all tail), two
+    decode rows and a row without a slot; without page work only the tail copy runs."""
+    import nvfp4_attn_kernel_b200._lib as L
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import quantize_kv_kernel as qkv
+
+    lib = L.load()
+    heads, slots, blocks = 2, 5, 6
+    rng = np.random.default_rng(41)
+    stream = torch.cuda.current_stream().cuda_stream
+    if with_pages:
+        qlen = np.array([1, 1, 1, 128, 300], dtype=np.int32)      # one-token rows first
+        seq = np.array([200, 513, 77, 128, 300], dtype=np.int32)
+        slot = np.array([4, 0, -1, 2, 1], dtype=np.int32)
+    else:
+        qlen = np.array([1, 1, 1], dtype=np.int32)
+        seq = np.array([200, 513, 77], dtype=np.int32)
+        slot = np.array([4, 0, -1], dtype=np.int32)
+    qsl = np.concatenate([[0], np.cumsum(qlen)]).astype(np.int32)
+    tokens = int(qsl[-1])
+    fp4, _ = O.split_lengths(seq)
+    dev = lambda a: torch.from_numpy(a).to(cuda_device)
+    d_qsl, d_seq, d_slot, d_fp4 = dev(qsl), dev(seq), dev(slot), dev(fp4)
+    key = bf16_tensor(rng.standard_normal((tokens, heads, 128)).astype(np.float32) + 1.0, cuda_device)
+    val = bf16_tensor(rng.standard_normal((tokens, heads, 128)).astype(np.float32), cuda_device)
+    shift = bf16_tensor(rng.standard_normal((heads, 128)).astype(np.float32), cuda_device)
+    # page work of the 300-token prompt: its tokens start at qsl[4]; pages go to blocks 5 and 2
+    if with_pages:
+        src = torch.tensor([int(qsl[4]), int(qsl[4]) + 128, 0], dtype=torch.int32, device=cuda_device)
+        dst = torch.tensor([5, 2, -1], dtype=torch.int32, device=cuda_device)
+    else:
+        src = torch.zeros(0, dtype=torch.int32, device=cuda_device)
+        dst = torch.zeros(0, dtype=torch.int32, device=cuda_device)
+    pitch = O.vllm_block_bytes(heads)
+    o1 = 128 * heads * 64
+    o2 = o1 + heads * 1024
+    o3 = o2 + o1
+
+    def views(cache):
+        flat = cache.view(-1)
+        return (flat.as_strided((blocks, 128, heads, 64), (pitch, heads * 64, 64, 1), 0),
+                qkv.scale_view(flat, blocks, heads, pitch, o1),
+                flat.as_strided((blocks, heads, 128, 64), (pitch, 128 * 64, 64, 1), o2),
+                qkv.scale_view(flat, blocks, heads, pitch, o3))
+
+    base_tail = torch.randn(2, slots, 128, heads, 128, device=cuda_device).to(torch.bfloat16)
+    # three launches
+    cache_a = torch.full((blocks, pitch), 0x3C, dtype=torch.uint8, device=cuda_device)
+    tail_a = base_tail.clone()
+    ka, ksa, va, vsa = views(cache_a)
+    if with_pages:
+        qkv.quantize_key_tokens_into(key, ka, ksa, src, dst, key_shift=shift)
+        qkv.quantize_value_tokens_into(val, va, vsa, src, dst)
+    L.check(lib.nvfp4_tail_append(key.data_ptr(), val.data_ptr(), key.stride(0), val.stride(0), shift.data_ptr(),
+                                  tail_a[0].data_ptr(), tail_a[1].data_ptr(), tail_a.stride(1), d_qsl.data_ptr(),
+                                  d_seq.data_ptr(), d_fp4.data_ptr(), d_slot.data_ptr(), tokens, len(seq), heads,
+                                  stream))
+    # one launch
+    cache_b = torch.full((blocks, pitch), 0x3C, dtype=torch.uint8, device=cuda_device)
+    tail_b = base_tail.clone()
+    kb, ksb, vb, vsb = views(cache_b)
+    work = int(dst.numel())
+    L.check(lib.nvfp4_write_kv(
+        key.data_ptr(), val.data_ptr(), key.stride(0), val.stride(0), shift.data_ptr(),
+        kb.data_ptr() if work else None, pitch, ksb.data_ptr() if work else None, pitch,
+        vb.data_ptr() if work else None, pitch, vsb.data_ptr() if work else None, pitch,
+        src.data_ptr() if work else None, dst.data_ptr() if work else None, work,
+        tail_b[0].data_ptr(), tail_b[1].data_ptr(), tail_b.stride(1), d_qsl.data_ptr(), d_seq.data_ptr(),
+        d_fp4.data_ptr(), d_slot.data_ptr(), tokens, len(seq), heads, stream))
+    torch.cuda.synchronize()
+    assert torch.equal(cache_a, cache_b) and torch.equal(tail_a, tail_b)
+    assert not torch.equal(tail_a, base_tail)
+    if with_pages:
+        assert not (cache_a[[5, 2]] == 0x3C).all() and (cache_a[[0, 1, 3, 4]] == 0x3C).all()
