@@ -52,37 +52,46 @@ __device__ unsigned long long* g_trace = nullptr;
 
 // Ring depths: as many 9 KB slots as two resident CTAs per SM leave room for.  V slots are
 // held about two pages longer than K slots, so the V ring is that much deeper.
-template <int G> struct KSlots { static constexpr int value = G <= 4 ? 4 : 3; };
-template <int G> struct VSlots { static constexpr int value = G <= 4 ? 6 : 5; };
+template <int G> struct KSlots { static constexpr int value = G <= 4 ? 4 : G <= 8 ? 3 : 2; };
+template <int G> struct VSlots { static constexpr int value = G <= 4 ? 6 : G <= 8 ? 5 : 3; };
 constexpr int kBatch = 2;                                         // pages handled per hand-over
 constexpr int kTileBytes = 8192;                                  // 128 rows x 64 B
 constexpr int kSlotBytes = kTileBytes + kSfBlockBytes;            // a tile and its scale block
-constexpr int kNQ = 8;                                            // MMA N
-constexpr int kTmemCols = 128;
+// MMA N (query slots): 8 covers every group size up to 8; a group of 16 takes N = 16
+template <int G> struct QuerySlots { static constexpr int value = G <= 8 ? 8 : G; };
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;        // 2 s
 
 // tensor-memory column map (32-bit columns); a "set" holds the kBatch pages of one hand-over
-constexpr int kColS = 0;     // 2 sets x 2 pages x 8 : S^T
-constexpr int kColO = 32;    // 2 sets x 2 pages x 8 : per-page O^T
-constexpr int kColSfQ = 64;  // 8 : 2 k-blocks x 4
-constexpr int kColSfK = 72;  // 8
-constexpr int kColSfP = 80;  // 8
-constexpr int kColSfV = 96;  // 2 sets x 2 pages x 8 : copied as soon as the V slot has landed
+template <int G>
+struct Cols {
+  static constexpr int NQ = QuerySlots<G>::value;
+  static constexpr int kSet = kBatch * NQ;       // columns of one set of S^T (or O^T)
+  static constexpr int kS = 0;                   // 2 sets x 2 pages x NQ : S^T
+  static constexpr int kO = 2 * kSet;            // 2 sets x 2 pages x NQ : per-page O^T
+  static constexpr int kSfQ = 4 * kSet;          // 8 : 2 k-blocks x 4
+  static constexpr int kSfK = kSfQ + 8;          // 8
+  static constexpr int kSfP = kSfK + 8;          // 8
+  static constexpr int kSfV = kSfP + 16;         // 2 sets x 2 pages x 8 : copied as soon as the V slot has landed
+  static constexpr int kUsed = kSfV + 2 * kBatch * 8;
+  static constexpr int kAlloc = kUsed <= 128 ? 128 : 256;   // a power of two
+  static_assert(kUsed <= 256, "two CTAs per SM leave 256 tensor-memory columns each");
+};
 
 template <int G>
 struct __align__(1024) Smem {
   static constexpr int kKS = KSlots<G>::value, kVS = VSlots<G>::value;
   uint8_t k_slot[kKS][kSlotBytes];              // K tile | K scales
   uint8_t v_slot[kVS][kSlotBytes];              // V tile | V scales
-  __align__(1024) uint8_t q_tile[512];          // 8 rows x 64 B, 64-byte swizzle
-  __align__(1024) uint8_t p_tile[2][kBatch][512];
+  static constexpr int NQ = QuerySlots<G>::value;
+  __align__(1024) uint8_t q_tile[NQ * 64];      // NQ rows x 64 B, 64-byte swizzle
+  __align__(1024) uint8_t p_tile[2][kBatch][NQ * 64];
   __align__(512) uint8_t q_sf[kSfBlockBytes];
   __align__(512) uint8_t p_sf[2][kBatch][kSfBlockBytes];
   __align__(16) float qb[G * kHeadDim];         // BF16 query as floats (tail)
   __align__(16) float pf[G * kHeadDim];         // P of the tail block
   __align__(16) float z[2][kBatch][G * kPage];  // scaled scores, [set][page][q][kv position]
-  float resc[8][8];                             // ring of per-page rescale factors, [page & 7][q]
-  float red_io[4 * 8];                          // reductions of the tail block and the epilogue
+  float resc[8][NQ];                            // ring of per-page rescale factors, [page & 7][q]
+  float red_io[4 * NQ];                         // reductions of the tail block and the epilogue
   volatile int page_ok[32];                     // [walk step & 31] 0: the page id was refused
   __align__(8) uint64_t k_full[kKS];
   uint64_t k_empty[kKS], v_full[kVS], v_empty[kVS];
@@ -184,11 +193,11 @@ __device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
   return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
 }
 
-// Instruction descriptor: E2M1 x E2M1 (format code 1), UE4M3 scales, K-major both, N = 8, M = 128, K = 64.
-constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((kNQ >> 3) << 17) | ((128u >> 4) << 24);
-
+// Instruction descriptor: E2M1 x E2M1 (format code 1), UE4M3 scales, K-major both, N = NQ, M = 128, K = 64.
+template <int NQ>
 __device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t sfa,
                                          uint32_t sfb, uint32_t accumulate) {
+  constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t)(NQ >> 3) << 17) | ((128u >> 4) << 24);
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %6, 0;\n\t"
@@ -462,6 +471,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   Smem<G>& sm = *reinterpret_cast<Smem<G>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr int kKS = KSlots<G>::value, kVS = VSlots<G>::value;
+  constexpr int NQ = QuerySlots<G>::value;
+  using C = Cols<G>;
   if (tid == 0) TRACE(1, 39, 0);
 #ifdef NVFP4_TRACE
   if (tid == 0 && g_trace) {
@@ -515,7 +526,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   if (warp == kQkWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(&sm.tmem_base)),
-                 "r"(kTmemCols)
+                 "r"(C::kAlloc)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -523,8 +534,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   if (!is_producer) {
     constexpr int kWorkers = kThreads - 64;
     const int wt = tid < kKProducerWarp * 32 ? tid : tid - 32;   // warps 0-7, 9, 10 -> 0..319
-    for (int i = wt; i < 512 / 16; i += kWorkers) reinterpret_cast<uint4*>(sm.q_tile)[i] = make_uint4(0, 0, 0, 0);
-    for (int i = wt; i < 2 * kBatch * 512 / 16; i += kWorkers)
+    for (int i = wt; i < NQ * 64 / 16; i += kWorkers) reinterpret_cast<uint4*>(sm.q_tile)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = wt; i < 2 * kBatch * NQ * 64 / 16; i += kWorkers)
       reinterpret_cast<uint4*>(sm.p_tile)[i] = make_uint4(0, 0, 0, 0);
     for (int i = wt; i < 2 * kBatch * kSfBlockBytes / 16; i += kWorkers)
       reinterpret_cast<uint4*>(sm.p_sf)[i] = make_uint4(0, 0, 0, 0);
@@ -623,9 +634,9 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
             p.q_fp4 + ((int64_t)w.row * p.heads_q + w.kvh * G + q) * 64 + c * 16);
         *reinterpret_cast<uint4*>(sm.q_tile + sw64_offset(q, c * 16)) = v;
       }
-      if (tid >= 64) {
-        reinterpret_cast<uint4*>(sm.q_sf)[tid - 64] = *(reinterpret_cast<const uint4*>(
-            p.q_sf + (int64_t)w.row * p.heads_q * kSfBlockBytes + (int64_t)w.kvh * kSfBlockBytes) + (tid - 64));
+      if (tid < 64) {   // after the rows above (a thread may have both jobs when G = 16)
+        reinterpret_cast<uint4*>(sm.q_sf)[tid] = *(reinterpret_cast<const uint4*>(
+            p.q_sf + (int64_t)w.row * p.heads_q * kSfBlockBytes + (int64_t)w.kvh * kSfBlockBytes) + tid);
       }
     } else if (tid < G * 8) {
       // no quantised query was supplied: quantise the BF16 rows of this KV head here, one
@@ -694,8 +705,10 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       if (tid == 0) TRACE(0, kb, 1);
       if (ok) {
         tc_fence_after();
-        uint32_t r[16];
-        tmem_ld16(tmem + lane_off + kColS + set * 16, r);
+        uint32_t r[C::kSet];
+#pragma unroll
+        for (int c = 0; c < C::kSet; c += 16)
+          tmem_ld16(tmem + lane_off + C::kS + set * C::kSet + c, *reinterpret_cast<uint32_t(*)[16]>(&r[c]));
         tc_fence_before();
         mbar_arrive(&sm.s_free[set]);
         const bool ok0 = sm.page_ok[i0 & 31] != 0;
@@ -703,7 +716,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 #pragma unroll
         for (int q = 0; q < G; ++q) {
           sm.z[set][0][q * kPage + tid] = ok0 ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY;
-          sm.z[set][1][q * kPage + tid] = ok1 ? __uint_as_float(r[8 + q]) * p.scale_log2 : -INFINITY;
+          sm.z[set][1][q * kPage + tid] = ok1 ? __uint_as_float(r[NQ + q]) * p.scale_log2 : -INFINITY;
         }
       }
       if (tid == 0) TRACE(0, kb, 2);
@@ -746,7 +759,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       const int q = warp + 4 * k;
       if (q < G) {
         const float ls = warp_sum(l_w[k]);
-        if (lane == 0) { sm.red_io[q] = ls; sm.red_io[8 + q] = m_w[k]; }
+        if (lane == 0) { sm.red_io[q] = ls; sm.red_io[NQ + q] = m_w[k]; }
       }
     }
     bar_and_256(3, alive);
@@ -774,14 +787,16 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       if (mbar_wait(&sm.o_full[set], (kb >> 1) & 1, sm, p.status)) {
         if (t == 0) TRACE(0, kb, 6);
         tc_fence_after();
-        uint32_t ro[16];
-        tmem_ld16(tmem + lane_off + kColO + set * 16, ro);
+        uint32_t ro[C::kSet];
+#pragma unroll
+        for (int c = 0; c < C::kSet; c += 16)
+          tmem_ld16(tmem + lane_off + C::kO + set * C::kSet + c, *reinterpret_cast<uint32_t(*)[16]>(&ro[c]));
         tc_fence_before();
         mbar_arrive(&sm.o_free[set]);
 #pragma unroll
         for (int q = 0; q < G; ++q) {
           o[q] = fmaf(o[q], sm.resc[j0 & 7][q], __uint_as_float(ro[q]));
-          if (two) o[q] = fmaf(o[q], sm.resc[(j0 + 1) & 7][q], __uint_as_float(ro[8 + q]));
+          if (two) o[q] = fmaf(o[q], sm.resc[(j0 + 1) & 7][q], __uint_as_float(ro[NQ + q]));
         }
         if (t == 0) TRACE(0, kb, 7);
       } else {
@@ -792,7 +807,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     if (stored) {
 #pragma unroll
       for (int q = 0; q < G; ++q) {
-        const float lq = sm.red_io[q], mq = sm.red_io[8 + q];
+        const float lq = sm.red_io[q], mq = sm.red_io[NQ + q];
         const int head = w.kvh * G + q;
         const float val = lq > 0.f ? __fdiv_rn(o[q], lq) : 0.f;
         if (p.emit_partial) {
@@ -841,8 +856,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       bool alive = mbar_wait(&sm.q_ready, 0, sm, p.status);
       if (alive) {
         tc_fence_after();
-        cp_sf(tmem + kColSfQ, smem_u32(sm.q_sf));
-        cp_sf(tmem + kColSfQ + 4, smem_u32(sm.q_sf + 512));
+        cp_sf(tmem + C::kSfQ, smem_u32(sm.q_sf));
+        cp_sf(tmem + C::kSfQ + 4, smem_u32(sm.q_sf + 512));
       }
       const uint64_t q_desc = desc_sw64(smem_u32(sm.q_tile));
       for (int kb = 0; kb < n_batches && alive; ++kb) {
@@ -857,12 +872,12 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
           TRACE(2, i, 0);
           tc_fence_after();
           const uint32_t st = smem_u32(sm.k_slot[s]);
-          cp_sf(tmem + kColSfK, st + kTileBytes);
-          cp_sf(tmem + kColSfK + 4, st + kTileBytes + 512);
+          cp_sf(tmem + C::kSfK, st + kTileBytes);
+          cp_sf(tmem + C::kSfK + 4, st + kTileBytes + 512);
           const uint64_t k_desc = desc_sw64(st);
-          const uint32_t d = tmem + kColS + set * 16 + u * 8;
-          mma_nvf4(d, k_desc, q_desc, tmem + kColSfK, tmem + kColSfQ, 0);
-          mma_nvf4(d, k_desc + 2, q_desc + 2, tmem + kColSfK + 4, tmem + kColSfQ + 4, 1);
+          const uint32_t d = tmem + C::kS + set * C::kSet + u * NQ;
+          mma_nvf4<NQ>(d, k_desc, q_desc, tmem + C::kSfK, tmem + C::kSfQ, 0);
+          mma_nvf4<NQ>(d, k_desc + 2, q_desc + 2, tmem + C::kSfK + 4, tmem + C::kSfQ + 4, 1);
           mma_commit(&sm.k_empty[s]);   // the K slot goes back once this page's product has retired
         }
         if (alive) mma_commit(&sm.s_full[set]);
@@ -890,7 +905,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
           if (!alive) break;
           tc_fence_after();
           const uint32_t st = smem_u32(sm.v_slot[s]);
-          const uint32_t c = tmem + kColSfV + (set * kBatch + u) * 8;
+          const uint32_t c = tmem + C::kSfV + (set * kBatch + u) * 8;
           cp_sf(c, st + kTileBytes);
           cp_sf(c + 4, st + kTileBytes + 512);
         }
@@ -903,14 +918,14 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
           const int j = kb * kBatch + u;
           if (j >= n_pages) break;
           const int s = j % kVS;
-          const uint32_t c = tmem + kColSfV + (set * kBatch + u) * 8;
-          cp_sf(tmem + kColSfP, smem_u32(sm.p_sf[set][u]));
-          cp_sf(tmem + kColSfP + 4, smem_u32(sm.p_sf[set][u] + 512));
+          const uint32_t c = tmem + C::kSfV + (set * kBatch + u) * 8;
+          cp_sf(tmem + C::kSfP, smem_u32(sm.p_sf[set][u]));
+          cp_sf(tmem + C::kSfP + 4, smem_u32(sm.p_sf[set][u] + 512));
           const uint64_t v_desc = desc_sw64(smem_u32(sm.v_slot[s]));
           const uint64_t p_desc = desc_sw64(smem_u32(sm.p_tile[set][u]));
-          const uint32_t d = tmem + kColO + set * 16 + u * 8;
-          mma_nvf4(d, v_desc, p_desc, c, tmem + kColSfP, 0);
-          mma_nvf4(d, v_desc + 2, p_desc + 2, c + 4, tmem + kColSfP + 4, 1);
+          const uint32_t d = tmem + C::kO + set * C::kSet + u * NQ;
+          mma_nvf4<NQ>(d, v_desc, p_desc, c, tmem + C::kSfP, 0);
+          mma_nvf4<NQ>(d, v_desc + 2, p_desc + 2, c + 4, tmem + C::kSfP + 4, 1);
           mma_commit(&sm.v_empty[s]);   // the V slot goes back once this page's product has retired
         }
         mma_commit(&sm.o_full[set]);
@@ -944,7 +959,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 #endif
   if (warp == kQkWarp) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kAlloc)
                  : "memory");
   }
 }
@@ -1061,7 +1076,7 @@ static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const 
 bool decode_sm100_supports(const DecodeParams& p) {
   if (p.heads_kv < 1 || p.heads_q % p.heads_kv) return false;
   const int g = p.heads_q / p.heads_kv;
-  return g == 1 || g == 2 || g == 4 || g == 8;
+  return g == 1 || g == 2 || g == 4 || g == 8 || g == 16;
 }
 
 cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream) {
@@ -1078,6 +1093,7 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream) {
     case 2: return sm100::launch_g<2>(p, km, vm, stream);
     case 4: return sm100::launch_g<4>(p, km, vm, stream);
     case 8: return sm100::launch_g<8>(p, km, vm, stream);
+    case 16: return sm100::launch_g<16>(p, km, vm, stream);
     default: return cudaErrorNotSupported;
   }
 }

@@ -468,3 +468,27 @@ def test_fused_tail_append_equals_append_then_decode(cuda_device, impl, with_shi
     assert torch.equal(got_k, want_k) and torch.equal(got_v, want_v)
     assert not torch.equal(want_k, prob.k_pages)          # something was appended
     assert torch.equal(got, want)
+
+
+def test_group_of_sixteen_runs_on_the_tensor_core_kernel(cuda_device):
+    """Sixteen query heads per KV head take an N = 16 product: rows with and without a tail, a
+    row shorter than a page, the split path, and agreement with the CUDA-core kernel."""
+    import nvfp4_attn_kernel_b200._lib as L
+
+    if not L.load().nvfp4_decode_impl_available(L.IMPL_SM100, 32, 2):
+        pytest.skip("this build's tensor-core kernel does not take 16 heads per KV head")
+    case = inputs.attention_case(97, 5, 32, 2, (128 * 6 + 77, 128 * 3, 90, 128 * 11 + 1, 1500), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    want = prob.oracle_from_bytes()
+    try:
+        _set_impl("sm100")
+        out = to_np(prob.decode())
+        split = to_np(prob.decode(num_splits=2))
+        _set_impl("generic")
+        generic = to_np(prob.decode())
+    finally:
+        _set_impl("auto")
+    assert np.isfinite(out).all()
+    assert np.abs(out - want).max() <= TOL, np.abs(out - want).max()
+    assert np.abs(split - prob.oracle_from_bytes(splits=2)).max() <= TOL
+    assert np.abs(out - generic).max() <= TOL
