@@ -54,7 +54,7 @@ extern "C" {
 /* decode implementations */
 #define NVFP4_IMPL_AUTO 0
 #define NVFP4_IMPL_GENERIC 1 /* CUDA-core kernel, any G = Hq/Hkv in {1,2,4,8,16,32} */
-#define NVFP4_IMPL_SM100 2   /* tcgen05 block-scaled MMA kernel, G <= 8 */
+#define NVFP4_IMPL_SM100 2   /* tcgen05 block-scaled MMA kernel, G in {1, 2, 4, 8, 16, 32} */
 
 const char* nvfp4_last_error(void);
 int nvfp4_version(void);

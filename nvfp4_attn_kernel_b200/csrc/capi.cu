@@ -388,7 +388,7 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   cudaError_t e;
   if (impl == NVFP4_IMPL_SM100) {
     if (!nvfp4::decode_sm100_supports(p))
-      return fail(NVFP4_ERR_UNSUPPORTED, "decode: the tensor-core kernel takes 1, 2, 4, 8 or 16 query heads per KV head");
+      return fail(NVFP4_ERR_UNSUPPORTED, "decode: the tensor-core kernel takes 1, 2, 4, 8, 16 or 32 query heads per KV head");
     e = nvfp4::launch_decode_sm100(p, st);
   } else if (impl == NVFP4_IMPL_GENERIC) {
     e = nvfp4::launch_decode_generic(p, st);

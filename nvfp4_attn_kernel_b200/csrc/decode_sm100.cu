@@ -15,10 +15,10 @@
 // K would sit in shared memory for all of that time, and the bytes in flight per CTA (which,
 // over the memory latency, set the rate a CTA can stream at) would shrink by as much.
 //
-// The product is formed transposed so that the G <= 8 query heads of a KV head are the
-// N = 8 side of the MMA and nothing is padded to 128:
-//   S^T[128 kv, 8 q] = K_page[128 kv, 128 d] . Q^T            (A = K tile as it lies in the page)
-//   O^T[128 d , 8 q] = V_page^T[128 d, 128 kv] . P^T          (A = V tile as it lies in the page)
+// The product is formed transposed so that the G query heads of a KV head are the N side of
+// the MMA (N = 8 for G <= 8, else N = G = 16 or 32) and nothing is padded to 128:
+//   S^T[128 kv, N q] = K_page[128 kv, 128 d] . Q^T            (A = K tile as it lies in the page)
+//   O^T[128 d , N q] = V_page^T[128 d, 128 kv] . P^T          (A = V tile as it lies in the page)
 // Both page layouts are already K-major A operands, and the 512-byte scale atoms of the
 // page format are copied to tensor memory with tcgen05.cp unchanged.
 // An output thread is channel t for every query head, so the running output lives in G
@@ -53,18 +53,20 @@ __device__ unsigned long long* g_trace = nullptr;
 // Ring depths: as many 9 KB slots as two resident CTAs per SM leave room for.  V slots are
 // held about two pages longer than K slots, so the V ring is that much deeper.
 template <int G> struct KSlots { static constexpr int value = G <= 4 ? 4 : G <= 8 ? 3 : 2; };
-template <int G> struct VSlots { static constexpr int value = G <= 4 ? 6 : G <= 8 ? 5 : 3; };
-constexpr int kBatch = 2;                                         // pages handled per hand-over
+template <int G> struct VSlots { static constexpr int value = G <= 4 ? 6 : G <= 8 ? 5 : G <= 16 ? 3 : 2; };
+// pages handled per hand-over: two, except where 32 query slots leave tensor memory for one
+template <int G> struct Batch { static constexpr int value = G <= 16 ? 2 : 1; };
 constexpr int kTileBytes = 8192;                                  // 128 rows x 64 B
 constexpr int kSlotBytes = kTileBytes + kSfBlockBytes;            // a tile and its scale block
 // MMA N (query slots): 8 covers every group size up to 8; a group of 16 takes N = 16
 template <int G> struct QuerySlots { static constexpr int value = G <= 8 ? 8 : G; };
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;        // 2 s
 
-// tensor-memory column map (32-bit columns); a "set" holds the kBatch pages of one hand-over
+// tensor-memory column map (32-bit columns); a "set" holds the pages of one hand-over
 template <int G>
 struct Cols {
   static constexpr int NQ = QuerySlots<G>::value;
+  static constexpr int kBatch = Batch<G>::value;
   static constexpr int kSet = kBatch * NQ;       // columns of one set of S^T (or O^T)
   static constexpr int kS = 0;                   // 2 sets x 2 pages x NQ : S^T
   static constexpr int kO = 2 * kSet;            // 2 sets x 2 pages x NQ : per-page O^T
@@ -83,6 +85,7 @@ struct __align__(1024) Smem {
   uint8_t k_slot[kKS][kSlotBytes];              // K tile | K scales
   uint8_t v_slot[kVS][kSlotBytes];              // V tile | V scales
   static constexpr int NQ = QuerySlots<G>::value;
+  static constexpr int kBatch = Batch<G>::value;
   __align__(1024) uint8_t q_tile[NQ * 64];      // NQ rows x 64 B, 64-byte swizzle
   __align__(1024) uint8_t p_tile[2][kBatch][NQ * 64];
   __align__(512) uint8_t q_sf[kSfBlockBytes];
@@ -472,6 +475,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr int kKS = KSlots<G>::value, kVS = VSlots<G>::value;
   constexpr int NQ = QuerySlots<G>::value;
+  constexpr int kBatch = Batch<G>::value;
   using C = Cols<G>;
   if (tid == 0) TRACE(1, 39, 0);
 #ifdef NVFP4_TRACE
@@ -638,11 +642,11 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         reinterpret_cast<uint4*>(sm.q_sf)[tid] = *(reinterpret_cast<const uint4*>(
             p.q_sf + (int64_t)w.row * p.heads_q * kSfBlockBytes + (int64_t)w.kvh * kSfBlockBytes) + tid);
       }
-    } else if (tid < G * 8) {
+    } else for (int it = tid; it < G * 8; it += 128) {
       // no quantised query was supplied: quantise the BF16 rows of this KV head here, one
-      // 16-channel group per thread, with the arithmetic of the stand-alone query quantiser
-      // (the scale block was zeroed during set-up)
-      const int q = tid >> 3, g = tid & 7;
+      // 16-channel group per thread and pass, with the arithmetic of the stand-alone query
+      // quantiser (the scale block was zeroed during set-up)
+      const int q = it >> 3, g = it & 7;
       const uint16_t* src = p.q_bf16 + (int64_t)w.row * p.q_row_stride +
                             (int64_t)(w.kvh * G + q) * p.q_head_stride + g * 16;
       float x[16];
@@ -699,7 +703,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     bool alive = true;
     for (int kb = 0; kb < n_batches; ++kb) {
       const int set = kb & 1, i0 = kb * kBatch;
-      const bool two = i0 + 1 < n_pages;
+      const bool two = kBatch == 2 && i0 + 1 < n_pages;
       if (tid == 0) TRACE(0, kb, 0);
       const bool ok = alive && mbar_wait(&sm.s_full[set], (kb >> 1) & 1, sm, p.status);
       if (tid == 0) TRACE(0, kb, 1);
@@ -716,7 +720,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 #pragma unroll
         for (int q = 0; q < G; ++q) {
           sm.z[set][0][q * kPage + tid] = ok0 ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY;
-          sm.z[set][1][q * kPage + tid] = ok1 ? __uint_as_float(r[NQ + q]) * p.scale_log2 : -INFINITY;
+          if constexpr (kBatch == 2)
+            sm.z[set][1][q * kPage + tid] = ok1 ? __uint_as_float(r[NQ + q]) * p.scale_log2 : -INFINITY;
         }
       }
       if (tid == 0) TRACE(0, kb, 2);
@@ -729,22 +734,29 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       for (int k = 0; k < QPW; ++k) {
         const int q = warp + 4 * k;
         if (q < G) {
-          const float4 za = *reinterpret_cast<const float4*>(&sm.z[set][0][q * kPage + 4 * lane]);
-          const float4 zb = *reinterpret_cast<const float4*>(&sm.z[set][1][q * kPage + 4 * lane]);
-          const PageMax ma = page_max(za), mb = page_max(zb);
-          // the pages are walked in order: the first page of the pair is quantised against the
+          // the pages are walked in order: the first page of a pair is quantised against the
           // maximum up to and including itself, the second against the maximum including both
+          const float4 za = *reinterpret_cast<const float4*>(&sm.z[set][0][q * kPage + 4 * lane]);
+          const PageMax ma = page_max(za);
           const float m1 = fmaxf(m_w[k], ma.page);
-          const float m2 = fmaxf(m1, mb.page);
           const float ra = (m_w[k] == -INFINITY) ? 0.f : exp2f(m_w[k] - m1);
-          const float rb = (m1 == -INFINITY) ? 0.f : exp2f(m1 - m2);
-          m_w[k] = m2;
           const float sa = quantize_page(za, ma.group, m1, sm.p_tile[set][0], sm.p_sf[set][0], q, lane);
-          const float sb = quantize_page(zb, mb.group, m2, sm.p_tile[set][1], sm.p_sf[set][1], q, lane);
-          l_w[k] = fmaf(fmaf(l_w[k], ra, sa), rb, sb);
-          if (lane == 0) {
-            sm.resc[i0 & 7][q] = ra;
-            sm.resc[(i0 + 1) & 7][q] = rb;
+          if constexpr (kBatch == 2) {
+            const float4 zb = *reinterpret_cast<const float4*>(&sm.z[set][1][q * kPage + 4 * lane]);
+            const PageMax mb = page_max(zb);
+            const float m2 = fmaxf(m1, mb.page);
+            const float rb = (m1 == -INFINITY) ? 0.f : exp2f(m1 - m2);
+            const float sb = quantize_page(zb, mb.group, m2, sm.p_tile[set][1], sm.p_sf[set][1], q, lane);
+            m_w[k] = m2;
+            l_w[k] = fmaf(fmaf(l_w[k], ra, sa), rb, sb);
+            if (lane == 0) {
+              sm.resc[i0 & 7][q] = ra;
+              sm.resc[(i0 + 1) & 7][q] = rb;
+            }
+          } else {
+            m_w[k] = m1;
+            l_w[k] = fmaf(l_w[k], ra, sa);
+            if (lane == 0) sm.resc[i0 & 7][q] = ra;
           }
         }
       }
@@ -783,7 +795,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     for (int kb = 0; kb < n_batches && alive; ++kb) {
       // fold the pair: o = o * rescale(j) + O_page(j), page by page
       const int set = kb & 1, j0 = kb * kBatch;
-      const bool two = j0 + 1 < n_pages;
+      const bool two = kBatch == 2 && j0 + 1 < n_pages;
       if (mbar_wait(&sm.o_full[set], (kb >> 1) & 1, sm, p.status)) {
         if (t == 0) TRACE(0, kb, 6);
         tc_fence_after();
@@ -796,7 +808,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 #pragma unroll
         for (int q = 0; q < G; ++q) {
           o[q] = fmaf(o[q], sm.resc[j0 & 7][q], __uint_as_float(ro[q]));
-          if (two) o[q] = fmaf(o[q], sm.resc[(j0 + 1) & 7][q], __uint_as_float(ro[NQ + q]));
+          if constexpr (kBatch == 2)
+            if (two) o[q] = fmaf(o[q], sm.resc[(j0 + 1) & 7][q], __uint_as_float(ro[NQ + q]));
         }
         if (t == 0) TRACE(0, kb, 7);
       } else {
@@ -1076,7 +1089,7 @@ static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const 
 bool decode_sm100_supports(const DecodeParams& p) {
   if (p.heads_kv < 1 || p.heads_q % p.heads_kv) return false;
   const int g = p.heads_q / p.heads_kv;
-  return g == 1 || g == 2 || g == 4 || g == 8 || g == 16;
+  return g == 1 || g == 2 || g == 4 || g == 8 || g == 16 || g == 32;
 }
 
 cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream) {
@@ -1094,6 +1107,7 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream) {
     case 4: return sm100::launch_g<4>(p, km, vm, stream);
     case 8: return sm100::launch_g<8>(p, km, vm, stream);
     case 16: return sm100::launch_g<16>(p, km, vm, stream);
+    case 32: return sm100::launch_g<32>(p, km, vm, stream);
     default: return cudaErrorNotSupported;
   }
 }

@@ -96,7 +96,7 @@ struct DecodeParams {
 // CUDA-core kernel: any G = Hq/Hkv in {1,2,4,8,16,32}.
 cudaError_t launch_decode_generic(const DecodeParams& p, cudaStream_t stream);
 
-// tcgen05 kernel: G <= 8.  Returns cudaErrorNotSupported when the shape is outside it.
+// tcgen05 kernel: G in {1, 2, 4, 8, 16, 32}.  Returns cudaErrorNotSupported when the shape is outside it.
 cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream);
 bool decode_sm100_supports(const DecodeParams& p);
 

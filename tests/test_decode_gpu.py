@@ -470,14 +470,17 @@ def test_fused_tail_append_equals_append_then_decode(cuda_device, impl, with_shi
     assert torch.equal(got, want)
 
 
-def test_group_of_sixteen_runs_on_the_tensor_core_kernel(cuda_device):
-    """Sixteen query heads per KV head take an N = 16 product: rows with and without a tail, a
-    row shorter than a page, the split path, and agreement with the CUDA-core kernel."""
+@pytest.mark.parametrize("heads", [(32, 2), (32, 1)])
+def test_wide_groups_run_on_the_tensor_core_kernel(cuda_device, heads):
+    """Sixteen and thirty-two query heads per KV head take N = 16 / N = 32 products (the latter
+    one page per hand-over): rows with and without a tail, a row shorter than a page, the split
+    path, and agreement with the CUDA-core kernel."""
     import nvfp4_attn_kernel_b200._lib as L
 
-    if not L.load().nvfp4_decode_impl_available(L.IMPL_SM100, 32, 2):
-        pytest.skip("this build's tensor-core kernel does not take 16 heads per KV head")
-    case = inputs.attention_case(97, 5, 32, 2, (128 * 6 + 77, 128 * 3, 90, 128 * 11 + 1, 1500), 1.0, 0.0)
+    heads_q, heads_kv = heads
+    if not L.load().nvfp4_decode_impl_available(L.IMPL_SM100, heads_q, heads_kv):
+        pytest.skip("this build's tensor-core kernel does not take this group size")
+    case = inputs.attention_case(97, 5, heads_q, heads_kv, (128 * 6 + 77, 128 * 3, 90, 128 * 11 + 1, 1500), 1.0, 0.0)
     prob = Problem(case, cuda_device)
     want = prob.oracle_from_bytes()
     try:
