@@ -61,6 +61,11 @@ class NVFP4Backend(FlashAttentionBackend):
         return [PAGE_SIZE]  # V is quantised along tokens a whole page at a time
 
     @classmethod
+    def supports_kv_cache_dtype(cls, kv_cache_dtype) -> bool:
+        # FlashAttention's own check is a fixed list
+        return kv_cache_dtype == NVFP4 or super().supports_kv_cache_dtype(kv_cache_dtype)
+
+    @classmethod
     def supports_block_size(cls, block_size: int | None) -> bool:
         return block_size is None or block_size == PAGE_SIZE
 
@@ -73,8 +78,9 @@ class NVFP4Backend(FlashAttentionBackend):
         return False  # connectors move pages by address and size, not by this layout
 
     @classmethod
-    def supports_combination(cls, head_size, dtype, kv_cache_dtype, block_size, use_mla, has_sink,
-                             use_sparse, use_mm_prefix, device_capability) -> str | None:
+    def supports_combination(cls, head_size, dtype, kv_cache_dtype, *rest, **more) -> str | None:
+        # the trailing arguments differ between vLLM releases (0.22 has no use_mm_prefix); only the
+        # first three matter here
         if kv_cache_dtype == NVFP4 and head_size != HEAD_SIZE:
             return f"NVFP4 decode is compiled for head_size {HEAD_SIZE}, got {head_size}"
         return None
