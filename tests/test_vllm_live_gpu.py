@@ -5,8 +5,9 @@ on the ``CUSTOM`` backend with the NVFP4 cache, serves six prompts of 5..300 tok
 greedy tokens each (every request crosses a page boundary, so tails are flushed), the slot
 control plane reports no error, and the token streams are IDENTICAL between the fused launch
 structure (query quantised in the decode kernel, tail copy in the decode launch) and the
-reference's separate launches.  Against vLLM's own FlashAttention backend with a BF16 cache the
-first token of every request (prefill attention, no cache involved) must agree.
+reference's separate launches, and between eager mode and CUDA graphs.  Against vLLM's own
+FlashAttention backend with a BF16 cache the first token of every request (prefill attention, no
+cache involved) must agree.
 """
 
 import json
@@ -53,3 +54,13 @@ def test_live_engine_first_tokens_agree_with_the_stock_backend(cuda_device):
     ours = run_engine()
     stock = run_engine("--stock")
     assert [t[0] for t in ours["tokens"]] == [t[0] for t in stock["tokens"]]
+
+
+def test_live_engine_cuda_graphs_equal_eager_mode(cuda_device):
+    """With CUDA graphs vLLM captures padded decode batches first (the slot table must start
+    empty afterwards, padding rows must own no slot) and replays them while serving: the tokens
+    must be those of eager mode and the control plane must report nothing."""
+    eager = run_engine()
+    graphs = run_engine("--graphs")
+    assert graphs["tokens"] == eager["tokens"]
+    assert all(word == 0 for words in graphs["control_plane_errors"] for word in words)
