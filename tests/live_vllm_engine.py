@@ -6,6 +6,8 @@ the flags choose the variant:
     --graphs          CUDA graphs instead of eager mode
     --separate        the reference's launch structure: separate query quantiser and tail copy
     --stock           vLLM's own FlashAttention backend with a BF16 cache (for comparison)
+    --shift           measure the key shift through the worker extension, serve with it, switch
+                      it off and serve again
 """
 
 import json
@@ -62,8 +64,22 @@ def main() -> None:
     # request crosses a page boundary (a tail flush) while it decodes 200 tokens
     prompts = [TokensPrompt(prompt_token_ids=rng.integers(3, 2000, n).tolist()) for n in (5, 130, 300, 128, 40, 257)]
     params = SamplingParams(temperature=0.0, max_tokens=200, ignore_eos=True, detokenize=False)
+    result = {}
+    if "--shift" in flags:
+        # what calibrate_key_shift does, with token prompts (this engine has no tokenizer): let
+        # every layer accumulate the K sum over one long prefill, freeze the mean, serve with it
+        from nvfp4_vllm import calibrate
+
+        assert any(llm.collective_rpc("nvfp4_begin_key_shift_measurement"))
+        llm.generate([TokensPrompt(prompt_token_ids=rng.integers(3, 2000, 700).tolist())],
+                     SamplingParams(temperature=0.0, max_tokens=1, detokenize=False), use_tqdm=False)
+        result["report"] = llm.collective_rpc("nvfp4_finish_key_shift_measurement", args=(None,))[0]
+        result["active"] = llm.collective_rpc("nvfp4_key_shift_is_active")
+        shifted = llm.generate(prompts, params, use_tqdm=False)
+        result["tokens_shifted"] = [list(o.outputs[0].token_ids) for o in shifted]
+        result["switched_off"] = calibrate.set_key_shift_enabled(llm, False)
     outs = llm.generate(prompts, params, use_tqdm=False)
-    result = {"tokens": [list(o.outputs[0].token_ids) for o in outs]}
+    result["tokens"] = [list(o.outputs[0].token_ids) for o in outs]
 
     if "--stock" not in flags:
         def error_words(worker):

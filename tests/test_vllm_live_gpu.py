@@ -64,3 +64,18 @@ def test_live_engine_cuda_graphs_equal_eager_mode(cuda_device):
     graphs = run_engine("--graphs")
     assert graphs["tokens"] == eager["tokens"]
     assert all(word == 0 for words in graphs["control_plane_errors"] for word in words)
+
+
+def test_live_engine_key_shift_measurement_and_switch(cuda_device):
+    """The key shift is measured through the worker extension while the engine runs (fp64 sum of
+    K over a 700-token prefill, per layer), the engine serves with it, and with the shift switched
+    off again it produces exactly the tokens of an engine that never had one."""
+    plain = run_engine()
+    shifted = run_engine("--shift")
+    report = shifted["report"]
+    assert report["tokens"] == 700 and report["shape"] == [2, 2, 128] and report["mean_abs"] > 0
+    assert shifted["active"] == [True] and shifted["switched_off"] is True
+    assert [len(t) for t in shifted["tokens_shifted"]] == [200] * 6
+    assert [t[0] for t in shifted["tokens_shifted"]] == [t[0] for t in plain["tokens"]]
+    assert shifted["tokens"] == plain["tokens"]
+    assert all(word == 0 for words in shifted["control_plane_errors"] for word in words)
