@@ -27,7 +27,12 @@ REQUIRED_ENGINE_KWARGS: dict[str, Any] = {
 def build_llm(model: str, *, key_shift: Any = "auto", **kwargs: Any):
     from vllm import LLM
 
+    from . import register
     from .calibrate import WORKER_EXTENSION_CLS, calibrate_key_shift
+
+    # The plugin entry point does this in every vLLM process of an installed package; doing it
+    # here as well covers an in-process engine core of a source checkout.
+    register()
 
     clash = {name: kwargs[name] for name, need in REQUIRED_ENGINE_KWARGS.items()
              if name in kwargs and kwargs[name] != need}
