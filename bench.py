@@ -601,6 +601,162 @@ def run_long_context(args) -> None:
         dist.destroy_process_group()
 
 
+def run_ragged(args) -> None:
+    """Ragged serving step on one GPU: 32 sequences with lengths log-uniform in [128, 32768], every
+    one with a BF16 tail, block tables drawn from a shuffled pool of 20000 pages.  A step is what a
+    layer costs while serving: the slot control plane, ONE decode launch (query quantised inside,
+    the step's K/V token appended to the tail inside, key shift on) and the tail flush; sequence
+    lengths advance by one token per step on the device, so tails fill and get sealed as they would
+    in an engine.  All launches of a step are inside the timed region."""
+    import numpy as np
+    import torch
+
+    import nvfp4_attn_kernel_b200._lib as L
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode
+    from nvfp4_attn_kernel_b200.nvfp4_vllm import layout
+    from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import quantize_kv_kernel as qkv
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit("the ragged workload runs on one GPU")
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    lib = L.load()
+    rows, pool_pages = ROWS, 20000
+    rng = np.random.default_rng(3)
+    lens = np.exp(rng.uniform(np.log(128), np.log(32768), rows)).astype(np.int64)
+    per_graph = 8
+    total_steps = (max(1, args.warmup // per_graph) + max(1, args.steps // per_graph) + 2) * per_graph
+    columns = int((lens.max() + total_steps) // PAGE + 2)
+    need = (lens + total_steps) // PAGE + 2                   # blocks a row may touch
+    ids = rng.permutation(np.arange(1, pool_pages))           # block 0 is vLLM's null block
+    table = np.zeros((rows, columns), dtype=np.int32)
+    at = 0
+    for r in range(rows):
+        table[r, :need[r]] = ids[at:at + need[r]]
+        at += int(need[r])
+    # page data: quantised once into a dense pool, then placed at the rows' block ids
+    full = (lens - 1) // PAGE
+    used = int(full.sum())
+    dense = build_pools(device, 1, -(-used // 128) * 128, 1)[0]
+    block = layout.page_bytes(HKV)
+    cache = torch.zeros(pool_pages, block, dtype=torch.uint8, device=device)
+    live_ids = np.concatenate([table[r, :full[r]] for r in range(rows)]).astype(np.int64)
+    cache[torch.from_numpy(live_ids).to(device)] = dense["cache"][:used]
+    del dense
+    k_fp4, k_sf, v_fp4, v_sf = layout.carve(cache, HKV, D)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(4)
+    tail_k = torch.randn(1, rows, PAGE, HKV, D, device=device, generator=gen).to(torch.bfloat16)
+    tail_v = torch.randn(1, rows, PAGE, HKV, D, device=device, generator=gen).to(torch.bfloat16)
+    q = torch.randn(rows, HQ, D, device=device, generator=gen).to(torch.bfloat16)
+    k_new = (torch.randn(rows, HKV, D, device=device, generator=gen) + 1.0).to(torch.bfloat16)
+    v_new = torch.randn(rows, HKV, D, device=device, generator=gen).to(torch.bfloat16)
+    shift = torch.ones(HKV, D, device=device).to(torch.bfloat16)
+    out = torch.zeros(rows, HQ, D, dtype=torch.bfloat16, device=device)
+    block_table = torch.from_numpy(table).to(device)
+    seq_lens = torch.from_numpy(lens.astype(np.int32)).to(device)
+    starts = torch.arange(rows + 1, dtype=torch.int32, device=device)
+    # the slot table as the prompts' prefill steps would have left it
+    plane = ControlPlane(max_num_seqs=rows, max_num_batched_tokens=rows, device=device)
+    plane.slot_keys.copy_(block_table[:, 0])
+    plane.slot_last_seq.copy_(seq_lens)
+    plane.slot_last_seen.zero_()
+    bases = torch.tensor([[t.data_ptr()] for t in (k_fp4, k_sf, v_fp4, v_sf)], dtype=torch.int64, device=device)
+
+    # One CTA walks a (row, KV head) serially, so the longest row sets the step time unless it is
+    # split: as many splits as give its longest piece about 32 pages (the lengths are host data
+    # in a serving engine too: the scheduler's seq_lens).
+    splits = args.num_splits
+    if splits <= 1:
+        splits = 1
+        while int(lens.max() + total_steps) // PAGE > 32 * splits:
+            splits *= 2
+
+    def step():
+        seq_lens.add_(1)
+        ctl = plane.prepare(block_table=block_table, seq_lens=seq_lens, query_start_loc=starts,
+                            num_reqs=rows, num_actual_tokens=rows)
+        _decode.decode_fp4(
+            query_fp4=None, query_scales=None, query_padded_bf16=None, query_bf16=q,
+            key_pages_fp4=k_fp4, key_scales=k_sf, value_pages_fp4=v_fp4, value_scales=v_sf,
+            fp4_page_table=block_table, seqused_fp4=ctl.seqused_fp4,
+            residual_key_pages_bf16=tail_k[0], residual_value_pages_bf16=tail_v[0],
+            residual_page_ids=ctl.row_to_slot, seqused_residual=ctl.seqused_residual,
+            softmax_scale=D ** -0.5, trusted_metadata=True, out=out, num_splits=splits,
+            append_key=k_new, append_value=v_new, key_shift=shift)
+        L.check(lib.nvfp4_tail_flush(
+            tail_k.data_ptr(), tail_v.data_ptr(), rows * PAGE, ctl.promotion_source_tokens.data_ptr(),
+            ctl.promotion_pages.data_ptr(), bases.data_ptr(), block, block, block, block, rows, 1, HKV,
+            torch.cuda.current_stream(device).cuda_stream))
+
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for _ in range(per_graph):
+            step()
+    done_before = 1 + per_graph          # the capture itself does not run the kernels
+    seq_lens.copy_(torch.from_numpy((lens + 1).astype(np.int32)).to(device))
+    done_before = 1
+    sampler = ClockSampler(0)
+    sampler.start()
+    warm = max(1, args.warmup // per_graph)
+    for _ in range(warm):
+        graph.replay()
+    torch.cuda.synchronize()
+    reps = max(1, args.steps // per_graph)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms_step = start.elapsed_time(end) / (reps * per_graph)
+    errors = int(plane.error_code.item())
+    # algorithmic bytes of the timed steps, from the lengths each of them saw
+    first = done_before + warm * per_graph
+    kv = 0.0
+    for s_ in range(first, first + reps * per_graph):
+        cur = lens + s_ + 1
+        fp4 = ((cur - 1) // PAGE) * PAGE
+        kv += HKV * float((fp4 * 144 + (cur - fp4) * 512).sum())
+    kv /= reps * per_graph
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = kv / (ms_step * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": METRIC, "value": rows / (ms_step * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": reps * per_graph, "warmup": warm * per_graph, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
+        "data": "synthetic",
+        "config": {
+            "workload": "ragged serving step: 32 seq, lengths log-uniform in [128, 32768] growing one token "
+                        "per step, BF16 tails, block tables from a shuffled pool of 20000 pages, key shift on",
+            "step": "slot control plane + one decode launch (query quantised and K/V token appended "
+                    f"inside, {splits} KV splits" + (" + merge launch" if splits > 1 else "")
+                    + ") + tail flush, all timed",
+            "l2": f"{kv / 1e6:.0f} MB of pages and tails per step against a 126 MB L2 (one cache, so a "
+                  "part of it may be served from L2)",
+            "timing": f"CUDA-graph replay of {per_graph} steps, CUDA events",
+        },
+        "hbm_gbs": achieved, "kv_bytes_per_step": kv,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_source": "measured" if peaks else "fallback",
+                     "traffic": None},
+        "cpu_baseline": None, "e2e": None, "gpu_launches": reps * per_graph * (4 if splits > 1 else 3),
+        "clocks": clocks, "control_plane_error_word": errors,
+    }), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -612,9 +768,10 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ctx", type=int, default=CTX,
                     help="context length per sequence (default: the headline workload's 4096)")
-    ap.add_argument("--workload", default="batch", choices=["batch", "long-context"],
+    ap.add_argument("--workload", default="batch", choices=["batch", "long-context", "ragged"],
                     help="batch: the headline uniform batch (default); long-context: 4 x 32768 split "
-                         "by page range over the GPUs")
+                         "by page range over the GPUs; ragged: 32 ragged sequences with tails, the "
+                         "whole serving step (control plane, decode with fused append, flush)")
     ap.add_argument("--exchange", default="fused", choices=["fused", "push", "peer", "nccl"])
     ap.add_argument("--pdl", action=argparse.BooleanOptionalAction, default=True,
                     help="launch the decode with programmatic stream serialization: a launch's set-up "
@@ -628,6 +785,8 @@ def main() -> None:
         run_reference(args)
     elif args.workload == "long-context":
         run_long_context(args)
+    elif args.workload == "ragged":
+        run_ragged(args)
     else:
         run_gpu(args)
 

@@ -522,6 +522,9 @@ def decode_fp4_split(
     out: torch.Tensor | None = None,
     trusted_metadata: bool = False,
     return_partials: bool = False,
+    append_key: torch.Tensor | None = None,
+    append_value: torch.Tensor | None = None,
+    key_shift: torch.Tensor | None = None,
 ):
     """Split-KV decode: split ``s`` owns pages ``[s*ceil(n/S), min((s+1)*ceil(n/S), n))``,
     the residual belongs to split 0; partials are merged by LSE weight.
@@ -548,6 +551,9 @@ def decode_fp4_split(
         softmax_scale=softmax_scale,
         out=out,
         trusted_metadata=trusted_metadata,
+        append_key=append_key,      # the split that owns the residual (split 0) appends
+        append_value=append_value,
+        key_shift=key_shift,
     )
     if num_splits <= 1 and not return_partials:
         return decode_fp4(**common)

@@ -248,8 +248,6 @@ def fp4_decode_impl(
         trusted_metadata=trusted_metadata,
     )
     if append_key is not None or append_value is not None or key_shift is not None:
-        if num_splits > 1:
-            raise ValueError("the fused tail append runs on the single-tile path only")
         shared.update(append_key=append_key, append_value=append_value, key_shift=key_shift)
     if num_splits > 1:
         return decode_fp4_split(**shared, num_splits=num_splits)

@@ -458,16 +458,17 @@ def test_fused_tail_append_equals_append_then_decode(cuda_device, impl, with_shi
                 tail_k.data_ptr(), tail_v.data_ptr(), tail_k.stride(0), starts.data_ptr(), seq_lens.data_ptr(),
                 common["seqused_fp4"].data_ptr(), common["residual_page_ids"].data_ptr(), rows, rows, heads_kv,
                 torch.cuda.current_stream().cuda_stream))
-        out = fp4_decode(prob.q, prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf,
+        out = fp4_decode(prob.q, prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, num_splits=splits,
                          residual_key_pages_bf16=tail_k, residual_value_pages_bf16=tail_v, **common, **extra)
         torch.cuda.synchronize()
         return out, tail_k, tail_v
 
-    want, want_k, want_v = run(False)
-    got, got_k, got_v = run(True)
-    assert torch.equal(got_k, want_k) and torch.equal(got_v, want_v)
-    assert not torch.equal(want_k, prob.k_pages)          # something was appended
-    assert torch.equal(got, want)
+    for splits in (1, 2):      # with splits, the split that owns the residual appends
+        want, want_k, want_v = run(False)
+        got, got_k, got_v = run(True)
+        assert torch.equal(got_k, want_k) and torch.equal(got_v, want_v)
+        assert not torch.equal(want_k, prob.k_pages)          # something was appended
+        assert torch.equal(got, want)
 
 
 @pytest.mark.parametrize("heads", [(32, 2), (32, 1)])
