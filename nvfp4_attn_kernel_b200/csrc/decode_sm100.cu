@@ -487,6 +487,24 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   }
 #endif
 
+  // A split of a short row often owns no page at all (the split count follows the longest row of
+  // the batch): such a CTA stores the empty partial and leaves before any set-up.  Only on the
+  // split path without the cross-GPU exchange, which counts the arrival of every split.
+  if (p.num_splits > 1 && p.emit_partial && !p.xchg_inbox) {
+    const TileWork w0 = resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x);
+    if (w0.last_page == w0.first_page && w0.tail_len == 0) {
+      if (tid < kHeadDim) {
+#pragma unroll
+        for (int q = 0; q < G; ++q) {
+          const int64_t idx = ((int64_t)w0.split * p.rows + w0.row) * p.heads_q + w0.kvh * G + q;
+          p.o_partial[idx * kHeadDim + tid] = 0.f;
+          if (tid == 0) p.lse_partial[idx] = -INFINITY;
+        }
+      }
+      return;
+    }
+  }
+
   // ---- set-up: barriers, tensor memory, zeroed operand tiles ----
   // Each producer warp prepares its own ring barriers and starts fetching before the CTA-wide
   // set-up barrier, so the first page tiles are in flight while tensor memory is allocated.
