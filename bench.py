@@ -669,11 +669,18 @@ def run_ragged(args) -> None:
     # as many splits as bring the longest piece to about 64 pages (measured here: 1 split 178 us,
     # 4 splits 112 us, 8 splits 131 us, 16 splits 163 us per step).  The lengths are host data in
     # a serving engine too (the scheduler's seq_lens).
+    # --balance-pages T cuts every row by its own length instead (pieces of about T pages).
     splits = args.num_splits
-    if splits <= 1:
+    balance = args.balance_pages if args.balance_pages > 0 else None
+    if balance:
+        splits = 1
+        space = torch.empty(_decode.balanced_workspace_bytes(rows, HQ, columns, balance),
+                            dtype=torch.uint8, device=device)
+    elif splits <= 1:
         splits = 1
         while int(lens.max() + total_steps) // PAGE > 64 * splits:
             splits *= 2
+    how = dict(balance_pages=balance, workspace=space) if balance else dict(num_splits=splits)
 
     def step():
         seq_lens.add_(1)
@@ -685,8 +692,8 @@ def run_ragged(args) -> None:
             fp4_page_table=block_table, seqused_fp4=ctl.seqused_fp4,
             residual_key_pages_bf16=tail_k[0], residual_value_pages_bf16=tail_v[0],
             residual_page_ids=ctl.row_to_slot, seqused_residual=ctl.seqused_residual,
-            softmax_scale=D ** -0.5, trusted_metadata=True, out=out, num_splits=splits,
-            append_key=k_new, append_value=v_new, key_shift=shift)
+            softmax_scale=D ** -0.5, trusted_metadata=True, out=out,
+            append_key=k_new, append_value=v_new, key_shift=shift, **how)
         L.check(lib.nvfp4_tail_flush(
             tail_k.data_ptr(), tail_v.data_ptr(), rows * PAGE, ctl.promotion_source_tokens.data_ptr(),
             ctl.promotion_pages.data_ptr(), bases.data_ptr(), block, block, block, block, rows, 1, HKV,
@@ -744,7 +751,9 @@ def run_ragged(args) -> None:
             "workload": "ragged serving step: 32 seq, lengths log-uniform in [128, 32768] growing one token "
                         "per step, BF16 tails, block tables from a shuffled pool of 20000 pages, key shift on",
             "step": "slot control plane + one decode launch (query quantised and K/V token appended "
-                    f"inside, {splits} KV splits" + (" + merge launch" if splits > 1 else "")
+                    "inside, " + (f"work list launch + pieces of {balance} pages per row + merge launch"
+                                  if balance else
+                                  f"{splits} KV splits" + (" + merge launch" if splits > 1 else ""))
                     + ") + tail flush, all timed",
             "l2": f"{kv / 1e6:.0f} MB of pages and tails per step against a 126 MB L2 (one cache, so a "
                   "part of it may be served from L2)",
@@ -754,7 +763,7 @@ def run_ragged(args) -> None:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": "measured" if peaks else "fallback",
                      "traffic": None},
-        "cpu_baseline": None, "e2e": None, "gpu_launches": reps * per_graph * (4 if splits > 1 else 3),
+        "cpu_baseline": None, "e2e": None, "gpu_launches": reps * per_graph * (5 if balance else 4 if splits > 1 else 3),
         "clocks": clocks, "control_plane_error_word": errors,
     }), flush=True)
 
@@ -767,6 +776,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--decode-impl", default="auto", choices=["auto", "generic", "sm100"])
     ap.add_argument("--num-splits", type=int, default=1)
+    ap.add_argument("--balance-pages", type=int, default=0,
+                    help="ragged workload: pieces of about this many pages per row (0: one split "
+                         "count for the batch)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ctx", type=int, default=CTX,
                     help="context length per sequence (default: the headline workload's 4096)")

@@ -353,6 +353,30 @@ int nvfp4_decode_exchange(const nvfp4_decode_args* args, const nvfp4_exchange_ar
 int nvfp4_probe_hbm_read(const void* ptr, size_t bytes, uint32_t* sink, void* stream);
 
 /*
+ * Split-KV decode with a split count per row ("balanced split").  No counterpart in the
+ * reference project, whose split count is one number for the whole batch
+ * (src/nvfp4_decode_kernel/_decode.py:1018-1049): in a ragged batch that number follows the
+ * longest row, so short rows are cut into pieces far smaller than a CTA's fixed cost is worth, or
+ * the long rows into pieces too long.
+ *
+ * Row r is cut into ceil(pages_r / target_pages) pieces (one piece if it has no FP4 page; its tail
+ * goes to the first piece, as in nvfp4_decode).  Each piece is computed exactly as split s of
+ * num_splits = that count would be, and the pieces of a row are merged by their log-sum-exp, so the
+ * result equals nvfp4_decode + nvfp4_lse_merge run row by row with that count.  Three launches on
+ * the stream (work list, decode, merge); the list is built on the device from seqused_fp4, so the
+ * call needs no host knowledge of the lengths and can be captured in a CUDA graph.
+ *
+ *  - args as for nvfp4_decode with num_splits = 1, out != NULL, o_partial = lse_partial =
+ *    out_indices = NULL, no NVFP4_DECODE_PROGRAMMATIC_LAUNCH; tensor-core kernel only.
+ *  - args.workspace must hold nvfp4_decode_balanced_workspace_bytes(rows, heads_q, max_pages,
+ *    target_pages) bytes (args.max_pages is the bound on a row's page count that the list's
+ *    capacity, nvfp4_decode_balanced_capacity, is derived from).
+ */
+int nvfp4_decode_balanced(const nvfp4_decode_args* args, int target_pages, void* stream);
+int64_t nvfp4_decode_balanced_capacity(int rows, int max_pages, int target_pages);
+size_t nvfp4_decode_balanced_workspace_bytes(int rows, int heads_q, int max_pages, int target_pages);
+
+/*
  * Split-KV decode for callers that cannot allocate.  No counterpart in the reference project
  * (its split path allocates and fills its partial buffers on every call,
  * src/nvfp4_decode_kernel/_decode.py:1051-1065).

@@ -41,6 +41,9 @@ EXPORTS = (
     "nvfp4_decode_exchange",
     "nvfp4_push_merge_inbox_floats",
     "nvfp4_decode_split_static",
+    "nvfp4_decode_balanced",
+    "nvfp4_decode_balanced_capacity",
+    "nvfp4_decode_balanced_workspace_bytes",
     "nvfp4_static_workspace_bytes",
     "nvfp4_decode_split_static_error",
 )
@@ -199,6 +202,12 @@ def _declare_control(lib) -> None:
 def _declare_static(lib) -> None:
     lib.nvfp4_decode_split_static.restype = c_int
     lib.nvfp4_decode_split_static.argtypes = [ctypes.POINTER(DecodeArgs), c_void_p]
+    lib.nvfp4_decode_balanced.restype = c_int
+    lib.nvfp4_decode_balanced.argtypes = [ctypes.POINTER(DecodeArgs), c_int, c_void_p]
+    lib.nvfp4_decode_balanced_capacity.restype = ctypes.c_int64
+    lib.nvfp4_decode_balanced_capacity.argtypes = [c_int, c_int, c_int]
+    lib.nvfp4_decode_balanced_workspace_bytes.restype = c_size_t
+    lib.nvfp4_decode_balanced_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
     lib.nvfp4_static_workspace_bytes.restype = c_size_t
     lib.nvfp4_static_workspace_bytes.argtypes = []
     lib.nvfp4_decode_split_static_error.restype = c_char_p

@@ -227,9 +227,50 @@ int nvfp4_decode_impl_available(int impl, int heads_q, int heads_kv) {
   return 0;
 }
 
-static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x, void* stream);
+static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x, int target_pages, void* stream);
 
-int nvfp4_decode(const nvfp4_decode_args* a, void* stream) { return decode_call(a, nullptr, stream); }
+int nvfp4_decode(const nvfp4_decode_args* a, void* stream) { return decode_call(a, nullptr, 0, stream); }
+
+// Balanced split: row r is cut into ceil(pages_r / target_pages) pieces (one if it has no page),
+// so the list of pieces is never longer than rows + rows * max_pages / target_pages.
+int64_t nvfp4_decode_balanced_capacity(int rows, int max_pages, int target_pages) {
+  if (rows <= 0 || max_pages < 0 || target_pages < 1) return 0;
+  return (int64_t)rows + (int64_t)rows * max_pages / target_pages;
+}
+
+namespace {
+struct BalancedLayout {
+  size_t o_part, lse_part, work, row_offset, row_count, total;
+};
+BalancedLayout balanced_layout(int rows, int heads_q, int64_t capacity) {
+  BalancedLayout l;
+  size_t at = 0;
+  auto take = [&](size_t bytes) { const size_t here = at; at += (bytes + 15) & ~(size_t)15; return here; };
+  l.o_part = take((size_t)capacity * heads_q * 128 * sizeof(float));
+  l.lse_part = take((size_t)capacity * heads_q * sizeof(float));
+  l.work = take((size_t)capacity * sizeof(int4));
+  l.row_offset = take((size_t)rows * sizeof(int32_t));
+  l.row_count = take((size_t)rows * sizeof(int32_t));
+  l.total = at;
+  return l;
+}
+}  // namespace
+
+size_t nvfp4_decode_balanced_workspace_bytes(int rows, int heads_q, int max_pages, int target_pages) {
+  const int64_t capacity = nvfp4_decode_balanced_capacity(rows, max_pages, target_pages);
+  if (capacity <= 0 || heads_q <= 0) return 0;
+  return balanced_layout(rows, heads_q, capacity).total;
+}
+
+int nvfp4_decode_balanced(const nvfp4_decode_args* a, int target_pages, void* stream) {
+  if (!a) return fail(NVFP4_ERR_INVALID, "decode: null argument block");
+  if (target_pages < 1) return fail(NVFP4_ERR_INVALID, "decode_balanced: target_pages must be at least 1, got %d", target_pages);
+  if (a->num_splits != 1 || !a->out || a->o_partial || a->lse_partial || a->out_indices)
+    return fail(NVFP4_ERR_INVALID,
+                "decode_balanced: the split is per row; give num_splits = 1, out, and neither partial "
+                "buffers nor out_indices");
+  return decode_call(a, nullptr, target_pages, stream);
+}
 
 int nvfp4_decode_exchange(const nvfp4_decode_args* a, const nvfp4_exchange_args* x, void* stream) {
   if (!x) return fail(NVFP4_ERR_INVALID, "decode_exchange: null exchange block");
@@ -243,10 +284,10 @@ int nvfp4_decode_exchange(const nvfp4_decode_args* a, const nvfp4_exchange_args*
     return fail(NVFP4_ERR_INVALID,
                 "decode_exchange: the merged rows go to the exchange block's out; give o_partial and "
                 "lse_partial for the local splits and leave args.out null");
-  return decode_call(a, x, stream);
+  return decode_call(a, x, 0, stream);
 }
 
-static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x, void* stream) {
+static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x, int target_pages, void* stream) {
   if (!a) return fail(NVFP4_ERR_INVALID, "decode: null argument block");
   if (a->rows < 0) return fail(NVFP4_ERR_INVALID, "decode: negative row count");
   if (a->rows == 0) return NVFP4_OK;
@@ -343,8 +384,25 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
 
   float* o_part = a->o_partial;
   float* lse_part = a->lse_partial;
-  const bool direct = a->num_splits == 1 && a->out != nullptr && !a->o_partial;
-  if (direct) {
+  const bool direct = a->num_splits == 1 && a->out != nullptr && !a->o_partial && !target_pages;
+  BalancedLayout bal{};
+  int64_t capacity = 0;
+  if (target_pages) {
+    capacity = nvfp4_decode_balanced_capacity(a->rows, a->max_pages, target_pages);
+    if (capacity > (int64_t)1 << 24)
+      return fail(NVFP4_ERR_INVALID, "decode_balanced: %lld pieces; raise target_pages", (long long)capacity);
+    bal = balanced_layout(a->rows, a->heads_q, capacity);
+    if (!a->workspace || a->workspace_bytes < bal.total)
+      return fail(NVFP4_ERR_INVALID, "decode_balanced: needs a workspace of %zu bytes, got %zu", bal.total,
+                  a->workspace_bytes);
+    if (!aligned16(a->workspace)) return fail(NVFP4_ERR_INVALID, "decode: workspace must be 16-byte aligned");
+    char* base = static_cast<char*>(a->workspace);
+    p.emit_partial = 1;
+    p.o_partial = o_part = reinterpret_cast<float*>(base + bal.o_part);
+    p.lse_partial = lse_part = reinterpret_cast<float*>(base + bal.lse_part);
+    p.work_list = reinterpret_cast<const int4*>(base + bal.work);
+    p.work_capacity = (int)capacity;
+  } else if (direct) {
     p.emit_partial = 0;
     p.out = static_cast<uint16_t*>(a->out);
     p.out_indices = a->out_indices;
@@ -386,6 +444,17 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
     p.xchg_world = x->world;
   }
   cudaError_t e;
+  if (target_pages) {
+    if (impl != NVFP4_IMPL_SM100 || !nvfp4::decode_sm100_supports(p) || p.pdl)
+      return fail(NVFP4_ERR_UNSUPPORTED,
+                  "decode_balanced: carried by the tensor-core kernel only, without programmatic launch");
+    char* base = static_cast<char*>(a->workspace);
+    e = nvfp4::launch_balanced_worklist(a->seqused_fp4, a->rows, a->max_pages, target_pages,
+                                        reinterpret_cast<int4*>(base + bal.work), (int)capacity,
+                                        reinterpret_cast<int32_t*>(base + bal.row_offset),
+                                        reinterpret_cast<int32_t*>(base + bal.row_count), a->status, st);
+    if (e != cudaSuccess) return cuda_fail(e, "work list launch");
+  }
   if (impl == NVFP4_IMPL_SM100) {
     if (!nvfp4::decode_sm100_supports(p))
       return fail(NVFP4_ERR_UNSUPPORTED, "decode: the tensor-core kernel takes 1, 2, 4, 8, 16 or 32 query heads per KV head");
@@ -397,7 +466,13 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   }
   if (e != cudaSuccess) return cuda_fail(e, "decode launch");
 
-  if (!direct && a->out) {
+  if (target_pages) {
+    const char* base = static_cast<const char*>(a->workspace);
+    e = nvfp4::launch_lse_merge_ranges(o_part, lse_part, reinterpret_cast<const int32_t*>(base + bal.row_offset),
+                                       reinterpret_cast<const int32_t*>(base + bal.row_count), a->rows,
+                                       a->heads_q, a->out, st);
+    if (e != cudaSuccess) return cuda_fail(e, "lse_merge launch");
+  } else if (!direct && a->out) {
     e = nvfp4::launch_lse_merge(o_part, (int64_t)a->rows * a->heads_q * 128, lse_part,
                                 (int64_t)a->rows * a->heads_q, nullptr, nullptr, a->num_splits,
                                 a->rows, a->heads_q, a->out, 0, a->out_indices, nullptr, st);

@@ -15,6 +15,7 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 struct TileWork {
   int row, kvh, split;
+  int64_t slot;               // where this CTA's partial goes: index into [slots][heads_q]
   int first_page, last_page;  // logical FP4 pages [first, last) owned by this split
   int tail_len;               // BF16 tail tokens owned by this split (0 if none)
   int tail_id;
@@ -47,16 +48,17 @@ __device__ __forceinline__ void set_status(uint32_t* status, uint32_t bit) {
 // Resolve what this CTA owns.  Metadata is device-resident and, on the trusted
 // path, unchecked by the host: anything out of range is clamped, flagged in the
 // sticky status word and never turned into an address.
-__device__ __forceinline__ TileWork resolve_work(const DecodeParams& p, int row, int kvh, int split) {
+__device__ __forceinline__ TileWork resolve_work(const DecodeParams& p, int row, int kvh, int split,
+                                                 int num_splits, int64_t slot) {
   TileWork w;
-  w.row = row; w.kvh = kvh; w.split = split;
+  w.row = row; w.kvh = kvh; w.split = split; w.slot = slot;
   int fp4 = p.seqused_fp4[row];
   int n = fp4 >> 7;
   if (fp4 < 0 || (fp4 & 127) || n > p.max_pages) {
     set_status(p.status, NVFP4_STATUS_BAD_LENGTH);
     n = fp4 < 0 ? 0 : (n > p.max_pages ? p.max_pages : n);
   }
-  const int per = (n + p.num_splits - 1) / p.num_splits;
+  const int per = (n + num_splits - 1) / num_splits;
   w.first_page = min(split * per, n);
   w.last_page = min((split + 1) * per, n);
   w.tail_len = 0;
@@ -75,6 +77,12 @@ __device__ __forceinline__ TileWork resolve_work(const DecodeParams& p, int row,
     }
   }
   return w;
+}
+
+// The classic grid (splits, heads_kv, rows): block (x, y, z) is split x of KV head y of row z.
+__device__ __forceinline__ TileWork resolve_grid_work(const DecodeParams& p) {
+  return resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x, p.num_splits,
+                      (int64_t)blockIdx.x * p.rows + blockIdx.z);
 }
 
 // max over the 128 softmax threads of G per-thread values; red is [4][G] floats.
@@ -113,6 +121,12 @@ __device__ __forceinline__ void block_sum_128(float (&v)[G], float* red, int tid
 __device__ __forceinline__ float exp2_rel(float z, float m) {
   return (m == -INFINITY) ? 0.f : exp2f(z - m);
 }
+
+// Value loads (8 bytes: four channels of a position) in flight per thread while the tail is
+// walked.  The walk is latency-bound, so this sets its number of round trips to memory; more
+// than four in flight costs the tensor-core kernel's main loop registers (measured: 8 in flight
+// +0.5 us, 16 in flight +2.8 us on a batch without any tail).
+constexpr int kTailValueBatch = 4;
 
 // The BF16 tail block, first half: thread = kv position.  Seeds the running max m and the
 // per-thread partial sums l, and leaves P (rounded to BF16, as floats) in pf[G][128].
@@ -191,34 +205,81 @@ __device__ __forceinline__ void tail_scores(const DecodeParams& p, const TileWor
   }
 }
 
-// Second half: thread = channel d, o[q] = sum_t P[q][t] * V[t][d].  The caller orders the
-// pf writes of tail_scores before this.  Positions past the tail length are never read, so
-// stale or non-finite bytes there cannot reach the output.
+// Second half: o[q] = sum_t P[q][t] * V[t][d], and thread tid ends up with channel d = tid.
+// The caller orders the pf writes of tail_scores before this; all 32 lanes of every calling
+// warp must be here.  The walk is latency-bound, so it is laid out for few round trips: a lane
+// takes four channels (8-byte loads) of every fourth position, kTailValueBatch loads in flight
+// at a time, and the four position lanes of a channel group are folded by shuffles at the end.
+// Positions past the tail length are never read, so stale or non-finite bytes there cannot
+// reach the output (their P is zero and their V is taken as zero).
+template <int G>
+__device__ __forceinline__ void tail_pv_walk(const uint16_t* vbase, int64_t vstride, const uint16_t* vnew,
+                                             int len, int fresh, const float* pf, int tid, float (&o)[G]) {
+  constexpr int kChunk = G < 4 ? G : 4;   // query heads per pass over the tail
+  const int plane = tid & 3;
+#pragma unroll
+  for (int q0 = 0; q0 < G; q0 += kChunk) {
+    float acc[kChunk][4];
+#pragma unroll
+    for (int q = 0; q < kChunk; ++q)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[q][i] = 0.f;
+#pragma unroll 1
+    for (int jb = 0; jb < 32 && 4 * jb < len; jb += kTailValueBatch) {
+      uint2 v[kTailValueBatch];
+#pragma unroll
+      for (int j = 0; j < kTailValueBatch; ++j) {
+        const int t = plane + 4 * (jb + j);
+        v[j] = make_uint2(0u, 0u);
+        if (t < len)
+          v[j] = __ldg(reinterpret_cast<const uint2*>(t == fresh ? vnew : vbase + t * vstride));
+      }
+#pragma unroll
+      for (int j = 0; j < kTailValueBatch; ++j) {
+        const int t = plane + 4 * (jb + j);
+        if (q0 == 0 && t == fresh)
+          *reinterpret_cast<uint2*>(const_cast<uint16_t*>(vbase) + t * vstride) = v[j];
+        const float vf[4] = {__uint_as_float(v[j].x << 16), __uint_as_float(v[j].x & 0xffff0000u),
+                             __uint_as_float(v[j].y << 16), __uint_as_float(v[j].y & 0xffff0000u)};
+#pragma unroll
+        for (int q = 0; q < kChunk; ++q) {
+          const float pw = pf[(q0 + q) * kHeadDim + t];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[q][i] = fmaf(pw, vf[i], acc[q][i]);
+        }
+      }
+    }
+    // fold the four position lanes; lane `plane` keeps channel ch0 + plane, which is channel tid
+    const bool up2 = (plane & 2) != 0, up1 = (plane & 1) != 0;
+#pragma unroll
+    for (int q = 0; q < kChunk; ++q) {
+      float k0 = up2 ? acc[q][2] : acc[q][0], k1 = up2 ? acc[q][3] : acc[q][1];
+      const float s0 = up2 ? acc[q][0] : acc[q][2], s1 = up2 ? acc[q][1] : acc[q][3];
+      k0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+      k1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+      float r = up1 ? k1 : k0;
+      const float s = up1 ? k0 : k1;
+      r += __shfl_xor_sync(0xffffffffu, s, 1);
+      o[q0 + q] = r;
+    }
+  }
+}
+
 template <int G>
 __device__ __forceinline__ void tail_pv(const DecodeParams& p, const TileWork& w, const float* pf,
                                         int tid, float (&o)[G]) {
   const int len = w.tail_len;
+  const int ch0 = (tid & ~31) + ((tid & 31) >> 2) * 4;
   const int64_t tok0 = (int64_t)w.tail_id * kPage;
-  const uint16_t* vcol = p.tail_value + (tok0 * p.heads_kv + w.kvh) * kHeadDim + tid;
   const int64_t vstride = (int64_t)p.heads_kv * kHeadDim;
-#pragma unroll
-  for (int q = 0; q < G; ++q) o[q] = 0.f;
+  const uint16_t* vbase = p.tail_value + (tok0 * p.heads_kv + w.kvh) * kHeadDim + ch0;
   // with the step's own token given, the last position comes from the source and is stored
-  const int stored = p.append_value != nullptr ? len - 1 : len;
-#pragma unroll 4
-  for (int t = 0; t < stored; ++t) {
-    const float v = bf16_bits_to_f32(__ldg(vcol + t * vstride));
-#pragma unroll
-    for (int q = 0; q < G; ++q) o[q] = fmaf(pf[q * kHeadDim + t], v, o[q]);
-  }
-  if (stored < len) {
-    const uint16_t bits = __ldg(p.append_value + (int64_t)w.row * p.append_value_stride +
-                                (int64_t)w.kvh * kHeadDim + tid);
-    const_cast<uint16_t*>(vcol)[stored * vstride] = bits;
-    const float v = bf16_bits_to_f32(bits);
-#pragma unroll
-    for (int q = 0; q < G; ++q) o[q] = fmaf(pf[q * kHeadDim + stored], v, o[q]);
-  }
+  const int fresh = p.append_value != nullptr ? len - 1 : -1;
+  const uint16_t* vnew = p.append_value != nullptr
+                             ? p.append_value + (int64_t)w.row * p.append_value_stride +
+                                   (int64_t)w.kvh * kHeadDim + ch0
+                             : nullptr;
+  tail_pv_walk<G>(vbase, vstride, vnew, len, fresh, pf, tid, o);
 }
 
 // Both halves on the same 128 threads (the CUDA-core kernel).
@@ -243,7 +304,7 @@ __device__ __forceinline__ void write_output(const DecodeParams& p, const TileWo
     const int head = w.kvh * G + q;
     const float val = l[q] > 0.f ? __fdiv_rn(o[q], l[q]) : 0.f;
     if (p.emit_partial) {
-      const int64_t idx = ((int64_t)w.split * p.rows + w.row) * p.heads_q + head;
+      const int64_t idx = w.slot * p.heads_q + head;
       p.o_partial[idx * kHeadDim + tid] = val;
       if (tid == 0)
         p.lse_partial[idx] = l[q] > 0.f ? (m[q] + log2f(l[q])) * kLn2 : -INFINITY;

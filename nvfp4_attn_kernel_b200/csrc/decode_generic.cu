@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(128) decode_generic_kernel(const DecodeParams 
   extern __shared__ __align__(16) uint8_t smem_raw[];
   GenericSmem<G>& sm = *reinterpret_cast<GenericSmem<G>*>(smem_raw);
   const int tid = threadIdx.x;
-  const TileWork w = resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x);
+  const TileWork w = resolve_grid_work(p);
 
   // ---- query: dequantise the G heads of this KV head ----
   for (int it = tid; it < G * 8; it += 128) {

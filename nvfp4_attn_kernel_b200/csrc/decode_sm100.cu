@@ -487,16 +487,30 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   }
 #endif
 
+  // Which work this CTA has.  With a work list (balanced split) the entry says so; otherwise the
+  // block index does.  row_of_block is what the early page-table fetch below may use before the
+  // row's lengths are known.
+  int row_of_block = blockIdx.z;
+  int4 entry = make_int4(0, 0, 0, 0);
+  if (p.work_list) {
+    entry = __ldg(p.work_list + blockIdx.x);
+    if (entry.x < 0) return;   // past the end of the list
+    row_of_block = entry.x;
+  }
+  auto resolve = [&]() {
+    return p.work_list ? resolve_work(p, entry.x, blockIdx.y, entry.y, entry.z, (int64_t)blockIdx.x)
+                       : resolve_grid_work(p);
+  };
   // A split of a short row often owns no page at all (the split count follows the longest row of
   // the batch): such a CTA stores the empty partial and leaves before any set-up.  Only on the
   // split path without the cross-GPU exchange, which counts the arrival of every split.
-  if (p.num_splits > 1 && p.emit_partial && !p.xchg_inbox) {
-    const TileWork w0 = resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x);
+  if ((p.num_splits > 1 || p.work_list) && p.emit_partial && !p.xchg_inbox) {
+    const TileWork w0 = resolve();
     if (w0.last_page == w0.first_page && w0.tail_len == 0) {
       if (tid < kHeadDim) {
 #pragma unroll
         for (int q = 0; q < G; ++q) {
-          const int64_t idx = ((int64_t)w0.split * p.rows + w0.row) * p.heads_q + w0.kvh * G + q;
+          const int64_t idx = w0.slot * p.heads_q + w0.kvh * G + q;
           p.o_partial[idx * kHeadDim + tid] = 0.f;
           if (tid == 0) p.lse_partial[idx] = -INFINITY;
         }
@@ -531,7 +545,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int col = lane + 32 * j;
-      if (col < p.max_pages) spec[j] = __ldg(p.page_table + (int64_t)blockIdx.z * p.page_table_row_stride + col);
+      if (col < p.max_pages) spec[j] = __ldg(p.page_table + (int64_t)row_of_block * p.page_table_row_stride + col);
     }
   }
   if (tid == 0) {
@@ -564,7 +578,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     if (!p.q_fp4)
       for (int i = wt; i < kSfBlockBytes / 16; i += kWorkers) reinterpret_cast<uint4*>(sm.q_sf)[i] = make_uint4(0, 0, 0, 0);
   }
-  const TileWork w = resolve_work(p, blockIdx.z, blockIdx.y, blockIdx.x);
+  const TileWork w = resolve();
   const int n_pages = w.last_page - w.first_page;
   const int n_batches = (n_pages + kBatch - 1) / kBatch;
 
@@ -842,7 +856,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         const int head = w.kvh * G + q;
         const float val = lq > 0.f ? __fdiv_rn(o[q], lq) : 0.f;
         if (p.emit_partial) {
-          const int64_t idx = ((int64_t)w.split * p.rows + w.row) * p.heads_q + head;
+          const int64_t idx = w.slot * p.heads_q + head;
           p.o_partial[idx * kHeadDim + t] = val;
           if (t == 0) p.lse_partial[idx] = lq > 0.f ? (mq + log2f(lq)) * kLn2 : -INFINITY;
         } else {
@@ -1085,6 +1099,7 @@ static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const 
   }
 #endif
   dim3 grid(p.num_splits, p.heads_kv, p.rows);
+  if (p.work_list) grid = dim3(p.work_capacity, p.heads_kv, 1);
   if (p.pdl) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;

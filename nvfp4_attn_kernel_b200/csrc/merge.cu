@@ -281,3 +281,107 @@ cudaError_t launch_push_merge(const float* o_local, int64_t o_split_stride, cons
 }
 
 }  // namespace nvfp4
+
+// ---------------------------------------------------------------------------
+// Balanced split: every row gets its own split count, ceil(pages / target_pages) (at least
+// one), so that each CTA walks about target_pages pages however ragged the batch is.
+// ---------------------------------------------------------------------------
+namespace nvfp4 {
+
+// One CTA.  Rows are taken 1024 at a time; within a chunk an inclusive scan over the rows'
+// split counts gives each row its first slot.  Entries past the end get row -1.
+__global__ void __launch_bounds__(1024)
+balanced_worklist_kernel(const int32_t* __restrict__ seqused_fp4, int rows, int max_pages, int target_pages,
+                         int4* __restrict__ work, int capacity, int32_t* __restrict__ row_offset,
+                         int32_t* __restrict__ row_count, uint32_t* __restrict__ status) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < rows; base += 1024) {
+    const int row = base + tid;
+    int count = 0;
+    if (row < rows) {
+      int fp4 = seqused_fp4[row];
+      int n = fp4 >> 7;
+      if (fp4 < 0 || n > max_pages) n = fp4 < 0 ? 0 : max_pages;   // the decode kernel reports it
+      count = n > 0 ? (n + target_pages - 1) / target_pages : 1;   // a row without pages may own a tail
+    }
+    int scan = count;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, scan, o);
+      if (lane >= o) scan += v;
+    }
+    if (lane == 31) warp_sums[warp] = scan;
+    __syncthreads();
+    if (warp == 0) {
+      int v = warp_sums[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+      }
+      warp_sums[lane] = v;
+    }
+    __syncthreads();
+    const int first = carry + (warp ? warp_sums[warp - 1] : 0) + scan - count;
+    if (row < rows) {
+      row_offset[row] = first;
+      row_count[row] = count;
+      for (int s = 0; s < count; ++s) {
+        if (first + s < capacity) work[first + s] = make_int4(row, s, count, 0);
+        else set_status(status, NVFP4_STATUS_BAD_LENGTH);   // cannot happen with the documented capacity
+      }
+    }
+    __syncthreads();
+    if (tid == 1023) carry = first + count;
+    __syncthreads();
+  }
+  for (int w = carry + tid; w < capacity; w += 1024) work[w] = make_int4(-1, 0, 0, 0);
+}
+
+// LSE merge where row r's partials are slots [row_offset[r], row_offset[r] + row_count[r]).
+__global__ void __launch_bounds__(128)
+lse_merge_ranges_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
+                        const int32_t* __restrict__ row_offset, const int32_t* __restrict__ row_count,
+                        int heads_q, uint16_t* __restrict__ out) {
+  const int head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
+  const int first = row_offset[row], count = row_count[row];
+  float mx = -INFINITY;
+  for (int s = 0; s < count; ++s) mx = fmaxf(mx, lse_parts[(int64_t)(first + s) * heads_q + head]);
+  float acc = 0.f, tot = 0.f;
+  if (mx != -INFINITY) {
+    for (int s = 0; s < count; ++s) {
+      const int64_t idx = (int64_t)(first + s) * heads_q + head;
+      const float ls = lse_parts[idx];
+      if (ls == -INFINITY) continue;
+      const float wgt = expf(ls - mx);
+      tot += wgt;
+      acc = fmaf(wgt, o_parts[idx * kHeadDim + d], acc);
+    }
+  }
+  const float val = tot > 0.f ? __fdiv_rn(acc, tot) : 0.f;
+  out[((int64_t)row * heads_q + head) * kHeadDim + d] = __bfloat16_as_ushort(__float2bfloat16_rn(val));
+}
+
+cudaError_t launch_balanced_worklist(const int32_t* seqused_fp4, int rows, int max_pages, int target_pages,
+                                     int4* work, int capacity, int32_t* row_offset, int32_t* row_count,
+                                     uint32_t* status, cudaStream_t stream) {
+  balanced_worklist_kernel<<<1, 1024, 0, stream>>>(seqused_fp4, rows, max_pages, target_pages, work, capacity,
+                                                   row_offset, row_count, status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_lse_merge_ranges(const float* o_parts, const float* lse_parts, const int32_t* row_offset,
+                                    const int32_t* row_count, int rows, int heads_q, void* out,
+                                    cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  dim3 grid(heads_q, rows);
+  lse_merge_ranges_kernel<<<grid, 128, 0, stream>>>(o_parts, lse_parts, row_offset, row_count, heads_q,
+                                                    static_cast<uint16_t*>(out));
+  return cudaGetLastError();
+}
+
+}  // namespace nvfp4

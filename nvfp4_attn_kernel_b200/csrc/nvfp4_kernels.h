@@ -91,6 +91,11 @@ struct DecodeParams {
   const uint16_t* append_key; const uint16_t* append_value;   // bf16 [rows][heads_kv][128], token strides below
   int64_t append_key_stride, append_value_stride;             // elements
   const uint16_t* key_shift;                                   // nullable bf16 [heads_kv][128]
+  // Work list of the balanced split (null: the grid is (splits, heads_kv, rows)).  Entry w =
+  // {row, split, splits of that row, unused}, row -1 = no work; the grid is (entries, heads_kv)
+  // and entry w stores its partial in slot w.
+  const int4* work_list;
+  int work_capacity;
 };
 
 // CUDA-core kernel: any G = Hq/Hkv in {1,2,4,8,16,32}.
@@ -122,6 +127,15 @@ cudaError_t launch_work_table(const int32_t* query_start_loc, const int32_t* seq
                               int64_t block_table_stride, int32_t* source_tokens,
                               int32_t* destination_pages, int num_reqs, int columns_per_row,
                               cudaStream_t stream);
+
+// Balanced split: a split count per row (ceil(pages / target_pages), at least 1).
+// work [capacity] entries, row_offset / row_count [rows]: first partial slot and split count of a row.
+cudaError_t launch_balanced_worklist(const int32_t* seqused_fp4, int rows, int max_pages, int target_pages,
+                                     int4* work, int capacity, int32_t* row_offset, int32_t* row_count,
+                                     uint32_t* status, cudaStream_t stream);
+cudaError_t launch_lse_merge_ranges(const float* o_parts, const float* lse_parts, const int32_t* row_offset,
+                                    const int32_t* row_count, int rows, int heads_q, void* out,
+                                    cudaStream_t stream);
 
 cudaError_t launch_peer_merge(const float* const* o_ptrs, const float* const* lse_ptrs,
                               int* const* flag_ptrs, int rank, int world, int epoch,

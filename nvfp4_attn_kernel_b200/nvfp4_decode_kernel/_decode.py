@@ -106,6 +106,11 @@ def _any(condition: torch.Tensor, message: str) -> None:
         raise ValueError(message)
 
 
+def balanced_workspace_bytes(rows: int, heads_q: int, max_pages: int, balance_pages: int) -> int:
+    """Bytes of workspace a ``balance_pages`` decode of this shape needs."""
+    return int(_lib.load().nvfp4_decode_balanced_workspace_bytes(rows, heads_q, max_pages, balance_pages))
+
+
 def decode_fp4(
     *,
     query_fp4: torch.Tensor | None,
@@ -137,8 +142,15 @@ def decode_fp4(
     append_key: torch.Tensor | None = None,
     append_value: torch.Tensor | None = None,
     key_shift: torch.Tensor | None = None,
+    balance_pages: int | None = None,
+    workspace: torch.Tensor | None = None,
 ) -> torch.Tensor | None:
     """Validate every tensor contract and launch the decode on the current stream.
+
+    ``balance_pages`` (an extension): cut every row into pieces of about that many FP4 pages,
+    each row by its own length, instead of one ``num_splits`` for the whole batch; ``workspace``
+    (uint8, ``balanced_workspace_bytes`` long) may be passed to keep the call free of
+    allocations.
 
     ``query_padded_bf16`` (``[rows, 128, heads_q, 128]``, row 0 of each tile live)
     carries the BF16 query that meets the BF16 residual page.
@@ -422,8 +434,23 @@ def decode_fp4(
 
     if out is None and _partials is None:
         out = torch.empty(rows, heads_q, HEAD_DIM, dtype=torch.bfloat16, device=device)
-    workspace = None
-    if num_splits > 1 and _partials is None:
+    if balance_pages is not None:
+        if not isinstance(balance_pages, int) or balance_pages < 1:
+            raise ValueError(f"balance_pages must be a positive integer, got {balance_pages!r}")
+        if num_splits != 1 or _partials is not None or out_indices is not None or _exchange is not None:
+            raise ValueError("balance_pages replaces num_splits; it takes neither partial buffers, "
+                             "out_indices nor the cross-GPU exchange")
+        if programmatic_launch:
+            raise ValueError("balance_pages cannot be combined with programmatic_launch")
+        need = balanced_workspace_bytes(rows, heads_q, fp4_page_table.shape[1], balance_pages)
+        if workspace is None:
+            workspace = torch.empty(need, dtype=torch.uint8, device=device)
+        elif (workspace.dtype is not torch.uint8 or workspace.device != device or workspace.numel() < need
+              or not workspace.is_contiguous() or workspace.data_ptr() % 16):
+            raise ValueError(f"workspace must be contiguous 16-byte aligned uint8 of at least {need} bytes")
+    elif workspace is not None:
+        raise ValueError("workspace is only taken together with balance_pages")
+    elif num_splits > 1 and _partials is None:
         need = _lib.load().nvfp4_decode_workspace_bytes(rows, heads_q, num_splits)
         workspace = torch.empty(need, dtype=torch.uint8, device=device)
 
@@ -488,7 +515,9 @@ def decode_fp4(
         raise ValueError("fp4_page_table rows overlap")
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream(device).cuda_stream
-        if _exchange is not None:   # an _lib.ExchangeArgs: decode and cross-GPU exchange in one launch
+        if balance_pages is not None:
+            _lib.check(_lib.load().nvfp4_decode_balanced(args, balance_pages, stream))
+        elif _exchange is not None:   # an _lib.ExchangeArgs: decode and cross-GPU exchange in one launch
             _lib.check(_lib.load().nvfp4_decode_exchange(args, _exchange, stream))
         else:
             _lib.check(_lib.load().nvfp4_decode(args, stream))

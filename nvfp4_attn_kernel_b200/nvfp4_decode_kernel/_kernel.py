@@ -139,6 +139,8 @@ def fp4_decode_impl(
     append_key=None,
     append_value=None,
     key_shift=None,
+    balance_pages=None,
+    balance_workspace=None,
 ):
     from ._decode import decode_fp4, decode_fp4_split
     from ._quantize import quantize_query
@@ -147,7 +149,10 @@ def fp4_decode_impl(
         raise ValueError(f"num_splits must be a positive power of two, got {num_splits!r}")
 
     plan_key = None
-    if CACHE_CALL_PLANS and trusted_metadata and num_splits == 1 and query_row_indices is None:
+    if balance_pages is not None and num_splits != 1:
+        raise ValueError("balance_pages sets a split count per row; leave num_splits at 1")
+    if (CACHE_CALL_PLANS and trusted_metadata and num_splits == 1 and query_row_indices is None
+            and balance_pages is None):
         plan_key = (
             _sig(query), _sig(key_pages_fp4), _sig(key_scales), _sig(value_pages_fp4), _sig(value_scales),
             _sig(fp4_page_table), _sig(seqused_fp4), _sig(query_fp4), _sig(query_scales),
@@ -215,6 +220,11 @@ def fp4_decode_impl(
     complete = all(item is not None for item in residual)
     absent = all(item is None for item in residual) and has_bf16 is None
     splittable = absent or (complete and bf16_query)
+    if balance_pages is not None and not splittable:
+        raise ValueError(
+            "balance_pages needs either no residual argument at all or a complete residual on the "
+            "BF16 query path, like num_splits > 1"
+        )
     if num_splits > 1 and not splittable:
         raise ValueError(
             "num_splits > 1 needs either no residual argument at all or a "
@@ -251,6 +261,9 @@ def fp4_decode_impl(
         shared.update(append_key=append_key, append_value=append_value, key_shift=key_shift)
     if num_splits > 1:
         return decode_fp4_split(**shared, num_splits=num_splits)
+    if balance_pages is not None:
+        return decode_fp4(**shared, out_indices=out_indices, balance_pages=balance_pages,
+                          workspace=balance_workspace)
     # a call that is ONE launch (query quantised in the kernel, or quantised by the caller) can
     # be repeated from its argument block
     sink = [] if plan_key is not None and (query_bf16 is not None or not bf16_query) else None

@@ -496,3 +496,72 @@ def test_wide_groups_run_on_the_tensor_core_kernel(cuda_device, heads):
     assert np.abs(out - want).max() <= TOL, np.abs(out - want).max()
     assert np.abs(split - prob.oracle_from_bytes(splits=2)).max() <= TOL
     assert np.abs(out - generic).max() <= TOL
+
+
+@pytest.mark.parametrize("target", [1, 3, 8])
+def test_balanced_split_gives_every_row_its_own_split_count(cuda_device, target):
+    """Row r is cut into ceil(pages_r / target) ranges: checked row by row against the oracle
+    run with that row's count, and against the library's own uniform split of that row."""
+    _set_impl("auto")
+    lengths = (1024 + 17, 128 * 5, 60, 128 * 13, 128)
+    case = inputs.attention_case(61, len(lengths), 8, 2, lengths, 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    out = to_np(prob.decode(balance_pages=target))
+    for row, length in enumerate(lengths):
+        pages = length // 128
+        count = max(1, -(-pages // target))
+        want = prob.oracle_from_bytes(rows=[row], splits=count)
+        assert np.abs(out[row] - want[0]).max() <= TOL, (row, count)
+    # a uniform batch cut into a power-of-two count: the very bytes of num_splits = that count
+    even = inputs.attention_case(62, 3, 8, 2, (128 * 8 + 5, 128 * 8, 128 * 8 + 127), 1.0, 0.0)
+    prob = Problem(even, cuda_device)
+    assert torch.equal(prob.decode(balance_pages=2), prob.decode(num_splits=4))
+
+
+def test_balanced_split_workspace_graph_replay_and_refusals(cuda_device):
+    from nvfp4_attn_kernel_b200 import _lib
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel._decode import balanced_workspace_bytes
+
+    _set_impl("auto")
+    lengths = (128 * 9 + 3, 128 * 2 + 90, 128 * 30)
+    case = inputs.attention_case(63, len(lengths), 8, 2, lengths, 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    columns = prob.page_table.shape[1]
+    need = balanced_workspace_bytes(3, 8, columns, 4)
+    capacity = _lib.load().nvfp4_decode_balanced_capacity(3, columns, 4)
+    assert capacity == 3 + 3 * columns // 4
+    assert need >= capacity * 8 * 129 * 4 + capacity * 16 + 2 * 3 * 4
+    # garbage in the workspace must not matter: every slot the merge reads is written by the call
+    space = torch.randint(0, 256, (need,), dtype=torch.uint8, device=cuda_device)
+    out = torch.empty(3, 8, 128, dtype=torch.bfloat16, device=cuda_device)
+    first = prob.decode(balance_pages=4, balance_workspace=space, out=out, trusted_metadata=True).clone()
+    want = to_np(first)
+    for row, length in enumerate(lengths):
+        ref = prob.oracle_from_bytes(rows=[row], splits=-(-(length // 128) // 4))
+        assert np.abs(want[row] - ref[0]).max() <= TOL
+    # the three launches replay from a CUDA graph after the lengths change on the device
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        prob.decode(balance_pages=4, balance_workspace=space, out=out, trusted_metadata=True)
+    out.zero_()
+    graph.replay()
+    assert torch.equal(out, first)
+    prob.seqused_fp4.copy_(torch.tensor([128 * 2, 128 * 1, 128 * 17], dtype=torch.int32))
+    graph.replay()
+    torch.cuda.synchronize()
+    shorter = to_np(out)
+    case2 = dict(case)
+    case2["seqused_fp4"] = np.array([256, 128, 128 * 17], dtype=np.int32)
+    prob.case = case2
+    for row, pages in enumerate((2, 1, 17)):
+        ref = prob.oracle_from_bytes(rows=[row], splits=-(-pages // 4))
+        assert np.abs(shorter[row] - ref[0]).max() <= TOL
+    with pytest.raises(ValueError, match="balance_pages"):
+        prob.decode(balance_pages=4, num_splits=2)
+    with pytest.raises(ValueError, match="balance_pages"):
+        prob.decode(balance_pages=0)
+    with pytest.raises(ValueError, match="workspace"):
+        prob.decode(balance_pages=4, balance_workspace=space[: need - 16])
+    with pytest.raises(ValueError, match="out_indices"):
+        prob.decode(balance_pages=4, out=out,
+                    out_indices=torch.arange(3, dtype=torch.int32, device=cuda_device))
