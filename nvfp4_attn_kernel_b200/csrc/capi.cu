@@ -389,7 +389,7 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   int64_t capacity = 0;
   if (target_pages) {
     capacity = nvfp4_decode_balanced_capacity(a->rows, a->max_pages, target_pages);
-    if (capacity > (int64_t)1 << 24)
+    if (capacity > 65535)
       return fail(NVFP4_ERR_INVALID, "decode_balanced: %lld pieces; raise target_pages", (long long)capacity);
     bal = balanced_layout(a->rows, a->heads_q, capacity);
     if (!a->workspace || a->workspace_bytes < bal.total)

@@ -493,12 +493,12 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   int row_of_block = blockIdx.z;
   int4 entry = make_int4(0, 0, 0, 0);
   if (p.work_list) {
-    entry = __ldg(p.work_list + blockIdx.x);
+    entry = __ldg(p.work_list + blockIdx.y);   // the grid is (KV heads, list entries)
     if (entry.x < 0) return;   // past the end of the list
     row_of_block = entry.x;
   }
   auto resolve = [&]() {
-    return p.work_list ? resolve_work(p, entry.x, blockIdx.y, entry.y, entry.z, (int64_t)blockIdx.x)
+    return p.work_list ? resolve_work(p, entry.x, blockIdx.x, entry.y, entry.z, (int64_t)blockIdx.y)
                        : resolve_grid_work(p);
   };
   // A split of a short row often owns no page at all (the split count follows the longest row of
@@ -1099,7 +1099,9 @@ static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const 
   }
 #endif
   dim3 grid(p.num_splits, p.heads_kv, p.rows);
-  if (p.work_list) grid = dim3(p.work_capacity, p.heads_kv, 1);
+  // CTAs start in the order of their linear index, x fastest: all KV heads of the first list
+  // entry, then of the second, ... - and the list holds the longest pieces first
+  if (p.work_list) grid = dim3(p.heads_kv, p.work_capacity, 1);
   if (p.pdl) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;

@@ -288,58 +288,55 @@ cudaError_t launch_push_merge(const float* o_local, int64_t o_split_stride, cons
 // ---------------------------------------------------------------------------
 namespace nvfp4 {
 
-// One CTA.  Rows are taken 1024 at a time; within a chunk an inclusive scan over the rows'
-// split counts gives each row its first slot.  Entries past the end get row -1.
+// One CTA.  The pieces are listed longest first (sixteen size classes; within a class in no
+// particular order - a row's result does not depend on where its pieces sit), because the
+// CTAs of the decode grid start in list order and the last ones to start should be the short
+// ones.  Entries past the end get row -1.
+constexpr int kSizeClasses = 16;
+
+__device__ __forceinline__ void balanced_row(const int32_t* seqused_fp4, int row, int max_pages, int target_pages,
+                                             int& count, int& size_class) {
+  const int fp4 = seqused_fp4[row];
+  int n = fp4 >> 7;
+  if (fp4 < 0 || n > max_pages) n = fp4 < 0 ? 0 : max_pages;   // the decode kernel reports it
+  count = n > 0 ? (n + target_pages - 1) / target_pages : 1;   // a row without pages may own a tail
+  const int piece = (n + count - 1) / count;                   // pages of the row's longest piece
+  size_class = kSizeClasses - 1 - min(kSizeClasses - 1, piece * kSizeClasses / (target_pages + 1));
+}
+
 __global__ void __launch_bounds__(1024)
 balanced_worklist_kernel(const int32_t* __restrict__ seqused_fp4, int rows, int max_pages, int target_pages,
                          int4* __restrict__ work, int capacity, int32_t* __restrict__ row_offset,
                          int32_t* __restrict__ row_count, uint32_t* __restrict__ status) {
-  __shared__ int warp_sums[32];
-  __shared__ int carry;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) carry = 0;
+  __shared__ int class_total[kSizeClasses], class_cursor[kSizeClasses];
+  __shared__ int used;
+  const int tid = threadIdx.x;
+  if (tid < kSizeClasses) class_total[tid] = 0;
   __syncthreads();
-  for (int base = 0; base < rows; base += 1024) {
-    const int row = base + tid;
-    int count = 0;
-    if (row < rows) {
-      int fp4 = seqused_fp4[row];
-      int n = fp4 >> 7;
-      if (fp4 < 0 || n > max_pages) n = fp4 < 0 ? 0 : max_pages;   // the decode kernel reports it
-      count = n > 0 ? (n + target_pages - 1) / target_pages : 1;   // a row without pages may own a tail
-    }
-    int scan = count;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, scan, o);
-      if (lane >= o) scan += v;
-    }
-    if (lane == 31) warp_sums[warp] = scan;
-    __syncthreads();
-    if (warp == 0) {
-      int v = warp_sums[lane];
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int u = __shfl_up_sync(0xffffffffu, v, o);
-        if (lane >= o) v += u;
-      }
-      warp_sums[lane] = v;
-    }
-    __syncthreads();
-    const int first = carry + (warp ? warp_sums[warp - 1] : 0) + scan - count;
-    if (row < rows) {
-      row_offset[row] = first;
-      row_count[row] = count;
-      for (int s = 0; s < count; ++s) {
-        if (first + s < capacity) work[first + s] = make_int4(row, s, count, 0);
-        else set_status(status, NVFP4_STATUS_BAD_LENGTH);   // cannot happen with the documented capacity
-      }
-    }
-    __syncthreads();
-    if (tid == 1023) carry = first + count;
-    __syncthreads();
+  for (int row = tid; row < rows; row += 1024) {
+    int count, size_class;
+    balanced_row(seqused_fp4, row, max_pages, target_pages, count, size_class);
+    atomicAdd(&class_total[size_class], count);
   }
-  for (int w = carry + tid; w < capacity; w += 1024) work[w] = make_int4(-1, 0, 0, 0);
+  __syncthreads();
+  if (tid == 0) {
+    int at = 0;
+    for (int c = 0; c < kSizeClasses; ++c) { class_cursor[c] = at; at += class_total[c]; }
+    used = at;
+  }
+  __syncthreads();
+  for (int row = tid; row < rows; row += 1024) {
+    int count, size_class;
+    balanced_row(seqused_fp4, row, max_pages, target_pages, count, size_class);
+    const int first = atomicAdd(&class_cursor[size_class], count);
+    row_offset[row] = first;
+    row_count[row] = count;
+    for (int s = 0; s < count; ++s) {
+      if (first + s < capacity) work[first + s] = make_int4(row, s, count, 0);
+      else set_status(status, NVFP4_STATUS_BAD_LENGTH);   // cannot happen with the documented capacity
+    }
+  }
+  for (int w = used + tid; w < capacity; w += 1024) work[w] = make_int4(-1, 0, 0, 0);
 }
 
 // LSE merge where row r's partials are slots [row_offset[r], row_offset[r] + row_count[r]).
