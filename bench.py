@@ -672,6 +672,9 @@ def run_ragged(args) -> None:
     # --balance-pages T cuts every row by its own length instead (pieces of about T pages).
     splits = args.num_splits
     balance = args.balance_pages if args.balance_pages > 0 else None
+    if args.balance_pages < 0:   # from what a scheduler knows on the host: the lengths
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        balance = _decode.balance_pages_heuristic(int(full.sum()), HKV, sms=sms)
     if balance:
         splits = 1
         space = torch.empty(_decode.balanced_workspace_bytes(rows, HQ, columns, balance),
@@ -776,9 +779,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--decode-impl", default="auto", choices=["auto", "generic", "sm100"])
     ap.add_argument("--num-splits", type=int, default=1)
-    ap.add_argument("--balance-pages", type=int, default=0,
+    ap.add_argument("--balance-pages", type=int, default=-1,
                     help="ragged workload: pieces of about this many pages per row (0: one split "
-                         "count for the batch)")
+                         "count for the batch; -1, the default: chosen from the lengths)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ctx", type=int, default=CTX,
                     help="context length per sequence (default: the headline workload's 4096)")

@@ -52,6 +52,21 @@ def split_k_heuristic(rows: int, heads_kv: int, max_pages_per_row: int, *, sms: 
     return best
 
 
+def balance_pages_heuristic(total_pages: int, heads_kv: int, *, sms: int, floor: int = 16) -> int:
+    """Piece length, in pages, for ``balance_pages`` from what the host knows of a ragged batch.
+
+    Two CTAs are resident per SM, so ``2 * sms`` pieces run at a time; a piece of about 1.5 times
+    an even share (``total_pages * heads_kv / (2 * sms)``) measured best on a batch of 32 rows with
+    lengths log-uniform in [128, 32768] (pieces of 24 / 32 / 48 / 64 pages: 85 / 80 / 74 / 75 us
+    per serving step with an even share of 31): shorter pieces pay the fixed cost of a CTA more
+    often, longer ones leave the end of the launch to a few long walks.  Never below ``floor``.
+    """
+    if total_pages < 1 or heads_kv < 1 or sms < 1:
+        return floor
+    share = total_pages * heads_kv / (2 * sms)
+    return max(floor, math.ceil(1.5 * share))
+
+
 def _need_cuda(tensor: torch.Tensor, name: str, device: torch.device) -> None:
     if not tensor.is_cuda:
         raise ValueError(f"{name} must be a CUDA tensor")

@@ -10,6 +10,8 @@ instead of a separate ``torch.sub``.
 
 from __future__ import annotations
 
+import os
+
 import torch
 from vllm.config import get_current_vllm_config
 from vllm.forward_context import get_forward_context
@@ -26,6 +28,13 @@ from .write import reset_new_request_tails, write_kv
 # A step of one-token rows only (pure decode) needs no page quantisation, and its tail copy can
 # ride in the decode launch: False keeps the reference's separate write_kv launch.
 FUSE_TAIL_APPEND = True
+
+# Pieces of this many pages per row instead of one CTA per (row, KV head) when the step's page
+# table is wider than a piece; 0 (the default, and the reference's behaviour) leaves rows whole.
+# The list of pieces is built on the device from the step's lengths, so a captured CUDA graph
+# follows the lengths of every replay.
+BALANCE_PAGES_ENV = "NVFP4_BALANCE_PAGES"
+BALANCE_PAGES = int(os.environ.get(BALANCE_PAGES_ENV, "0") or 0)
 
 
 class NVFP4Impl(FlashAttentionImpl):
@@ -133,6 +142,11 @@ class NVFP4Impl(FlashAttentionImpl):
         runtime = self.runtime
         key_fp4, key_sf, value_fp4, value_sf = runtime.views(self.layer_index, kv_cache)
         pages = attn_metadata.decode_page_columns
+        extra = self._take_fused_kv()
+        if BALANCE_PAGES > 0 and pages > BALANCE_PAGES:
+            # rows longer than a piece are cut by their own device-side lengths
+            extra.update(balance_pages=BALANCE_PAGES, balance_workspace=runtime.balance_workspace(
+                rows, query.shape[1], pages, BALANCE_PAGES))
         fp4_decode(
             query=query[:rows], key_pages_fp4=key_fp4, key_scales=key_sf,
             value_pages_fp4=value_fp4, value_scales=value_sf,
@@ -145,7 +159,7 @@ class NVFP4Impl(FlashAttentionImpl):
             softmax_scale=self.scale,
             trusted_metadata=True,   # produced on the device this same step; never read back
             query_padded_scratch=runtime.query_padded, query_fp4_scratch=runtime.query_fp4,
-            query_scales_scratch=runtime.query_scales, out=output[:rows], **self._take_fused_kv())
+            query_scales_scratch=runtime.query_scales, out=output[:rows], **extra)
 
     def _take_fused_kv(self) -> dict:
         fused, self._fused_kv = self._fused_kv, None

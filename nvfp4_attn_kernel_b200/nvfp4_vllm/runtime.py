@@ -79,6 +79,17 @@ class LayerRuntime:
         self._bases: torch.Tensor | None = None
         self._expected_layer = 0
 
+    def balance_workspace(self, rows: int, heads_q: int, columns: int, balance_pages: int) -> torch.Tensor:
+        """Scratch for a decode with a split count per row; kept, and grown when a step needs more."""
+        from ..nvfp4_decode_kernel._decode import balanced_workspace_bytes
+
+        need = balanced_workspace_bytes(rows, heads_q, columns, balance_pages)
+        held = getattr(self, "_balance_workspace", None)
+        if held is None or held.numel() < need:
+            held = torch.empty(need, dtype=torch.uint8, device=self.tail_key.device)
+            self._balance_workspace = held
+        return held
+
     @property
     def tail_bytes(self) -> int:
         return 2 * self.tail_key.numel() * self.tail_key.element_size()

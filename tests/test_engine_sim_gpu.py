@@ -33,8 +33,9 @@ class Request:
         self.values = [np.zeros((0, HEADS_KV, DIM), np.float32) for _ in range(LAYERS)]
 
 
-def oracle_row(request, layer, query, shift, scale):
-    """Attention of one decode row over the request's whole history, as the cache holds it."""
+def oracle_row(request, layer, query, shift, scale, piece=None):
+    """Attention of one decode row over the request's whole history, as the cache holds it.
+    With ``piece`` the row is cut into ceil(pages / piece) page ranges merged by LSE weight."""
     keys = O.bf16_round(request.keys[layer] - shift[None]) if shift is not None else request.keys[layer]
     values = request.values[layer]
     full = (request.length - 1) // 128
@@ -54,14 +55,24 @@ def oracle_row(request, layer, query, shift, scale):
     q = query[None]
     q_dq = O.dequantize_query(*O.quantize_query(q, HEADS_KV), HEADS_KV)
     table = np.arange(max(full, 1), dtype=np.int32)[None]
-    return O.attention_from_dequantized(
-        q, q_dq, k_dq, v_dq, table, np.array([full * 128], np.int32), tail_key=tail_k,
-        tail_value=tail_v, tail_ids=np.array([0], np.int32),
-        seqused_residual=np.array([rest], np.int32), softmax_scale=scale)[0]
+    common = dict(tail_key=tail_k, tail_value=tail_v, tail_ids=np.array([0], np.int32),
+                  seqused_residual=np.array([rest], np.int32), softmax_scale=scale)
+    args = (q, q_dq, k_dq, v_dq, table, np.array([full * 128], np.int32))
+    count = max(1, -(-full // piece)) if piece else 1
+    if count == 1:
+        return O.attention_from_dequantized(*args, **common)[0]
+    parts, lses = [], []
+    for s in range(count):
+        o, lse = O.attention_from_dequantized(
+            *args, **common, page_range=(lambda n, s=s: O.split_page_range(n, s, count)),
+            owns_tail=s == 0, return_lse=True)
+        parts.append(o)
+        lses.append(lse)
+    return O.lse_merge(np.stack(parts), np.stack(lses))[0]
 
 
-@pytest.mark.parametrize("fuse_append", [False, True])
-def test_serving_loop(cuda_device, fuse_append):
+@pytest.mark.parametrize("fuse_append,piece", [(False, None), (True, None), (True, 1), (False, 2)])
+def test_serving_loop(cuda_device, fuse_append, piece):
     from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import fp4_decode
     from nvfp4_attn_kernel_b200.nvfp4_vllm import layout, promote
     from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane
@@ -126,6 +137,9 @@ def test_serving_loop(cuda_device, fuse_append):
             key_dev, value_dev = bf16_tensor(key, dev), bf16_tensor(value, dev)
             extra = dict(append_key=key_dev, append_value=value_dev,
                          key_shift=runtime.active_key_shift[layer]) if fused else {}
+            if piece and columns > piece:   # what the backend does with NVFP4_BALANCE_PAGES set
+                extra.update(balance_pages=piece, balance_workspace=runtime.balance_workspace(
+                    decode_rows, HEADS_Q, columns, piece))
             if not fused:
                 write_kv(key=key_dev, value=value_dev, key_pages_fp4=k_fp4,
                          key_scales=k_sf, value_pages_fp4=v_fp4, value_scales=v_sf,
@@ -148,7 +162,8 @@ def test_serving_loop(cuda_device, fuse_append):
                     query_fp4_scratch=runtime.query_fp4, query_scales_scratch=runtime.query_scales, **extra)
                 got = to_np(got)
                 for row in range(decode_rows):
-                    want = oracle_row(batch[row], layer, query[row], shift_np[layer], scale)
+                    want = oracle_row(batch[row], layer, query[row], shift_np[layer], scale,
+                                      piece if piece and columns > piece else None)
                     err = float(np.abs(got[row] - want).max())
                     assert err < TOL, (batch[row].name, batch[row].length, layer, err)
                     checked += 1

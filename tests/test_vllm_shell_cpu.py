@@ -415,3 +415,16 @@ def test_control_plane_argument_checks():
     plane.reset()
     plane.raise_for_errors()
     assert int(plane.slot_keys.max()) == control.FREE_KEY
+
+
+def test_balance_pages_heuristic():
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel._decode import balance_pages_heuristic
+
+    # 1152 pages x 8 KV heads over 296 resident CTAs: an even share of 31 pages, pieces of 47
+    assert balance_pages_heuristic(1152, 8, sms=148) == 47
+    assert balance_pages_heuristic(10, 8, sms=148) == 16          # never below the floor
+    assert balance_pages_heuristic(0, 8, sms=148) == 16
+    assert balance_pages_heuristic(1152, 8, sms=148, floor=64) == 64
+    # more work, longer pieces; more SMs, shorter ones
+    assert balance_pages_heuristic(4000, 8, sms=148) > balance_pages_heuristic(2000, 8, sms=148)
+    assert balance_pages_heuristic(4000, 8, sms=296) < balance_pages_heuristic(4000, 8, sms=148)
