@@ -231,6 +231,15 @@ typedef struct nvfp4_decode_args {
 #define NVFP4_DECODE_PROGRAMMATIC_LAUNCH 1u
 
 /*
+ * NVFP4_DECODE_REUSE_WORK_LIST (nvfp4_decode_balanced only): the workspace still holds the list
+ * of pieces that an earlier nvfp4_decode_balanced call on this stream built from the same
+ * seqused_fp4 values, rows, max_pages and target_pages; the list launch is skipped.  Meant for
+ * the layers of one model step, whose lengths are the same: the first layer builds the list, the
+ * others reuse it (their partial results overwrite the earlier layer's in the same workspace).
+ */
+#define NVFP4_DECODE_REUSE_WORK_LIST 2u
+
+/*
  * With out != NULL the merged bf16 result is written (for num_splits > 1 the
  * partials go through o_partial/lse_partial if given, else through workspace).
  * With out == NULL the call only emits the partials (used by the cross-GPU
@@ -368,6 +377,7 @@ int nvfp4_probe_hbm_read(const void* ptr, size_t bytes, uint32_t* sink, void* st
  *
  *  - args as for nvfp4_decode with num_splits = 1, out != NULL, o_partial = lse_partial =
  *    out_indices = NULL, no NVFP4_DECODE_PROGRAMMATIC_LAUNCH; tensor-core kernel only.
+ *  - args.flags may carry NVFP4_DECODE_REUSE_WORK_LIST (two launches instead of three).
  *  - args.workspace must hold nvfp4_decode_balanced_workspace_bytes(rows, heads_q, max_pages,
  *    target_pages) bytes (args.max_pages is the bound on a row's page count that the list's
  *    capacity, nvfp4_decode_balanced_capacity, is derived from).

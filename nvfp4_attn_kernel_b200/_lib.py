@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(HERE, "libnvfp4_b200.so")
 
 IMPL_AUTO, IMPL_GENERIC, IMPL_SM100 = 0, 1, 2
 DECODE_PROGRAMMATIC_LAUNCH = 1
+DECODE_REUSE_WORK_LIST = 2
 STATUS_BAD_PAGE_ID, STATUS_BAD_TAIL_ID, STATUS_WAIT_TIMEOUT, STATUS_BAD_LENGTH = 1, 2, 4, 8
 ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED = 1, 2, 3
 

@@ -359,8 +359,10 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.num_splits = a->num_splits;
   p.status = a->status;
-  if (a->flags & ~NVFP4_DECODE_PROGRAMMATIC_LAUNCH)
+  if (a->flags & ~(NVFP4_DECODE_PROGRAMMATIC_LAUNCH | NVFP4_DECODE_REUSE_WORK_LIST))
     return fail(NVFP4_ERR_INVALID, "decode: unknown flag bits %#x", a->flags);
+  if ((a->flags & NVFP4_DECODE_REUSE_WORK_LIST) && !target_pages)
+    return fail(NVFP4_ERR_INVALID, "decode: only nvfp4_decode_balanced has a work list to reuse");
   p.pdl = (a->flags & NVFP4_DECODE_PROGRAMMATIC_LAUNCH) ? 1 : 0;
   if ((a->append_key == nullptr) != (a->append_value == nullptr))
     return fail(NVFP4_ERR_INVALID, "decode: append_key and append_value go together");
@@ -449,7 +451,7 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
       return fail(NVFP4_ERR_UNSUPPORTED,
                   "decode_balanced: carried by the tensor-core kernel only, without programmatic launch");
     char* base = static_cast<char*>(a->workspace);
-    e = nvfp4::launch_balanced_worklist(a->seqused_fp4, a->rows, a->max_pages, target_pages,
+    e = (a->flags & NVFP4_DECODE_REUSE_WORK_LIST) ? cudaSuccess : nvfp4::launch_balanced_worklist(a->seqused_fp4, a->rows, a->max_pages, target_pages,
                                         reinterpret_cast<int4*>(base + bal.work), (int)capacity,
                                         reinterpret_cast<int32_t*>(base + bal.row_offset),
                                         reinterpret_cast<int32_t*>(base + bal.row_count), a->status, st);

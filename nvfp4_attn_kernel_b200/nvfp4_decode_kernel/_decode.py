@@ -159,13 +159,15 @@ def decode_fp4(
     key_shift: torch.Tensor | None = None,
     balance_pages: int | None = None,
     workspace: torch.Tensor | None = None,
+    reuse_work_list: bool = False,
 ) -> torch.Tensor | None:
     """Validate every tensor contract and launch the decode on the current stream.
 
     ``balance_pages`` (an extension): cut every row into pieces of about that many FP4 pages,
     each row by its own length, instead of one ``num_splits`` for the whole batch; ``workspace``
     (uint8, ``balanced_workspace_bytes`` long) may be passed to keep the call free of
-    allocations.
+    allocations.  ``reuse_work_list``: ``workspace`` still holds the list of pieces of an earlier
+    call with the same lengths and shapes (the layers of one model step), so it is not rebuilt.
 
     ``query_padded_bf16`` (``[rows, 128, heads_q, 128]``, row 0 of each tile live)
     carries the BF16 query that meets the BF16 residual page.
@@ -458,13 +460,15 @@ def decode_fp4(
         if programmatic_launch:
             raise ValueError("balance_pages cannot be combined with programmatic_launch")
         need = balanced_workspace_bytes(rows, heads_q, fp4_page_table.shape[1], balance_pages)
+        if reuse_work_list and workspace is None:
+            raise ValueError("reuse_work_list needs the workspace of the call that built the list")
         if workspace is None:
             workspace = torch.empty(need, dtype=torch.uint8, device=device)
         elif (workspace.dtype is not torch.uint8 or workspace.device != device or workspace.numel() < need
               or not workspace.is_contiguous() or workspace.data_ptr() % 16):
             raise ValueError(f"workspace must be contiguous 16-byte aligned uint8 of at least {need} bytes")
-    elif workspace is not None:
-        raise ValueError("workspace is only taken together with balance_pages")
+    elif workspace is not None or reuse_work_list:
+        raise ValueError("workspace and reuse_work_list are only taken together with balance_pages")
     elif num_splits > 1 and _partials is None:
         need = _lib.load().nvfp4_decode_workspace_bytes(rows, heads_q, num_splits)
         workspace = torch.empty(need, dtype=torch.uint8, device=device)
@@ -526,6 +530,8 @@ def decode_fp4(
         # CTAs may start while the previous kernel in the stream drains; pages, scales, table and
         # lengths must not be that kernel's output (query, tail and outputs may be)
         args.flags = _lib.DECODE_PROGRAMMATIC_LAUNCH
+    if reuse_work_list:
+        args.flags |= _lib.DECODE_REUSE_WORK_LIST
     if args.page_table_row_stride < args.max_pages:
         raise ValueError("fp4_page_table rows overlap")
     with torch.cuda.device(device):

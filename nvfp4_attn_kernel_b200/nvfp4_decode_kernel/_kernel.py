@@ -141,6 +141,7 @@ def fp4_decode_impl(
     key_shift=None,
     balance_pages=None,
     balance_workspace=None,
+    balance_reuse=False,
 ):
     from ._decode import decode_fp4, decode_fp4_split
     from ._quantize import quantize_query
@@ -263,7 +264,7 @@ def fp4_decode_impl(
         return decode_fp4_split(**shared, num_splits=num_splits)
     if balance_pages is not None:
         return decode_fp4(**shared, out_indices=out_indices, balance_pages=balance_pages,
-                          workspace=balance_workspace)
+                          workspace=balance_workspace, reuse_work_list=balance_reuse)
     # a call that is ONE launch (query quantised in the kernel, or quantised by the caller) can
     # be repeated from its argument block
     sink = [] if plan_key is not None and (query_bf16 is not None or not bf16_query) else None

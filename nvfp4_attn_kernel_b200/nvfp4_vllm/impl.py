@@ -145,8 +145,9 @@ class NVFP4Impl(FlashAttentionImpl):
         extra = self._take_fused_kv()
         if BALANCE_PAGES > 0 and pages > BALANCE_PAGES:
             # rows longer than a piece are cut by their own device-side lengths
+            # (the lengths are the step's: the first layer builds the list, the others reuse it)
             extra.update(balance_pages=BALANCE_PAGES, balance_workspace=runtime.balance_workspace(
-                rows, query.shape[1], pages, BALANCE_PAGES))
+                rows, query.shape[1], pages, BALANCE_PAGES), balance_reuse=self.layer_index > 0)
         fp4_decode(
             query=query[:rows], key_pages_fp4=key_fp4, key_scales=key_sf,
             value_pages_fp4=value_fp4, value_scales=value_sf,

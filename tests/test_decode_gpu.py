@@ -539,6 +539,15 @@ def test_balanced_split_workspace_graph_replay_and_refusals(cuda_device):
     for row, length in enumerate(lengths):
         ref = prob.oracle_from_bytes(rows=[row], splits=-(-(length // 128) // 4))
         assert np.abs(want[row] - ref[0]).max() <= TOL
+    # another layer of the same step: other query, same lengths - the list in the workspace is reused
+    other = (prob.q.float() * -0.5 + 0.25).to(torch.bfloat16)
+    fresh = prob.decode(query=other, balance_pages=4, trusted_metadata=True)
+    space[: need // 2].random_(0, 256)   # the partials of the earlier call are garbage by now
+    reused = prob.decode(query=other, balance_pages=4, balance_workspace=space, balance_reuse=True,
+                         trusted_metadata=True)
+    assert torch.equal(reused, fresh)
+    with pytest.raises(ValueError, match="reuse_work_list"):
+        prob.decode(balance_pages=4, balance_reuse=True)
     # the three launches replay from a CUDA graph after the lengths change on the device
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):

@@ -139,7 +139,7 @@ def test_serving_loop(cuda_device, fuse_append, piece):
                          key_shift=runtime.active_key_shift[layer]) if fused else {}
             if piece and columns > piece:   # what the backend does with NVFP4_BALANCE_PAGES set
                 extra.update(balance_pages=piece, balance_workspace=runtime.balance_workspace(
-                    decode_rows, HEADS_Q, columns, piece))
+                    decode_rows, HEADS_Q, columns, piece), balance_reuse=layer > 0)
             if not fused:
                 write_kv(key=key_dev, value=value_dev, key_pages_fp4=k_fp4,
                          key_scales=k_sf, value_pages_fp4=v_fp4, value_scales=v_sf,
