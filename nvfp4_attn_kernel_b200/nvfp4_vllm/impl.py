@@ -10,8 +10,6 @@ instead of a separate ``torch.sub``.
 
 from __future__ import annotations
 
-import os
-
 import torch
 from vllm.config import get_current_vllm_config
 from vllm.forward_context import get_forward_context
@@ -21,7 +19,7 @@ from vllm.v1.attention.backends.flash_attn import FlashAttentionImpl
 from ..nvfp4_decode_kernel import fp4_decode
 from . import promote
 from .guards import NVFP4, check_layer_supported, check_supported
-from .runtime import LayerRuntime
+from .runtime import LayerRuntime, piece_pages
 from .write import reset_new_request_tails, write_kv
 
 
@@ -29,12 +27,6 @@ from .write import reset_new_request_tails, write_kv
 # ride in the decode launch: False keeps the reference's separate write_kv launch.
 FUSE_TAIL_APPEND = True
 
-# Pieces of this many pages per row instead of one CTA per (row, KV head) when the step's page
-# table is wider than a piece; 0 (the default, and the reference's behaviour) leaves rows whole.
-# The list of pieces is built on the device from the step's lengths, so a captured CUDA graph
-# follows the lengths of every replay.
-BALANCE_PAGES_ENV = "NVFP4_BALANCE_PAGES"
-BALANCE_PAGES = int(os.environ.get(BALANCE_PAGES_ENV, "0") or 0)
 
 
 class NVFP4Impl(FlashAttentionImpl):
@@ -143,11 +135,14 @@ class NVFP4Impl(FlashAttentionImpl):
         key_fp4, key_sf, value_fp4, value_sf = runtime.views(self.layer_index, kv_cache)
         pages = attn_metadata.decode_page_columns
         extra = self._take_fused_kv()
-        if BALANCE_PAGES > 0 and pages > BALANCE_PAGES:
-            # rows longer than a piece are cut by their own device-side lengths
-            # (the lengths are the step's: the first layer builds the list, the others reuse it)
-            extra.update(balance_pages=BALANCE_PAGES, balance_workspace=runtime.balance_workspace(
-                rows, query.shape[1], pages, BALANCE_PAGES), balance_reuse=self.layer_index > 0)
+        piece = piece_pages(rows, key_fp4.shape[2], pages, runtime.sm_count)
+        if piece:
+            # Rows longer than a piece are cut by their own device-side lengths (the list of pieces
+            # is built on the device, so a captured CUDA graph follows the lengths of every
+            # replay); the lengths are the step's, so the first layer builds the list and the
+            # others reuse it.
+            extra.update(balance_pages=piece, balance_workspace=runtime.balance_workspace(
+                rows, query.shape[1], pages, piece), balance_reuse=self.layer_index > 0)
         fp4_decode(
             query=query[:rows], key_pages_fp4=key_fp4, key_scales=key_sf,
             value_pages_fp4=value_fp4, value_scales=value_sf,

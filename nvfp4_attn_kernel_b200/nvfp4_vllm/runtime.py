@@ -21,6 +21,37 @@ PAGE_SIZE = 128
 KEY_SHIFT_ENV = "NVFP4_KEY_SHIFT"
 
 
+# How a decode step's rows are cut into pieces of pages (the balanced split, not in the reference):
+# "auto" (default) - piece length from the step's shape, see piece_pages; "0" - never, rows stay
+# whole as in the reference; a positive number - pieces of that many pages.
+BALANCE_PAGES_ENV = "NVFP4_BALANCE_PAGES"
+
+
+def piece_pages(rows: int, heads_kv: int, columns: int, sms: int, setting: str | None = None) -> int:
+    """Pages per piece for a decode step of ``rows`` rows whose page table is ``columns`` wide, or
+    0 to leave the rows whole.
+
+    The host knows the step's shape, not its lengths, so "auto" plans for full rows: pieces of
+    1.5 times an even share of ``rows * columns * heads_kv`` page walks over the ``2 * sms``
+    resident CTAs, at least 16 pages.  A batch that fills the GPU with whole rows (32 rows x 8 KV
+    heads x 32 pages on 148 SMs: share 28, piece 42 > 32 columns) is left alone; one or a few long
+    rows (1 row x 8 heads x 256 pages: piece 16, 128 CTAs instead of 8) are cut.  The list of
+    pieces itself follows the lengths on the device, so short rows still get one piece.
+    """
+    from ..nvfp4_decode_kernel._decode import balance_pages_heuristic
+
+    if setting is None:
+        setting = os.environ.get(BALANCE_PAGES_ENV, "auto")
+    setting = setting.strip().lower() or "auto"
+    if setting == "auto":
+        piece = balance_pages_heuristic(rows * columns, heads_kv, sms=sms)
+    else:
+        piece = int(setting)
+        if piece < 0:
+            raise ValueError(f"{BALANCE_PAGES_ENV} must be 'auto', 0 or a positive page count, got {setting!r}")
+    return piece if 0 < piece < columns else 0
+
+
 def load_key_shift(num_layers: int, num_kv_heads: int, head_dim: int, device, dtype):
     """The per-channel constant subtracted from post-RoPE K on its way into the cache, or None.
 
@@ -51,6 +82,8 @@ class LayerRuntime:
     def __init__(self, *, num_layers: int, num_slots: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, device) -> None:
         self.num_layers = num_layers
+        self.sm_count = (torch.cuda.get_device_properties(device).multi_processor_count
+                         if torch.device(device).type == "cuda" else 148)
         self.num_kv_heads = num_kv_heads
         self.head_dim = head_dim
         self.key_shift_enabled = True

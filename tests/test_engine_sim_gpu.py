@@ -76,7 +76,7 @@ def test_serving_loop(cuda_device, fuse_append, piece):
     from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import fp4_decode
     from nvfp4_attn_kernel_b200.nvfp4_vllm import layout, promote
     from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane
-    from nvfp4_attn_kernel_b200.nvfp4_vllm.runtime import LayerRuntime
+    from nvfp4_attn_kernel_b200.nvfp4_vllm.runtime import LayerRuntime, piece_pages
     from nvfp4_attn_kernel_b200.nvfp4_vllm.write import (PageWorkTable, reset_new_request_tails,
                                                          write_kv)
 
@@ -137,7 +137,9 @@ def test_serving_loop(cuda_device, fuse_append, piece):
             key_dev, value_dev = bf16_tensor(key, dev), bf16_tensor(value, dev)
             extra = dict(append_key=key_dev, append_value=value_dev,
                          key_shift=runtime.active_key_shift[layer]) if fused else {}
-            if piece and columns > piece:   # what the backend does with NVFP4_BALANCE_PAGES set
+            cut = piece_pages(decode_rows, HEADS_KV, columns, runtime.sm_count, str(piece or 0))
+            assert cut == (piece if piece and columns > piece else 0)
+            if cut:   # what the backend does with NVFP4_BALANCE_PAGES set to a page count
                 extra.update(balance_pages=piece, balance_workspace=runtime.balance_workspace(
                     decode_rows, HEADS_Q, columns, piece), balance_reuse=layer > 0)
             if not fused:

@@ -428,3 +428,26 @@ def test_balance_pages_heuristic():
     # more work, longer pieces; more SMs, shorter ones
     assert balance_pages_heuristic(4000, 8, sms=148) > balance_pages_heuristic(2000, 8, sms=148)
     assert balance_pages_heuristic(4000, 8, sms=296) < balance_pages_heuristic(4000, 8, sms=148)
+
+
+def test_piece_pages_policy(monkeypatch):
+    from nvfp4_attn_kernel_b200.nvfp4_vllm.runtime import BALANCE_PAGES_ENV, piece_pages
+
+    monkeypatch.delenv(BALANCE_PAGES_ENV, raising=False)
+    # a batch that fills the GPU with whole rows is left alone
+    assert piece_pages(32, 8, 32, 148) == 0
+    # one long row: 8 CTAs would walk 256 pages each; pieces of 16 pages make 128 CTAs
+    assert piece_pages(1, 8, 256, 148) == 16
+    assert piece_pages(4, 8, 256, 148) == 42
+    # short tables are never cut
+    assert piece_pages(1, 8, 16, 148) == 0
+    # explicit settings
+    assert piece_pages(32, 8, 32, 148, "0") == 0
+    assert piece_pages(32, 8, 32, 148, "8") == 8
+    assert piece_pages(32, 8, 8, 148, "8") == 0
+    monkeypatch.setenv(BALANCE_PAGES_ENV, "0")
+    assert piece_pages(1, 8, 256, 148) == 0
+    monkeypatch.setenv(BALANCE_PAGES_ENV, "24")
+    assert piece_pages(1, 8, 256, 148) == 24
+    with pytest.raises(ValueError):
+        piece_pages(1, 8, 256, 148, "-3")
