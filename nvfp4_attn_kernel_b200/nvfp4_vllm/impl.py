@@ -37,11 +37,13 @@ class NVFP4Impl(FlashAttentionImpl):
         cache = config.cache_config
         self.nvfp4 = cache is not None and cache.cache_dtype == NVFP4
         self.num_slots = 0
+        self.max_pages = 0
         if self.nvfp4:
             check_layer_supported(self)
             # prefill attends this pass's BF16 K/V and decode quantises to FP4, never FP8
             self.supports_quant_query_input = False
             self.num_slots = config.scheduler_config.max_num_seqs
+            self.max_pages = -(-int(getattr(config.model_config, "max_model_len", 0) or 0) // 128)
         self.runtime: LayerRuntime | None = None
         self.layer_index = 0
         self._fused_kv = None   # (key, value, shift) of a pure decode step, appended by the decode launch
@@ -62,7 +64,7 @@ class NVFP4Impl(FlashAttentionImpl):
         num_heads, num_kv_heads, head_dim = shapes.pop()
         runtime = LayerRuntime(num_layers=len(modules), num_slots=self.num_slots,
                                num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
-                               device=device)
+                               device=device, max_pages=self.max_pages)
         for index, module in enumerate(modules):
             module.impl.runtime = runtime
             module.impl.layer_index = index

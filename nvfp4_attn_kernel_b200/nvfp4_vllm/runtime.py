@@ -80,8 +80,10 @@ class LayerRuntime:
     """Tail buffers, cache views and query scratch of one model."""
 
     def __init__(self, *, num_layers: int, num_slots: int, num_heads: int, num_kv_heads: int,
-                 head_dim: int, device) -> None:
+                 head_dim: int, device, max_pages: int = 0) -> None:
         self.num_layers = num_layers
+        self.num_slots = num_slots
+        self.num_heads = num_heads
         self.sm_count = (torch.cuda.get_device_properties(device).multi_processor_count
                          if torch.device(device).type == "cuda" else 148)
         self.num_kv_heads = num_kv_heads
@@ -111,13 +113,36 @@ class LayerRuntime:
         self._by_layer: dict[int, tuple[torch.Tensor, ...]] = {}
         self._bases: torch.Tensor | None = None
         self._expected_layer = 0
+        self._balance_workspace: torch.Tensor | None = None
+        if max_pages > 0:
+            self.reserve_balance_workspace(max_pages)
+
+    def reserve_balance_workspace(self, max_pages: int, limit_bytes: int = 256 << 20) -> int:
+        """Allocate, once, the scratch of the largest decode step that ``piece_pages`` would cut:
+        any row count up to the slot count at the model's longest context.  Called with the other
+        allocations of the first forward pass, so the KV cache is sized around it and no decode
+        step allocates.  Returns the bytes reserved (0 when nothing would be cut, or when an
+        explicit piece length makes the worst case larger than ``limit_bytes``: the scratch then
+        grows on demand)."""
+        from ..nvfp4_decode_kernel._decode import balanced_workspace_bytes
+
+        worst = 0
+        for rows in range(1, self.num_slots + 1):
+            piece = piece_pages(rows, self.num_kv_heads, max_pages, self.sm_count)
+            if piece:
+                worst = max(worst, balanced_workspace_bytes(rows, self.num_heads, max_pages, piece))
+        if not 0 < worst <= limit_bytes:
+            return 0
+        self._balance_workspace = torch.empty(worst, dtype=torch.uint8, device=self.tail_key.device)
+        return worst
 
     def balance_workspace(self, rows: int, heads_q: int, columns: int, balance_pages: int) -> torch.Tensor:
-        """Scratch for a decode with a split count per row; kept, and grown when a step needs more."""
+        """Scratch for a decode with a split count per row: the reserved one, grown only when a
+        step needs more than was planned for."""
         from ..nvfp4_decode_kernel._decode import balanced_workspace_bytes
 
         need = balanced_workspace_bytes(rows, heads_q, columns, balance_pages)
-        held = getattr(self, "_balance_workspace", None)
+        held = self._balance_workspace
         if held is None or held.numel() < need:
             held = torch.empty(need, dtype=torch.uint8, device=self.tail_key.device)
             self._balance_workspace = held

@@ -451,3 +451,33 @@ def test_piece_pages_policy(monkeypatch):
     assert piece_pages(1, 8, 256, 148) == 24
     with pytest.raises(ValueError):
         piece_pages(1, 8, 256, 148, "-3")
+
+
+def test_runtime_reserves_the_balanced_split_scratch(monkeypatch):
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel._decode import balanced_workspace_bytes
+
+    monkeypatch.delenv(runtime.KEY_SHIFT_ENV, raising=False)
+    monkeypatch.delenv(runtime.BALANCE_PAGES_ENV, raising=False)
+    rt = runtime.LayerRuntime(num_layers=1, num_slots=8, num_heads=8, num_kv_heads=2, head_dim=128,
+                              device="cpu", max_pages=256)
+    held = rt._balance_workspace
+    assert held is not None
+    # every step that the policy would cut fits the reserved scratch: nothing grows
+    for rows in range(1, 9):
+        for columns in (32, 100, 256):
+            piece = runtime.piece_pages(rows, 2, columns, rt.sm_count)
+            if piece:
+                assert balanced_workspace_bytes(rows, 8, columns, piece) <= held.numel()
+                assert rt.balance_workspace(rows, 8, columns, piece) is held
+    # switched off, or a short model: nothing is reserved
+    monkeypatch.setenv(runtime.BALANCE_PAGES_ENV, "0")
+    assert runtime.LayerRuntime(num_layers=1, num_slots=8, num_heads=8, num_kv_heads=2, head_dim=128,
+                                device="cpu", max_pages=256)._balance_workspace is None
+    monkeypatch.delenv(runtime.BALANCE_PAGES_ENV)
+    assert runtime.LayerRuntime(num_layers=1, num_slots=8, num_heads=8, num_kv_heads=2, head_dim=128,
+                                device="cpu", max_pages=8)._balance_workspace is None
+    # an explicit tiny piece whose worst case is huge: left to grow on demand
+    monkeypatch.setenv(runtime.BALANCE_PAGES_ENV, "1")
+    big = runtime.LayerRuntime(num_layers=1, num_slots=64, num_heads=64, num_kv_heads=8, head_dim=128,
+                               device="cpu", max_pages=4096)
+    assert big._balance_workspace is None
