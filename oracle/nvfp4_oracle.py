@@ -558,6 +558,20 @@ def split_page_range(n_pages: int, split: int, num_splits: int):
     return first, last
 
 
+def balanced_split_counts(seqused_fp4, target_pages: int):
+    """Split count per row of the balanced split (an extension of this build, no counterpart in the
+    reference, whose ``num_splits`` is one number per batch): ``ceil(pages / target_pages)``, one
+    for a row without FP4 pages (its tail still needs a piece).  Piece ``s`` of a row with count
+    ``c`` owns ``split_page_range(pages, s, c)``; piece 0 owns the tail."""
+    pages = np.asarray(seqused_fp4, dtype=np.int64) // PAGE
+    return np.maximum(1, -(-pages // int(target_pages))).astype(np.int64)
+
+
+def balanced_capacity(rows: int, max_pages: int, target_pages: int) -> int:
+    """Upper bound on the number of pieces: every row at ``max_pages`` pages."""
+    return rows + rows * max_pages // target_pages
+
+
 def lse_merge(o_parts, lse_parts, return_lse: bool = False):
     """o_parts [S, rows, Hq, D] fp32 normalised, lse_parts [S, rows, Hq].
 

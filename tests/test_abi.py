@@ -45,6 +45,61 @@ def test_workspace_size():
     assert lib.nvfp4_decode_workspace_bytes(0, 32, 8) == 0
 
 
+def test_balanced_split_sizes_and_refusals():
+    """Host arithmetic of the balanced split: the capacity bounds the number of pieces of any
+    batch, the workspace holds partials, list and the per-row ranges, and the entry refuses what
+    its header says it refuses - all before anything is launched."""
+    import numpy as np
+
+    import nvfp4_oracle as O
+
+    lib = L.load()
+    rng = np.random.default_rng(5)
+    for _ in range(200):
+        rows = int(rng.integers(1, 70))
+        max_pages = int(rng.integers(0, 300))
+        target = int(rng.integers(1, 80))
+        capacity = lib.nvfp4_decode_balanced_capacity(rows, max_pages, target)
+        assert capacity == O.balanced_capacity(rows, max_pages, target)
+        lengths = rng.integers(0, max_pages + 1, rows) * 128
+        assert int(O.balanced_split_counts(lengths, target).sum()) <= capacity
+        full = np.full(rows, max_pages * 128)
+        assert int(O.balanced_split_counts(full, target).sum()) <= capacity
+        heads_q = int(rng.choice([8, 32, 64]))
+        need = lib.nvfp4_decode_balanced_workspace_bytes(rows, heads_q, max_pages, target)
+        floor = capacity * heads_q * 129 * 4 + capacity * 16 + 2 * rows * 4
+        assert floor <= need <= floor + 5 * 16
+    assert lib.nvfp4_decode_balanced_capacity(0, 32, 8) == 0
+    assert lib.nvfp4_decode_balanced_capacity(4, 32, 0) == 0
+    assert lib.nvfp4_decode_balanced_workspace_bytes(4, 0, 32, 8) == 0
+
+    assert lib.nvfp4_decode_balanced(None, 8, None) == L.ERR_INVALID
+    args = L.DecodeArgs()
+    args.rows, args.heads_q, args.heads_kv, args.softmax_scale, args.num_splits = 2, 32, 8, 0.1, 1
+    assert lib.nvfp4_decode_balanced(ctypes.byref(args), 0, None) == L.ERR_INVALID
+    assert "target_pages" in L.last_error()
+    assert lib.nvfp4_decode_balanced(ctypes.byref(args), 8, None) == L.ERR_INVALID   # no out
+    assert "num_splits = 1, out" in L.last_error()
+    args.num_splits = 2
+    assert lib.nvfp4_decode_balanced(ctypes.byref(args), 8, None) == L.ERR_INVALID
+    # the reuse flag belongs to the balanced entry alone
+    args.num_splits = 1
+    args.flags = L.DECODE_REUSE_WORK_LIST
+    args.q_bf16 = args.k_packed = args.k_sf = args.v_packed = args.v_sf = 1 << 20
+    args.page_table = args.seqused_fp4 = args.out = 1 << 20
+    args.k_pitch = args.v_pitch = 128 * 8 * 64
+    args.k_sf_pitch = args.v_sf_pitch = 8 * 1024
+    args.max_pages = args.page_table_row_stride = 4
+    args.num_pages = 16
+    args.q_bf16_row_stride, args.q_bf16_head_stride = 32 * 128, 128
+    assert lib.nvfp4_decode(ctypes.byref(args), None) == L.ERR_INVALID
+    assert "work list to reuse" in L.last_error()
+    # and the balanced entry wants its workspace before it launches anything
+    args.flags = 0
+    assert lib.nvfp4_decode_balanced(ctypes.byref(args), 2, None) == L.ERR_INVALID
+    assert "workspace" in L.last_error()
+
+
 def test_argument_errors_are_reported_without_a_device():
     lib = L.load()
     assert lib.nvfp4_decode(None, None) == L.ERR_INVALID
