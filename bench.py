@@ -179,7 +179,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
-def build_pools(device, rows=None, pages_per_row=None, num_pools=None):
+def build_pools(device, rows=None, pages_per_row=None, num_pools=None, hkv=None):
     """Disjoint page pools in the vLLM block layout, filled by the library's quantisers."""
     import torch
 
@@ -188,10 +188,11 @@ def build_pools(device, rows=None, pages_per_row=None, num_pools=None):
     ROWS_, PAGES_PER_ROW_ = rows or ROWS, pages_per_row or PAGES_PER_ROW
     POOL_PAGES_ = ROWS_ * PAGES_PER_ROW_
     NUM_POOLS_ = num_pools or NUM_POOLS
+    HKV_ = hkv or HKV
 
-    block = 2 * (PAGE * HKV * 64 + HKV * 1024)
-    o1 = PAGE * HKV * 64
-    o2 = o1 + HKV * 1024
+    block = 2 * (PAGE * HKV_ * 64 + HKV_ * 1024)
+    o1 = PAGE * HKV_ * 64
+    o2 = o1 + HKV_ * 1024
     o3 = o2 + o1
     pools = []
     gen = torch.Generator(device=device)
@@ -199,18 +200,18 @@ def build_pools(device, rows=None, pages_per_row=None, num_pools=None):
     for _ in range(NUM_POOLS_):
         cache = torch.empty(POOL_PAGES_, block, dtype=torch.uint8, device=device)
         flat = cache.view(-1)
-        kview = flat.as_strided((POOL_PAGES_, PAGE, HKV, 64), (block, HKV * 64, 64, 1), 0)
-        vview = flat.as_strided((POOL_PAGES_, HKV, D, 64), (block, D * 64, 64, 1), o2)
-        ksf = qkv.scale_view(flat, POOL_PAGES_, HKV, block, o1)
-        vsf = qkv.scale_view(flat, POOL_PAGES_, HKV, block, o3)
+        kview = flat.as_strided((POOL_PAGES_, PAGE, HKV_, 64), (block, HKV_ * 64, 64, 1), 0)
+        vview = flat.as_strided((POOL_PAGES_, HKV_, D, 64), (block, D * 64, 64, 1), o2)
+        ksf = qkv.scale_view(flat, POOL_PAGES_, HKV_, block, o1)
+        vsf = qkv.scale_view(flat, POOL_PAGES_, HKV_, block, o3)
         chunk = min(128, POOL_PAGES_)
         while POOL_PAGES_ % chunk:
             chunk -= 1
-        offset = torch.randn(HKV, D, device=device, generator=gen) * 2.0
+        offset = torch.randn(HKV_, D, device=device, generator=gen) * 2.0
         shift = None
         for lo in range(0, POOL_PAGES_, chunk):
-            k = (torch.randn(chunk * PAGE, HKV, D, device=device, generator=gen) + offset).to(torch.bfloat16)
-            v = torch.randn(chunk * PAGE, HKV, D, device=device, generator=gen).to(torch.bfloat16)
+            k = (torch.randn(chunk * PAGE, HKV_, D, device=device, generator=gen) + offset).to(torch.bfloat16)
+            v = torch.randn(chunk * PAGE, HKV_, D, device=device, generator=gen).to(torch.bfloat16)
             if shift is None:
                 shift = k.double().mean(0).to(torch.bfloat16).contiguous()  # per-channel K mean
             src = torch.arange(chunk, dtype=torch.int32, device=device) * PAGE
@@ -771,6 +772,176 @@ def run_ragged(args) -> None:
     }), flush=True)
 
 
+def run_model_step(args) -> None:
+    """One GPU's share of a full-model decode step under tensor parallelism by KV head: 32 layers,
+    batch 32, contexts uniform in [1024, 16384] growing one token per step, 1 KV head and 4 query
+    heads on this GPU (8 KV heads over 8 GPUs; the ranks share nothing, so every rank of a
+    multi-GPU launch runs the same shape on its own heads).  A step = the slot control plane once,
+    then per layer ONE decode call (query quantised and the step's K/V token appended inside, key
+    shift on, rows cut into pieces by the step's shape: work list in the first layer, reused by
+    the others), then one tail flush over all layers.  Every layer has its own block array (same
+    block ids, as in vLLM) and its own tails."""
+    import numpy as np
+    import torch
+
+    import nvfp4_attn_kernel_b200._lib as L
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode
+    from nvfp4_attn_kernel_b200.nvfp4_vllm import layout
+    from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane
+    from nvfp4_attn_kernel_b200.nvfp4_vllm.runtime import piece_pages
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    lib = L.load()
+    layers, rows, hkv, hq = 32, ROWS, 1, 4
+    rng = np.random.default_rng(5)
+    lens = rng.integers(1024, 16385, rows).astype(np.int64)
+    total_steps = args.warmup + args.steps + 3
+    columns = int((lens.max() + total_steps) // PAGE + 2)
+    need = (lens + total_steps) // PAGE + 2
+    pool_pages = int(need.sum()) + 1                          # block 0 is vLLM's null block
+    ids = rng.permutation(np.arange(1, pool_pages))
+    table = np.zeros((rows, columns), dtype=np.int32)
+    at = 0
+    for r in range(rows):
+        table[r, :need[r]] = ids[at:at + need[r]]
+        at += int(need[r])
+    dense = build_pools(device, 1, 2048, 1, hkv=hkv)[0]["cache"]
+    block = layout.page_bytes(hkv)
+    index = torch.arange(pool_pages, device=device)
+    caches = [dense[(index + 97 * layer) % dense.shape[0]].contiguous() for layer in range(layers)]
+    del dense
+    views = [layout.carve(cache, hkv, D) for cache in caches]
+    gen = torch.Generator(device=device)
+    gen.manual_seed(6)
+    tail_k = torch.randn(layers, rows, PAGE, hkv, D, device=device, generator=gen).to(torch.bfloat16)
+    tail_v = torch.randn(layers, rows, PAGE, hkv, D, device=device, generator=gen).to(torch.bfloat16)
+    q = torch.randn(layers, rows, hq, D, device=device, generator=gen).to(torch.bfloat16)
+    k_new = (torch.randn(layers, rows, hkv, D, device=device, generator=gen) + 1.0).to(torch.bfloat16)
+    v_new = torch.randn(layers, rows, hkv, D, device=device, generator=gen).to(torch.bfloat16)
+    shift = torch.ones(hkv, D, device=device).to(torch.bfloat16)
+    out = torch.zeros(layers, rows, hq, D, dtype=torch.bfloat16, device=device)
+    block_table = torch.from_numpy(table).to(device)
+    seq_lens = torch.from_numpy(lens.astype(np.int32)).to(device)
+    starts = torch.arange(rows + 1, dtype=torch.int32, device=device)
+    plane = ControlPlane(max_num_seqs=rows, max_num_batched_tokens=rows, device=device)
+    plane.slot_keys.copy_(block_table[:, 0])
+    plane.slot_last_seq.copy_(seq_lens)
+    plane.slot_last_seen.zero_()
+    bases = torch.tensor([[v[i].data_ptr() for v in views] for i in range(4)], dtype=torch.int64,
+                         device=device)
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    piece = piece_pages(rows, hkv, columns, sms) if args.balance_pages < 0 else max(0, args.balance_pages)
+    if piece >= columns:
+        piece = 0
+    space = torch.empty(_decode.balanced_workspace_bytes(rows, hq, columns, piece) if piece else 16,
+                        dtype=torch.uint8, device=device)
+
+    def step():
+        seq_lens.add_(1)
+        ctl = plane.prepare(block_table=block_table, seq_lens=seq_lens, query_start_loc=starts,
+                            num_reqs=rows, num_actual_tokens=rows)
+        for layer in range(layers):
+            k_fp4, k_sf, v_fp4, v_sf = views[layer]
+            how = dict(balance_pages=piece, workspace=space, reuse_work_list=layer > 0) if piece else {}
+            _decode.decode_fp4(
+                query_fp4=None, query_scales=None, query_padded_bf16=None, query_bf16=q[layer],
+                key_pages_fp4=k_fp4, key_scales=k_sf, value_pages_fp4=v_fp4, value_scales=v_sf,
+                fp4_page_table=block_table, seqused_fp4=ctl.seqused_fp4,
+                residual_key_pages_bf16=tail_k[layer], residual_value_pages_bf16=tail_v[layer],
+                residual_page_ids=ctl.row_to_slot, seqused_residual=ctl.seqused_residual,
+                softmax_scale=D ** -0.5, trusted_metadata=True, out=out[layer],
+                append_key=k_new[layer], append_value=v_new[layer], key_shift=shift, **how)
+        L.check(lib.nvfp4_tail_flush(
+            tail_k.data_ptr(), tail_v.data_ptr(), rows * PAGE, ctl.promotion_source_tokens.data_ptr(),
+            ctl.promotion_pages.data_ptr(), bases.data_ptr(), block, block, block, block, rows, layers, hkv,
+            torch.cuda.current_stream(device).cuda_stream))
+
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step()
+    seq_lens.copy_(torch.from_numpy((lens + 1).astype(np.int32)).to(device))
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    clocks = sampler.stop() if sampler else None
+    ms_step = ms / args.steps
+    errors = int(plane.error_code.item())
+    # algorithmic bytes of the timed steps on this GPU, from the lengths each of them saw
+    first = 1 + max(3, args.warmup)
+    kv = 0.0
+    for s_ in range(first, first + args.steps):
+        cur = lens + s_ + 1
+        fp4 = ((cur - 1) // PAGE) * PAGE
+        kv += layers * hkv * float((fp4 * 144 + (cur - fp4) * 512).sum())
+    kv /= args.steps
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = kv / (ms_step * 1e-3) / 1e9
+    if rank == 0:
+        launches = layers * ((2 if piece else 1)) + (1 if piece else 0) + 2
+        print(json.dumps({
+            "metric": METRIC, "value": rows / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
+            "data": "synthetic",
+            "config": {
+                "workload": "full-model decode step, Llama-3.1-8B attention shapes: 32 layers, 32 seq, contexts "
+                            "uniform in [1024, 16384] growing one token per step, BF16 tails, key shift on; tensor "
+                            "parallel by KV head over 8 GPUs: 1 KV head and 4 query heads per GPU",
+                "step": "slot control plane once + per layer one decode call (query quantised and K/V token "
+                        "appended inside" + (f", rows cut into pieces of {piece} pages: work list in layer 0, "
+                                              "reused by the others, + merge launch" if piece else "")
+                        + ") + one tail flush over all layers, all timed",
+                "ranks": "every rank runs this shape on its own heads (no data-path collective); value is the "
+                         "batch's tokens per second of attention time, ms_per_step the max over ranks",
+                "l2": f"{kv / 1e6:.0f} MB of pages and tails per step and GPU against a 126 MB L2",
+                "timing": "CUDA-graph replay of one step, CUDA events, max over ranks",
+            },
+            "attention_us_per_layer": ms_step * 1e3 / layers,
+            "hbm_gbs_per_gpu": achieved, "kv_bytes_per_step_per_gpu": kv,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": "measured" if peaks else "fallback",
+                         "traffic": None},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": args.steps * launches,
+            "clocks": clocks, "control_plane_error_word": errors,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -785,10 +956,12 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ctx", type=int, default=CTX,
                     help="context length per sequence (default: the headline workload's 4096)")
-    ap.add_argument("--workload", default="batch", choices=["batch", "long-context", "ragged"],
+    ap.add_argument("--workload", default="batch", choices=["batch", "long-context", "ragged", "model-step"],
                     help="batch: the headline uniform batch (default); long-context: 4 x 32768 split "
                          "by page range over the GPUs; ragged: 32 ragged sequences with tails, the "
-                         "whole serving step (control plane, decode with fused append, flush)")
+                         "whole serving step (control plane, decode with fused append, flush); "
+                         "model-step: 32 layers of one GPU's head shard (1 KV head, 4 query heads), "
+                         "contexts uniform in [1024, 16384]")
     ap.add_argument("--exchange", default="fused", choices=["fused", "push", "peer", "nccl"])
     ap.add_argument("--pdl", action=argparse.BooleanOptionalAction, default=True,
                     help="launch the decode with programmatic stream serialization: a launch's set-up "
@@ -804,6 +977,8 @@ def main() -> None:
         run_long_context(args)
     elif args.workload == "ragged":
         run_ragged(args)
+    elif args.workload == "model-step":
+        run_model_step(args)
     else:
         run_gpu(args)
 
