@@ -236,6 +236,8 @@ typedef struct nvfp4_decode_args {
  * seqused_fp4 values, rows, max_pages and target_pages; the list launch is skipped.  Meant for
  * the layers of one model step, whose lengths are the same: the first layer builds the list, the
  * others reuse it (their partial results overwrite the earlier layer's in the same workspace).
+ * The list is trusted like trusted metadata: over a workspace that holds no such list the kernel
+ * would follow whatever row numbers the bytes spell.
  */
 #define NVFP4_DECODE_REUSE_WORK_LIST 2u
 
