@@ -242,6 +242,26 @@ typedef struct nvfp4_decode_args {
 #define NVFP4_DECODE_REUSE_WORK_LIST 2u
 
 /*
+ * NVFP4_DECODE_PERSISTENT (tensor-core kernel, 1, 2, 4 or 8 query heads per KV head; the launch
+ * shape of the reference's persistent scheduler, src/nvfp4_decode_kernel/_fa4/tile_scheduler.py:202-211,
+ * with page-granular shares in place of whole tiles): ONE launch of two CTAs per SM.  The step's
+ * page tiles (and BF16 tails, weighted) are cut into equal shares, one per CTA, from the
+ * device-resident lengths; a CTA sets up once and walks the pieces of its share back to back.  A
+ * (row, KV head) tile that falls into several shares is merged by the piece that finishes last, in
+ * a fixed order, so identical calls give identical bits.  Requires num_splits = 1, out != NULL, no
+ * partial buffers; out_indices, the fused tail append and NVFP4_DECODE_PROGRAMMATIC_LAUNCH are
+ * honoured.  workspace / workspace_bytes: at least nvfp4_decode_persistent_workspace_bytes(rows,
+ * heads_q, heads_kv) bytes (computed for the current device), 16-byte aligned, ZERO-FILLED ONCE
+ * before the first call; the kernel leaves it ready for the next call.  Calls that share a
+ * workspace must not overlap on the device.  The result agrees with the plain call within the
+ * re-association of the merge (a tile cut into pieces is folded as split partials are).
+ */
+#define NVFP4_DECODE_PERSISTENT 4u
+size_t nvfp4_decode_persistent_workspace_bytes(int rows, int heads_q, int heads_kv);
+/* 1 if NVFP4_DECODE_PERSISTENT takes this shape on the current device, else 0. */
+int nvfp4_decode_persistent_supported(int rows, int heads_q, int heads_kv);
+
+/*
  * With out != NULL the merged bf16 result is written (for num_splits > 1 the
  * partials go through o_partial/lse_partial if given, else through workspace).
  * With out == NULL the call only emits the partials (used by the cross-GPU

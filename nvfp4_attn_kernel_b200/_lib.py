@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(HERE, "libnvfp4_b200.so")
 IMPL_AUTO, IMPL_GENERIC, IMPL_SM100 = 0, 1, 2
 DECODE_PROGRAMMATIC_LAUNCH = 1
 DECODE_REUSE_WORK_LIST = 2
+DECODE_PERSISTENT = 4
 STATUS_BAD_PAGE_ID, STATUS_BAD_TAIL_ID, STATUS_WAIT_TIMEOUT, STATUS_BAD_LENGTH = 1, 2, 4, 8
 ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED = 1, 2, 3
 
@@ -47,6 +48,8 @@ EXPORTS = (
     "nvfp4_decode_balanced_workspace_bytes",
     "nvfp4_static_workspace_bytes",
     "nvfp4_decode_split_static_error",
+    "nvfp4_decode_persistent_workspace_bytes",
+    "nvfp4_decode_persistent_supported",
 )
 
 
@@ -209,6 +212,10 @@ def _declare_static(lib) -> None:
     lib.nvfp4_decode_balanced_capacity.argtypes = [c_int, c_int, c_int]
     lib.nvfp4_decode_balanced_workspace_bytes.restype = c_size_t
     lib.nvfp4_decode_balanced_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
+    lib.nvfp4_decode_persistent_workspace_bytes.restype = c_size_t
+    lib.nvfp4_decode_persistent_workspace_bytes.argtypes = [c_int, c_int, c_int]
+    lib.nvfp4_decode_persistent_supported.restype = c_int
+    lib.nvfp4_decode_persistent_supported.argtypes = [c_int, c_int, c_int]
     lib.nvfp4_static_workspace_bytes.restype = c_size_t
     lib.nvfp4_static_workspace_bytes.argtypes = []
     lib.nvfp4_decode_split_static_error.restype = c_char_p

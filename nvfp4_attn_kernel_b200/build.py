@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_NAME = "libnvfp4_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
 
-SOURCES = ["capi.cu", "quantize.cu", "decode_generic.cu", "decode_sm100.cu", "merge.cu",
+SOURCES = ["capi.cu", "quantize.cu", "decode_generic.cu", "decode_sm100.cu", "decode_persistent.cu", "merge.cu",
            "decode_static_ws.cu", "control.cu", "probe.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -231,6 +231,21 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
 
 int nvfp4_decode(const nvfp4_decode_args* a, void* stream) { return decode_call(a, nullptr, 0, stream); }
 
+size_t nvfp4_decode_persistent_workspace_bytes(int rows, int heads_q, int heads_kv) {
+  if (rows <= 0 || !valid_group(heads_q, heads_kv)) return 0;
+  return nvfp4::decode_persistent_workspace_bytes(rows, heads_q, heads_kv);
+}
+
+int nvfp4_decode_persistent_supported(int rows, int heads_q, int heads_kv) {
+  if (rows < 0 || !valid_group(heads_q, heads_kv)) return 0;
+  nvfp4::DecodeParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.rows = rows;
+  p.heads_q = heads_q;
+  p.heads_kv = heads_kv;
+  return nvfp4::decode_persistent_supports(p) ? 1 : 0;
+}
+
 // Balanced split: row r is cut into ceil(pages_r / target_pages) pieces (one if it has no page),
 // so the list of pieces is never longer than rows + rows * max_pages / target_pages.
 int64_t nvfp4_decode_balanced_capacity(int rows, int max_pages, int target_pages) {
@@ -359,7 +374,7 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.num_splits = a->num_splits;
   p.status = a->status;
-  if (a->flags & ~(NVFP4_DECODE_PROGRAMMATIC_LAUNCH | NVFP4_DECODE_REUSE_WORK_LIST))
+  if (a->flags & ~(NVFP4_DECODE_PROGRAMMATIC_LAUNCH | NVFP4_DECODE_REUSE_WORK_LIST | NVFP4_DECODE_PERSISTENT))
     return fail(NVFP4_ERR_INVALID, "decode: unknown flag bits %#x", a->flags);
   if ((a->flags & NVFP4_DECODE_REUSE_WORK_LIST) && !target_pages)
     return fail(NVFP4_ERR_INVALID, "decode: only nvfp4_decode_balanced has a work list to reuse");
@@ -426,6 +441,23 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int impl = a->impl;
   if (impl == NVFP4_IMPL_AUTO) impl = nvfp4::decode_sm100_supports(p) ? NVFP4_IMPL_SM100 : NVFP4_IMPL_GENERIC;
+  if (a->flags & NVFP4_DECODE_PERSISTENT) {
+    if (!direct || x)
+      return fail(NVFP4_ERR_INVALID,
+                  "decode: the persistent launch writes the final rows only (num_splits = 1, out given, no "
+                  "partial buffers, no exchange, not nvfp4_decode_balanced)");
+    if (impl != NVFP4_IMPL_SM100 || !nvfp4::decode_persistent_supports(p))
+      return fail(NVFP4_ERR_UNSUPPORTED,
+                  "decode: the persistent launch takes 1, 2, 4 or 8 query heads per KV head on the tensor-core "
+                  "kernel (see nvfp4_decode_persistent_supported)");
+    const size_t need = nvfp4::decode_persistent_workspace_bytes(a->rows, a->heads_q, a->heads_kv);
+    if (!a->workspace || a->workspace_bytes < need)
+      return fail(NVFP4_ERR_INVALID, "decode: the persistent launch needs a workspace of %zu bytes, got %zu", need,
+                  a->workspace_bytes);
+    if (!aligned16(a->workspace)) return fail(NVFP4_ERR_INVALID, "decode: workspace must be 16-byte aligned");
+    cudaError_t pe = nvfp4::launch_decode_persistent(p, a->workspace, st);
+    return pe == cudaSuccess ? NVFP4_OK : cuda_fail(pe, "persistent decode launch");
+  }
   if (p.pdl && (impl != NVFP4_IMPL_SM100 || x))
     return fail(NVFP4_ERR_UNSUPPORTED,
                 "decode: programmatic launch is carried by the plain tensor-core decode only");

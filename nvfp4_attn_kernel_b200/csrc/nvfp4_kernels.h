@@ -96,6 +96,8 @@ struct DecodeParams {
   // and entry w stores its partial in slot w.
   const int4* work_list;
   int work_capacity;
+  // Persistent kernel: arrivals per (row, KV head) tile, zero between launches.
+  int* tile_counters;
 };
 
 // CUDA-core kernel: any G = Hq/Hkv in {1,2,4,8,16,32}.
@@ -104,6 +106,15 @@ cudaError_t launch_decode_generic(const DecodeParams& p, cudaStream_t stream);
 // tcgen05 kernel: G in {1, 2, 4, 8, 16, 32}.  Returns cudaErrorNotSupported when the shape is outside it.
 cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream);
 bool decode_sm100_supports(const DecodeParams& p);
+
+// Persistent tcgen05 kernel (one launch, equal shares of page tiles per resident CTA, pieces of a
+// tile merged by the piece that arrives last): G in {1, 2, 4, 8}, final BF16 output only.
+// workspace: decode_persistent_workspace_bytes() bytes whose first rows * heads_kv ints were
+// zero-filled once.
+cudaError_t launch_decode_persistent(const DecodeParams& p, void* workspace, cudaStream_t stream);
+bool decode_persistent_supports(const DecodeParams& p);
+size_t decode_persistent_workspace_bytes(int rows, int heads_q, int heads_kv);
+int decode_persistent_ctas();
 
 cudaError_t launch_lse_merge(const float* o_parts, int64_t o_split_stride, const float* lse_parts,
                              int64_t lse_split_stride, const float* const* o_ptrs,

@@ -126,6 +126,18 @@ def balanced_workspace_bytes(rows: int, heads_q: int, max_pages: int, balance_pa
     return int(_lib.load().nvfp4_decode_balanced_workspace_bytes(rows, heads_q, max_pages, balance_pages))
 
 
+def persistent_workspace(rows: int, heads_q: int, heads_kv: int, device) -> torch.Tensor | None:
+    """Zero-filled scratch for ``decode_fp4(persistent_workspace=...)`` on ``device`` for up to
+    ``rows`` rows, or None when the persistent launch does not take the shape.  Allocate it once
+    (outside any graph capture) and pass it to every call; calls that share it must not overlap."""
+    with torch.cuda.device(device):
+        lib = _lib.load()
+        if not lib.nvfp4_decode_persistent_supported(rows, heads_q, heads_kv):
+            return None
+        need = int(lib.nvfp4_decode_persistent_workspace_bytes(rows, heads_q, heads_kv))
+    return torch.zeros(need, dtype=torch.uint8, device=device)
+
+
 def decode_fp4(
     *,
     query_fp4: torch.Tensor | None,
@@ -160,8 +172,13 @@ def decode_fp4(
     balance_pages: int | None = None,
     workspace: torch.Tensor | None = None,
     reuse_work_list: bool = False,
+    persistent_workspace: torch.Tensor | None = None,
 ) -> torch.Tensor | None:
     """Validate every tensor contract and launch the decode on the current stream.
+
+    ``persistent_workspace`` (an extension; from :func:`persistent_workspace`, zero-filled once):
+    run the step as ONE persistent launch of two CTAs per SM that share the step's page tiles
+    equally, whatever the rows' lengths (``NVFP4_DECODE_PERSISTENT`` of the C ABI).
 
     ``balance_pages`` (an extension): cut every row into pieces of about that many FP4 pages,
     each row by its own length, instead of one ``num_splits`` for the whole batch; ``workspace``
@@ -451,6 +468,8 @@ def decode_fp4(
 
     if out is None and _partials is None:
         out = torch.empty(rows, heads_q, HEAD_DIM, dtype=torch.bfloat16, device=device)
+    if balance_pages is not None and persistent_workspace is not None:
+        raise ValueError("balance_pages and persistent_workspace are two ways to cut the step; give one")
     if balance_pages is not None:
         if not isinstance(balance_pages, int) or balance_pages < 1:
             raise ValueError(f"balance_pages must be a positive integer, got {balance_pages!r}")
@@ -469,6 +488,17 @@ def decode_fp4(
             raise ValueError(f"workspace must be contiguous 16-byte aligned uint8 of at least {need} bytes")
     elif workspace is not None or reuse_work_list:
         raise ValueError("workspace and reuse_work_list are only taken together with balance_pages")
+    elif persistent_workspace is not None:
+        if num_splits != 1 or _partials is not None or _exchange is not None:
+            raise ValueError("the persistent launch writes the final rows: no num_splits, partial "
+                             "buffers or cross-GPU exchange")
+        with torch.cuda.device(device):
+            need = int(_lib.load().nvfp4_decode_persistent_workspace_bytes(rows, heads_q, heads_kv))
+        if (persistent_workspace.dtype is not torch.uint8 or persistent_workspace.device != device
+                or persistent_workspace.numel() < need or not persistent_workspace.is_contiguous()
+                or persistent_workspace.data_ptr() % 16):
+            raise ValueError(f"persistent_workspace must be contiguous 16-byte aligned uint8 of at least {need} bytes")
+        workspace = persistent_workspace
     elif num_splits > 1 and _partials is None:
         need = _lib.load().nvfp4_decode_workspace_bytes(rows, heads_q, num_splits)
         workspace = torch.empty(need, dtype=torch.uint8, device=device)
@@ -532,6 +562,8 @@ def decode_fp4(
         args.flags = _lib.DECODE_PROGRAMMATIC_LAUNCH
     if reuse_work_list:
         args.flags |= _lib.DECODE_REUSE_WORK_LIST
+    if persistent_workspace is not None:
+        args.flags |= _lib.DECODE_PERSISTENT
     if args.page_table_row_stride < args.max_pages:
         raise ValueError("fp4_page_table rows overlap")
     with torch.cuda.device(device):

@@ -142,6 +142,7 @@ def fp4_decode_impl(
     balance_pages=None,
     balance_workspace=None,
     balance_reuse=False,
+    persistent_workspace=None,
 ):
     from ._decode import decode_fp4, decode_fp4_split
     from ._quantize import quantize_query
@@ -160,7 +161,7 @@ def fp4_decode_impl(
             _sig(residual_key_pages_bf16), _sig(residual_value_pages_bf16), _sig(residual_page_ids),
             _sig(seqused_residual), _sig(has_bf16), _sig(out), _sig(out_indices),
             _sig(query_padded_scratch), _sig(query_fp4_scratch), _sig(query_scales_scratch),
-            _sig(append_key), _sig(append_value), _sig(key_shift),
+            _sig(append_key), _sig(append_value), _sig(key_shift), _sig(persistent_workspace),
             softmax_scale, FUSE_QUERY_QUANT, _decode_module().DEFAULT_IMPL,
         )
         plan = _PLANS.get(plan_key)
@@ -260,6 +261,10 @@ def fp4_decode_impl(
     )
     if append_key is not None or append_value is not None or key_shift is not None:
         shared.update(append_key=append_key, append_value=append_value, key_shift=key_shift)
+    if persistent_workspace is not None:
+        if num_splits > 1 or balance_pages is not None:
+            raise ValueError("persistent_workspace replaces num_splits and balance_pages")
+        shared.update(persistent_workspace=persistent_workspace)
     if num_splits > 1:
         return decode_fp4_split(**shared, num_splits=num_splits)
     if balance_pages is not None:

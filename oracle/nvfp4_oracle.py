@@ -572,6 +572,96 @@ def balanced_capacity(rows: int, max_pages: int, target_pages: int) -> int:
     return rows + rows * max_pages // target_pages
 
 
+# --------------------------------------------------------------------------
+# schedule of the persistent decode launch (no counterpart in the reference, whose persistent
+# scheduler hands out whole tiles: _fa4/tile_scheduler.py:202-211).  Restated here so that the
+# parity tests can run the attention oracle piece by piece and merge, which is what the
+# reference's split path defines for a row cut into page ranges (_decode.py:982-1171).
+# --------------------------------------------------------------------------
+
+PERSISTENT_MIN_SHARE = 4
+
+
+def persistent_tail_units(tail_len: int) -> int:
+    """Cost of a BF16 tail in units of one NVFP4 page."""
+    return 4 + (tail_len >> 3) if tail_len > 0 else 0
+
+
+def persistent_pieces(seqused_fp4, seqused_tail, tail_ids, tail_pages: int, heads_kv: int,
+                      max_pages: int, ctas: int):
+    """Pieces of every (row, KV head) tile: ``{(row, kvh): [(first_page, last_page, owns_tail), ...]}``
+    in the order they are merged.  A row costs ``max(1, pages + tail units)`` units, the rows lie
+    end to end, and the CTAs form ``ctas // heads_kv`` groups of ``heads_kv``: group j of
+    ``ce = min(groups, ceil(T / 4))`` owns units ``[j T // ce, (j + 1) T // ce)`` and its CTA h
+    walks KV head h of them, so every KV head of a row is cut at the same places.  Unit 0 of a row
+    stands for its tail, the units after the tail units for pages 0, 1, ...  A group whose share
+    of a row holds neither the tail nor a page still contributes an (empty) piece."""
+    rows = len(seqused_fp4)
+    info = []
+    for r in range(rows):
+        fp4 = int(seqused_fp4[r])
+        n = fp4 >> 7
+        if fp4 < 0 or n > max_pages:
+            n = 0 if fp4 < 0 else max_pages
+        tl = 0
+        if seqused_tail is not None and int(seqused_tail[r]) > 0:
+            ln = min(int(seqused_tail[r]), PAGE)
+            tid = int(tail_ids[r])
+            if 0 <= tid < tail_pages:
+                tl = ln
+        info.append((n, tl, max(1, n + persistent_tail_units(tl))))
+    total = sum(c for _, _, c in info)
+    ce = min(ctas // heads_kv, -(-total // PERSISTENT_MIN_SHARE))
+    pieces = {}
+    u = 0
+    for r, (n, tl, cost) in enumerate(info):
+        tw = persistent_tail_units(tl)
+        c_first = ((u + 1) * ce - 1) // total
+        c_last = ((u + cost) * ce - 1) // total
+        tile = []
+        for c in range(c_first, c_last + 1):
+            u0, u1 = c * total // ce, (c + 1) * total // ce
+            lo, hi = max(u0, u) - u, min(u1, u + cost) - u
+            first = min(max(lo, tw) - tw, n)
+            last = min(max(hi, tw) - tw, n)
+            tile.append((first, last, tl > 0 and lo == 0))
+        for h in range(heads_kv):
+            pieces[(r, h)] = tile
+        u += cost
+    return pieces
+
+
+def attention_in_pieces(pieces, q_bf16, q_dq, k_dq_pages, v_dq_pages, page_table, seqused_fp4,
+                        tail_key=None, tail_value=None, tail_ids=None, seqused_residual=None,
+                        softmax_scale=None, tiles=None):
+    """The attention oracle run piece by piece over ``pieces`` (see ``persistent_pieces``) and
+    merged by LSE weight per tile.  ``tiles``: restrict to these (row, kvh) keys; other output
+    rows stay zero."""
+    rows, hq, d = q_dq.shape
+    hkv = k_dq_pages.shape[2]
+    g = hq // hkv
+    out = np.zeros((rows, hq, d), dtype=np.float32)
+    for (r, h), tile in pieces.items():
+        if tiles is not None and (r, h) not in tiles:
+            continue
+        hs = slice(h * g, (h + 1) * g)
+        parts, lses = [], []
+        for first, last, owns_tail in tile:
+            o, lse = attention_from_dequantized(
+                q_bf16[r:r + 1, hs], q_dq[r:r + 1, hs], k_dq_pages[:, :, h:h + 1], v_dq_pages[:, :, h:h + 1],
+                page_table[r:r + 1], seqused_fp4[r:r + 1],
+                tail_key=None if tail_key is None else tail_key[:, :, h:h + 1],
+                tail_value=None if tail_value is None else tail_value[:, :, h:h + 1],
+                tail_ids=None if tail_ids is None else tail_ids[r:r + 1],
+                seqused_residual=None if seqused_residual is None else seqused_residual[r:r + 1],
+                softmax_scale=softmax_scale, page_range=(lambda n, a=first, b=last: (a, b)),
+                owns_tail=owns_tail, return_lse=True)
+            parts.append(o)
+            lses.append(lse)
+        out[r, hs] = lse_merge(np.stack(parts), np.stack(lses))[0]
+    return out
+
+
 def lse_merge(o_parts, lse_parts, return_lse: bool = False):
     """o_parts [S, rows, Hq, D] fp32 normalised, lse_parts [S, rows, Hq].
 

@@ -74,6 +74,22 @@ class Problem:
         args.update(kw)
         return fp4_decode(**args)
 
+    def decode_direct(self, **kw):
+        """The host layer under ``fp4_decode`` (BF16 query quantised in the launch); takes
+        ``status`` and the other arguments the operator's signature does not carry."""
+        from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode
+
+        args = dict(
+            query_fp4=None, query_scales=None, query_padded_bf16=None, query_bf16=self.q,
+            key_pages_fp4=self.k_fp4, key_scales=self.k_sf, value_pages_fp4=self.v_fp4,
+            value_scales=self.v_sf, fp4_page_table=self.page_table, seqused_fp4=self.seqused_fp4,
+            residual_key_pages_bf16=self.k_pages, residual_value_pages_bf16=self.v_pages,
+            residual_page_ids=self.residual_page_ids, seqused_residual=self.seqused_residual,
+            softmax_scale=self.softmax_scale,
+        )
+        args.update(kw)
+        return _decode.decode_fp4(**args)
+
     def oracle_from_bytes(self, rows=None, splits: int = 1):
         """Oracle fed with the library's dequantised Q/K/V bytes.  With ``splits`` > 1 the
         oracle runs once per page range (the tail goes with range 0) and the partials are
@@ -106,6 +122,34 @@ class Problem:
             parts.append(o)
             lses.append(lse)
         return O.lse_merge(np.stack(parts), np.stack(lses))
+
+
+def persistent_ctas(device) -> int:
+    """CTAs of the persistent decode launch on this device: two per SM."""
+    return 2 * torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def oracle_persistent(prob: "Problem", tiles=None, with_tail: bool = True):
+    """The attention oracle over the pieces the persistent launch cuts this problem into, fed the
+    library's own dequantised bytes; ``tiles`` restricts it to some (row, kvh) pairs."""
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _quantize
+
+    c = prob.case
+    rows_n = prob.q.shape[0]
+    q_fp4, q_sf = _quantize.quantize_query(prob.q, heads_kv=prob.heads_kv)
+    storage = q_sf.as_strided((rows_n, prob.heads_q * 1024), (prob.heads_q * 1024, 1))
+    q_dq = O.dequantize_query(to_np(q_fp4), to_np(storage).reshape(rows_n, 1, prob.heads_q, 2, 32, 4, 4),
+                              prob.heads_kv)
+    k_dq = O.dequantize_key_pages(to_np(prob.k_fp4), scale_bytes(prob.k_sf))
+    v_dq = O.dequantize_value_pages(to_np(prob.v_fp4), scale_bytes(prob.v_sf))
+    tail = dict(tail_key=c["k_pages"], tail_value=c["v_pages"], tail_ids=c["residual_page_ids"],
+                seqused_residual=c["seqused_residual"]) if with_tail else {}
+    pieces = O.persistent_pieces(
+        c["seqused_fp4"], c["seqused_residual"] if with_tail else None,
+        c["residual_page_ids"] if with_tail else None, c["k_pages"].shape[0], prob.heads_kv,
+        c["page_table"].shape[1], persistent_ctas(prob.device))
+    return O.attention_in_pieces(pieces, c["q"], q_dq, k_dq, v_dq, c["page_table"], c["seqused_fp4"],
+                                 softmax_scale=c["softmax_scale"], tiles=tiles, **tail), pieces
 
 
 def interleave_vllm(k_fp4, k_sf, v_fp4, v_sf):
