@@ -12,11 +12,17 @@
 // unit 0 - the reference gives the tail to split 0, fp4_decode_kernel.py:159), the units after
 // it for logical pages 0, 1, ...
 //
-// A piece that covers its whole tile stores the BF16 output row directly.  Any other piece stores
-// a partial (normalised fp32 O and natural-log LSE, the split format of the reference,
-// fp4_decode_kernel.py:5186-5196) into one of the CTA's two scratch slots and counts its arrival
-// on the tile; the piece that arrives last folds the tile's pieces in CTA order (so the result
-// does not depend on who came last) with the arithmetic of the LSE merge kernel.
+// A piece that covers its whole row stores the BF16 output row directly.  A row cut over several
+// groups is folded by the group that holds its first unit.  Rows lie in order, so every other
+// group meets the row as the FIRST piece of its share: it stores a partial (normalised fp32 O and
+// natural-log LSE, the split format of the reference, fp4_decode_kernel.py:5186-5196) into the
+// CTA's scratch slot, every value together with the launch's tag in one 8-byte word, and waits
+// for nothing: no fence, no counter.  The folding group meets the row as the LAST piece of its
+// share: by then the others have normally arrived, it fetches their words while its own last
+// pages are in flight and folds them with its own values out of registers, in group order and
+// with the arithmetic of the LSE merge kernel.  Only for words still missing at its very end does
+// it wait (bounded) - for CTAs of higher index only, whose first piece depends on nobody, so the
+// wait cannot be circular.
 //
 // Inside a CTA the roles are those of the one-tile kernel (decode_sm100.cu): warps 0-3 score
 // threads, 4-7 output threads, 8 / 11 K and V producers, 9 / 10 the two MMA issuers.  The rings,
@@ -27,9 +33,8 @@
 // softmax state, and the output threads' epilogue.
 //
 // Every device-side wait is bounded; on expiry the CTA raises NVFP4_STATUS_WAIT_TIMEOUT, keeps
-// walking its schedule without touching data (every piece still counts its arrival, marked
-// failed, so the tile counters return to zero), drains its copies, frees tensor memory and
-// returns.
+// walking its schedule without touching data (a storing piece marks its partial failed and the
+// folding piece then leaves the row alone), drains its copies, frees tensor memory and returns.
 #include "sm100_device.cuh"
 
 namespace nvfp4 {
@@ -97,8 +102,6 @@ struct __align__(1024) Smem {
   uint64_t q_full[2], seg_done[8], drain[2];
   uint32_t tmem_base;
   volatile int abort_flag;
-  volatile int direct[2];                       // the output threads' decision for the CTA's k-th cut piece
-  volatile int fold_late[2];                    // the k-th cut piece turned out to be its tile's last arrival
 };
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
@@ -192,7 +195,7 @@ __device__ __forceinline__ void build_schedule(const DecodeParams& p, SM& sm, in
           s.tail_id = owns_tail ? tid : -1;
           s.c_first = (int)(((U + 1) * ce - 1) / T);       // groups that hold the row's first and last unit
           s.c_last = (int)(((U + cost) * ce - 1) / T);
-          s.slot = (lo == 0 && hi == cost) ? -1 : 2 * (int)blockIdx.x + (c == s.c_first ? 1 : 0);
+          s.slot = (lo == 0 && hi == cost) ? -1 : (int)blockIdx.x;
           s.pad = 0;
           sm.seg[pos] = s;
         }
@@ -204,149 +207,167 @@ __device__ __forceinline__ void build_schedule(const DecodeParams& p, SM& sm, in
   if (lane == 0) sm.nseg = count;
 }
 
-__device__ __forceinline__ int slot_of(const DecodeParams& p, const Seg& sg, int group) {
-  return 2 * (group * p.heads_kv + sg.kvh) + (group == sg.c_first ? 1 : 0);
-}
+// ---- the scratch slots: values that carry their own arrival flag ----
+// A storing piece writes every value of its partial as an 8-byte word {value bits, tag}, the tag
+// being this launch's number.  An 8-byte store lands whole, so a reader that finds the tag it
+// expects has the value: the writer needs neither a fence nor a counter and never waits, and a
+// slot never has to be cleared (the next launch expects the next tag).  A piece that failed
+// writes its LSE words with kFailBit set instead.
+constexpr uint32_t kFailBit = 0x80000000u;
 
-// Fold the pieces of a tile in group order out of the scratch slots and store the BF16 row: the
-// 128 output threads (thread t = channel t).  The arithmetic per channel is that of the LSE merge
-// kernel, and of merge_direct below.
+// slot of the partial that group `group` stores for KV head kvh: one per CTA, a CTA stores at most
+// one partial (the row that began in an earlier group)
+__device__ __forceinline__ int slot_of(const DecodeParams& p, int kvh, int group) { return group * p.heads_kv + kvh; }
+
+// word `i` of slot `slot`: words [0, G * 128) the normalised O, [G * 128, G * 129) the LSEs
 template <int G>
-__device__ __forceinline__ void merge_tile(const DecodeParams& p, const Seg& sg, int t) {
-  const int64_t orow = p.out_indices ? (int64_t)p.out_indices[sg.row] : (int64_t)sg.row;
-#pragma unroll 1
-  for (int q = 0; q < G; ++q) {
-    float mx = -INFINITY;
-    for (int c = sg.c_first; c <= sg.c_last; ++c)
-      mx = fmaxf(mx, __ldcg(p.lse_partial + (int64_t)slot_of(p, sg, c) * G + q));
-    float tot = 0.f, acc = 0.f;
-    for (int c = sg.c_first; c <= sg.c_last; ++c) {
-      const int slot = slot_of(p, sg, c);
-      const float ls = __ldcg(p.lse_partial + (int64_t)slot * G + q);
-      const float ov = __ldcg(p.o_partial + ((int64_t)slot * G + q) * kHeadDim + t);
-      if (ls == -INFINITY) continue;   // an empty piece weighs nothing, whatever its O holds
-      const float wgt = expf(ls - mx);
-      tot += wgt;
-      acc = fmaf(wgt, ov, acc);
+__device__ __forceinline__ uint2* slot_word(const DecodeParams& p, int slot, int i) {
+  return reinterpret_cast<uint2*>(p.o_partial) + (int64_t)slot * (G * (kHeadDim + 1)) + i;
+}
+__device__ __forceinline__ void st_word(uint2* at, float v, uint32_t tag) {
+  asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(at), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_word(const uint2* at) {
+  uint2 v;
+  asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(at) : "memory");
+  return v;
+}
+// The value of a word once it carries `tag` (bounded wait).  *bad is set when the writer marked
+// the piece failed or the wait ran out.
+__device__ __forceinline__ float wait_word(const uint2* at, uint2 have, uint32_t tag, uint32_t* status, bool* bad) {
+  if (have.y == tag) return __uint_as_float(have.x);
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    if (have.y == tag) return __uint_as_float(have.x);
+    if (have.y == (tag | kFailBit)) { *bad = true; return 0.f; }
+    if (global_ns() - t0 > kWaitLimitNs) {
+      set_status(status, NVFP4_STATUS_WAIT_TIMEOUT);
+      *bad = true;
+      return 0.f;
     }
-    const float r = tot > 0.f ? __fdiv_rn(acc, tot) : 0.f;
-    p.out[(orow * p.heads_q + sg.kvh * G + q) * kHeadDim + t] = __bfloat16_as_ushort(__float2bfloat16_rn(r));
+    __nanosleep(40);
+    have = ld_word(at);
   }
 }
 
-// Pieces other than the running one that the output threads fold themselves (see below); a tile
-// cut into more pieces goes through the scratch slots.
+// Pieces other than the folding one whose values are fetched ahead into registers; a row cut into
+// more pieces is folded with loads at the end.
 template <int G> struct DirectOthers { static constexpr int value = G <= 4 ? 2 : 1; };
 
-// The other pieces of a tile, fetched by the output threads (thread t = channel t) while their
-// own piece's last pages are in flight.
+// Values of the other pieces of a row, fetched by an output thread (thread t = channel t) while
+// its own piece's last pages are in flight.
 template <int G>
 struct Others {
   float o[G][DirectOthers<G>::value], lse[G][DirectOthers<G>::value];
 };
 
+// Returns true if every word carried the tag (the values are then in `ot`); else the fold loads
+// them again at its end, and waits.
 template <int G>
-__device__ __forceinline__ void fetch_others(const DecodeParams& p, const Seg& sg, int my_group, int t,
-                                             Others<G>& ot) {
-  int j = 0;
-  for (int c = sg.c_first; c <= sg.c_last; ++c) {
-    if (c == my_group) continue;
-    const int slot = slot_of(p, sg, c);
+__device__ __forceinline__ bool fetch_others(const DecodeParams& p, const Seg& sg, int t, uint32_t tag, Others<G>& ot) {
+  // the folding piece lies in group c_first: the others are c_first + 1 .. c_last
+  bool all = true;
+#pragma unroll
+  for (int jj = 0; jj < DirectOthers<G>::value; ++jj) {
+    const int c = sg.c_first + 1 + jj;
+    if (c > sg.c_last) break;
+    const int slot = slot_of(p, sg.kvh, c);
+    uint2 wl[G], wo[G];
 #pragma unroll
     for (int q = 0; q < G; ++q) {
-#pragma unroll
-      for (int jj = 0; jj < DirectOthers<G>::value; ++jj)
-        if (jj == j) {
-          ot.lse[q][jj] = __ldcg(p.lse_partial + (int64_t)slot * G + q);
-          ot.o[q][jj] = __ldcg(p.o_partial + ((int64_t)slot * G + q) * kHeadDim + t);
-        }
+      wl[q] = ld_word(slot_word<G>(p, slot, G * kHeadDim + q));
+      wo[q] = ld_word(slot_word<G>(p, slot, q * kHeadDim + t));
     }
-    ++j;
+#pragma unroll
+    for (int q = 0; q < G; ++q) {
+      all = all && wl[q].y == tag && wo[q].y == tag;
+      ot.lse[q][jj] = __uint_as_float(wl[q].x);
+      ot.o[q][jj] = __uint_as_float(wo[q].x);
+    }
   }
+  return all;
 }
 
-// The same fold as merge_tile_warp with this piece's values out of registers: group order, so the
-// bits do not depend on which piece ran last or on which of the two routes folded the tile.
+// Fold a row: this piece (group c_first, values in registers) and the pieces of the groups after
+// it, in group order, with the arithmetic of the LSE merge kernel; store the BF16 row.  Values
+// not fetched ahead are loaded now, waiting (bounded) for words that have not arrived.  Returns
+// false, storing nothing, if a piece failed.
 template <int G>
-__device__ __forceinline__ void merge_direct(const DecodeParams& p, const Seg& sg, int my_group, int t,
-                                             const float (&val)[G], const float (&lse)[G], const Others<G>& ot) {
+__device__ __forceinline__ bool fold_row(const DecodeParams& p, const Seg& sg, int t, uint32_t tag,
+                                         const float (&val)[G], const float (&lse)[G], const Others<G>& ot,
+                                         bool fetched) {
   const int64_t orow = p.out_indices ? (int64_t)p.out_indices[sg.row] : (int64_t)sg.row;
+  const int others = sg.c_last - sg.c_first;
+  bool bad = false;
+  float mx[G], tot[G], acc[G];
 #pragma unroll
-  for (int q = 0; q < G; ++q) {
-    float mx = lse[q];
-    int j = 0;
-    for (int c = sg.c_first; c <= sg.c_last; ++c) {
-      if (c == my_group) continue;
+  for (int q = 0; q < G; ++q) mx[q] = lse[q];
+  if (fetched) {
 #pragma unroll
-      for (int jj = 0; jj < DirectOthers<G>::value; ++jj)
-        if (jj == j) mx = fmaxf(mx, ot.lse[q][jj]);
-      ++j;
-    }
-    float tot = 0.f, acc = 0.f;
-    j = 0;
-    for (int c = sg.c_first; c <= sg.c_last; ++c) {
-      float ls = lse[q], ov = val[q];
-      if (c != my_group) {
+    for (int jj = 0; jj < DirectOthers<G>::value; ++jj)
+      if (jj < others) {
 #pragma unroll
-        for (int jj = 0; jj < DirectOthers<G>::value; ++jj)
-          if (jj == j) { ls = ot.lse[q][jj]; ov = ot.o[q][jj]; }
-        ++j;
+        for (int q = 0; q < G; ++q) mx[q] = fmaxf(mx[q], ot.lse[q][jj]);
       }
-      if (ls == -INFINITY) continue;
-      const float wgt = expf(ls - mx);
-      tot += wgt;
-      acc = fmaf(wgt, ov, acc);
-    }
-    const float r = tot > 0.f ? __fdiv_rn(acc, tot) : 0.f;
-    p.out[(orow * p.heads_q + sg.kvh * G + q) * kHeadDim + t] = __bfloat16_as_ushort(__float2bfloat16_rn(r));
-  }
-}
-
-__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// End of a piece, output threads (thread t = channel t).  A whole tile: store the row.  A cut
-// piece: either fold it with the other pieces fetched meanwhile (direct: they had all arrived when
-// this piece looked, shortly before its end) and store the row, or store the partial into the
-// scratch slot and count the arrival.  The count's answer (was this the tile's last piece?) is
-// left in flight in thread 0's register `ticket` and only looked at when the CTA has run out of
-// pieces, so these threads wait for the fence but never for the atomic's round trip.
-template <int G, class SM>
-__device__ __forceinline__ void finish_piece(const DecodeParams& p, const Seg& sg, SM& sm, int t, bool direct,
-                                             const float (&val)[G], const float (&lse)[G],
-                                             const Others<G>& ot, bool ok, int& ticket) {
-  const int64_t orow = p.out_indices ? (int64_t)p.out_indices[sg.row] : (int64_t)sg.row;
-  if (sg.slot < 0) {
-    if (ok) {
+  } else {
+    for (int j = 0; j < others; ++j) {
+      const int slot = slot_of(p, sg.kvh, sg.c_first + 1 + j);
+      uint2 w[G];
+#pragma unroll
+      for (int q = 0; q < G; ++q) w[q] = ld_word(slot_word<G>(p, slot, G * kHeadDim + q));
 #pragma unroll
       for (int q = 0; q < G; ++q)
-        p.out[(orow * p.heads_q + sg.kvh * G + q) * kHeadDim + t] =
-            __bfloat16_as_ushort(__float2bfloat16_rn(val[q]));
+        mx[q] = fmaxf(mx[q], wait_word(slot_word<G>(p, slot, G * kHeadDim + q), w[q], tag, p.status, &bad));
     }
-    return;
   }
-  int* counter = p.tile_counters + sg.row * p.heads_kv + sg.kvh;
-  if (direct) {
-    // every other piece has arrived: nobody else touches the tile any more
-    if (ok) merge_direct<G>(p, sg, (int)blockIdx.x / p.heads_kv, t, val, lse, ot);
-    if (t == 0) *counter = 0;   // ready for the next launch
-    return;
-  }
-  if (ok) {
 #pragma unroll
-    for (int q = 0; q < G; ++q) {
-      p.o_partial[((int64_t)sg.slot * G + q) * kHeadDim + t] = val[q];
-      if (t == 0) p.lse_partial[(int64_t)sg.slot * G + q] = lse[q];
+  for (int q = 0; q < G; ++q) {
+    tot[q] = 0.f; acc[q] = 0.f;
+    if (lse[q] != -INFINITY) {   // an empty piece weighs nothing, whatever its O holds
+      const float wgt = expf(lse[q] - mx[q]);
+      tot[q] = wgt;
+      acc[q] = wgt * val[q];
     }
   }
-  ok = bar_and_128(6, ok);   // every thread's stores are issued (and the verdict is one for all)
-  if (t == 0) {
-    __threadfence();         // ... and visible before the arrival is
-    ticket = atomicAdd(counter, ok ? 1 : 0x10001);
+  if (fetched) {
+#pragma unroll
+    for (int jj = 0; jj < DirectOthers<G>::value; ++jj)
+      if (jj < others) {
+#pragma unroll
+        for (int q = 0; q < G; ++q) {
+          if (ot.lse[q][jj] == -INFINITY) continue;
+          const float wgt = expf(ot.lse[q][jj] - mx[q]);
+          tot[q] += wgt;
+          acc[q] = fmaf(wgt, ot.o[q][jj], acc[q]);
+        }
+      }
+  } else {
+    for (int j = 0; j < others; ++j) {
+      const int slot = slot_of(p, sg.kvh, sg.c_first + 1 + j);
+      uint2 wl[G], wo[G];
+#pragma unroll
+      for (int q = 0; q < G; ++q) {
+        wl[q] = ld_word(slot_word<G>(p, slot, G * kHeadDim + q));
+        wo[q] = ld_word(slot_word<G>(p, slot, q * kHeadDim + t));
+      }
+#pragma unroll
+      for (int q = 0; q < G; ++q) {
+        const float ls = wait_word(slot_word<G>(p, slot, G * kHeadDim + q), wl[q], tag, p.status, &bad);
+        const float ov = wait_word(slot_word<G>(p, slot, q * kHeadDim + t), wo[q], tag, p.status, &bad);
+        if (ls == -INFINITY) continue;
+        const float wgt = expf(ls - mx[q]);
+        tot[q] += wgt;
+        acc[q] = fmaf(wgt, ov, acc[q]);
+      }
+    }
   }
+  if (bad) return false;
+#pragma unroll
+  for (int q = 0; q < G; ++q) {
+    const float r = tot[q] > 0.f ? __fdiv_rn(acc[q], tot[q]) : 0.f;
+    p.out[(orow * p.heads_q + sg.kvh * G + q) * kHeadDim + t] = __bfloat16_as_ushort(__float2bfloat16_rn(r));
+  }
+  return true;
 }
 
 template <int G>
@@ -363,13 +384,14 @@ decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   const bool is_k_producer = warp == kKProducerWarp, is_v_producer = warp == kVProducerWarp;
   const bool is_producer = is_k_producer || is_v_producer;
   if (is_k_producer) {
-    build_schedule<G>(p, sm, lane);
     if (lane == 0) {
       for (int s = 0; s < kKS; ++s) { mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1); }
       for (int s = 0; s < kVS; ++s) { mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1); }
       sm.abort_flag = 0;
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    build_schedule<G>(p, sm, lane);
+    __syncwarp();
   }
   if (tid == 0) {
     for (int b = 0; b < 2; ++b) {
@@ -401,17 +423,13 @@ decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     if (!p.q_fp4)
       for (int i = wt; i < 2 * kSfBlockBytes / 16; i += kWorkers) reinterpret_cast<uint4*>(sm.q_sf)[i] = make_uint4(0, 0, 0, 0);
   }
+  // the K producer needs nothing the others prepare: it only signals the set-up barrier
   tc_fence_before();
-  __syncthreads();
+  if (is_k_producer) asm volatile("bar.arrive 4, %0;" ::"n"(kThreads) : "memory");
+  else asm volatile("bar.sync 4, %0;" ::"n"(kThreads) : "memory");
   tc_fence_after();
-  const uint32_t tmem = sm.tmem_base;
-  const int nseg = sm.nseg;
-  if (nseg == 0) {   // no share of this step: give tensor memory back and leave
-    __syncthreads();
-    if (warp == kQkWarp)
-      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kAlloc) : "memory");
-    return;
-  }
+  const uint32_t tmem = is_k_producer ? 0u : sm.tmem_base;
+  const int nseg = sm.nseg;   // no share of this step (nseg 0): every role falls through its loop
 
   if (warp < 4) {
     // =====================  score threads  =====================
@@ -610,43 +628,31 @@ decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     const uint32_t lane_off = (uint32_t)((warp - 4) * 32) << 16;
     if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");   // before the tail is read or anything is stored
     bool alive = true;
-    int page_g = 0, kb_g = 0, ai = 0, cut = 0;   // cut: cut pieces (those with a scratch slot) seen so far
-    int ticket0 = -1, ticket1 = -1;              // thread 0: answers of the arrival counts (-1: none asked)
+    int page_g = 0, kb_g = 0, ai = 0;
     const int my_group = (int)blockIdx.x / p.heads_kv;
+    // this launch's tag for the scratch slots: one more than the launches that completed on them
+    const uint32_t tag = (uint32_t)(*reinterpret_cast<volatile int*>(p.tile_counters) + 1) & ~kFailBit;
     for (int s = 0; s < nseg; ++s) {
       const Seg& sg = sm.seg[s];
       const int n_pages = sg.last_page - sg.first_page;
       float o[G], lse[G];
 #pragma unroll
       for (int q = 0; q < G; ++q) { o[q] = 0.f; lse[q] = -INFINITY; }
-      // A cut piece looks at its tile's arrival count shortly before its own end: if every other
-      // piece has arrived (the usual case for the piece a CTA ends with - its neighbour ran the
-      // rest of the tile first), these threads fetch the others' partials while the last pages
-      // are folded and fold the tile straight out of registers.
+      // A row cut over several groups is folded by the group that holds its first unit: every
+      // other group walks its piece of the row FIRST (rows lie in order) and stores its partial,
+      // waiting for nothing; the folding group walks its piece LAST, so the others have normally
+      // arrived long before it ends.  It fetches their words one hand-over before its last, while
+      // its last pages are folded, and only waits (bounded) for words still missing at its end.
       const bool is_cut = sg.slot >= 0;
-      const int k = cut;
-      if (is_cut) ++cut;
+      const bool folds = is_cut && my_group == sg.c_first;
       const int others = sg.c_last - sg.c_first;
       const int n_batches = (n_pages + kBatch - 1) / kBatch;
-      bool direct = false;
-      int peek = -1;
+      bool fetched = false;
       Others<G> ot;
       auto look = [&]() {
-        if (t == 0 && others <= DirectOthers<G>::value)
-          peek = ld_acquire_gpu(p.tile_counters + sg.row * p.heads_kv + sg.kvh);
+        if (others <= DirectOthers<G>::value) fetched = fetch_others<G>(p, sg, t, tag, ot);
       };
-      auto decide = [&]() {
-        if (t == 0) sm.direct[k] = peek == others ? 1 : 0;
-        asm volatile("bar.sync 6, 128;" ::: "memory");
-        direct = sm.direct[k] != 0;
-        if (direct) fetch_others<G>(p, sg, my_group, t, ot);
-      };
-      if (is_cut && n_batches < 2) look();
-      if (n_pages == 0 && sg.tail_len == 0) {   // an empty piece: a zero row, or an empty partial
-        if (is_cut) decide();
-        finish_piece<G>(p, sg, sm, t, direct, o, lse, ot, !sm.abort_flag, k == 0 ? ticket0 : ticket1);
-        continue;
-      }
+      if (folds && n_batches < 2) look();
       if (sg.tail_len > 0) {
         TileWork w;
         w.row = sg.row; w.kvh = sg.kvh; w.split = 0; w.slot = 0; w.first_page = sg.first_page;
@@ -655,13 +661,10 @@ decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         tail_pv<G>(p, w, sm.pf, t, o);
         asm volatile("bar.arrive 5, 256;" ::: "memory");   // P of this tail has been consumed
       }
-      if (is_cut && n_batches == 0) decide();
       for (int kb = 0; kb < n_batches; ++kb, ++kb_g) {
         const int set = kb_g & 1, j0 = page_g + kb * kBatch;
         const bool two = kb * kBatch + 1 < n_pages;
-        // look one hand-over before the last, decide (and start fetching) at the last
-        if (is_cut && kb == n_batches - 2) look();
-        if (is_cut && kb == n_batches - 1) decide();
+        if (folds && kb == n_batches - 2) look();
         if (alive && mbar_wait(&sm.o_full[set], (kb_g >> 1) & 1, sm, p.status)) {
           tc_fence_after();
           uint32_t ro[C::kSet];
@@ -681,40 +684,39 @@ decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
         }
       }
       page_g += n_pages;
-      if (alive && !mbar_wait(&sm.seg_done[ai & 7], (ai >> 3) & 1, sm, p.status)) alive = false;
       float val[G];
+      if (n_pages > 0 || sg.tail_len > 0) {
+        if (alive && !mbar_wait(&sm.seg_done[ai & 7], (ai >> 3) & 1, sm, p.status)) alive = false;
 #pragma unroll
-      for (int q = 0; q < G; ++q) {
-        const float lq = sm.fin[ai & 7][q], mq = sm.fin[ai & 7][NQ + q];
-        val[q] = lq > 0.f ? __fdiv_rn(o[q], lq) : 0.f;
-        lse[q] = lq > 0.f ? (mq + log2f(lq)) * kLn2 : -INFINITY;
-      }
-      ++ai;
-      finish_piece<G>(p, sg, sm, t, direct, val, lse, ot, alive, k == 0 ? ticket0 : ticket1);
-    }
-    // The arrival counts' answers: a cut piece that was its tile's last arrival after all (the
-    // others came between its look and its count) folds the tile now.
-    if (cut > 0) {
-      if (t == 0) {
-        int kk = 0;
-        for (int s = 0; s < nseg && kk < 2; ++s) {
-          const Seg& sg = sm.seg[s];
-          if (sg.slot < 0) continue;
-          const int ticket = kk == 0 ? ticket0 : ticket1;
-          int fold = 0;
-          if (ticket >= 0 && (ticket & 0xffff) == sg.c_last - sg.c_first) {
-            p.tile_counters[sg.row * p.heads_kv + sg.kvh] = 0;   // ready for the next launch
-            fold = (ticket >> 16) == 0 && !sm.abort_flag;        // a failed piece: nothing to fold
-          }
-          sm.fold_late[kk++] = fold;
+        for (int q = 0; q < G; ++q) {
+          const float lq = sm.fin[ai & 7][q], mq = sm.fin[ai & 7][NQ + q];
+          val[q] = lq > 0.f ? __fdiv_rn(o[q], lq) : 0.f;
+          lse[q] = lq > 0.f ? (mq + log2f(lq)) * kLn2 : -INFINITY;
         }
-        __threadfence();   // the other pieces' partials, after the count that saw them arrive
+        ++ai;
+      } else {   // an empty piece: a zero row, or an empty partial
+#pragma unroll
+        for (int q = 0; q < G; ++q) val[q] = 0.f;
       }
-      asm volatile("bar.sync 6, 128;" ::: "memory");
-      int kk = 0;
-      for (int s = 0; s < nseg && kk < 2; ++s) {
-        if (sm.seg[s].slot < 0) continue;
-        if (sm.fold_late[kk++]) merge_tile<G>(p, sm.seg[s], t);
+      const bool ok = alive && !sm.abort_flag;
+      // ---- end of the piece ----
+      if (!is_cut) {
+        if (ok) {
+          const int64_t orow = p.out_indices ? (int64_t)p.out_indices[sg.row] : (int64_t)sg.row;
+#pragma unroll
+          for (int q = 0; q < G; ++q)
+            p.out[(orow * p.heads_q + sg.kvh * G + q) * kHeadDim + t] =
+                __bfloat16_as_ushort(__float2bfloat16_rn(val[q]));
+        }
+      } else if (!folds) {
+        // a failed piece marks its LSE words, so that the folding piece leaves the row alone
+#pragma unroll
+        for (int q = 0; q < G; ++q) {
+          if (ok) st_word(slot_word<G>(p, sg.slot, q * kHeadDim + t), val[q], tag);
+          if (t == 0) st_word(slot_word<G>(p, sg.slot, G * kHeadDim + q), lse[q], ok ? tag : (tag | kFailBit));
+        }
+      } else if (ok) {
+        fold_row<G>(p, sg, t, tag, val, lse, ot, fetched);
       }
     }
   } else if (is_producer) {
@@ -898,8 +900,19 @@ decode_persistent_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
   __syncthreads();
   if (warp == kQkWarp) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kAlloc)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(sm.tmem_base), "r"(C::kAlloc)
                  : "memory");
+  }
+  // The CTA that leaves last counts the launch: the next one tags its scratch words one higher.
+  // (Thread 0 has passed griddepcontrol.wait, so under a programmatic launch the previous
+  // launch's own count is complete.)
+  if (tid == 0) {
+    int* launches = p.tile_counters;
+    int* left = p.tile_counters + 1;
+    if (atomicAdd(left, 1) == (int)gridDim.x - 1) {
+      *left = 0;
+      *launches = (*reinterpret_cast<volatile int*>(launches) + 1) & 0x3fffffff;
+    }
   }
 }
 
@@ -956,13 +969,13 @@ bool decode_persistent_supports(const DecodeParams& p) {
 
 size_t decode_persistent_workspace_bytes(int rows, int heads_q, int heads_kv) {
   const int ctas = decode_persistent_ctas();
-  if (ctas < 1 || heads_kv < 1) return 0;
+  if (ctas < 1 || heads_kv < 1 || rows < 1) return 0;
   const size_t g = (size_t)(heads_q / heads_kv);
-  const size_t counters = ((size_t)rows * heads_kv * sizeof(int) + 255) / 256 * 256;
-  return counters + (size_t)2 * ctas * g * (kHeadDim + 1) * sizeof(float);
+  return 256 + (size_t)ctas * g * (kHeadDim + 1) * 2 * sizeof(uint32_t);
 }
 
-// workspace: [tile counters, zero-filled once][partial O: 2 ctas slots x G x 128][LSE: 2 ctas x G]
+// workspace: [launch counter, CTAs that have left: two ints, zero-filled once, padded to 256 bytes]
+//            [one scratch slot per CTA: G x 129 words {value, tag}]
 cudaError_t launch_decode_persistent(const DecodeParams& p0, void* workspace, cudaStream_t stream) {
   if (p0.rows == 0) return cudaSuccess;
   if (!decode_persistent_supports(p0)) return cudaErrorNotSupported;
@@ -970,10 +983,9 @@ cudaError_t launch_decode_persistent(const DecodeParams& p0, void* workspace, cu
   const int ctas = decode_persistent_ctas();
   const int g = p0.heads_q / p0.heads_kv;
   DecodeParams p = p0;
-  const size_t counters = ((size_t)p.rows * p.heads_kv * sizeof(int) + 255) / 256 * 256;
   p.tile_counters = static_cast<int*>(workspace);
-  p.o_partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counters);
-  p.lse_partial = p.o_partial + (size_t)2 * ctas * g * kHeadDim;
+  p.o_partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
+  p.lse_partial = nullptr;
   p.emit_partial = 0;
   p.num_splits = 1;
   // no more CTAs than shares of kMinShare units the longest possible step could fill
