@@ -33,7 +33,7 @@ POOL_PAGES = ROWS * PAGES_PER_ROW          # 1024 pages = 151 MB of NVFP4 K+V pe
 NUM_POOLS = 2                              # alternate so that L2 (126 MB) cannot hold a step's KV
 KV_BYTES = ROWS * CTX * HKV * 144          # algorithmic bytes of one step (144 B per token-head)
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch of the default workload, from
-# the capture summarised in profiles/decode_sm100_kernel__batch32x4096__ncu_full.md
+# an ncu capture of that kernel (a constant: this program does not measure it)
 NCU_TRAFFIC_BYTES = 151_684_608 + 6_503_680
 METRIC = "decode_attn_tokens_per_s"
 UNIT = "tokens/s"
@@ -86,21 +86,24 @@ def cpu_path(steps: int, warmup: int, rows_per_step: int | None = None):
     ctx = mp.get_context("spawn")
     os.environ.setdefault("OMP_NUM_THREADS", "1")
     workers = min(cores, rows)
-    busy = 0.0
+    per_step = []
     with ctx.Pool(workers) as pool:
         for w in range(warmup):
             pool.map(_cpu_row, [(1000 + w * rows + r, CTX) for r in range(rows)])
         for s in range(steps):
-            # input generation happens inside the workers but outside their timers
-            busy += sum(t for t, _ in pool.map(_cpu_row, [(s * rows + r, CTX) for r in range(rows)]))
-    dt = busy / workers  # wall time of the oracle work with every worker busy
+            # input generation happens inside the workers but outside their timers; a step's time is
+            # the oracle work with every worker busy
+            per_step.append(sum(t for t, _ in pool.map(_cpu_row, [(s * rows + r, CTX) for r in range(rows)]))
+                            / workers)
+    dt = sorted(per_step)[len(per_step) // 2]
     return dict(
-        value=rows * steps / dt,
-        ms_per_step=1e3 * dt / steps,
+        value=rows / dt,
+        ms_per_step=1e3 * dt,
         cores=min(cores, rows),
         rows=rows,
-        sample=f"{steps} step(s) of {rows} of the {ROWS} sequences (4096 ctx each, Q/K/V/P "
-               f"quantisation included), one process per sequence on {min(cores, rows)} cores",
+        sample=f"median of {steps} step(s) after {warmup} warm-up, each {rows} of the {ROWS} sequences "
+               f"({CTX} ctx each, Q/K/V/P quantisation included), one process per sequence on "
+               f"{min(cores, rows)} cores",
     )
 
 
@@ -108,7 +111,7 @@ def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 3))
+    steps = max(1, min(args.steps, 5))
     res = cpu_path(steps, min(args.warmup, 1))
     line = {
         "impl": "reference",
@@ -224,12 +227,75 @@ def build_pools(device, rows=None, pages_per_row=None, num_pools=None, hkv=None)
     return pools
 
 
+def load_peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        return {}
+
+
+def pin_rank_to_cores(local: int, world: int) -> str:
+    """One process per GPU on one host: give every rank its own slice of the host's cores, so
+    that eight Python interpreters do not migrate over each other's caches."""
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+        if world > 1 and len(cores) >= 2 * world:
+            per = len(cores) // world
+            mine = cores[local * per:(local + 1) * per]
+            os.sched_setaffinity(0, mine)
+            return f"{per} cores per rank"
+    except (AttributeError, OSError):
+        pass
+    return "unpinned"
+
+
+def _median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2]
+
+
+def sampled_row_parity(pool, q, out_row, row, device):
+    """max-abs of one output row against the CPU attention oracle fed the library's own
+    dequantised bytes of that row's pages.  Test infrastructure used as a checker, outside every
+    timed region."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+    import torch
+
+    import nvfp4_oracle as O
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _quantize
+
+    ids = pool["table"][row].long()
+    k_dq = O.dequantize_key_pages(pool["k"][ids].contiguous().cpu().numpy(),
+                                  _scale_rows(pool["ksf"], ids))
+    v_dq = O.dequantize_value_pages(pool["v"][ids].contiguous().cpu().numpy(),
+                                    _scale_rows(pool["vsf"], ids))
+    q_fp4, q_sf = _quantize.quantize_query(q[row:row + 1].contiguous(), heads_kv=HKV)
+    storage = q_sf.as_strided((1, HQ * 1024), (HQ * 1024, 1)).cpu().numpy().reshape(1, 1, HQ, 2, 32, 4, 4)
+    q_dq = O.dequantize_query(q_fp4.view(torch.uint8).cpu().numpy(), storage, HKV)
+    n = ids.numel()
+    want = O.attention_from_dequantized(
+        q[row:row + 1].float().cpu().numpy(), q_dq, k_dq, v_dq, np.arange(n, dtype=np.int32).reshape(1, n),
+        np.array([n * PAGE], dtype=np.int32), softmax_scale=D ** -0.5)
+    return float(np.abs(out_row.float().cpu().numpy() - want[0]).max())
+
+
+def _scale_rows(view, ids):
+    """[len(ids), Hkv * 1024] scale bytes of the given pages of a pitched scale view."""
+    import torch
+
+    heads = view.shape[-1]
+    flat = view.view(torch.uint8).as_strided((view.shape[0], heads * 1024), (view.stride(0), 1),
+                                             view.storage_offset())
+    return flat[ids].contiguous().cpu().numpy()
+
+
 def run_gpu(args) -> None:
     import torch
     import torch.distributed as dist
 
     import nvfp4_attn_kernel_b200._lib as L
-    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import fp4_decode
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import host_io_step
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -238,7 +304,9 @@ def run_gpu(args) -> None:
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the kernels")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    pinning = pin_rank_to_cores(local, world)
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # the page-range exchange below uses plain peer stores
         dist.init_process_group("nccl", device_id=device)
     lib = L.load()
     impl = {"auto": L.IMPL_AUTO, "generic": L.IMPL_GENERIC, "sm100": L.IMPL_SM100}[args.decode_impl]
@@ -294,8 +362,8 @@ def run_gpu(args) -> None:
         quantised beforehand and the launch only streams the pages."""
         L.check(lib.nvfp4_decode(ctypes.byref((fused if with_q else dargs)[i % NUM_POOLS]), stream))
 
-    def timed_graph(with_q, steps, warmup):
-        """Capture NUM_POOLS steps into a CUDA graph, replay, time with events on its stream."""
+    def make_graph(with_q):
+        """NUM_POOLS steps (one per page pool) in one CUDA graph on a side stream."""
         side = torch.cuda.Stream(device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -306,39 +374,51 @@ def run_gpu(args) -> None:
         with torch.cuda.graph(graph, stream=side):
             for i in range(NUM_POOLS):
                 step(i, torch.cuda.current_stream().cuda_stream, with_q)
-        reps = max(1, steps // NUM_POOLS)
-        for _ in range(max(1, warmup // NUM_POOLS)):
-            graph.replay()
+        return graph
+
+    def timed(graph, replays):
+        """ms for `replays` replays: barrier + synchronize on both sides, CUDA events, max over ranks."""
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        for _ in range(reps):
+        for _ in range(replays):
             graph.replay()
         end.record()
         torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
         if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
             dist.barrier()
-        return start.elapsed_time(end), reps * NUM_POOLS
+        return ms
 
+    REPEATS = 5
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms, done = timed_graph(True, args.steps, args.warmup)
-    if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_step = ms / done
-    # the decode kernel alone (roofline numerator is the KV stream)
-    ms_k, done_k = timed_graph(False, args.steps, args.warmup)
+    g_step, g_kernel = make_graph(True), make_graph(False)
+    for _ in range(max(2, args.warmup // NUM_POOLS)):
+        g_step.replay()
+        g_kernel.replay()
+    # (1) the contract's region: exactly --steps steps, five times over; the line's value is the median
+    k_replays = max(1, args.steps // NUM_POOLS)
+    done = k_replays * NUM_POOLS
+    k_ms = [timed(g_step, k_replays) / done for _ in range(REPEATS)]
+    ms_step = _median(k_ms)
+    # (2) long repeats (each at least 20 ms, so that the clock sampler sees the load): the step and
+    #     the decode kernel alone (pre-quantised query, plain launches inside the graph)
+    long_replays = max(k_replays, int(20.0 / (ms_step * NUM_POOLS)) + 1)
+    long_step = [timed(g_step, long_replays) / (long_replays * NUM_POOLS) for _ in range(REPEATS)]
+    long_kernel = [timed(g_kernel, long_replays) / (long_replays * NUM_POOLS) for _ in range(REPEATS)]
     clocks = sampler.stop() if rank == 0 else None
-    kernel_s = ms_k / done_k * 1e-3
+    kernel_s = _median(long_kernel) * 1e-3
 
     # the floor on this GPU: a launch that only reads the step's bytes, same pools, same timing
-    def read_floor(steps, warmup):
+    def read_floor():
         sink = torch.zeros(1, dtype=torch.int32, device=device)
         side = torch.cuda.Stream(device)
         side.wait_stream(torch.cuda.current_stream())
@@ -348,70 +428,77 @@ def run_gpu(args) -> None:
                 cache = pools[i]["cache"]
                 L.check(lib.nvfp4_probe_hbm_read(cache.data_ptr(), cache.numel(), sink.data_ptr(),
                                                  torch.cuda.current_stream().cuda_stream))
-        reps = max(1, steps // NUM_POOLS)
-        for _ in range(max(1, warmup // NUM_POOLS)):
+        for _ in range(3):
             graph.replay()
-        torch.cuda.synchronize()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(reps):
-            graph.replay()
-        end.record()
-        torch.cuda.synchronize()
-        return start.elapsed_time(end) / (reps * NUM_POOLS) * 1e-3
+        reps = max(50, long_replays // 2)
+        return _median([timed(graph, reps) / (reps * NUM_POOLS) for _ in range(3)]) * 1e-3
 
-    floor_s = read_floor(min(args.steps, 400), args.warmup)
+    floor_s = read_floor()
 
-    # end to end through the public operator with host buffers
+    # end to end through the operator's host-buffer call: pinned query in, pinned rows out, the
+    # copies and the wait inside the timed region, one call into the library per step
     q_host = q.cpu().pin_memory()
     out_host = torch.empty_like(out, device="cpu").pin_memory()
-    q_sf_scratch = torch.zeros(ROWS, 1, HQ, 2, 32, 4, 4, dtype=torch.uint8, device=device)
-    q_fp4_scratch = torch.zeros(ROWS, 1, HQ, 64, dtype=torch.uint8, device=device)
     q_dev = torch.empty_like(q)
+    host_steps = [host_io_step(q_dev, p["k"], p["ksf"], p["v"], p["vsf"], p["table"], seqused, out=out)
+                  for p in pools]
 
-    def e2e_step(i):
-        pool = pools[i % NUM_POOLS]
-        q_dev.copy_(q_host, non_blocking=True)
-        fp4_decode(q_dev, pool["k"], pool["ksf"], pool["v"], pool["vsf"], pool["table"], seqused,
-                   out=out, trusted_metadata=True, num_splits=splits,
-                   query_fp4_scratch=q_fp4_scratch, query_scales_scratch=q_sf_scratch)
-        out_host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+    def e2e_region(n):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record()
+        for i in range(n):
+            host_steps[i % NUM_POOLS](q_host, out_host)
+        e2.record()
+        torch.cuda.synchronize()
+        ms = s2.elapsed_time(e2)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / n
 
-    e2e_steps = min(args.steps, 200)
-    for i in range(max(3, min(args.warmup, 10))):
-        e2e_step(i)
+    e2e_steps = max(done, 200)
+    e2e_region(max(3, min(args.warmup, 20)))
+    e2e_ms = [e2e_region(e2e_steps) for _ in range(REPEATS)]
+    e2e_step = _median(e2e_ms)
     if world > 1:
         dist.barrier()
-    torch.cuda.synchronize()
-    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s2.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    e2.record()
-    torch.cuda.synchronize()
-    e2e_ms = s2.elapsed_time(e2)
-    if world > 1:
-        t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-        dist.barrier()
 
-    bad = int(status.item())
+    # parity of what was timed: one sampled row of the last step against the CPU oracle
+    parity = None
     if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except (OSError, ValueError):
-            pass
+        L.check(lib.nvfp4_decode(ctypes.byref(fused[0]), torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        parity = {"row": 5, "max_abs_vs_oracle": sampled_row_parity(pools[0], q, out[5], 5, device),
+                  "bound": 2e-2,
+                  "oracle": "numpy attention oracle on the library's dequantised bytes of the row's 32 pages "
+                            "(P quantised per 16 positions against the running maximum, as the reference's)"}
+    bad = int(status.item())
+
+    # the two partitioned workloads of the multi-GPU configurations, measured after the headline
+    extras = {}
+    if world > 1 and not args.no_multi_gpu_records:
+        sub = argparse.Namespace(**vars(args))
+        sub.steps, sub.warmup = 200, 20
+        extras["long_context"] = run_long_context(sub, sub=True)
+        sub.steps, sub.warmup = 24, 4
+        extras["tp_model_step"] = run_model_step(sub, sub=True)
+
+    if rank == 0:
+        peaks = load_peaks()
         peak = float(peaks.get("hbm_gbs", 6650.0))
         achieved = KV_BYTES / kernel_s / 1e9
+        chained = KV_BYTES / (_median(long_step) * 1e-3) / 1e9
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            res = cpu_path(1, 0)
+            res = cpu_path(3, 1)
             cpu = {"value": res["value"], "unit": UNIT, "cores": res["cores"], "kind": "port",
                    "sample": res["sample"]}
         launches_per_step = 1 + (1 if splits > 1 else 0)   # decode (query quantised inside) [+ merge]
+        launches = (REPEATS * done + REPEATS * 2 * long_replays * NUM_POOLS) * launches_per_step
         line = {
             "metric": METRIC, "value": world * ROWS / (ms_step * 1e-3), "unit": UNIT,
             "n_gpus": world, "steps": done, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -421,41 +508,69 @@ def run_gpu(args) -> None:
                 "workload": WORKLOAD,
                 "l2": f"{NUM_POOLS} rotating page pools of {KV_BYTES / 1e6:.0f} MB each (> 126 MB L2), "
                       "alternated every step",
-                "timing": "CUDA-graph replay, CUDA events on the replay stream, max over ranks",
+                "timing": f"CUDA-graph replay, CUDA events on the replay stream, barrier + synchronize on "
+                          f"both sides, max over ranks; value = median of {REPEATS} regions of exactly "
+                          f"{done} steps",
                 "step": "one decode launch (BF16 query quantised inside)"
                         + (", launches chained with programmatic stream serialization" if pdl else "")
                         + "; decode_kernel_us / roofline: the same kernel with a pre-quantised query, "
                           "plain launches",
                 "decode_impl": args.decode_impl, "num_splits": splits,
-                "sharding": "independent batch of 32 sequences per GPU, no collective",
+                "sharding": "independent batch of 32 sequences per GPU, no collective"
+                            + (f"; ranks pinned: {pinning}" if world > 1 else ""),
+            },
+            "repeats": {
+                "n": REPEATS,
+                "step_us": {"regions_of_steps": done, "median": ms_step * 1e3, "min": min(k_ms) * 1e3,
+                            "max": max(k_ms) * 1e3},
+                "step_us_long": {"steps_per_region": long_replays * NUM_POOLS, "median": _median(long_step) * 1e3,
+                                 "min": min(long_step) * 1e3, "max": max(long_step) * 1e3},
+                "decode_kernel_us_long": {"steps_per_region": long_replays * NUM_POOLS,
+                                          "median": kernel_s * 1e6, "min": min(long_kernel) * 1e3,
+                                          "max": max(long_kernel) * 1e3},
+                "e2e_us": {"steps_per_region": e2e_steps, "median": e2e_step * 1e3, "min": min(e2e_ms) * 1e3,
+                           "max": max(e2e_ms) * 1e3},
             },
             "hbm_gbs": achieved, "frac_of_8000": achieved / 8000.0,
             "decode_kernel_us": kernel_s * 1e6,
+            "target": {"decode_kernel_us_for_75pct_of_8000_gbs": KV_BYTES / 6.0e12 * 1e6},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
                          "peak_source": "measured" if peaks else "fallback",
+                         "basis": "decode kernel alone, pre-quantised query, plain launches (decode_kernel_us)",
+                         "frac_of_chained_step": chained / peak,
+                         "chained_step_note": "the step of identical launches chained with programmatic "
+                                              "stream serialization hides a launch's set-up under its "
+                                              "predecessor's drain; a best case, not the kernel",
                          "traffic": args.ncu_traffic if args.ncu_traffic is not None else (
                              NCU_TRAFFIC_BYTES if (CTX == 4096 and splits == 1 and args.decode_impl != "generic")
                              else None),
+                         "traffic_source": "constant: dram__bytes_read.sum + dram__bytes_write.sum per launch of "
+                                           "an ncu capture of this kernel and workload, not measured by this run",
                          "read_only_launch_us": floor_s * 1e6,
                          "kernel_over_read_only_launch": kernel_s / floor_s},
+            "parity": parity,
             "cpu_baseline": cpu,
-            "e2e": {"value": world * ROWS * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
+            "e2e": {"value": world * ROWS / (e2e_step * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
-                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
-            "gpu_launches": done * launches_per_step,
+                    "ms_per_step": e2e_step, "steps": e2e_steps,
+                    "call": "host_io_step: nvfp4_decode_host_io (copy in, decode, copy out, wait) per step"},
+            "gpu_launches": launches,
             "clocks": clocks,
             "device_status_word": bad,
         }
+        line.update(extras)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_long_context(args) -> None:
+def run_long_context(args, sub: bool = False):
     """Long-context workload: 4 sequences x 32768 context, the KV pages of every sequence split
     by page range over the ranks (rank r holds only its pages), partial results merged over
-    NVLink.  Strong scaling: the total work is fixed as the number of GPUs grows."""
+    NVLink.  Strong scaling: the total work is fixed as the number of GPUs grows.
+    ``sub``: called by the headline run on an initialised process group; returns the record
+    (rank 0) instead of printing a line."""
     import torch
     import torch.distributed as dist
 
@@ -469,12 +584,14 @@ def run_long_context(args) -> None:
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if world > 1:
+    if world > 1 and not sub:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=device)
-    rows, ctx = 4, 32768
+    rows, ctx = getattr(args, "lc_rows", 4), getattr(args, "lc_ctx", 32768)
     pages = ctx // PAGE
     if pages % world:
+        if sub:
+            return {"skipped": f"{pages} pages do not divide over {world} ranks"} if rank == 0 else None
         raise SystemExit("the page count must divide over the ranks")
     local_pages = pages // world
     kv_bytes = rows * ctx * HKV * 144
@@ -567,15 +684,13 @@ def run_long_context(args) -> None:
     done = reps * num_pools
     ms_step = ms / done
     status = int(grp.status.item()) if grp is not None else 0
+    check = page_range_check(device, world, rank, args.exchange) if world > 1 else None
+    line = None
     if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except (OSError, ValueError):
-            pass
+        peaks = load_peaks()
         peak = float(peaks.get("hbm_gbs", 6650.0))
         per_gpu = kv_bytes / world / (ms_step * 1e-3) / 1e9
-        print(json.dumps({
+        line = ({
             "metric": METRIC, "value": rows / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": done, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
@@ -597,9 +712,61 @@ def run_long_context(args) -> None:
                                     else 2 if world == 1 or args.exchange == "push"
                                     else (2 if splits > 1 else 1) + (2 if args.exchange == "nccl" else 1)),
             "clocks": clocks, "device_status_word": status,
-        }), flush=True)
-    if world > 1:
+            "us_per_step": ms_step * 1e3, "frac_of_peak_per_gpu": per_gpu / peak,
+        })
+        if check:
+            line.update(check)
+        if not sub:
+            print(json.dumps(line), flush=True)
+    del pools
+    torch.cuda.empty_cache()
+    if world > 1 and not sub:
         dist.destroy_process_group()
+    return line
+
+
+def page_range_check(device, world, rank, exchange):
+    """Correctness of the cross-GPU page-range exchange on a small problem every rank can hold:
+    bit identity with the one-GPU split path (same partials, same merge order) and the distance to
+    the CPU oracle run split by split.  Collective: every rank calls it.  Uses the parity tests'
+    problem builder and the oracle as checkers, outside every timed region."""
+    for extra in (os.path.join(ROOT, "oracle"), os.path.join(ROOT, "tests"), os.path.join(ROOT, "tests", "golden")):
+        if extra not in sys.path:
+            sys.path.insert(0, extra)
+    import torch
+    import torch.distributed as dist
+
+    import inputs
+    from helpers import Problem
+    from nvfp4_attn_kernel_b200 import sharding
+
+    lens = tuple(128 * (world * 3 + i) + (33, 0, 128, 77)[i % 4] for i in range(4))
+    case = inputs.attention_case(71, 4, HQ, HKV, lens, 1.0, 0.0)
+    prob = Problem(case, device)   # every rank holds the whole small cache; it only READS its range
+    grp = sharding.PageRangeGroup(dist.group.WORLD, 4, HQ, device, exchange=exchange, heads_kv=HKV)
+    table, lseq = sharding.local_page_table(prob.page_table, prob.seqused_fp4, rank, world)
+    tail = {}
+    if rank == 0:
+        tail = dict(residual_key_pages_bf16=prob.k_pages, residual_value_pages_bf16=prob.v_pages,
+                    residual_page_ids=prob.residual_page_ids, seqused_residual=prob.seqused_residual)
+    out = torch.zeros(4, HQ, D, dtype=torch.bfloat16, device=device)
+    same = True
+    want = prob.decode(num_splits=world)
+    for _ in range(3):
+        sharding.decode_page_range(grp, prob.q, prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, table, lseq,
+                                   out=out, softmax_scale=prob.softmax_scale, **tail)
+        torch.cuda.synchronize()
+        same = same and bool(torch.equal(out, want))
+    err = None
+    if rank == 0:
+        oracle = torch.from_numpy(prob.oracle_from_bytes(splits=world)).to(device)
+        err = float((out.float() - oracle).abs().max())
+    flags = [None] * world
+    dist.all_gather_object(flags, (same, int(grp.status.item())))
+    return {"check": {"problem": f"4 rows of {lens} tokens with tails, page ranges over {world} GPUs",
+                      "bitwise_equal_to_one_gpu_split": all(f[0] for f in flags),
+                      "device_status_words": [f[1] for f in flags],
+                      "max_abs_vs_oracle_rows": err, "bound": 2e-2}}
 
 
 def run_ragged(args) -> None:
@@ -685,6 +852,9 @@ def run_ragged(args) -> None:
         while int(lens.max() + total_steps) // PAGE > 64 * splits:
             splits *= 2
     how = dict(balance_pages=balance, workspace=space) if balance else dict(num_splits=splits)
+    if args.persistent:
+        balance, splits = None, 1
+        how = dict(persistent_workspace=_decode.persistent_workspace(rows, HQ, HKV, device))
 
     def step():
         seq_lens.add_(1)
@@ -755,7 +925,8 @@ def run_ragged(args) -> None:
             "workload": "ragged serving step: 32 seq, lengths log-uniform in [128, 32768] growing one token "
                         "per step, BF16 tails, block tables from a shuffled pool of 20000 pages, key shift on",
             "step": "slot control plane + one decode launch (query quantised and K/V token appended "
-                    "inside, " + (f"work list launch + pieces of {balance} pages per row + merge launch"
+                    "inside, " + ("one persistent launch of two CTAs per SM" if args.persistent else
+                                  f"work list launch + pieces of {balance} pages per row + merge launch"
                                   if balance else
                                   f"{splits} KV splits" + (" + merge launch" if splits > 1 else ""))
                     + ") + tail flush, all timed",
@@ -772,8 +943,11 @@ def run_ragged(args) -> None:
     }), flush=True)
 
 
-def run_model_step(args) -> None:
-    """One GPU's share of a full-model decode step under tensor parallelism by KV head: 32 layers,
+def run_model_step(args, sub: bool = False):
+    """``sub``: called by the headline run on an initialised process group; returns the record
+    (rank 0) instead of printing a line.
+
+    One GPU's share of a full-model decode step under tensor parallelism by KV head: 32 layers,
     batch 32, contexts uniform in [1024, 16384] growing one token per step, 1 KV head and 4 query
     heads on this GPU (8 KV heads over 8 GPUs; the ranks share nothing, so every rank of a
     multi-GPU launch runs the same shape on its own heads).  A step = the slot control plane once,
@@ -795,8 +969,8 @@ def run_model_step(args) -> None:
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if world > 1:
-        import torch.distributed as dist
+    import torch.distributed as dist
+    if world > 1 and not sub:
         dist.init_process_group("nccl", device_id=device)
     lib = L.load()
     layers, rows, hkv, hq = 32, ROWS, 1, 4
@@ -840,6 +1014,7 @@ def run_model_step(args) -> None:
     piece = piece_pages(rows, hkv, columns, sms) if args.balance_pages < 0 else max(0, args.balance_pages)
     if piece >= columns:
         piece = 0
+    pws = _decode.persistent_workspace(rows, hq, hkv, device) if args.persistent else None
     space = torch.empty(_decode.balanced_workspace_bytes(rows, hq, columns, piece) if piece else 16,
                         dtype=torch.uint8, device=device)
 
@@ -850,6 +1025,8 @@ def run_model_step(args) -> None:
         for layer in range(layers):
             k_fp4, k_sf, v_fp4, v_sf = views[layer]
             how = dict(balance_pages=piece, workspace=space, reuse_work_list=layer > 0) if piece else {}
+            if args.persistent:
+                how = dict(persistent_workspace=pws)
             _decode.decode_fp4(
                 query_fp4=None, query_scales=None, query_padded_bf16=None, query_bf16=q[layer],
                 key_pages_fp4=k_fp4, key_scales=k_sf, value_pages_fp4=v_fp4, value_scales=v_sf,
@@ -903,16 +1080,13 @@ def run_model_step(args) -> None:
         fp4 = ((cur - 1) // PAGE) * PAGE
         kv += layers * hkv * float((fp4 * 144 + (cur - fp4) * 512).sum())
     kv /= args.steps
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except (OSError, ValueError):
-        pass
+    peaks = load_peaks()
     peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = kv / (ms_step * 1e-3) / 1e9
+    line = None
     if rank == 0:
         launches = layers * ((2 if piece else 1)) + (1 if piece else 0) + 2
-        print(json.dumps({
+        line = ({
             "metric": METRIC, "value": rows / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4",
@@ -937,9 +1111,180 @@ def run_model_step(args) -> None:
                          "traffic": None},
             "cpu_baseline": None, "e2e": None, "gpu_launches": args.steps * launches,
             "clocks": clocks, "control_plane_error_word": errors,
-        }), flush=True)
-    if world > 1:
+        })
+        if not sub:
+            print(json.dumps(line), flush=True)
+    del caches, views, tail_k, tail_v
+    torch.cuda.empty_cache()
+    if world > 1 and not sub:
         dist.destroy_process_group()
+    return line
+
+
+# The reference project's published decode timings (its own kernel on an SM100 part it reports as
+# a renamed B200; CUDA-graph replay, pre-quantised K/V/Q, page-aligned, no tail):
+# docs/reports/data/llama31-8b-gqa-seqlen-sweep.json and docs/reports/1.decode-baseline-comparison.md:14-19.
+PUBLISHED_SHAPES = [
+    # (batch, context, Hkv, reference us, reference TB/s)
+    (16, 4096, 8, 19.2, 3.93),
+    (32, 4096, 8, None, None),
+    (64, 4096, 8, 65.0, 4.65),
+    (4, 32768, 8, 42.5, 3.55),
+    (16, 32768, 8, 112.8, 5.35),
+    (16, 131072, 8, 430.0, 5.62),
+]
+PUBLISHED_GROUP_PEAKS = {1: 6.58, 4: 5.55, 8: 4.36, 16: 2.83, 32: 1.52}   # TB/s, best shape per group size
+
+
+def run_published(args) -> None:
+    """The shapes the reference publishes numbers for, measured with its protocol: pre-quantised
+    query, page-aligned contexts without a tail, CUDA-graph replay over rotating page pools, median
+    of five repeats; and the sweep over query heads per KV head at 32 query heads.  For every shape
+    the launch forms this library offers are timed and the best is reported with its name."""
+    import torch
+
+    import nvfp4_attn_kernel_b200._lib as L
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode
+    from nvfp4_attn_kernel_b200.nvfp4_vllm.runtime import piece_pages
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit("the published-shape workload runs on one GPU")
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    lib = L.load()
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    sampler = ClockSampler(0)
+    sampler.start()
+
+    def measure(batch, ctx, hkv):
+        pages = ctx // PAGE
+        pool_bytes = batch * ctx * hkv * 144
+        num_pools = max(2, -(-2 * 132 * 2 ** 20 // pool_bytes))   # what lies between two uses of a pool exceeds L2
+        pools = build_pools(device, batch, pages, num_pools, hkv=hkv)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(11)
+        q = torch.randn(batch, HQ, D, device=device, generator=gen).to(torch.bfloat16)
+        q_fp4 = torch.zeros(batch, 1, HQ, 64, dtype=torch.uint8, device=device)
+        q_sf = torch.zeros(batch, HQ * 1024, dtype=torch.uint8, device=device)
+        L.check(lib.nvfp4_quantize_q(q.data_ptr(), q.stride(0), q.stride(1), None, q_fp4.data_ptr(),
+                                     q_sf.data_ptr(), None, batch, HQ, hkv,
+                                     torch.cuda.current_stream().cuda_stream))
+        out = torch.zeros(batch, HQ, D, dtype=torch.bfloat16, device=device)
+        seq = torch.full((batch,), ctx, dtype=torch.int32, device=device)
+        status = torch.zeros(1, dtype=torch.int32, device=device)
+        piece = piece_pages(batch, hkv, pages, sms)
+        forms = {"whole rows": {}}
+        if 0 < piece < pages:
+            need = int(lib.nvfp4_decode_balanced_workspace_bytes(batch, HQ, pages, piece))
+            forms[f"pieces of {piece} pages + merge launch"] = dict(
+                target=piece, ws=torch.empty(need, dtype=torch.uint8, device=device))
+        if lib.nvfp4_decode_persistent_supported(batch, HQ, hkv):
+            need = int(lib.nvfp4_decode_persistent_workspace_bytes(batch, HQ, hkv))
+            forms["one persistent launch"] = dict(persistent=True, ws=torch.zeros(need, dtype=torch.uint8, device=device))
+
+        def args_for(pool, form):
+            a = L.DecodeArgs()
+            a.q_fp4, a.q_sf = q_fp4.data_ptr(), q_sf.data_ptr()
+            a.k_packed, a.k_pitch = pool["k"].data_ptr(), pool["block"]
+            a.k_sf, a.k_sf_pitch = pool["ksf"].data_ptr(), pool["block"]
+            a.v_packed, a.v_pitch = pool["v"].data_ptr(), pool["block"]
+            a.v_sf, a.v_sf_pitch = pool["vsf"].data_ptr(), pool["block"]
+            a.num_pages = batch * pages
+            a.page_table, a.page_table_row_stride, a.max_pages = pool["table"].data_ptr(), pages, pages
+            a.seqused_fp4 = seq.data_ptr()
+            a.out = out.data_ptr()
+            a.rows, a.heads_q, a.heads_kv = batch, HQ, hkv
+            a.softmax_scale = D ** -0.5
+            a.num_splits, a.impl = 1, L.IMPL_AUTO
+            a.status = status.data_ptr()
+            if "ws" in form:
+                a.workspace, a.workspace_bytes = form["ws"].data_ptr(), form["ws"].numel()
+            if form.get("persistent"):
+                a.flags = L.DECODE_PERSISTENT
+            return a
+
+        results = {}
+        for name, form in forms.items():
+            sets = [args_for(p, form) for p in pools]
+
+            def launch(a, stream, form=form):
+                if "target" in form:
+                    L.check(lib.nvfp4_decode_balanced(ctypes.byref(a), form["target"], stream))
+                else:
+                    L.check(lib.nvfp4_decode(ctypes.byref(a), stream))
+
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for a in sets:
+                    launch(a, side.cuda_stream)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for a in sets:
+                    launch(a, torch.cuda.current_stream().cuda_stream)
+            for _ in range(5):
+                graph.replay()
+            torch.cuda.synchronize()
+            one = None
+            times = []
+            for _ in range(5):
+                reps = 5 if one is None else max(5, int(10.0 / (one * len(sets))))   # ~10 ms per repeat
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                for _ in range(reps):
+                    graph.replay()
+                end.record()
+                torch.cuda.synchronize()
+                one = start.elapsed_time(end) / (reps * len(sets))
+                times.append(one)
+            results[name] = _median(times[1:]) * 1e3
+        best = min(results, key=results.get)
+        us = results[best]
+        del pools
+        torch.cuda.empty_cache()
+        return {"us": us, "tb_per_s": pool_bytes / (us * 1e-6) / 1e12, "form": best,
+                "all_forms_us": results, "pools": num_pools, "device_status_word": int(status.item())}
+
+    rows = []
+    for batch, ctx, hkv, ref_us, ref_tbs in PUBLISHED_SHAPES:
+        r = measure(batch, ctx, hkv)
+        r.update({"shape": f"b{batch} x s{ctx}, Hq32/Hkv{hkv}", "reference_us": ref_us, "reference_tb_per_s": ref_tbs,
+                  "speedup_vs_reference": (ref_us / r["us"]) if ref_us else None})
+        rows.append(r)
+    sweep = []
+    for group, ref_peak in PUBLISHED_GROUP_PEAKS.items():
+        r = measure(32, 16384, HQ // group)
+        r.update({"shape": f"b32 x s16384, Hq32/Hkv{HQ // group} (G = {group})",
+                  "reference_peak_tb_per_s_best_shape": ref_peak})
+        sweep.append(r)
+    clocks = sampler.stop()
+    # can the reference's own kernel be imported on this machine?  (its sources travel only as a
+    # git-ignored copy for checker use; without them there is nothing to try)
+    ref_src = os.path.join(ROOT, "oracle", "_ref", "src")
+    if os.path.isdir(os.path.join(ref_src, "nvfp4_decode_kernel")):
+        proc = subprocess.run(
+            [sys.executable, "-c", "import sys; sys.path.insert(0, sys.argv[1]); import nvfp4_decode_kernel._decode",
+             ref_src], capture_output=True, text=True, timeout=300)
+        attempt = "imports" if proc.returncode == 0 else (proc.stderr.strip().splitlines() or ["failed"])[-1][:300]
+    else:
+        attempt = "the reference's sources are not on this machine"
+    peaks = load_peaks()
+    head = next(r for r in rows if r["shape"].startswith("b32 x s4096"))
+    print(json.dumps({
+        "metric": "decode_us_at_published_shapes", "value": head["us"], "unit": "us", "n_gpus": 1,
+        "steps": 0, "warmup": 0, "ms_per_step": head["us"] * 1e-3, "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
+        "config": {"workload": "the reference's published decode shapes with its protocol: pre-quantised query, "
+                               "no tail, CUDA-graph replay over rotating pools, median of 4 repeats after one "
+                               "discarded; value = b32 x s4096",
+                   "reference_hardware": "an SM100 GPU with 148 SMs that nvidia-smi calls L20A, taken by the "
+                                         "reference's authors for a renamed B200"},
+        "published_shapes": rows, "group_sweep": sweep,
+        "reference_kernel_on_this_machine": attempt,
+        "hbm_peak_gbs_measured": peaks.get("hbm_gbs"),
+        "cpu_baseline": None, "e2e": None, "gpu_launches": None, "clocks": clocks,
+    }), flush=True)
 
 
 def main() -> None:
@@ -953,10 +1298,17 @@ def main() -> None:
     ap.add_argument("--balance-pages", type=int, default=-1,
                     help="ragged workload: pieces of about this many pages per row (0: one split "
                          "count for the batch; -1, the default: chosen from the lengths)")
+    ap.add_argument("--persistent", action="store_true",
+                    help="ragged / model-step workloads: run the decode as one persistent launch "
+                         "(NVFP4_DECODE_PERSISTENT) instead of work list + pieces + merge")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-multi-gpu-records", action="store_true",
+                    help="with more than one GPU: skip the long-context exchange and the tensor-parallel "
+                         "model step that are measured after the headline")
     ap.add_argument("--ctx", type=int, default=CTX,
                     help="context length per sequence (default: the headline workload's 4096)")
-    ap.add_argument("--workload", default="batch", choices=["batch", "long-context", "ragged", "model-step"],
+    ap.add_argument("--workload", default="batch",
+                    choices=["batch", "long-context", "ragged", "model-step", "published"],
                     help="batch: the headline uniform batch (default); long-context: 4 x 32768 split "
                          "by page range over the GPUs; ragged: 32 ragged sequences with tails, the "
                          "whole serving step (control plane, decode with fused append, flush); "
@@ -979,6 +1331,8 @@ def main() -> None:
         run_ragged(args)
     elif args.workload == "model-step":
         run_model_step(args)
+    elif args.workload == "published":
+        run_published(args)
     else:
         run_gpu(args)
 

@@ -454,6 +454,17 @@ int nvfp4_peer_merge(const float* const* o_part_ptrs, const float* const* lse_pa
                      int32_t* const* flag_ptrs, int rank, int world, int epoch, int32_t* epoch_state,
                      int rows, int heads_q, void* out, int out_is_f32, uint32_t* status, void* stream);
 
+/*
+ * One decode step for a caller whose query and result live in HOST memory (no counterpart in the
+ * reference, whose operator takes device tensors; it saves such a caller three trips through its
+ * framework per step): copies q_host (pinned, q_bytes: the BF16 query exactly as args->q_bf16 with
+ * its strides lays it out) to args->q_bf16 on `stream`, runs nvfp4_decode(args), copies
+ * out_bytes of args->out to out_host (pinned) and waits for the stream.  Everything args points
+ * to stays device memory, the KV pages stay resident.  Returns after the result is in out_host.
+ */
+int nvfp4_decode_host_io(const nvfp4_decode_args* args, const void* q_host, size_t q_bytes, void* out_host,
+                         size_t out_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -50,6 +50,7 @@ EXPORTS = (
     "nvfp4_decode_split_static_error",
     "nvfp4_decode_persistent_workspace_bytes",
     "nvfp4_decode_persistent_supported",
+    "nvfp4_decode_host_io",
 )
 
 
@@ -216,6 +217,8 @@ def _declare_static(lib) -> None:
     lib.nvfp4_decode_persistent_workspace_bytes.argtypes = [c_int, c_int, c_int]
     lib.nvfp4_decode_persistent_supported.restype = c_int
     lib.nvfp4_decode_persistent_supported.argtypes = [c_int, c_int, c_int]
+    lib.nvfp4_decode_host_io.restype = c_int
+    lib.nvfp4_decode_host_io.argtypes = [ctypes.POINTER(DecodeArgs), c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]
     lib.nvfp4_static_workspace_bytes.restype = c_size_t
     lib.nvfp4_static_workspace_bytes.argtypes = []
     lib.nvfp4_decode_split_static_error.restype = c_char_p

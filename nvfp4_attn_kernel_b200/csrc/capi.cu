@@ -231,6 +231,22 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
 
 int nvfp4_decode(const nvfp4_decode_args* a, void* stream) { return decode_call(a, nullptr, 0, stream); }
 
+int nvfp4_decode_host_io(const nvfp4_decode_args* a, const void* q_host, size_t q_bytes, void* out_host,
+                         size_t out_bytes, void* stream) {
+  if (!a || !q_host || !out_host) return fail(NVFP4_ERR_INVALID, "decode_host_io: null argument");
+  if (!a->q_bf16 || !a->out)
+    return fail(NVFP4_ERR_INVALID, "decode_host_io: args must carry the device BF16 query buffer and out");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(const_cast<void*>(a->q_bf16), q_host, q_bytes, cudaMemcpyHostToDevice, st);
+  if (e != cudaSuccess) return cuda_fail(e, "decode_host_io: query copy");
+  const int rc = decode_call(a, nullptr, 0, stream);
+  if (rc != NVFP4_OK) return rc;
+  e = cudaMemcpyAsync(out_host, a->out, out_bytes, cudaMemcpyDeviceToHost, st);
+  if (e != cudaSuccess) return cuda_fail(e, "decode_host_io: result copy");
+  e = cudaStreamSynchronize(st);
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "decode_host_io: stream synchronisation");
+}
+
 size_t nvfp4_decode_persistent_workspace_bytes(int rows, int heads_q, int heads_kv) {
   if (rows <= 0 || !valid_group(heads_q, heads_kv)) return 0;
   return nvfp4::decode_persistent_workspace_bytes(rows, heads_q, heads_kv);

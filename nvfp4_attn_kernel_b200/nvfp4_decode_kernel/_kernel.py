@@ -97,6 +97,56 @@ def _launch_plan(plan, out):
     return out if scattered else out[:rows]
 
 
+class HostIoStep:
+    """A decode step whose query arrives in, and whose result leaves to, pinned HOST memory.
+
+    Built once from the arguments of a ``fp4_decode`` call (BF16 query quantised in the launch,
+    ``trusted_metadata`` semantics: nothing is read back from the device), which is validated and
+    run; afterwards ``step(query_host, out_host)`` is ONE call into the library
+    (``nvfp4_decode_host_io``): copy the query in, decode, copy the rows out, wait.  The KV pages
+    and the step's metadata tensors stay on the device and are read afresh on every call.
+    """
+
+    def __init__(self, query: torch.Tensor, *args, out: torch.Tensor, **kwargs):
+        from ._decode import decode_fp4  # noqa: F401  (validates through fp4_decode_impl below)
+
+        if not _kernel_can_quantise(query):
+            raise ValueError("query must be a BF16 CUDA tensor [rows, heads_q, 128] the kernel can quantise itself")
+        if out is None or not out.is_contiguous():
+            raise ValueError("out must be a contiguous BF16 CUDA tensor")
+        global CACHE_CALL_PLANS
+        kwargs = dict(kwargs, out=out, trusted_metadata=True)
+        before, CACHE_CALL_PLANS = CACHE_CALL_PLANS, True
+        try:
+            fp4_decode_impl(query, *args, **kwargs)      # validates, runs once, leaves its plan behind
+        finally:
+            CACHE_CALL_PLANS = before
+        plan = next((p for p in reversed(list(_PLANS.values()))
+                     if p[0].q_bf16 == query.data_ptr() and p[0].out == out.data_ptr()), None)
+        if plan is None:
+            raise RuntimeError("this call does not run as one launch (num_splits, balance_pages or "
+                               "query_row_indices were given)")
+        self._args = plan[0]
+        self._device = plan[3]
+        self._keep = (query, out, args, kwargs)   # the argument block holds raw addresses
+        self.query_bytes = query.shape[0] * query.stride(0) * 2 if query.shape[0] > 1 else query.numel() * 2
+        self.out_bytes = plan[1] * plan[2] * 128 * 2
+
+    def __call__(self, query_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        from .. import _lib
+
+        if not (query_host.is_pinned() and out_host.is_pinned()):
+            raise ValueError("query_host and out_host must be pinned host tensors")
+        if query_host.numel() * query_host.element_size() < self.query_bytes or \
+                out_host.numel() * out_host.element_size() < self.out_bytes:
+            raise ValueError("host buffers are smaller than the device query / result")
+        index = self._device.index
+        stream = torch._C._cuda_getCurrentRawStream(index)
+        with torch.cuda.device(index):
+            _lib.check(_lib.load().nvfp4_decode_host_io(self._args, query_host.data_ptr(), self.query_bytes,
+                                                        out_host.data_ptr(), self.out_bytes, stream))
+
+
 def _kernel_can_quantise(query: torch.Tensor) -> bool:
     return (
         query.dtype is torch.bfloat16
