@@ -26,6 +26,21 @@
 // in a fresh accumulator and is folded in as o = o * rescale + O_page, exactly the order
 // of the attention oracle.
 //
+// Two forms of the kernel.  The narrow one (kGroups = 1, 384 threads) is built for two CTAs per SM
+// and is what a launch that fills the GPU twice over runs on: there the page stream is bound by
+// HBM.  A launch with at most one CTA per SM is bound by a CTA's own page period instead - the
+// chain scores -> maximum -> exp2 -> quantise -> hand-over through the four score warps - so the
+// wide form (kGroups = 2, 512 threads, one CTA per SM, deeper rings, 128 registers per thread)
+// has a second pair of issuing threads and a second group of four score warps (measured: with an
+// SM to itself a CTA's period was the 1800 cycles per pair of pages that ONE thread needs to issue
+// the waits, scale copies, products and commits of V^T . P^T): the hand-overs alternate between
+// the two sets of issuers and score warps, and since
+// a page's probabilities are quantised against the running maximum of everything walked before
+// it, a group passes the maximum on (per warp, through shared memory) as soon as it has its own
+// pages' maxima, before it goes on to exp2 and the quantisation.  The rescale factors per page,
+// and with them the folded output, are those of the narrow form; only the row sum is kept in two
+// parts that are joined at the end.
+//
 // Every device-side wait is bounded; on expiry the CTA raises NVFP4_STATUS_WAIT_TIMEOUT,
 // drains what it has in flight, frees its tensor memory and returns.
 #include "sm100_device.cuh"
@@ -36,33 +51,41 @@ namespace sm100 {
 
 // Ring depths: as many 9 KB slots as two resident CTAs per SM leave room for.  V slots are
 // held about two pages longer than K slots, so the V ring is that much deeper.
-template <int G> struct KSlots { static constexpr int value = G <= 4 ? 4 : G <= 8 ? 3 : 2; };
-template <int G> struct VSlots { static constexpr int value = G <= 4 ? 6 : G <= 8 ? 5 : G <= 16 ? 3 : 2; };
+template <int G, int kGroups> struct KSlots {
+  static constexpr int value = kGroups == 2 ? (G <= 8 ? 8 : 6) : G <= 4 ? 4 : G <= 8 ? 3 : 2;
+};
+template <int G, int kGroups> struct VSlots {
+  static constexpr int value = kGroups == 2 ? (G <= 4 ? 12 : G <= 8 ? 10 : G <= 16 ? 8 : 6)
+                                            : G <= 4 ? 6 : G <= 8 ? 5 : G <= 16 ? 3 : 2;
+};
 // pages handled per hand-over: two, except where 32 query slots leave tensor memory for one
 template <int G> struct Batch { static constexpr int value = G <= 16 ? 2 : 1; };
 // MMA N (query slots): 8 covers every group size up to 8; a group of 16 takes N = 16
 template <int G> struct QuerySlots { static constexpr int value = G <= 8 ? 8 : G; };
 
 // tensor-memory column map (32-bit columns); a "set" holds the pages of one hand-over
-template <int G>
+template <int G, int kGroups>
 struct Cols {
   static constexpr int NQ = QuerySlots<G>::value;
   static constexpr int kBatch = Batch<G>::value;
   static constexpr int kSet = kBatch * NQ;       // columns of one set of S^T (or O^T)
   static constexpr int kS = 0;                   // 2 sets x 2 pages x NQ : S^T
   static constexpr int kO = 2 * kSet;            // 2 sets x 2 pages x NQ : per-page O^T
-  static constexpr int kSfQ = 4 * kSet;          // 8 : 2 k-blocks x 4
-  static constexpr int kSfK = kSfQ + 8;          // 8
-  static constexpr int kSfP = kSfK + 8;          // 8
+  // scale columns of the operands an issuer copies right before its products: one block of 8
+  // (2 k-blocks x 4) per issuer of the kind (the wide form has two of each)
+  static constexpr int kSfQ = 4 * kSet;
+  static constexpr int kSfK = kSfQ + 8 * kGroups;
+  static constexpr int kSfP = kSfK + 8 * kGroups;
   static constexpr int kSfV = kSfP + 16;         // 2 sets x 2 pages x 8 : copied as soon as the V slot has landed
   static constexpr int kUsed = kSfV + 2 * kBatch * 8;
   static constexpr int kAlloc = kUsed <= 128 ? 128 : 256;   // a power of two
   static_assert(kUsed <= 256, "two CTAs per SM leave 256 tensor-memory columns each");
+  static_assert(kGroups == 1 || kSfP + 16 >= kSfP + 8 * kGroups, "scale columns of the second P issuer");
 };
 
-template <int G>
+template <int G, int kGroups>
 struct __align__(1024) Smem {
-  static constexpr int kKS = KSlots<G>::value, kVS = VSlots<G>::value;
+  static constexpr int kKS = KSlots<G, kGroups>::value, kVS = VSlots<G, kGroups>::value;
   uint8_t k_slot[kKS][kSlotBytes];              // K tile | K scales
   uint8_t v_slot[kVS][kSlotBytes];              // V tile | V scales
   static constexpr int NQ = QuerySlots<G>::value;
@@ -75,12 +98,15 @@ struct __align__(1024) Smem {
   __align__(16) float pf[G * kHeadDim];         // P of the tail block
   __align__(16) float z[2][kBatch][G * kPage];  // scaled scores, [set][page][q][kv position]
   float resc[8][NQ];                            // ring of per-page rescale factors, [page & 7][q]
-  float red_io[4 * NQ];                         // reductions of the tail block and the epilogue
+  float red_io[4 * NQ];                         // reductions of the tail block
+  float fin[2][2 * NQ];                         // per score group: row sums and the maxima they refer to
+  volatile float m_val[2][NQ];                  // running maximum handed from one score group to the other, [pairs done & 1]
+  volatile int m_seq[4];                        // [score warp] pairs whose maximum m_val already holds
   volatile int page_ok[32];                     // [walk step & 31] 0: the page id was refused
   __align__(8) uint64_t k_full[kKS];
   uint64_t k_empty[kKS], v_full[kVS], v_empty[kVS];
   uint64_t s_full[2], s_free[2], p_full[2], o_full[2], o_free[2];
-  uint64_t q_ready, drain[2];
+  uint64_t q_ready, drain[4];
   uint32_t tmem_base;
   volatile int abort_flag;
   volatile int xchg_last, xchg_ready;           // hand-overs among the output threads during the exchange
@@ -239,17 +265,23 @@ __device__ __forceinline__ void exchange_tile(const DecodeParams& p, const TileW
   }
 }
 
-template <int G>
-__global__ void __launch_bounds__(kThreads, 2)
+// narrow: 12 warps; wide: plus a second group of four score warps (12-15), a second pair of
+// issuers (16, 17) and a second pair of producers (18, 19)
+template <int kGroups> struct ThreadsOf { static constexpr int value = 384 + 256 * (kGroups - 1); };
+
+template <int G, int kGroups>
+__global__ void __launch_bounds__(ThreadsOf<kGroups>::value, kGroups == 1 ? 2 : 1)
 decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                     const DecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
-  Smem<G>& sm = *reinterpret_cast<Smem<G>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Smem<G, kGroups>& sm =
+      *reinterpret_cast<Smem<G, kGroups>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kThreads = ThreadsOf<kGroups>::value;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  constexpr int kKS = KSlots<G>::value, kVS = VSlots<G>::value;
+  constexpr int kKS = KSlots<G, kGroups>::value, kVS = VSlots<G, kGroups>::value;
   constexpr int NQ = QuerySlots<G>::value;
   constexpr int kBatch = Batch<G>::value;
-  using C = Cols<G>;
+  using C = Cols<G, kGroups>;
 
   // Which work this CTA has.  With a work list (balanced split) the entry says so; otherwise the
   // block index does.  row_of_block is what the early page-table fetch below may use before the
@@ -286,10 +318,13 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   // ---- set-up: barriers, tensor memory, zeroed operand tiles ----
   // Each producer warp prepares its own ring barriers and starts fetching before the CTA-wide
   // set-up barrier, so the first page tiles are in flight while tensor memory is allocated.
-  const bool is_k_producer = warp == kKProducerWarp, is_v_producer = warp == kVProducerWarp;
+  // (the wide form's second producers, warps 18 / 19, take the odd walk steps; they join in after
+  // the set-up barrier)
+  const bool is_k_producer = warp == kKProducerWarp || warp == 18, is_v_producer = warp == kVProducerWarp || warp == 19;
   const bool is_producer = is_k_producer || is_v_producer;
+  const bool second_producer = warp >= 18;
   int spec[4] = {-1, -1, -1, -1};
-  if (is_producer) {
+  if (is_producer && !second_producer) {
     if (lane == 0) {
       if (is_k_producer) {
         for (int s = 0; s < kKS; ++s) { mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1); }
@@ -313,14 +348,14 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     }
   }
   if (tid == 0) {
+    for (int wq = 0; wq < 4; ++wq) sm.m_seq[wq] = 0;
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.s_full[b], 1); mbar_init(&sm.s_free[b], 128);
       mbar_init(&sm.p_full[b], 128);
       mbar_init(&sm.o_full[b], 1); mbar_init(&sm.o_free[b], 128);
     }
     mbar_init(&sm.q_ready, 128);
-    mbar_init(&sm.drain[0], 1);
-    mbar_init(&sm.drain[1], 1);
+    for (int b = 0; b < 4; ++b) mbar_init(&sm.drain[b], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kQkWarp) {
@@ -332,8 +367,9 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   }
   // rows G..7 of the N = 8 operands and their scale rows stay zero for the whole kernel
   if (!is_producer) {
-    constexpr int kWorkers = kThreads - 64;
-    const int wt = tid < kKProducerWarp * 32 ? tid : tid - 32;   // warps 0-7, 9, 10 -> 0..319
+    constexpr int kWorkers = kThreads - 64 * kGroups;
+    // warps 0-7, 9, 10 -> 0..319, the second score group's warps 12-15 -> 320..447
+    const int wt = tid < kKProducerWarp * 32 ? tid : tid < kVProducerWarp * 32 ? tid - 32 : tid - 64;
     for (int i = wt; i < NQ * 64 / 16; i += kWorkers) reinterpret_cast<uint4*>(sm.q_tile)[i] = make_uint4(0, 0, 0, 0);
     for (int i = wt; i < 2 * kBatch * NQ * 64 / 16; i += kWorkers)
       reinterpret_cast<uint4*>(sm.p_tile)[i] = make_uint4(0, 0, 0, 0);
@@ -373,7 +409,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   };
   // ids: lane l of a producer warp holds the page id of walk step 32c + l of the current chunk c
   int ids = -1, issued = 0;
-  if (is_producer) {
+  if (second_producer) issued = n_pages < (is_k_producer ? kKS : kVS) ? n_pages : (is_k_producer ? kKS : kVS);
+  if (is_producer && !second_producer) {
     const int slots = is_k_producer ? kKS : kVS;
     // chunk 0 out of the columns fetched ahead; every lane executes the same four shuffles
     const int idx0 = w.last_page - 1 - lane;  // pages are walked from the last to the first
@@ -399,20 +436,25 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     issued = first;
   }
   uint32_t tmem = 0;
-  if (!is_producer) {
+  if (!is_producer || second_producer) {
     tc_fence_before();
     asm volatile("bar.sync 4, %0;" ::"n"(kThreads) : "memory");
     tc_fence_after();
     tmem = sm.tmem_base;
   }
 
-  if (warp < 4) {
+  if (warp < 4 || (warp >= 12 && warp < 16)) {
     // =====================  score threads  =====================
     // Pages are handed over in pairs.  While a pair's scores are processed, warp w owns query
     // heads q = w, w + 4 (< G) over ALL 128 kv positions of each page, four consecutive
     // positions per lane: the page maximum is a warp reduction, a 16-position scale group is
     // four adjacent lanes and the packed E2M1 bytes of P are formed without any exchange.
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    // In the wide form a second group of four warps (warps 12-15) takes every other hand-over:
+    // group g works on set g of the score, P and output buffers.
+    const int grp = warp < 4 ? 0 : 1;
+    const int stid = tid & 127, swarp = stid >> 5;   // thread and warp within the group
+    const int bar_id = grp == 0 ? 1 : 7;             // the group's own named barrier
+    const uint32_t lane_off = (uint32_t)(swarp * 32) << 16;
     // Under a programmatic launch everything up to here, and the producers' and issuers' work,
     // may run while the previous kernel drains.  The query and the tail may be that kernel's
     // output: wait for it, and only then let this launch's own dependents go.
@@ -420,6 +462,11 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       asm volatile("griddepcontrol.wait;" ::: "memory");
       if (tid == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
+    constexpr int QPW = (G + 3) / 4;
+    float m_w[QPW], l_w[QPW];
+#pragma unroll
+    for (int k = 0; k < QPW; ++k) { m_w[k] = -INFINITY; l_w[k] = 0.f; }
+    if (grp == 0) {
     // query operand: G packed rows, swizzled; its scale block; the BF16 copy for the tail
     if (p.q_fp4) {
       if (tid < G * 4) {
@@ -451,10 +498,6 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     fence_proxy_async();
     mbar_arrive(&sm.q_ready);
 
-    constexpr int QPW = (G + 3) / 4;
-    float m_w[QPW], l_w[QPW];
-#pragma unroll
-    for (int k = 0; k < QPW; ++k) { m_w[k] = -INFINITY; l_w[k] = 0.f; }
     if (w.tail_len > 0) {
       for (int it = tid; it < G * 16; it += 128) {
         const int q = it >> 4, c = it & 15;
@@ -487,11 +530,12 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
           if (qq == q) { m_w[k] = m[qq]; l_w[k] = lane == 0 ? l[qq] : 0.f; }
       }
     }
+    }   // group 0: query and tail
 
     // A thread whose wait expired keeps walking the loop's barrier points with ok = false, so
-    // the 128 threads always leave the loop together.
+    // the 128 threads of a group always leave the loop together.
     bool alive = true;
-    for (int kb = 0; kb < n_batches; ++kb) {
+    for (int kb = grp; kb < n_batches; kb += kGroups) {
       const int set = kb & 1, i0 = kb * kBatch;
       const bool two = kBatch == 2 && i0 + 1 < n_pages;
       const bool ok = alive && mbar_wait(&sm.s_full[set], (kb >> 1) & 1, sm, p.status);
@@ -507,58 +551,126 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         const bool ok1 = two && sm.page_ok[(i0 + 1) & 31] != 0;
 #pragma unroll
         for (int q = 0; q < G; ++q) {
-          sm.z[set][0][q * kPage + tid] = ok0 ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY;
+          sm.z[set][0][q * kPage + stid] = ok0 ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY;
           if constexpr (kBatch == 2)
-            sm.z[set][1][q * kPage + tid] = ok1 ? __uint_as_float(r[NQ + q]) * p.scale_log2 : -INFINITY;
+            sm.z[set][1][q * kPage + stid] = ok1 ? __uint_as_float(r[NQ + q]) * p.scale_log2 : -INFINITY;
         }
       }
-      if (!bar_and_128(1, ok)) { alive = false; break; }
+      if (!bar_and<128>(bar_id, ok)) { alive = false; break; }
       // P.V of the pair two hand-overs back has retired: its P tiles, their scale rows and the
       // rescale slots of the pair four hand-overs back may be overwritten
       if (kb >= 2 && !mbar_wait(&sm.o_full[set], ((kb - 2) >> 1) & 1, sm, p.status)) alive = false;
+      // the page maxima first: in the wide form the other group is waiting for them
+      // (with many heads per warp the scores are read from shared memory again further down
+      // rather than kept in registers)
+      constexpr bool kKeepZ = QPW <= 2;
+      float4 za[kKeepZ ? QPW : 1], zb[kKeepZ ? QPW : 1];
+      PageMax ma[QPW], mb[QPW];
 #pragma unroll
       for (int k = 0; k < QPW; ++k) {
-        const int q = warp + 4 * k;
+        const int q = swarp + 4 * k;
+        if (q < G) {
+          const float4 a = *reinterpret_cast<const float4*>(&sm.z[set][0][q * kPage + 4 * lane]);
+          ma[k] = page_max(a);
+          if constexpr (kKeepZ) za[k] = a;
+          if constexpr (kBatch == 2) {
+            const float4 b = *reinterpret_cast<const float4*>(&sm.z[set][1][q * kPage + 4 * lane]);
+            mb[k] = page_max(b);
+            if constexpr (kKeepZ) zb[k] = b;
+          }
+        }
+      }
+      float m_before[QPW];   // running maximum of everything walked before this pair
+#pragma unroll
+      for (int k = 0; k < QPW; ++k) m_before[k] = m_w[k];
+      if constexpr (kGroups == 2) {
+        if (kb > 0) {
+          // the other group publishes the maximum after pair kb - 1 for this warp's heads
+          if (lane == 0) {
+            const unsigned long long t0 = global_ns();
+            uint32_t spins = 0;
+            while (sm.m_seq[swarp] < kb) {
+              if (sm.abort_flag) break;
+              if ((++spins & 1023u) == 0 && global_ns() - t0 > kWaitLimitNs) {
+                sm.abort_flag = 1;
+                set_status(p.status, NVFP4_STATUS_WAIT_TIMEOUT);
+                break;
+              }
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int k = 0; k < QPW; ++k) {
+            const int q = swarp + 4 * k;
+            if (q < G) m_before[k] = sm.m_val[kb & 1][q];
+          }
+        }
+      }
+      float m1[QPW], m2[QPW];
+#pragma unroll
+      for (int k = 0; k < QPW; ++k) {
+        const int q = swarp + 4 * k;
         if (q < G) {
           // the pages are walked in order: the first page of a pair is quantised against the
           // maximum up to and including itself, the second against the maximum including both
-          const float4 za = *reinterpret_cast<const float4*>(&sm.z[set][0][q * kPage + 4 * lane]);
-          const PageMax ma = page_max(za);
-          const float m1 = fmaxf(m_w[k], ma.page);
-          const float ra = (m_w[k] == -INFINITY) ? 0.f : exp2f(m_w[k] - m1);
-          const float sa = quantize_page(za, ma.group, m1, sm.p_tile[set][0], sm.p_sf[set][0], q, lane);
+          m1[k] = fmaxf(m_before[k], ma[k].page);
+          m2[k] = m1[k];
+          if constexpr (kBatch == 2) m2[k] = fmaxf(m1[k], mb[k].page);
+          if constexpr (kGroups == 2)
+            if (lane == 0) sm.m_val[(kb + 1) & 1][q] = m2[k];
+        }
+      }
+      if constexpr (kGroups == 2) {
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          sm.m_seq[swarp] = kb + 1;   // the other group may go on
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < QPW; ++k) {
+        const int q = swarp + 4 * k;
+        if (q < G) {
+          // this group's part of the row sum refers to its own last maximum: bring it to the
+          // maximum before this pair (the other group's pair may have raised it)
+          if constexpr (kGroups == 2)
+            if (m_w[k] != -INFINITY && m_before[k] != m_w[k]) l_w[k] *= exp2f(m_w[k] - m_before[k]);
+          const float ra = (m_before[k] == -INFINITY) ? 0.f : exp2f(m_before[k] - m1[k]);
+          float4 a;
+          if constexpr (kKeepZ) a = za[k];
+          else a = *reinterpret_cast<const float4*>(&sm.z[set][0][q * kPage + 4 * lane]);
+          const float sa = quantize_page(a, ma[k].group, m1[k], sm.p_tile[set][0], sm.p_sf[set][0], q, lane);
           if constexpr (kBatch == 2) {
-            const float4 zb = *reinterpret_cast<const float4*>(&sm.z[set][1][q * kPage + 4 * lane]);
-            const PageMax mb = page_max(zb);
-            const float m2 = fmaxf(m1, mb.page);
-            const float rb = (m1 == -INFINITY) ? 0.f : exp2f(m1 - m2);
-            const float sb = quantize_page(zb, mb.group, m2, sm.p_tile[set][1], sm.p_sf[set][1], q, lane);
-            m_w[k] = m2;
+            const float rb = (m1[k] == -INFINITY) ? 0.f : exp2f(m1[k] - m2[k]);
+            float4 b;
+            if constexpr (kKeepZ) b = zb[k];
+            else b = *reinterpret_cast<const float4*>(&sm.z[set][1][q * kPage + 4 * lane]);
+            const float sb = quantize_page(b, mb[k].group, m2[k], sm.p_tile[set][1], sm.p_sf[set][1], q, lane);
             l_w[k] = fmaf(fmaf(l_w[k], ra, sa), rb, sb);
             if (lane == 0) {
               sm.resc[i0 & 7][q] = ra;
               sm.resc[(i0 + 1) & 7][q] = rb;
             }
           } else {
-            m_w[k] = m1;
             l_w[k] = fmaf(l_w[k], ra, sa);
             if (lane == 0) sm.resc[i0 & 7][q] = ra;
           }
+          m_w[k] = m2[k];
         }
       }
       fence_proxy_async();
       mbar_arrive(&sm.p_full[set]);
     }
-    // row sums and final maxima of every query head, for the output threads
+    // the group's part of the row sums and the maxima they refer to, for the output threads
 #pragma unroll
     for (int k = 0; k < QPW; ++k) {
-      const int q = warp + 4 * k;
+      const int q = swarp + 4 * k;
       if (q < G) {
         const float ls = warp_sum(l_w[k]);
-        if (lane == 0) { sm.red_io[q] = ls; sm.red_io[NQ + q] = m_w[k]; }
+        if (lane == 0) { sm.fin[grp][q] = ls; sm.fin[grp][NQ + q] = m_w[k]; }
       }
     }
-    bar_and_256(3, alive);
+    bar_and<128 * (kGroups + 1)>(3, alive);
   } else if (warp < 8) {
     // =====================  output threads: thread t = channel t  =====================
     const int t = tid - 128;
@@ -597,11 +709,20 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         alive = false;
       }
     }
-    const bool stored = bar_and_256(3, alive);
+    const bool stored = bar_and<128 * (kGroups + 1)>(3, alive);
     if (stored) {
 #pragma unroll
       for (int q = 0; q < G; ++q) {
-        const float lq = sm.red_io[q], mq = sm.red_io[NQ + q];
+        float lq = sm.fin[0][q], mq = sm.fin[0][NQ + q];
+        if constexpr (kGroups == 2) {
+          // join the two groups' parts of the row sum at the larger (the final) maximum
+          const float l1 = sm.fin[1][q], mq1 = sm.fin[1][NQ + q];
+          const float mf = fmaxf(mq, mq1);
+          const float a0 = mq == -INFINITY ? 0.f : lq * exp2f(mq - mf);
+          const float a1 = mq1 == -INFINITY ? 0.f : l1 * exp2f(mq1 - mf);
+          lq = a0 + a1;
+          mq = mf;
+        }
         const int head = w.kvh * G + q;
         const float val = lq > 0.f ? __fdiv_rn(o[q], lq) : 0.f;
         if (p.emit_partial) {
@@ -617,40 +738,88 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     if (p.xchg_inbox) exchange_tile<G>(p, w, sm, t, stored, xchg_epoch);
   } else if (is_producer) {
     // =====================  producers (K ring: warp 8, V ring: warp 11)  =====================
-    // An issuing lane takes every kProducerLanes-th page and reads its own page-table entries,
-    // one step ahead of their use.
-    if (lane < kProducerLanes) {
+    if constexpr (kGroups == 1) {
+      // Narrow form (two CTAs per SM, the page stream bound by HBM): lane 0 walks the table
+      // itself, reading its entries one step ahead of their use.
+      if (lane == 0) {
+        const int slots = is_k_producer ? kKS : kVS;
+        const int32_t* table = p.page_table + (int64_t)w.row * p.page_table_row_stride;
+        int i = issued;
+        int64_t next = i < n_pages ? table[w.last_page - 1 - i] : -1;
+        for (; i < n_pages; ++i) {
+          int64_t pid = next;
+          if (i + 1 < n_pages) next = table[w.last_page - 1 - (i + 1)];
+          if (pid < 0 || pid >= p.num_pages) {
+            if (is_k_producer) set_status(p.status, NVFP4_STATUS_BAD_PAGE_ID);
+            pid = -1;
+          }
+          const int s = i % slots;
+          uint64_t* freed = is_k_producer ? &sm.k_empty[s] : &sm.v_empty[s];
+          if (!mbar_wait(freed, ((i / slots) & 1) ^ 1, sm, p.status)) break;
+          issue_slot(is_k_producer, s, i, pid);
+        }
+      }
+    } else {
+    // Wide form (a CTA with an SM to itself, bound by its own page period): the page ids of a
+    // walk are read 32 at a time, one per lane and one chunk ahead of their use - a load per
+    // page in the issuing thread's own loop costs it a memory round trip per page, and the ring
+    // then fills at two pages a microsecond whatever its depth - and two producers of each kind
+    // take the walk steps alternately; lane 0 of each takes its ids by shuffle and issues.
+    {
       const int slots = is_k_producer ? kKS : kVS;
       const int32_t* table = p.page_table + (int64_t)w.row * p.page_table_row_stride;
-      int i = issued + lane;
-      int64_t next = i < n_pages ? table[w.last_page - 1 - i] : -1;
-      for (; i < n_pages; i += kProducerLanes) {
-        int64_t pid = next;
-        if (i + kProducerLanes < n_pages) next = table[w.last_page - 1 - (i + kProducerLanes)];
-        if (pid < 0 || pid >= p.num_pages) {
-          if (is_k_producer) set_status(p.status, NVFP4_STATUS_BAD_PAGE_ID);
-          pid = -1;
+      auto chunk_ids = [&](int base) {   // lane l: the page id of walk step base + l, or -1 past the end
+        const int idx = w.last_page - 1 - (base + lane);
+        return idx >= w.first_page ? __ldg(table + idx) : -1;
+      };
+      int alive = 1;
+      if (second_producer) ids = chunk_ids(0);
+      int ids_next = n_pages > 32 ? chunk_ids(32) : -1;
+      const int parity = second_producer ? 1 : 0;
+      for (int base = 0; base < n_pages && alive; base += 32) {
+        if (base > 0) {
+          ids = ids_next;
+          if (base + 32 < n_pages) ids_next = chunk_ids(base + 32);
         }
-        const int s = i % slots;
-        uint64_t* freed = is_k_producer ? &sm.k_empty[s] : &sm.v_empty[s];
-        if (!mbar_wait(freed, ((i / slots) & 1) ^ 1, sm, p.status)) break;
-        issue_slot(is_k_producer, s, i, pid);
+        const int in_chunk = min(32, n_pages - base);
+        for (int j = (base == 0 ? issued : 0); j < in_chunk; ++j) {
+          if (kGroups == 2 && (j & 1) != parity) continue;   // the other producer of the kind takes it
+          int64_t pid = __shfl_sync(0xffffffffu, ids, j);
+          if (lane == 0) {
+            if (pid < 0 || pid >= p.num_pages) {
+              if (is_k_producer) set_status(p.status, NVFP4_STATUS_BAD_PAGE_ID);
+              pid = -1;
+            }
+            const int i = base + j, s = i % slots;
+            uint64_t* freed = is_k_producer ? &sm.k_empty[s] : &sm.v_empty[s];
+            if (!mbar_wait(freed, ((i / slots) & 1) ^ 1, sm, p.status)) alive = 0;
+            else issue_slot(is_k_producer, s, i, pid);
+          }
+          alive = __shfl_sync(0xffffffffu, alive, 0);
+          if (!alive) break;
+        }
       }
     }
+    }
     __syncwarp();
-  } else if (warp == kQkWarp) {
+  } else if (warp == kQkWarp || warp == 16) {
     // =====================  MMA issuer 1: S^T = K . Q^T  =====================
     // Issuing a tcgen05 instruction costs the issuing thread some 60 cycles and a barrier
-    // wait about twice that, so the two products of a page are issued by two threads.
+    // wait about twice that, so the two products of a page are issued by two threads - and in
+    // the wide form, where a CTA has an SM to itself and the issue rate is what bounds its page
+    // period, by two threads each: issuer ig takes the hand-overs kb = ig, ig + 2, ... (set ig of
+    // the buffers) with scale columns of its own.
+    const int ig = warp == kQkWarp ? 0 : 1;
     if (lane == 0 && n_pages > 0) {
       bool alive = mbar_wait(&sm.q_ready, 0, sm, p.status);
+      const uint32_t sfq = tmem + C::kSfQ + 8 * ig, sfk = tmem + C::kSfK + 8 * ig;
       if (alive) {
         tc_fence_after();
-        cp_sf(tmem + C::kSfQ, smem_u32(sm.q_sf));
-        cp_sf(tmem + C::kSfQ + 4, smem_u32(sm.q_sf + 512));
+        cp_sf(sfq, smem_u32(sm.q_sf));
+        cp_sf(sfq + 4, smem_u32(sm.q_sf + 512));
       }
       const uint64_t q_desc = desc_sw64(smem_u32(sm.q_tile));
-      for (int kb = 0; kb < n_batches && alive; ++kb) {
+      for (int kb = ig; kb < n_batches && alive; kb += kGroups) {
         const int set = kb & 1;
         alive = mbar_wait(&sm.s_free[set], ((kb >> 1) & 1) ^ 1, sm, p.status);
         for (int u = 0; u < kBatch && alive; ++u) {
@@ -661,26 +830,28 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
           if (!alive) break;
           tc_fence_after();
           const uint32_t st = smem_u32(sm.k_slot[s]);
-          cp_sf(tmem + C::kSfK, st + kTileBytes);
-          cp_sf(tmem + C::kSfK + 4, st + kTileBytes + 512);
+          cp_sf(sfk, st + kTileBytes);
+          cp_sf(sfk + 4, st + kTileBytes + 512);
           const uint64_t k_desc = desc_sw64(st);
           const uint32_t d = tmem + C::kS + set * C::kSet + u * NQ;
-          mma_nvf4<NQ>(d, k_desc, q_desc, tmem + C::kSfK, tmem + C::kSfQ, 0);
-          mma_nvf4<NQ>(d, k_desc + 2, q_desc + 2, tmem + C::kSfK + 4, tmem + C::kSfQ + 4, 1);
+          mma_nvf4<NQ>(d, k_desc, q_desc, sfk, sfq, 0);
+          mma_nvf4<NQ>(d, k_desc + 2, q_desc + 2, sfk + 4, sfq + 4, 1);
           mma_commit(&sm.k_empty[s]);   // the K slot goes back once this page's product has retired
         }
         if (alive) mma_commit(&sm.s_full[set]);
       }
       // everything this thread issued must have retired before tensor memory is freed
-      mma_commit(&sm.drain[0]);
-      mbar_wait(&sm.drain[0], 0, sm, p.status);
+      mma_commit(&sm.drain[ig]);
+      mbar_wait(&sm.drain[ig], 0, sm, p.status);
     }
     __syncwarp();
-  } else if (warp == kPvWarp) {
+  } else if (warp == kPvWarp || warp == 17) {
     // =====================  MMA issuer 2: O^T = V^T . P^T  =====================
+    const int ig = warp == kPvWarp ? 0 : 1;
     if (lane == 0 && n_pages > 0) {
       bool alive = true;
-      for (int kb = 0; kb < n_batches && alive; ++kb) {
+      const uint32_t sfp = tmem + C::kSfP + 8 * ig;
+      for (int kb = ig; kb < n_batches && alive; kb += kGroups) {
         const int set = kb & 1;
         // The V slots of a pair land long before its probabilities are ready: their scale
         // blocks go to tensor memory now (columns of their own per page of the pair), which
@@ -706,19 +877,19 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
           if (j >= n_pages) break;
           const int s = j % kVS;
           const uint32_t c = tmem + C::kSfV + (set * kBatch + u) * 8;
-          cp_sf(tmem + C::kSfP, smem_u32(sm.p_sf[set][u]));
-          cp_sf(tmem + C::kSfP + 4, smem_u32(sm.p_sf[set][u] + 512));
+          cp_sf(sfp, smem_u32(sm.p_sf[set][u]));
+          cp_sf(sfp + 4, smem_u32(sm.p_sf[set][u] + 512));
           const uint64_t v_desc = desc_sw64(smem_u32(sm.v_slot[s]));
           const uint64_t p_desc = desc_sw64(smem_u32(sm.p_tile[set][u]));
           const uint32_t d = tmem + C::kO + set * C::kSet + u * NQ;
-          mma_nvf4<NQ>(d, v_desc, p_desc, c, tmem + C::kSfP, 0);
-          mma_nvf4<NQ>(d, v_desc + 2, p_desc + 2, c + 4, tmem + C::kSfP + 4, 1);
+          mma_nvf4<NQ>(d, v_desc, p_desc, c, sfp, 0);
+          mma_nvf4<NQ>(d, v_desc + 2, p_desc + 2, c + 4, sfp + 4, 1);
           mma_commit(&sm.v_empty[s]);   // the V slot goes back once this page's product has retired
         }
         mma_commit(&sm.o_full[set]);
       }
-      mma_commit(&sm.drain[1]);
-      mbar_wait(&sm.drain[1], 0, sm, p.status);
+      mma_commit(&sm.drain[2 + ig]);
+      mbar_wait(&sm.drain[2 + ig], 0, sm, p.status);
     }
     __syncwarp();
   }
@@ -726,7 +897,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   // ---- teardown ----
   tc_fence_before();
   __syncthreads();
-  if (is_producer && lane == 0 && sm.abort_flag) {
+  if (is_producer && !second_producer && lane == 0 && sm.abort_flag) {
     // copies still in flight must land before the CTA's shared memory is handed on
     const int slots = is_k_producer ? kKS : kVS;
     for (int s = 0; s < slots; ++s) {
@@ -744,16 +915,18 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 }
 
 
-template <int G>
+template <int G, int kGroups>
 static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const CUtensorMap& vm,
                             cudaStream_t stream) {
-  const size_t smem = sizeof(Smem<G>) + 1024;
+  const size_t smem = sizeof(Smem<G, kGroups>) + 1024;
+  static_assert(sizeof(Smem<G, kGroups>) + 1024 <= (kGroups == 1 ? 115712 : 232448),
+                "shared memory of one CTA (two per SM in the narrow form)");
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    e = cudaFuncSetAttribute(decode_sm100_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaFuncSetAttribute(decode_sm100_kernel<G, kGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
@@ -761,21 +934,38 @@ static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const 
   // CTAs start in the order of their linear index, x fastest: all KV heads of the first list
   // entry, then of the second, ... - and the list holds the longest pieces first
   if (p.work_list) grid = dim3(p.heads_kv, p.work_capacity, 1);
-  if (p.pdl) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, decode_sm100_kernel<G>, km, vm, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(ThreadsOf<kGroups>::value);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, decode_sm100_kernel<G, kGroups>, km, vm, p);
+}
+
+// The wide form pays when a CTA's own page period, not HBM, bounds the launch: at most one CTA
+// per SM.  Sixteen and more query heads per KV head always take it (their score threads need its
+// register budget).
+template <int G>
+static cudaError_t launch_form(const DecodeParams& p, const CUtensorMap& km, const CUtensorMap& vm,
+                               cudaStream_t stream) {
+  static int sms[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  int n = 148;
+  if (dev >= 0 && dev < 64) {
+    if (!sms[dev] && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms[dev] = 148;
+    n = sms[dev];
   }
-  decode_sm100_kernel<G><<<grid, kThreads, smem, stream>>>(km, vm, p);
-  return cudaGetLastError();
+  const int64_t ctas = p.work_list ? (int64_t)p.heads_kv * p.work_capacity
+                                   : (int64_t)p.num_splits * p.heads_kv * p.rows;
+  const bool wide = !p.xchg_inbox && (G >= 16 || ctas <= n);
+  return wide ? launch_g<G, 2>(p, km, vm, stream) : launch_g<G, 1>(p, km, vm, stream);
 }
 
 }  // namespace sm100
@@ -796,12 +986,12 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream) {
   e = sm100::make_map(1, p.v_packed, p.v_pitch, p.num_pages, p.heads_kv, &vm);
   if (e != cudaSuccess) return e;
   switch (p.heads_q / p.heads_kv) {
-    case 1: return sm100::launch_g<1>(p, km, vm, stream);
-    case 2: return sm100::launch_g<2>(p, km, vm, stream);
-    case 4: return sm100::launch_g<4>(p, km, vm, stream);
-    case 8: return sm100::launch_g<8>(p, km, vm, stream);
-    case 16: return sm100::launch_g<16>(p, km, vm, stream);
-    case 32: return sm100::launch_g<32>(p, km, vm, stream);
+    case 1: return sm100::launch_form<1>(p, km, vm, stream);
+    case 2: return sm100::launch_form<2>(p, km, vm, stream);
+    case 4: return sm100::launch_form<4>(p, km, vm, stream);
+    case 8: return sm100::launch_form<8>(p, km, vm, stream);
+    case 16: return sm100::launch_form<16>(p, km, vm, stream);
+    case 32: return sm100::launch_form<32>(p, km, vm, stream);
     default: return cudaErrorNotSupported;
   }
 }

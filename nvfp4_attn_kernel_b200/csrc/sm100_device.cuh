@@ -148,7 +148,6 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "memory");
 }
 
-constexpr int kProducerLanes = 1;   // lanes of a producer warp that issue loads (more measured no faster)
 constexpr int kKProducerWarp = 8;
 constexpr int kQkWarp = 9;   // also owns the tensor-memory allocation
 constexpr int kPvWarp = 10;
@@ -187,8 +186,20 @@ __device__ __forceinline__ int sw64_offset(int row, int byte_col) {
   return row * 64 + ((((byte_col >> 4) ^ ((row >> 1) & 3))) << 4) + (byte_col & 15);
 }
 
-constexpr int kThreads = 384;
-static_assert(kThreads == 384, "the set-up barrier is written for 384 threads");
+// Barrier over N threads (a multiple of 32) that also ANDs a predicate across them.
+template <int N>
+__device__ __forceinline__ bool bar_and(int bar_id, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "bar.red.and.pred p, %1, %3, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(bar_id), "r"((uint32_t)pred), "n"(N)
+      : "memory");
+  return out != 0;
+}
 
 // One page of scores for one query head, seen by the 32 lanes of its owner warp (four
 // consecutive kv positions per lane): group and page maxima.
