@@ -419,6 +419,14 @@ def run_gpu(args) -> None:
 
     # the floor on this GPU: a launch that only reads the step's bytes, same pools, same timing
     def read_floor():
+        import ctypes
+
+        from nvfp4_attn_kernel_b200 import build as _build
+
+        read_floor_lib = ctypes.CDLL(_build.BENCH_AID_PATH)   # a measurement aid, not the product library
+        read_floor_lib.bench_read_floor.restype = ctypes.c_int
+        read_floor_lib.bench_read_floor.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p,
+                                                    ctypes.c_void_p]
         sink = torch.zeros(1, dtype=torch.int32, device=device)
         side = torch.cuda.Stream(device)
         side.wait_stream(torch.cuda.current_stream())
@@ -426,8 +434,10 @@ def run_gpu(args) -> None:
         with torch.cuda.graph(graph, stream=side):
             for i in range(NUM_POOLS):
                 cache = pools[i]["cache"]
-                L.check(lib.nvfp4_probe_hbm_read(cache.data_ptr(), cache.numel(), sink.data_ptr(),
-                                                 torch.cuda.current_stream().cuda_stream))
+                rc = read_floor_lib.bench_read_floor(cache.data_ptr(), cache.numel(), sink.data_ptr(),
+                                                     torch.cuda.current_stream().cuda_stream)
+                if rc:
+                    raise RuntimeError(f"bench_read_floor: CUDA error {rc}")
         for _ in range(3):
             graph.replay()
         reps = max(50, long_replays // 2)
@@ -843,6 +853,9 @@ def run_ragged(args) -> None:
     if args.balance_pages < 0:   # from what a scheduler knows on the host: the lengths
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         balance = _decode.balance_pages_heuristic(int(full.sum()), HKV, sms=sms)
+    if args.wide:
+        balance = _decode.wide_piece_pages((lens + total_steps) // PAGE, HKV,
+                                           sms=torch.cuda.get_device_properties(device).multi_processor_count)
     if balance:
         splits = 1
         space = torch.empty(_decode.balanced_workspace_bytes(rows, HQ, columns, balance),
@@ -852,6 +865,8 @@ def run_ragged(args) -> None:
         while int(lens.max() + total_steps) // PAGE > 64 * splits:
             splits *= 2
     how = dict(balance_pages=balance, workspace=space) if balance else dict(num_splits=splits)
+    if args.wide:
+        how["wide_form"] = True
     if args.persistent:
         balance, splits = None, 1
         how = dict(persistent_workspace=_decode.persistent_workspace(rows, HQ, HKV, device))
@@ -1012,6 +1027,8 @@ def run_model_step(args, sub: bool = False):
                          device=device)
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     piece = piece_pages(rows, hkv, columns, sms) if args.balance_pages < 0 else max(0, args.balance_pages)
+    if args.wide:
+        piece = _decode.wide_piece_pages((lens + total_steps) // PAGE, hkv, sms=sms)
     if piece >= columns:
         piece = 0
     pws = _decode.persistent_workspace(rows, hq, hkv, device) if args.persistent else None
@@ -1025,6 +1042,8 @@ def run_model_step(args, sub: bool = False):
         for layer in range(layers):
             k_fp4, k_sf, v_fp4, v_sf = views[layer]
             how = dict(balance_pages=piece, workspace=space, reuse_work_list=layer > 0) if piece else {}
+            if args.wide:
+                how["wide_form"] = True
             if args.persistent:
                 how = dict(persistent_workspace=pws)
             _decode.decode_fp4(
@@ -1298,6 +1317,9 @@ def main() -> None:
     ap.add_argument("--balance-pages", type=int, default=-1,
                     help="ragged workload: pieces of about this many pages per row (0: one split "
                          "count for the batch; -1, the default: chosen from the lengths)")
+    ap.add_argument("--wide", action="store_true",
+                    help="ragged / model-step workloads: cut the rows, from their host-side lengths, into at "
+                         "most one piece per SM and run the decode on the kernel's wide form")
     ap.add_argument("--persistent", action="store_true",
                     help="ragged / model-step workloads: run the decode as one persistent launch "
                          "(NVFP4_DECODE_PERSISTENT) instead of work list + pieces + merge")

@@ -115,6 +115,19 @@ int nvfp4_tail_append(const void* key, const void* value, int64_t key_token_stri
                       int num_reqs, int heads_kv, void* stream);
 
 /*
+ * Calibration of the key shift: sum[h][d] += the sum over the step's tokens of key[t][h][d],
+ * accumulated in fp64, in one launch.
+ * ref: the accumulation in NVFP4Impl.do_kv_cache_update, src/nvfp4_vllm/impl.py:137-144
+ * (key[:num_actual_tokens].double().sum(dim=0) added to key_shift_sum[layer]).
+ *   key  [tokens][Hkv][128] bf16, token stride in elements (multiple of 8), 16-byte aligned
+ *   sum  [Hkv][128] fp64 accumulator of this layer (device)
+ * The addends are BF16 numbers, so the fp64 partial sums are exact for any realistic spread of
+ * magnitudes and the result does not depend on the order of the additions.
+ */
+int nvfp4_key_sum_accumulate(const void* key, int64_t key_token_stride, int num_tokens, int heads_kv,
+                             double* sum, void* stream);
+
+/*
  * One layer's K/V of a step in ONE launch: every full page of this step's prompts quantised
  * into its block (work table: src_tokens / dst_pages, -1 = skip; key shift fused) and every other
  * token copied to its row's tail slot (key shift fused).  Replaces the three launches of
@@ -262,6 +275,18 @@ size_t nvfp4_decode_persistent_workspace_bytes(int rows, int heads_q, int heads_
 int nvfp4_decode_persistent_supported(int rows, int heads_q, int heads_kv);
 
 /*
+ * NVFP4_DECODE_WIDE_FORM (tensor-core kernel; a hint, no counterpart in the reference): the caller
+ * expects at most one busy CTA per SM - rows x KV heads x pieces at or below the SM count.  Such a
+ * launch is bound by a CTA's own page period, not by HBM, and runs on the kernel's wide form: one
+ * CTA per SM with two sets of producers, issuers and score warps and deeper rings.  Without the
+ * flag the library chooses from what it can see (the grid of nvfp4_decode; for
+ * nvfp4_decode_balanced the capacity of the list, an upper bound that is often far above the
+ * pieces a step really has - a caller that knows the lengths on the host should say).  The
+ * results are the same bits either way except for the row sum's association (see the kernel).
+ */
+#define NVFP4_DECODE_WIDE_FORM 8u
+
+/*
  * With out != NULL the merged bf16 result is written (for num_splits > 1 the
  * partials go through o_partial/lse_partial if given, else through workspace).
  * With out == NULL the call only emits the partials (used by the cross-GPU
@@ -374,16 +399,6 @@ typedef struct nvfp4_exchange_args {
 int nvfp4_decode_exchange(const nvfp4_decode_args* args, const nvfp4_exchange_args* x, void* stream);
 
 /*
- * Measurement aid, no counterpart in the reference project: one launch that reads
- * [ptr, ptr + bytes) once with plain 16-byte loads from every SM and discards the data.
- * Its duration over the page pools of a decode step is the floor for any launch that has to
- * touch those bytes on this GPU; bench.py reports it beside the decode kernel's duration.
- * sink: nullable device word (written only in the practically impossible case that the
- * checksum of the data equals a constant; it keeps the loads alive).
- */
-int nvfp4_probe_hbm_read(const void* ptr, size_t bytes, uint32_t* sink, void* stream);
-
-/*
  * Split-KV decode with a split count per row ("balanced split").  No counterpart in the
  * reference project, whose split count is one number for the whole batch
  * (src/nvfp4_decode_kernel/_decode.py:1018-1049): in a ragged batch that number follows the
@@ -423,8 +438,14 @@ size_t nvfp4_decode_balanced_workspace_bytes(int rows, int heads_q, int max_page
  *    o_partial and lse_partial are ignored / must be NULL.
  *  - rows * heads_q * num_splits * 516 bytes must fit the array, otherwise NVFP4_ERR_INVALID with
  *    a message (nvfp4_decode_split_static_error()) that names both sizes.
- *  - The first call on a device looks the array's address up (with that device current); make
- *    that first call before any stream capture.
+ *  - Set-up: the first call on a device (with that device current) looks the array's address
+ *    up before it checks anything else.  The CUDA runtime loads the module holding the array at
+ *    that moment, which takes the array's bytes out of the device's free memory - once, by the
+ *    module loader, not by an allocation call, and measured on a B200 as exactly
+ *    NVFP4_STATIC_WORKSPACE_BYTES.  A caller that sizes its KV cache from the free memory makes
+ *    that first call beforehand, and before any stream capture: nvfp4_decode_split_static(NULL,
+ *    NULL) does the set-up and then returns NVFP4_ERR_INVALID ("null argument block").  Every
+ *    later call on the device leaves both the allocator and the free-memory count untouched.
  *  - All calls on a device share the one array: two calls whose kernels may overlap on the GPU
  *    (different streams, no ordering) race on it.  Nothing in it needs clearing between calls -
  *    every slot that the merge reads is written by the decode kernel of the same call.

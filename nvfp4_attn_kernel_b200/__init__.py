@@ -50,4 +50,6 @@ def install_aliases() -> None:
     if not any(isinstance(finder, _AliasFinder) for finder in sys.meta_path):
         sys.meta_path.insert(0, _AliasFinder())
     for name in _ALIASES:
-        importlib.import_module(name)
+        # set, not imported: when this runs from the installed stand-in package of the same
+        # name, that stand-in is in sys.modules already and must be replaced by the real one
+        sys.modules[name] = importlib.import_module(f"{__name__}.{name}")

@@ -17,6 +17,7 @@ IMPL_AUTO, IMPL_GENERIC, IMPL_SM100 = 0, 1, 2
 DECODE_PROGRAMMATIC_LAUNCH = 1
 DECODE_REUSE_WORK_LIST = 2
 DECODE_PERSISTENT = 4
+DECODE_WIDE_FORM = 8
 STATUS_BAD_PAGE_ID, STATUS_BAD_TAIL_ID, STATUS_WAIT_TIMEOUT, STATUS_BAD_LENGTH = 1, 2, 4, 8
 ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED = 1, 2, 3
 
@@ -37,8 +38,8 @@ EXPORTS = (
     "nvfp4_peer_merge",
     "nvfp4_control_step",
     "nvfp4_work_table",
-    "nvfp4_probe_hbm_read",
     "nvfp4_write_kv",
+    "nvfp4_key_sum_accumulate",
     "nvfp4_push_merge",
     "nvfp4_decode_exchange",
     "nvfp4_push_merge_inbox_floats",
@@ -197,8 +198,8 @@ def _declare_control(lib) -> None:
                                    + [c_void_p, c_int64] * 4 + [c_void_p, c_void_p, c_int]
                                    + [c_void_p, c_void_p, c_int64] + [c_void_p] * 4
                                    + [c_int, c_int, c_int, c_void_p])
-    lib.nvfp4_probe_hbm_read.restype = c_int
-    lib.nvfp4_probe_hbm_read.argtypes = [c_void_p, c_size_t, c_void_p, c_void_p]
+    lib.nvfp4_key_sum_accumulate.restype = c_int
+    lib.nvfp4_key_sum_accumulate.argtypes = [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]
     lib.nvfp4_work_table.restype = c_int
     lib.nvfp4_work_table.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                      c_int, c_int, c_void_p]

@@ -17,7 +17,10 @@ LIB_NAME = "libnvfp4_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
 
 SOURCES = ["capi.cu", "quantize.cu", "decode_generic.cu", "decode_sm100.cu", "decode_persistent.cu", "merge.cu",
-           "decode_static_ws.cu", "control.cu", "probe.cu"]
+           "decode_static_ws.cu", "control.cu", "key_sum.cu"]
+# measurement aid of bench.py, a library of its own so that the product's ABI carries no test code
+BENCH_AID_SOURCE = "bench_read_floor.cu"
+BENCH_AID_PATH = os.path.join(HERE, "libnvfp4_bench_read_floor.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
@@ -33,7 +36,7 @@ def _nvcc() -> str:
 
 
 def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+    if not os.path.exists(LIB_PATH) or not os.path.exists(BENCH_AID_PATH):
         return True
     built = os.path.getmtime(LIB_PATH)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
@@ -54,6 +57,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
         sys.stderr.write(proc.stdout + proc.stderr)
     if proc.returncode:
         raise RuntimeError(f"nvcc failed with exit code {proc.returncode}")
+    aid = subprocess.run([_nvcc(), *NVCC_FLAGS, "-o", BENCH_AID_PATH + ".tmp", os.path.join(CSRC, BENCH_AID_SOURCE)],
+                         capture_output=True, text=True)
+    if aid.returncode:
+        sys.stderr.write(aid.stdout + aid.stderr)
+        raise RuntimeError(f"nvcc failed with exit code {aid.returncode} on {BENCH_AID_SOURCE}")
+    os.replace(BENCH_AID_PATH + ".tmp", BENCH_AID_PATH)
     os.replace(LIB_PATH + ".tmp", LIB_PATH)
     return LIB_PATH
 

@@ -168,6 +168,21 @@ int nvfp4_write_kv(const void* key, const void* value, int64_t key_token_stride,
   return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "write_kv launch");
 }
 
+int nvfp4_key_sum_accumulate(const void* key, int64_t key_token_stride, int num_tokens, int heads_kv,
+                             double* sum, void* stream) {
+  if (num_tokens < 0) return fail(NVFP4_ERR_INVALID, "key_sum_accumulate: negative token count");
+  if (num_tokens == 0) return NVFP4_OK;
+  if (!key || !sum) return fail(NVFP4_ERR_INVALID, "key_sum_accumulate: null argument");
+  if (heads_kv < 1 || heads_kv > 4096) return fail(NVFP4_ERR_INVALID, "key_sum_accumulate: bad heads_kv");
+  if (key_token_stride < (int64_t)heads_kv * 128 || (key_token_stride % 8) || !aligned16(key) ||
+      (reinterpret_cast<uintptr_t>(sum) & 7))
+    return fail(NVFP4_ERR_INVALID,
+                "key_sum_accumulate: the token stride must cover a token and keep 16-byte alignment");
+  cudaError_t e = nvfp4::launch_key_sum(key, key_token_stride, num_tokens, heads_kv, sum,
+                                        static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "key_sum_accumulate launch");
+}
+
 int nvfp4_tail_reset(void* tail_key, void* tail_value, int64_t tail_layer_stride,
                      int64_t tail_slot_stride, int layers, const int32_t* query_start_loc,
                      const int32_t* seq_lens, const int32_t* row_to_slot, int num_reqs, int heads_kv,
@@ -390,11 +405,13 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   p.num_splits = a->num_splits;
   p.status = a->status;
-  if (a->flags & ~(NVFP4_DECODE_PROGRAMMATIC_LAUNCH | NVFP4_DECODE_REUSE_WORK_LIST | NVFP4_DECODE_PERSISTENT))
+  if (a->flags & ~(NVFP4_DECODE_PROGRAMMATIC_LAUNCH | NVFP4_DECODE_REUSE_WORK_LIST | NVFP4_DECODE_PERSISTENT |
+                   NVFP4_DECODE_WIDE_FORM))
     return fail(NVFP4_ERR_INVALID, "decode: unknown flag bits %#x", a->flags);
   if ((a->flags & NVFP4_DECODE_REUSE_WORK_LIST) && !target_pages)
     return fail(NVFP4_ERR_INVALID, "decode: only nvfp4_decode_balanced has a work list to reuse");
   p.pdl = (a->flags & NVFP4_DECODE_PROGRAMMATIC_LAUNCH) ? 1 : 0;
+  p.wide_hint = (a->flags & NVFP4_DECODE_WIDE_FORM) ? 1 : 0;
   if ((a->append_key == nullptr) != (a->append_value == nullptr))
     return fail(NVFP4_ERR_INVALID, "decode: append_key and append_value go together");
   if (a->append_key) {
@@ -582,13 +599,6 @@ int nvfp4_control_step(const int32_t* block_table, int64_t block_table_stride, i
                        num_reqs, num_actual_tokens, num_slots};
   cudaError_t e = nvfp4::launch_control(a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "control_step launch");
-}
-
-int nvfp4_probe_hbm_read(const void* ptr, size_t bytes, uint32_t* sink, void* stream) {
-  if (!ptr && bytes) return fail(NVFP4_ERR_INVALID, "probe_hbm_read: null range");
-  if (!aligned16(ptr)) return fail(NVFP4_ERR_INVALID, "probe_hbm_read: the range must be 16-byte aligned");
-  cudaError_t e = nvfp4::launch_read_probe(ptr, bytes, sink, static_cast<cudaStream_t>(stream));
-  return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "probe_hbm_read launch");
 }
 
 int nvfp4_work_table(const int32_t* query_start_loc, const int32_t* seqused_fp4, const int32_t* row_to_slot,

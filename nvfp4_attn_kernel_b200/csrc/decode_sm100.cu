@@ -125,13 +125,31 @@ __device__ __forceinline__ void exchange_tile(const DecodeParams& p, const TileW
   __threadfence();   // this CTA's partial is visible before its arrival is counted
   asm volatile("bar.sync 6, 128;" ::: "memory");
   if (t == 0) {
-    sm.xchg_last = stored && atomicAdd(p.xchg_counters + tile, 1) == p.num_splits - 1;
+    // every split counts its arrival, stored or not (a split whose wait expired marks the count
+    // failed): the tile always completes, its counter returns to zero and the epoch advances, so
+    // one expired wait cannot leave stale counts behind for the launches that follow
+    const int seen = atomicAdd(p.xchg_counters + tile, stored ? 1 : 0x10001);
+    const bool last = (seen & 0xffff) == p.num_splits - 1;
+    sm.xchg_last = last ? (((seen >> 16) == 0 && stored) ? 1 : 2) : 0;   // 2: complete, but a split failed
     sm.xchg_ready = 1;
   }
   asm volatile("bar.sync 6, 128;" ::: "memory");
   if (!sm.xchg_last) return;
   __threadfence();
   if (t == 0) p.xchg_counters[tile] = 0;   // ready for the next launch
+  if (sm.xchg_last == 2) {
+    // nothing to fold or to push: the status word says why, the peers' waits for this tile run
+    // out with a status of their own; the launch still counts the tile as done
+    if (t == 0) {
+      set_status(p.status, NVFP4_STATUS_WAIT_TIMEOUT);
+      if (atomicAdd(p.xchg_epoch_state + 1, 1) == tiles - 1) {
+        p.xchg_epoch_state[1] = 0;
+        __threadfence();
+        *reinterpret_cast<volatile int*>(p.xchg_epoch_state) = epoch;
+      }
+    }
+    return;
+  }
   const int rank = p.xchg_rank, world = p.xchg_world;
   const int64_t pairs = (int64_t)p.rows * p.heads_q;
   const int64_t copy_elems = (int64_t)world * pairs * kInboxStride;
@@ -964,7 +982,7 @@ static cudaError_t launch_form(const DecodeParams& p, const CUtensorMap& km, con
   }
   const int64_t ctas = p.work_list ? (int64_t)p.heads_kv * p.work_capacity
                                    : (int64_t)p.num_splits * p.heads_kv * p.rows;
-  const bool wide = !p.xchg_inbox && (G >= 16 || ctas <= n);
+  const bool wide = !p.xchg_inbox && (G >= 16 || ctas <= n || p.wide_hint);
   return wide ? launch_g<G, 2>(p, km, vm, stream) : launch_g<G, 1>(p, km, vm, stream);
 }
 

@@ -54,6 +54,19 @@ size_t nvfp4_static_workspace_bytes(void) { return kStaticWorkspaceBytes; }
 
 int nvfp4_decode_split_static(const nvfp4_decode_args* args, void* stream) {
   g_static_error[0] = 0;
+  // Set-up comes before every argument check.  Resolving the array's address the first time on
+  // a device makes the CUDA runtime load the module that holds the array, and that takes the
+  // array's bytes out of the device's free memory - once, not per call, and not through
+  // cudaMalloc.  A caller that must know its free memory exactly (an engine about to size its
+  // KV cache) therefore makes one call first - a call with args = NULL does the set-up and is
+  // then refused - and every later call on that device leaves the free memory alone.
+  void* workspace = nullptr;
+  cudaError_t e = workspace_for_current_device(&workspace);
+  if (e != cudaSuccess) {
+    snprintf(g_static_error, sizeof(g_static_error), "decode_split_static: cudaGetSymbolAddress: %s",
+             cudaGetErrorString(e));
+    return NVFP4_ERR_CUDA;
+  }
   if (!args) {
     snprintf(g_static_error, sizeof(g_static_error), "decode_split_static: null argument block");
     return NVFP4_ERR_INVALID;
@@ -70,13 +83,6 @@ int nvfp4_decode_split_static(const nvfp4_decode_args* args, void* stream) {
              "workspace holds %zu; use nvfp4_decode with a caller-owned workspace",
              args->num_splits, args->rows, args->heads_q, need, kStaticWorkspaceBytes);
     return NVFP4_ERR_INVALID;
-  }
-  void* workspace = nullptr;
-  cudaError_t e = workspace_for_current_device(&workspace);
-  if (e != cudaSuccess) {
-    snprintf(g_static_error, sizeof(g_static_error), "decode_split_static: cudaGetSymbolAddress: %s",
-             cudaGetErrorString(e));
-    return NVFP4_ERR_CUDA;
   }
   nvfp4_decode_args with_ws = *args;
   with_ws.workspace = workspace;

@@ -96,8 +96,9 @@ struct DecodeParams {
   // and entry w stores its partial in slot w.
   const int4* work_list;
   int work_capacity;
-  // Persistent kernel: arrivals per (row, KV head) tile, zero between launches.
+  // Persistent kernel: launch counter and leaving CTAs of the scratch slots.
   int* tile_counters;
+  int wide_hint;              // 1: the caller expects at most one busy CTA per SM
 };
 
 // CUDA-core kernel: any G = Hq/Hkv in {1,2,4,8,16,32}.
@@ -159,7 +160,8 @@ cudaError_t launch_push_merge(const float* o_local, int64_t o_split_stride, cons
                               int rows, int heads_q, void* out, int out_is_f32, uint32_t* status,
                               cudaStream_t stream);
 
-// Reads [ptr, ptr + bytes) once with plain loads and discards it (bandwidth floor of a launch).
-cudaError_t launch_read_probe(const void* ptr, size_t bytes, unsigned* sink, cudaStream_t stream);
+// sum[c] += the fp64 sum over tokens of key[t][c] (c over heads_kv * 128 channels).
+cudaError_t launch_key_sum(const void* key, int64_t token_stride, int tokens, int heads_kv, double* sum,
+                           cudaStream_t stream);
 
 }  // namespace nvfp4

@@ -67,6 +67,27 @@ def balance_pages_heuristic(total_pages: int, heads_kv: int, *, sms: int, floor:
     return max(floor, math.ceil(1.5 * share))
 
 
+def wide_piece_pages(page_counts, heads_kv: int, *, sms: int, floor: int = 4) -> int:
+    """Piece length, in pages, that cuts rows of ``page_counts`` FP4 pages into at most ``sms``
+    pieces per KV head set - one busy CTA per SM, the launch shape of the kernel's wide form
+    (``wide_form=True``) - from lengths the caller knows on the host.  The smallest such length,
+    never below ``floor``."""
+    counts = [int(n) for n in page_counts if int(n) > 0]
+    if not counts or heads_kv < 1 or sms < heads_kv:
+        return floor
+    budget = sms // heads_kv
+    lo, hi = floor, max(floor, max(counts))
+    if sum(-(-n // lo) for n in counts) <= budget:
+        return lo
+    while lo < hi:          # smallest T with sum(ceil(n / T)) <= budget
+        mid = (lo + hi) // 2
+        if sum(-(-n // mid) for n in counts) <= budget:
+            hi = mid
+        else:
+            lo = mid + 1
+    return lo
+
+
 def _need_cuda(tensor: torch.Tensor, name: str, device: torch.device) -> None:
     if not tensor.is_cuda:
         raise ValueError(f"{name} must be a CUDA tensor")
@@ -173,8 +194,12 @@ def decode_fp4(
     workspace: torch.Tensor | None = None,
     reuse_work_list: bool = False,
     persistent_workspace: torch.Tensor | None = None,
+    wide_form: bool = False,
 ) -> torch.Tensor | None:
     """Validate every tensor contract and launch the decode on the current stream.
+
+    ``wide_form`` (a hint): the caller expects at most one busy CTA per SM (rows x KV heads x
+    pieces at or below the SM count); see ``NVFP4_DECODE_WIDE_FORM``.
 
     ``persistent_workspace`` (an extension; from :func:`persistent_workspace`, zero-filled once):
     run the step as ONE persistent launch of two CTAs per SM that share the step's page tiles
@@ -564,6 +589,8 @@ def decode_fp4(
         args.flags |= _lib.DECODE_REUSE_WORK_LIST
     if persistent_workspace is not None:
         args.flags |= _lib.DECODE_PERSISTENT
+    if wide_form:
+        args.flags |= _lib.DECODE_WIDE_FORM
     if args.page_table_row_stride < args.max_pages:
         raise ValueError("fp4_page_table rows overlap")
     with torch.cuda.device(device):

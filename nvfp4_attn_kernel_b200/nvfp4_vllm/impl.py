@@ -20,7 +20,7 @@ from ..nvfp4_decode_kernel import fp4_decode
 from . import promote
 from .guards import NVFP4, check_layer_supported, check_supported
 from .runtime import LayerRuntime, piece_pages
-from .write import reset_new_request_tails, write_kv
+from .write import accumulate_key_sum, reset_new_request_tails, write_kv
 
 
 # A step of one-token rows only (pure decode) needs no page quantisation, and its tail copy can
@@ -84,8 +84,7 @@ class NVFP4Impl(FlashAttentionImpl):
                                     seq_lens=metadata.seq_lens, row_to_slot=metadata.row_to_slot)
         shift = None
         if runtime.key_shift_sum is not None:
-            runtime.key_shift_sum[self.layer_index] += (
-                key[: metadata.num_actual_tokens].double().sum(dim=0))
+            accumulate_key_sum(key[: metadata.num_actual_tokens], runtime.key_shift_sum[self.layer_index])
             if self.layer_index == 0:
                 runtime.key_shift_tokens += metadata.num_actual_tokens
         elif runtime.active_key_shift is not None:
@@ -138,13 +137,19 @@ class NVFP4Impl(FlashAttentionImpl):
         pages = attn_metadata.decode_page_columns
         extra = self._take_fused_kv()
         piece = piece_pages(rows, key_fp4.shape[2], pages, runtime.sm_count)
-        if piece:
+        space = runtime.balance_workspace(rows, query.shape[1], pages, piece) if piece else None
+        if space is not None:
             # Rows longer than a piece are cut by their own device-side lengths (the list of pieces
             # is built on the device, so a captured CUDA graph follows the lengths of every
-            # replay); the lengths are the step's, so the first layer builds the list and the
-            # others reuse it.
-            extra.update(balance_pages=piece, balance_workspace=runtime.balance_workspace(
-                rows, query.shape[1], pages, piece), balance_reuse=self.layer_index > 0)
+            # replay); the lengths are the step's, so the step's first cut layer builds the list
+            # and the others reuse it - but only a list that was built for this very step and
+            # shape in this very scratch (layer 0 starts a step; a layer that finds no such list,
+            # e.g. because the first layers of a model do not come through here, builds it).
+            key = (attn_metadata.seqused_fp4.data_ptr(), rows, pages, piece, space.data_ptr())
+            if self.layer_index == 0:
+                runtime.work_list_reusable(None)
+            extra.update(balance_pages=piece, balance_workspace=space,
+                         balance_reuse=runtime.work_list_reusable(key))
         fp4_decode(
             query=query[:rows], key_pages_fp4=key_fp4, key_scales=key_sf,
             value_pages_fp4=value_fp4, value_scales=value_sf,

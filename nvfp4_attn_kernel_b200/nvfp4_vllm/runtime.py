@@ -114,39 +114,67 @@ class LayerRuntime:
         self._bases: torch.Tensor | None = None
         self._expected_layer = 0
         self._balance_workspace: torch.Tensor | None = None
+        self._work_list_key: tuple | None = None
         if max_pages > 0:
             self.reserve_balance_workspace(max_pages)
 
     def reserve_balance_workspace(self, max_pages: int, limit_bytes: int = 256 << 20) -> int:
         """Allocate, once, the scratch of the largest decode step that ``piece_pages`` would cut:
-        any row count up to the slot count at the model's longest context.  Called with the other
-        allocations of the first forward pass, so the KV cache is sized around it and no decode
-        step allocates.  Returns the bytes reserved (0 when nothing would be cut, or when an
-        explicit piece length makes the worst case larger than ``limit_bytes``: the scratch then
-        grows on demand)."""
-        from ..nvfp4_decode_kernel._decode import balanced_workspace_bytes
-
-        worst = 0
-        for rows in range(1, self.num_slots + 1):
-            piece = piece_pages(rows, self.num_kv_heads, max_pages, self.sm_count)
-            if piece:
-                worst = max(worst, balanced_workspace_bytes(rows, self.num_heads, max_pages, piece))
+        any row count up to the slot count and any page-table width up to the model's longest
+        context (a step's width follows its longest row, and the need is not monotone in it: the
+        piece length is rounded up from the width).  Called with the other allocations of the
+        first forward pass, so the KV cache is sized around it and no decode step allocates.
+        Returns the bytes reserved (0 when nothing would be cut, or when the worst case is larger
+        than ``limit_bytes``: steps then leave their rows whole)."""
+        worst = self.balance_need_worst(max_pages)
         if not 0 < worst <= limit_bytes:
             return 0
         self._balance_workspace = torch.empty(worst, dtype=torch.uint8, device=self.tail_key.device)
         return worst
 
-    def balance_workspace(self, rows: int, heads_q: int, columns: int, balance_pages: int) -> torch.Tensor:
-        """Scratch for a decode with a split count per row: the reserved one, grown only when a
-        step needs more than was planned for."""
-        from ..nvfp4_decode_kernel._decode import balanced_workspace_bytes
+    def balance_need_worst(self, max_pages: int) -> int:
+        """The largest ``balance_need`` over every step shape the policy can meet."""
+        worst = 0
+        for rows in range(1, self.num_slots + 1):
+            for columns in range(1, max_pages + 1):
+                piece = piece_pages(rows, self.num_kv_heads, columns, self.sm_count)
+                if piece:
+                    worst = max(worst, self.balance_need(rows, self.num_heads, columns, piece))
+        return worst
 
-        need = balanced_workspace_bytes(rows, heads_q, columns, balance_pages)
+    @staticmethod
+    def balance_need(rows: int, heads_q: int, columns: int, piece: int) -> int:
+        """Bytes of scratch a step of this shape needs when cut into pieces of ``piece`` pages:
+        the arithmetic of ``nvfp4_decode_balanced_workspace_bytes`` (partial outputs and LSEs of
+        every possible piece, the list of pieces, two ints per row; each part rounded up to 16)."""
+        capacity = rows + rows * columns // piece
+        up16 = lambda n: (n + 15) & ~15   # noqa: E731
+        return (up16(capacity * heads_q * 128 * 4) + up16(capacity * heads_q * 4) + up16(capacity * 16)
+                + 2 * up16(rows * 4))
+
+    def balance_workspace(self, rows: int, heads_q: int, columns: int, balance_pages: int):
+        """Scratch for a decode with a split count per row, or None when the reserved scratch is
+        too small for this step (it then runs with whole rows).  A buffer that was handed out is
+        never released or replaced: a captured CUDA graph holds its address."""
+        need = self.balance_need(rows, heads_q, columns, balance_pages)
         held = self._balance_workspace
-        if held is None or held.numel() < need:
-            held = torch.empty(need, dtype=torch.uint8, device=self.tail_key.device)
+        if held is None:
+            # nothing was reserved (a runtime built without a model length): allocate once, for
+            # the largest shape this table width allows, and keep it for good
+            held = torch.empty(max(need, self.balance_need_worst(columns)), dtype=torch.uint8,
+                               device=self.tail_key.device)
             self._balance_workspace = held
-        return held
+        return held if held.numel() >= need else None
+
+    def work_list_reusable(self, key: tuple) -> bool:
+        """Layers of one step share the list of pieces that the step's first cut layer built.
+        ``key`` names the step and its shape (lengths tensor, rows, columns, piece, scratch): True
+        if a list for exactly that is in the scratch already, else the caller builds it and the
+        key is remembered."""
+        if self._work_list_key == key:
+            return True
+        self._work_list_key = key
+        return False
 
     @property
     def tail_bytes(self) -> int:

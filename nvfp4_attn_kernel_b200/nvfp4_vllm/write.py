@@ -32,6 +32,24 @@ def reset_new_request_tails(*, tail_key: torch.Tensor, tail_value: torch.Tensor,
             seq_lens.shape[0], heads, _stream(tail_key.device)))
 
 
+def accumulate_key_sum(key: torch.Tensor, key_sum: torch.Tensor) -> None:
+    """``key_sum += key.double().sum(dim=0)`` in one launch: the accumulation the key-shift
+    calibration runs per layer and step (reference: ``NVFP4Impl.do_kv_cache_update``,
+    ``src/nvfp4_vllm/impl.py:137-144``).  ``key``: ``[tokens, heads, 128]`` BF16 with dense
+    tokens (any token stride that keeps 16-byte alignment); ``key_sum``: ``[heads, 128]`` FP64,
+    contiguous, on the same device."""
+    tokens, heads, dim = key.shape
+    if key.dtype is not torch.bfloat16 or dim != 128 or key.stride(2) != 1 or key.stride(1) != dim:
+        raise ValueError("key must be BF16 [tokens, heads, 128] with dense tokens")
+    if key_sum.dtype is not torch.float64 or tuple(key_sum.shape) != (heads, dim) or \
+            not key_sum.is_contiguous() or key_sum.device != key.device:
+        raise ValueError("key_sum must be a contiguous FP64 [heads, 128] tensor on key's device")
+    with torch.cuda.device(key.device):
+        _lib.check(_lib.load().nvfp4_key_sum_accumulate(
+            key.data_ptr(), key.stride(0) if tokens > 1 else heads * dim, tokens, heads,
+            key_sum.data_ptr(), _stream(key.device)))
+
+
 class PageWorkTable:
     """Which full pages this step must quantise: a dense rows x columns rectangle, -1 = none."""
 

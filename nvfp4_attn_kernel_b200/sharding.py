@@ -232,6 +232,14 @@ class PageRangeGroup:
         else:
             import torch.distributed as dist
 
+            # A step with NCCL's all-gather between this library's hand-launched kernels did not
+            # finish when it was captured into one CUDA graph on two GPUs (the same step finishes
+            # with plain launches).  Until that is understood the combination is refused here
+            # rather than left to stall a serving process that captures its decode step.
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(
+                    "PageRangeGroup(exchange='nccl') cannot be captured into a CUDA graph: launch it "
+                    "with plain launches, or use exchange='fused', 'push' or 'peer', which capture")
             dist.all_gather_into_tensor(self._gathered, self._buf, group=self.group)
             per_copy = self._o_elems + self._lse_elems
             with torch.cuda.device(self.device):

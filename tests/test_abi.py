@@ -148,3 +148,26 @@ def test_host_side_checks_of_the_python_operator():
     assert split_k_heuristic(32, 8, 32, sms=148) == 1
     assert split_k_heuristic(1, 8, 1, sms=148) == 1
     assert split_k_heuristic(1, 1, 64, sms=148) == 32
+
+
+def test_wide_piece_pages_fills_one_cta_per_sm():
+    """The piece length for the kernel's wide form: the smallest one that cuts the rows into at
+    most sms // heads_kv pieces, never below the floor."""
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel._decode import wide_piece_pages
+
+    def pieces(counts, t):
+        return sum(-(-n // t) for n in counts if n > 0)
+
+    for counts, heads_kv, sms in (([32] * 16, 8, 148), ([257, 3, 0, 64, 1000], 8, 148), ([5], 1, 148),
+                                  ([4096] * 4, 8, 148), ([7] * 300, 8, 148), ([100, 200], 2, 8)):
+        t = wide_piece_pages(counts, heads_kv, sms=sms)
+        budget = sms // heads_kv
+        live = [n for n in counts if n > 0]
+        assert t >= 4
+        if pieces(live, max(max(live), 4)) <= budget:      # the budget can be met at all
+            assert pieces(live, t) <= budget
+            assert t == 4 or pieces(live, t - 1) > budget   # and no shorter piece meets it
+    assert wide_piece_pages([], 8, sms=148) == 4
+    assert wide_piece_pages([0, 0], 8, sms=148) == 4
+    assert wide_piece_pages([50], 8, sms=4) == 4           # fewer SMs than KV heads: the floor
+    assert wide_piece_pages([32] * 16, 8, sms=148, floor=2) == 32

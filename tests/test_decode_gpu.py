@@ -574,3 +574,57 @@ def test_balanced_split_workspace_graph_replay_and_refusals(cuda_device):
     with pytest.raises(ValueError, match="out_indices"):
         prob.decode(balance_pages=4, out=out,
                     out_indices=torch.arange(3, dtype=torch.int32, device=cuda_device))
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_kv_head_shard_equals_the_same_heads_of_the_full_call(cuda_device, world, splits):
+    """Tensor parallelism by KV head needs no exchange inside attention: the decode of a rank's
+    ``sharding.kv_head_slice`` (its query heads, its narrower K/V pages and tails) gives, bit for
+    bit, those heads of the 32/8 call.  The quantised bytes are per (token, head), so the rank's
+    own quantisation of its slice is the same bytes as the slice of the full cache."""
+    from nvfp4_attn_kernel_b200 import sharding
+
+    rows, hq, hkv = 3, 32, 8
+    case = inputs.attention_case(4100 + world, rows, hq, hkv, (128 * 9 + 17, 128 * 4, 77), 1.0, 0.5)
+    full = Problem(case, cuda_device)
+    kw = dict(num_splits=splits) if splits > 1 else {}
+    want = full.decode(**kw)
+    for rank in range(world):
+        q_heads, kv_heads = sharding.kv_head_slice(rank, world, hq, hkv)
+        local = dict(case)
+        local["q"] = case["q"][:, q_heads]
+        local["k_pages"] = case["k_pages"][:, :, kv_heads]
+        local["v_pages"] = case["v_pages"][:, :, kv_heads]
+        part = Problem(local, cuda_device)
+        assert part.heads_q == hq // world and part.heads_kv == hkv // world
+        assert torch.equal(part.k_fp4, full.k_fp4[:, :, kv_heads])
+        got = part.decode(**kw)
+        assert torch.equal(got, want[:, q_heads]), (world, rank)
+
+
+def test_kv_head_shard_of_a_large_batch_matches_under_the_same_kernel_form(cuda_device):
+    """A batch whose full launch exceeds one CTA per SM runs the kernel's narrow form while a
+    rank's eighth of it fits the wide form.  The two forms add a row's pages in a different order
+    (results agree to output rounding, not bit for bit), so the bit-for-bit statement about
+    KV-head shards is made under one form: with the full call asked to take the wide form too,
+    every shard equals its heads exactly; against the default (narrow) full call it stays within
+    output rounding."""
+    from nvfp4_attn_kernel_b200 import sharding
+
+    rows, hq, hkv, world = 40, 32, 8, 8
+    lens = [128 * (3 + i % 5) + (i * 13) % 128 for i in range(rows)]
+    case = inputs.attention_case(4200, rows, hq, hkv, lens, 1.0, 0.0)
+    full = Problem(case, cuda_device)
+    narrow = full.decode_direct(trusted_metadata=True)
+    wide = full.decode_direct(trusted_metadata=True, wide_form=True)
+    assert (narrow.float() - wide.float()).abs().max().item() <= 2e-3
+    for rank in (0, 3, 7):
+        q_heads, kv_heads = sharding.kv_head_slice(rank, world, hq, hkv)
+        local = dict(case)
+        local["q"] = case["q"][:, q_heads]
+        local["k_pages"] = case["k_pages"][:, :, kv_heads]
+        local["v_pages"] = case["v_pages"][:, :, kv_heads]
+        got = Problem(local, cuda_device).decode_direct(trusted_metadata=True)
+        assert torch.equal(got, wide[:, q_heads]), rank
+        assert (got.float() - narrow[:, q_heads].float()).abs().max().item() <= 2e-3

@@ -87,6 +87,7 @@ def test_serving_loop(cuda_device, fuse_append, piece):
     work = PageWorkTable(max_num_seqs=SLOTS, max_num_batched_tokens=1024, device=dev)
     runtime = LayerRuntime(num_layers=LAYERS, num_slots=SLOTS, num_heads=HEADS_Q,
                            num_kv_heads=HEADS_KV, head_dim=DIM, device=dev)
+    scratch, built = [None], set()   # the cut steps' scratch and which (step, shape) lists it holds
     shift_np = O.bf16_round(rng.standard_normal((LAYERS, HEADS_KV, DIM)).astype(np.float32) * 2)
     runtime.key_shift = bf16_tensor(shift_np, dev)
     caches = [torch.zeros(BLOCKS, layout.page_bytes(HEADS_KV), dtype=torch.uint8, device=dev)
@@ -100,7 +101,7 @@ def test_serving_loop(cuda_device, fuse_append, piece):
     script = [[a, b], [a, b], [b, a], [a, b, c], [a, c, b], [a, c], [a, c], [c, a], [a, c, d],
               [d, a, c], [a, d]]
     checked = 0
-    for batch in script:
+    for step_index, batch in enumerate(script):
         query_lens = [r.prompt if r.length == 0 else 1 for r in batch]
         assert [n > 1 for n in query_lens] == sorted(n > 1 for n in query_lens)
         for r, n in zip(batch, query_lens):
@@ -140,8 +141,13 @@ def test_serving_loop(cuda_device, fuse_append, piece):
             cut = piece_pages(decode_rows, HEADS_KV, columns, runtime.sm_count, str(piece or 0))
             assert cut == (piece if piece and columns > piece else 0)
             if cut:   # what the backend does with NVFP4_BALANCE_PAGES set to a page count
-                extra.update(balance_pages=piece, balance_workspace=runtime.balance_workspace(
-                    decode_rows, HEADS_Q, columns, piece), balance_reuse=layer > 0)
+                need = runtime.balance_need(decode_rows, HEADS_Q, columns, piece)
+                if scratch[0] is None or scratch[0].numel() < need:
+                    scratch[0] = torch.empty(4 * need, dtype=torch.uint8, device=dev)
+                    built.clear()
+                list_key = (step_index, decode_rows, columns)
+                extra.update(balance_pages=piece, balance_workspace=scratch[0], balance_reuse=list_key in built)
+                built.add(list_key)
             if not fused:
                 write_kv(key=key_dev, value=value_dev, key_pages_fp4=k_fp4,
                          key_scales=k_sf, value_pages_fp4=v_fp4, value_scales=v_sf,

@@ -308,3 +308,41 @@ def test_write_kv_single_launch_equals_the_three_launches(cuda_device, with_page
     assert not torch.equal(tail_a, base_tail)
     if with_pages:
         assert not (cache_a[[5, 2]] == 0x3C).all() and (cache_a[[0, 1, 3, 4]] == 0x3C).all()
+
+
+@pytest.mark.parametrize("tokens,heads,padded", [(1, 8, False), (7, 2, False), (333, 8, True), (40000, 8, False),
+                                                 (4097, 1, True)])
+def test_key_sum_accumulate_equals_the_fp64_sum(cuda_device, tokens, heads, padded):
+    """The calibration's accumulation (reference: src/nvfp4_vllm/impl.py:137-144,
+    ``key.double().sum(dim=0)``; its CPU test of the fp64 accumulator is
+    tests/e2e/test_key_shift.py:134-153).  BF16 addends make every fp64 partial sum exact, so
+    the launch must equal the fp64 sum bit for bit, whatever the order it added in; a second
+    call adds on top of the first."""
+    from nvfp4_attn_kernel_b200.nvfp4_vllm.write import accumulate_key_sum
+
+    gen = torch.Generator(device=cuda_device)
+    gen.manual_seed(tokens * 31 + heads)
+    width = heads * 128
+    # multiples of 1/64 below 16: every fp64 partial sum is exact, whatever the order
+    store = torch.randn(tokens, width + (64 if padded else 0), device=cuda_device, generator=gen) * 3.0 + 1.5
+    store = (torch.round(store.clamp(-15, 15) * 64) / 64).to(torch.bfloat16)
+    key = store[:, :width].view(tokens, heads, 128) if not padded else \
+        store.as_strided((tokens, heads, 128), (width + 64, 128, 1))
+    acc = torch.zeros(heads, 128, dtype=torch.float64, device=cuda_device)
+    accumulate_key_sum(key, acc)
+    want = key.double().sum(dim=0)
+    # the oracle side of the claim: numpy's own fp64 sum of the same values
+    want_np = to_np(key.float()).astype(np.float64).sum(axis=0)
+    assert np.array_equal(want.cpu().numpy(), want_np)
+    assert torch.equal(acc, want)
+    accumulate_key_sum(key[: max(1, tokens // 2)], acc)
+    assert torch.equal(acc, want + key[: max(1, tokens // 2)].double().sum(dim=0))
+    # unconstrained values (a few land next to zero, with bits far below the sum's last place)
+    wild = (torch.randn(tokens, heads, 128, device=cuda_device, generator=gen) * 0.3).to(torch.bfloat16)
+    acc.zero_()
+    accumulate_key_sum(wild, acc)
+    assert torch.allclose(acc, wild.double().sum(dim=0), rtol=0, atol=1e-10)
+    with pytest.raises(ValueError):
+        accumulate_key_sum(key, acc.float())
+    with pytest.raises(ValueError):
+        accumulate_key_sum(key.float(), acc)

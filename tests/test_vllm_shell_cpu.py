@@ -462,13 +462,24 @@ def test_runtime_reserves_the_balanced_split_scratch(monkeypatch):
                               device="cpu", max_pages=256)
     held = rt._balance_workspace
     assert held is not None
-    # every step that the policy would cut fits the reserved scratch: nothing grows
+    # EVERY step shape that the policy would cut fits the reserved scratch (the need is not
+    # monotone in the table width), and the scratch handed out is always the reserved one
     for rows in range(1, 9):
-        for columns in (32, 100, 256):
+        for columns in range(1, 257):
             piece = runtime.piece_pages(rows, 2, columns, rt.sm_count)
             if piece:
-                assert balanced_workspace_bytes(rows, 8, columns, piece) <= held.numel()
+                need = rt.balance_need(rows, 8, columns, piece)
+                assert need == balanced_workspace_bytes(rows, 8, columns, piece)   # the library's own figure
+                assert need <= held.numel()
                 assert rt.balance_workspace(rows, 8, columns, piece) is held
+    # a step that does not fit gets None (it runs with whole rows); the buffer is never replaced
+    assert rt.balance_workspace(8, 8, 256, 1) is None
+    assert rt._balance_workspace is held
+    # the shape the advisor found short of its reservation: 32 slots, one KV head, 1024 pages
+    tp = runtime.LayerRuntime(num_layers=1, num_slots=32, num_heads=4, num_kv_heads=1, head_dim=128,
+                              device="cpu", max_pages=1024)
+    piece = runtime.piece_pages(32, 1, 111, tp.sm_count)
+    assert piece and tp.balance_need(32, 4, 111, piece) <= tp._balance_workspace.numel()
     # switched off, or a short model: nothing is reserved
     monkeypatch.setenv(runtime.BALANCE_PAGES_ENV, "0")
     assert runtime.LayerRuntime(num_layers=1, num_slots=8, num_heads=8, num_kv_heads=2, head_dim=128,
@@ -476,8 +487,18 @@ def test_runtime_reserves_the_balanced_split_scratch(monkeypatch):
     monkeypatch.delenv(runtime.BALANCE_PAGES_ENV)
     assert runtime.LayerRuntime(num_layers=1, num_slots=8, num_heads=8, num_kv_heads=2, head_dim=128,
                                 device="cpu", max_pages=8)._balance_workspace is None
-    # an explicit tiny piece whose worst case is huge: left to grow on demand
+    # an explicit tiny piece whose worst case is huge: nothing reserved, steps leave their rows whole
     monkeypatch.setenv(runtime.BALANCE_PAGES_ENV, "1")
     big = runtime.LayerRuntime(num_layers=1, num_slots=64, num_heads=64, num_kv_heads=8, head_dim=128,
                                device="cpu", max_pages=4096)
     assert big._balance_workspace is None
+
+
+def test_work_list_is_reused_only_for_the_step_that_built_it():
+    rt = runtime.LayerRuntime(num_layers=2, num_slots=4, num_heads=8, num_kv_heads=2, head_dim=128,
+                              device="cpu", max_pages=64)
+    key = (1234, 4, 40, 16, 99)
+    rt.work_list_reusable(None)                           # layer 0 clears the record
+    assert rt.work_list_reusable(key) is False            # nobody built this list yet
+    assert rt.work_list_reusable(key) is True             # the next layer of the step finds it
+    assert rt.work_list_reusable((1234, 3, 40, 16, 99)) is False   # another shape: rebuilt

@@ -63,11 +63,25 @@ def test_static_workspace_decode_matches_the_regular_entry_point(cuda_device):
         L.check(lib.nvfp4_decode(ctypes.byref(a), stream))
         got = torch.full_like(want, 9.0)
         b = _args(L, prob, q_fp4, q_sf, padded, got, splits)
+        # Set-up, as the header describes it: the first call on a device resolves the array's
+        # address (the runtime loads the module that holds the array then); a NULL block does
+        # just that and is refused.
+        assert lib.nvfp4_decode_split_static(None, None) == L.ERR_INVALID
+        assert b"null argument block" in lib.nvfp4_decode_split_static_error()
+        # Two views of "no allocation" over two calls in a row: torch's caching allocator handed
+        # out nothing, and the driver's count of free device memory (which also sees a cudaMalloc
+        # made behind torch's back, and the module loader) did not move.
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated(cuda_device)
-        rc = lib.nvfp4_decode_split_static(ctypes.byref(b), stream)
-        assert rc == 0, lib.nvfp4_decode_split_static_error().decode()
+        free_before, total_before = torch.cuda.mem_get_info(cuda_device)
+        for _ in range(2):
+            rc = lib.nvfp4_decode_split_static(ctypes.byref(b), stream)
+            assert rc == 0, lib.nvfp4_decode_split_static_error().decode()
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated(cuda_device) == before
+        free_after, total_after = torch.cuda.mem_get_info(cuda_device)
+        assert total_after == total_before
+        assert free_after >= free_before, (free_before, free_after)
         # same kernels, same partials, same merge order: identical, and inside the parity bound
         assert torch.equal(got, want)
         assert np.abs(to_np(got) - prob.oracle_from_bytes(splits=splits)).max() <= 2e-2
