@@ -29,7 +29,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 bool valid_group(int heads_q, int heads_kv) {
   if (heads_kv < 1 || heads_q < 1 || heads_q % heads_kv) return false;
   const int g = heads_q / heads_kv;
-  return g == 1 || g == 2 || g == 4 || g == 8 || g == 16 || g == 32;
+  return (g >= 1 && g <= 8) || g == 16 || g == 32;
 }
 
 }  // namespace
@@ -277,11 +277,12 @@ int nvfp4_decode_persistent_supported(int rows, int heads_q, int heads_kv) {
   return nvfp4::decode_persistent_supports(p) ? 1 : 0;
 }
 
-// Balanced split: row r is cut into ceil(pages_r / target_pages) pieces (one if it has no page),
-// so the list of pieces is never longer than rows + rows * max_pages / target_pages.
+// Balanced split: row r is cut into ceil(pages_r / target_pages) pieces of pages plus one piece
+// for its BF16 tail if it holds one (one empty piece if it has neither), so the list of pieces is
+// never longer than 2 * rows + rows * max_pages / target_pages.
 int64_t nvfp4_decode_balanced_capacity(int rows, int max_pages, int target_pages) {
   if (rows <= 0 || max_pages < 0 || target_pages < 1) return 0;
-  return (int64_t)rows + (int64_t)rows * max_pages / target_pages;
+  return 2 * (int64_t)rows + (int64_t)rows * max_pages / target_pages;
 }
 
 namespace {
@@ -339,7 +340,7 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   if (a->rows == 0) return NVFP4_OK;
   if (!valid_group(a->heads_q, a->heads_kv))
     return fail(NVFP4_ERR_UNSUPPORTED,
-                "decode: heads_q/heads_kv = %d/%d; the ratio must be one of 1,2,4,8,16,32", a->heads_q,
+                "decode: heads_q/heads_kv = %d/%d; the ratio must be 1 to 8, 16 or 32", a->heads_q,
                 a->heads_kv);
   if (!(a->softmax_scale > 0.f) || !(a->softmax_scale < 3.0e38f))
     return fail(NVFP4_ERR_INVALID, "softmax_scale must be finite and positive");
@@ -516,7 +517,7 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
       return fail(NVFP4_ERR_UNSUPPORTED,
                   "decode_balanced: carried by the tensor-core kernel only, without programmatic launch");
     char* base = static_cast<char*>(a->workspace);
-    e = (a->flags & NVFP4_DECODE_REUSE_WORK_LIST) ? cudaSuccess : nvfp4::launch_balanced_worklist(a->seqused_fp4, a->rows, a->max_pages, target_pages,
+    e = (a->flags & NVFP4_DECODE_REUSE_WORK_LIST) ? cudaSuccess : nvfp4::launch_balanced_worklist(a->seqused_fp4, (a->tail_key && a->seqused_tail) ? a->seqused_tail : nullptr, a->rows, a->max_pages, target_pages,
                                         reinterpret_cast<int4*>(base + bal.work), (int)capacity,
                                         reinterpret_cast<int32_t*>(base + bal.row_offset),
                                         reinterpret_cast<int32_t*>(base + bal.row_count), a->status, st);
@@ -524,7 +525,7 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   }
   if (impl == NVFP4_IMPL_SM100) {
     if (!nvfp4::decode_sm100_supports(p))
-      return fail(NVFP4_ERR_UNSUPPORTED, "decode: the tensor-core kernel takes 1, 2, 4, 8, 16 or 32 query heads per KV head");
+      return fail(NVFP4_ERR_UNSUPPORTED, "decode: the tensor-core kernel takes 1 to 8, 16 or 32 query heads per KV head");
     e = nvfp4::launch_decode_sm100(p, st);
   } else if (impl == NVFP4_IMPL_GENERIC) {
     e = nvfp4::launch_decode_generic(p, st);

@@ -48,8 +48,12 @@ __device__ __forceinline__ void set_status(uint32_t* status, uint32_t bit) {
 // Resolve what this CTA owns.  Metadata is device-resident and, on the trusted
 // path, unchecked by the host: anything out of range is clamped, flagged in the
 // sticky status word and never turned into an address.
+// ``what``: which part of the row a piece may own.  The classic split gives the tail to split 0;
+// a work list names page pieces and tail pieces separately.
+constexpr int kSplitZeroOwnsTail = 0, kPagesOnly = 1, kTailOnly = 2;
+
 __device__ __forceinline__ TileWork resolve_work(const DecodeParams& p, int row, int kvh, int split,
-                                                 int num_splits, int64_t slot) {
+                                                 int num_splits, int64_t slot, int what = kSplitZeroOwnsTail) {
   TileWork w;
   w.row = row; w.kvh = kvh; w.split = split; w.slot = slot;
   int fp4 = p.seqused_fp4[row];
@@ -61,9 +65,11 @@ __device__ __forceinline__ TileWork resolve_work(const DecodeParams& p, int row,
   const int per = (n + num_splits - 1) / num_splits;
   w.first_page = min(split * per, n);
   w.last_page = min((split + 1) * per, n);
+  if (what == kTailOnly) w.first_page = w.last_page = 0;
   w.tail_len = 0;
   w.tail_id = -1;
-  if (split == 0 && p.tail_key != nullptr && p.seqused_tail != nullptr) {
+  if ((what == kTailOnly || (what == kSplitZeroOwnsTail && split == 0)) && p.tail_key != nullptr &&
+      p.seqused_tail != nullptr) {
     int len = p.seqused_tail[row];
     if (len > 0) {
       if (len > kPage) { set_status(p.status, NVFP4_STATUS_BAD_LENGTH); len = kPage; }
@@ -243,6 +249,7 @@ __device__ __forceinline__ void tail_pv_walk(const uint16_t* vbase, int64_t vstr
                              __uint_as_float(v[j].y << 16), __uint_as_float(v[j].y & 0xffff0000u)};
 #pragma unroll
         for (int q = 0; q < kChunk; ++q) {
+          if (q0 + q >= G) continue;   // a group size that is no multiple of the chunk
           const float pw = pf[(q0 + q) * kHeadDim + t];
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[q][i] = fmaf(pw, vf[i], acc[q][i]);
@@ -260,7 +267,7 @@ __device__ __forceinline__ void tail_pv_walk(const uint16_t* vbase, int64_t vstr
       float r = up1 ? k1 : k0;
       const float s = up1 ? k0 : k1;
       r += __shfl_xor_sync(0xffffffffu, s, 1);
-      o[q0 + q] = r;
+      if (q0 + q < G) o[q0 + q] = r;
     }
   }
 }

@@ -202,7 +202,11 @@ cudaError_t launch_decode_generic(const DecodeParams& p, cudaStream_t stream) {
   switch (p.heads_q / p.heads_kv) {
     case 1: return launch_g<1>(p, stream);
     case 2: return launch_g<2>(p, stream);
+    case 3: return launch_g<3>(p, stream);
     case 4: return launch_g<4>(p, stream);
+    case 5: return launch_g<5>(p, stream);
+    case 6: return launch_g<6>(p, stream);
+    case 7: return launch_g<7>(p, stream);
     case 8: return launch_g<8>(p, stream);
     case 16: return launch_g<16>(p, stream);
     case 32: return launch_g<32>(p, stream);

@@ -30,7 +30,7 @@
 // and is what a launch that fills the GPU twice over runs on: there the page stream is bound by
 // HBM.  A launch with at most one CTA per SM is bound by a CTA's own page period instead - the
 // chain scores -> maximum -> exp2 -> quantise -> hand-over through the four score warps - so the
-// wide form (kGroups = 2, 512 threads, one CTA per SM, deeper rings, 128 registers per thread)
+// wide form (kGroups = 2, 640 threads, one CTA per SM, deeper rings, 128 registers per thread)
 // has a second pair of issuing threads and a second group of four score warps (measured: with an
 // SM to itself a CTA's period was the 1800 cycles per pair of pages that ONE thread needs to issue
 // the waits, scale copies, products and commits of V^T . P^T): the hand-overs alternate between
@@ -283,6 +283,192 @@ __device__ __forceinline__ void exchange_tile(const DecodeParams& p, const TileW
   }
 }
 
+// ---- a work-list piece that holds nothing but a row's BF16 tail ----
+// The balanced split lists a row's tail as a piece of its own.  Its CTA needs none of the page
+// machinery (no ring, no tensor memory): every K and V row of the tail is fetched into shared
+// memory with one bulk copy each, all of them in flight at once (one round trip to memory
+// instead of the dozen a walk with loads into registers takes), and the scores, the softmax
+// and P . V run out of shared memory.  Arithmetic as in tail_scores / tail_pv: BF16 query
+// against BF16 keys, P rounded to BF16 before it meets V, the row sum over the unrounded P.
+constexpr int kTailPitch = kHeadDim + 8;   // elements; rows 272 bytes apart: 16-byte aligned, no bank conflicts
+
+template <int G>
+struct __align__(128) TailSmem {
+  __align__(16) uint16_t k[kPage][kTailPitch];
+  __align__(16) uint16_t v[kPage][kTailPitch];
+  __align__(16) float qb[G * kHeadDim];   // the query as floats
+  __align__(16) float pt[kPage * G];      // P, [position][query head]
+  __align__(16) float o2[G * kHeadDim];   // the odd positions' share of the output
+  float red[4 * G];
+  float m[G], l[G];
+  __align__(8) uint64_t bar;
+};
+
+template <int G, int kThreads>
+__device__ __noinline__ void tail_piece(const DecodeParams& p, const TileWork& w, TailSmem<G>& ts) {
+  static_assert(kThreads >= 384, "the copies, the fresh token and the query are spread over 384 threads");
+  const int tid = threadIdx.x, len = w.tail_len;
+  const int64_t tok0 = (int64_t)w.tail_id * kPage;
+  // with the step's own token given, the tail's last position comes from the source (one BF16
+  // subtract of the key shift, as the tail copy does it) and is stored for the steps to come
+  const bool has_fresh = p.append_key != nullptr;
+  const int copied = has_fresh ? len - 1 : len;
+  if (tid == 0) {
+    mbar_init(&ts.bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (copied > 0) mbar_expect_tx(&ts.bar, (uint32_t)copied * 2u * kHeadDim * 2u);
+    else mbar_arrive(&ts.bar);
+  }
+  __syncthreads();
+  if (tid < 2 * kPage) {
+    const int t = tid & (kPage - 1);
+    const bool is_v = tid >= kPage;
+    if (t < copied) {
+      const uint16_t* src = (is_v ? p.tail_value : p.tail_key) + ((tok0 + t) * p.heads_kv + w.kvh) * kHeadDim;
+      bulk_load(smem_u32(is_v ? &ts.v[t][0] : &ts.k[t][0]), src, kHeadDim * 2, &ts.bar);
+    }
+  } else if (tid < 2 * kPage + 32) {
+    if (has_fresh) {
+      const int c = tid & 15;
+      if (tid < 2 * kPage + 16) {
+        uint4 k = __ldg(reinterpret_cast<const uint4*>(p.append_key + (int64_t)w.row * p.append_key_stride +
+                                                       (int64_t)w.kvh * kHeadDim) + c);
+        if (p.key_shift) {
+          float x[8], y[8];
+          unpack_bf16x8(k, x);
+          unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(p.key_shift + (int64_t)w.kvh * kHeadDim) + c), y);
+          uint32_t pk[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat16 a = __float2bfloat16_rn(x[2 * i] - y[2 * i]);
+            const __nv_bfloat16 b = __float2bfloat16_rn(x[2 * i + 1] - y[2 * i + 1]);
+            pk[i] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+          }
+          k = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+        reinterpret_cast<uint4*>(const_cast<uint16_t*>(p.tail_key) +
+                                 ((tok0 + len - 1) * p.heads_kv + w.kvh) * kHeadDim)[c] = k;
+        reinterpret_cast<uint4*>(&ts.k[len - 1][0])[c] = k;
+      } else {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.append_value + (int64_t)w.row * p.append_value_stride +
+                                                             (int64_t)w.kvh * kHeadDim) + c);
+        reinterpret_cast<uint4*>(const_cast<uint16_t*>(p.tail_value) +
+                                 ((tok0 + len - 1) * p.heads_kv + w.kvh) * kHeadDim)[c] = v;
+        reinterpret_cast<uint4*>(&ts.v[len - 1][0])[c] = v;
+      }
+    }
+  } else {
+    for (int it = tid - (2 * kPage + 32); it < G * 16; it += kThreads - (2 * kPage + 32)) {
+      const int q = it >> 4, c = it & 15;
+      float f[8];
+      if (p.q_bf16) {
+        unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(p.q_bf16 + (int64_t)w.row * p.q_row_stride +
+                                                           (int64_t)(w.kvh * G + q) * p.q_head_stride + c * 8)), f);
+      } else {
+        // no BF16 query supplied: the tail meets the dequantised NVFP4 query
+        const uint32_t pk = *reinterpret_cast<const uint32_t*>(
+            p.q_fp4 + ((int64_t)w.row * p.heads_q + w.kvh * G + q) * 64 + c * 4);
+        const float sc = e4m3_to_f32(p.q_sf[(int64_t)w.row * p.heads_q * kSfBlockBytes +
+                                            (int64_t)w.kvh * kSfBlockBytes + sf_offset(q, c >> 1)]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = e2m1_to_f32((pk >> (4 * i)) & 15u) * sc;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ts.qb[q * kHeadDim + c * 8 + i] = f[i];
+    }
+  }
+  // bounded wait for the copies; a CTA whose wait expired stores the empty partial
+  bool landed = mbar_try(&ts.bar, 0);
+  if (!landed) {
+    const unsigned long long t0 = global_ns();
+    uint32_t spins = 0;
+    while (!(landed = mbar_try(&ts.bar, 0)))
+      if ((++spins & 1023u) == 0 && global_ns() - t0 > kWaitLimitNs) break;
+  }
+  landed = __syncthreads_and(landed) != 0;   // also: query and fresh rows visible
+  if (!landed) {
+    if (tid == 0) set_status(p.status, NVFP4_STATUS_WAIT_TIMEOUT);
+    if (tid < kHeadDim) {
+#pragma unroll
+      for (int q = 0; q < G; ++q) {
+        const int64_t idx = w.slot * p.heads_q + w.kvh * G + q;
+        p.o_partial[idx * kHeadDim + tid] = 0.f;
+        if (tid == 0) p.lse_partial[idx] = -INFINITY;
+      }
+    }
+    return;
+  }
+  if (tid < kPage) {   // thread = position
+    float z[G];
+#pragma unroll
+    for (int q = 0; q < G; ++q) z[q] = -INFINITY;
+    if (tid < len) {
+      float acc[G];
+#pragma unroll
+      for (int q = 0; q < G; ++q) acc[q] = 0.f;
+#pragma unroll 4
+      for (int c = 0; c < 16; ++c) {
+        float kf[8];
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(&ts.k[tid][c * 8]), kf);
+#pragma unroll
+        for (int q = 0; q < G; ++q) {
+          const float4 qa = *reinterpret_cast<const float4*>(ts.qb + q * kHeadDim + c * 8);
+          const float4 qc = *reinterpret_cast<const float4*>(ts.qb + q * kHeadDim + c * 8 + 4);
+          acc[q] = fmaf(kf[0], qa.x, acc[q]); acc[q] = fmaf(kf[1], qa.y, acc[q]);
+          acc[q] = fmaf(kf[2], qa.z, acc[q]); acc[q] = fmaf(kf[3], qa.w, acc[q]);
+          acc[q] = fmaf(kf[4], qc.x, acc[q]); acc[q] = fmaf(kf[5], qc.y, acc[q]);
+          acc[q] = fmaf(kf[6], qc.z, acc[q]); acc[q] = fmaf(kf[7], qc.w, acc[q]);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < G; ++q) z[q] = acc[q] * p.scale_log2;
+    }
+    float m[G], l[G];
+#pragma unroll
+    for (int q = 0; q < G; ++q) m[q] = z[q];
+    block_max_128<G>(m, ts.red, tid, 1);
+#pragma unroll
+    for (int q = 0; q < G; ++q) {
+      const float pe = exp2_rel(z[q], m[q]);
+      l[q] = pe;
+      ts.pt[tid * G + q] = __bfloat162float(__float2bfloat16_rn(pe));   // P of the tail meets V as BF16
+    }
+    block_sum_128<G>(l, ts.red, tid, 1);
+    if (tid == 0) {
+#pragma unroll
+      for (int q = 0; q < G; ++q) { ts.m[q] = m[q]; ts.l[q] = l[q]; }
+    }
+  }
+  __syncthreads();
+  // P . V: thread (half, channel) takes every other position; the halves are joined below
+  const int half = tid >> 7, d = tid & (kHeadDim - 1);
+  float o[G];
+#pragma unroll
+  for (int q = 0; q < G; ++q) o[q] = 0.f;
+  if (half < 2) {
+    for (int t = half; t < len; t += 2) {
+      const float vf = __uint_as_float((uint32_t)ts.v[t][d] << 16);
+#pragma unroll
+      for (int q = 0; q < G; ++q) o[q] = fmaf(ts.pt[t * G + q], vf, o[q]);
+    }
+    if (half == 1) {
+#pragma unroll
+      for (int q = 0; q < G; ++q) ts.o2[q * kHeadDim + d] = o[q];
+    }
+  }
+  __syncthreads();
+  if (half == 0) {
+#pragma unroll
+    for (int q = 0; q < G; ++q) {
+      const float lq = ts.l[q];
+      const float val = lq > 0.f ? __fdiv_rn(o[q] + ts.o2[q * kHeadDim + d], lq) : 0.f;
+      const int64_t idx = w.slot * p.heads_q + w.kvh * G + q;
+      p.o_partial[idx * kHeadDim + d] = val;
+      if (d == 0) p.lse_partial[idx] = lq > 0.f ? (ts.m[q] + log2f(lq)) * kLn2 : -INFINITY;
+    }
+  }
+}
+
 // narrow: 12 warps; wide: plus a second group of four score warps (12-15), a second pair of
 // issuers (16, 17) and a second pair of producers (18, 19)
 template <int kGroups> struct ThreadsOf { static constexpr int value = 384 + 256 * (kGroups - 1); };
@@ -290,7 +476,7 @@ template <int kGroups> struct ThreadsOf { static constexpr int value = 384 + 256
 template <int G, int kGroups>
 __global__ void __launch_bounds__(ThreadsOf<kGroups>::value, kGroups == 1 ? 2 : 1)
 decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                    const DecodeParams p) {
+                    const __grid_constant__ DecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   Smem<G, kGroups>& sm =
       *reinterpret_cast<Smem<G, kGroups>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -311,8 +497,10 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     if (entry.x < 0) return;   // past the end of the list
     row_of_block = entry.x;
   }
+  // a work-list entry is either some of a row's pages (entry.w = 0) or the row's tail alone (1)
   auto resolve = [&]() {
-    return p.work_list ? resolve_work(p, entry.x, blockIdx.x, entry.y, entry.z, (int64_t)blockIdx.y)
+    return p.work_list ? resolve_work(p, entry.x, blockIdx.x, entry.y, entry.z, (int64_t)blockIdx.y,
+                                      entry.w ? kTailOnly : kPagesOnly)
                        : resolve_grid_work(p);
   };
   // A split of a short row often owns no page at all (the split count follows the longest row of
@@ -330,6 +518,14 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
         }
       }
       return;
+    }
+    // (the narrow form with 16 or 32 query heads per KV head - only the cross-GPU exchange runs
+    // it, never a work list - has no room for the staging; there the general path below serves)
+    if constexpr (sizeof(TailSmem<G>) <= sizeof(Smem<G, kGroups>)) {
+      if (p.work_list && entry.w) {
+        tail_piece<G, kThreads>(p, w0, *reinterpret_cast<TailSmem<G>*>(&sm));
+        return;
+      }
     }
   }
 
@@ -991,7 +1187,7 @@ static cudaError_t launch_form(const DecodeParams& p, const CUtensorMap& km, con
 bool decode_sm100_supports(const DecodeParams& p) {
   if (p.heads_kv < 1 || p.heads_q % p.heads_kv) return false;
   const int g = p.heads_q / p.heads_kv;
-  return g == 1 || g == 2 || g == 4 || g == 8 || g == 16 || g == 32;
+  return (g >= 1 && g <= 8) || g == 16 || g == 32;
 }
 
 cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream) {
@@ -1006,7 +1202,11 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream) {
   switch (p.heads_q / p.heads_kv) {
     case 1: return sm100::launch_form<1>(p, km, vm, stream);
     case 2: return sm100::launch_form<2>(p, km, vm, stream);
+    case 3: return sm100::launch_form<3>(p, km, vm, stream);
     case 4: return sm100::launch_form<4>(p, km, vm, stream);
+    case 5: return sm100::launch_form<5>(p, km, vm, stream);
+    case 6: return sm100::launch_form<6>(p, km, vm, stream);
+    case 7: return sm100::launch_form<7>(p, km, vm, stream);
     case 8: return sm100::launch_form<8>(p, km, vm, stream);
     case 16: return sm100::launch_form<16>(p, km, vm, stream);
     case 32: return sm100::launch_form<32>(p, km, vm, stream);

@@ -140,11 +140,14 @@ cudaError_t launch_work_table(const int32_t* query_start_loc, const int32_t* seq
                               int32_t* destination_pages, int num_reqs, int columns_per_row,
                               cudaStream_t stream);
 
-// Balanced split: a split count per row (ceil(pages / target_pages), at least 1).
-// work [capacity] entries, row_offset / row_count [rows]: first partial slot and split count of a row.
-cudaError_t launch_balanced_worklist(const int32_t* seqused_fp4, int rows, int max_pages, int target_pages,
-                                     int4* work, int capacity, int32_t* row_offset, int32_t* row_count,
-                                     uint32_t* status, cudaStream_t stream);
+// Balanced split: row r gets ceil(pages / target_pages) pieces of pages plus, when seqused_tail
+// (nullable) says it holds a BF16 tail, one piece for the tail alone; at least one piece.
+// work [capacity] entries (row, piece, page pieces of the row, 1 for the tail piece), row_offset /
+// row_count [rows]: first partial slot and piece count of a row.
+cudaError_t launch_balanced_worklist(const int32_t* seqused_fp4, const int32_t* seqused_tail, int rows,
+                                     int max_pages, int target_pages, int4* work, int capacity,
+                                     int32_t* row_offset, int32_t* row_count, uint32_t* status,
+                                     cudaStream_t stream);
 cudaError_t launch_lse_merge_ranges(const float* o_parts, const float* lse_parts, const int32_t* row_offset,
                                     const int32_t* row_count, int rows, int heads_q, void* out,
                                     cudaStream_t stream);

@@ -298,8 +298,11 @@ def decode_fp4(
     if heads_kv < 1 or heads_q % heads_kv:
         raise ValueError("heads_q must be divisible by heads_kv")
     group = heads_q // heads_kv
-    if PAGE_SIZE % group:
-        raise ValueError("128 must be divisible by the query-heads-per-KV-head ratio")
+    # (the reference takes only ratios that divide 128, _decode.py:617-622: its MMA packs
+    # tokens x heads into 128 rows.  Here the heads are the N side of the product, so every ratio
+    # up to 8 fits the N = 8 tile; 16 and 32 have tiles of their own.)
+    if not (1 <= group <= 8 or group in (16, 32)):
+        raise ValueError("the query-heads-per-KV-head ratio must be 1 to 8, 16 or 32")
 
     want_q_sf = (32, 4, 1, 4, 2, heads_kv, rows)
     want_page_sf = (page_count, 32, 4, 1, 4, 2, heads_kv)
@@ -350,12 +353,10 @@ def decode_fp4(
             "residual_page_ids, and seqused_residual must be provided together"
         )
     if has_residual:
-        if not fused_query:
-            if query_padded_bf16 is None:
-                raise ValueError(
-                    "pre-quantized query with a BF16 residual requires "
-                    "query_padded_bf16 support; use the BF16 query path"
-                )
+        # A pre-quantised query may come without its BF16 copy (the reference refuses that,
+        # _decode.py:703-707): the tail then meets the dequantised NVFP4 query, whose values
+        # (E2M1 x E4M3: six significant bits) are exact in BF16.
+        if not fused_query and query_padded_bf16 is not None:
             _need_cuda(query_padded_bf16, "query_padded_bf16", device)
             want_padded = (rows, PAGE_SIZE, heads_q, HEAD_DIM)
             if (

@@ -271,17 +271,18 @@ def fp4_decode_impl(
                 seqused_residual)
     complete = all(item is not None for item in residual)
     absent = all(item is None for item in residual) and has_bf16 is None
-    splittable = absent or (complete and bf16_query)
+    # (the reference splits a residual only on the BF16 query path, _decode.py:982-1016; here a
+    # pre-quantised query splits too - its tail meets the dequantised query in whichever piece owns it)
+    splittable = absent or complete
     if balance_pages is not None and not splittable:
         raise ValueError(
-            "balance_pages needs either no residual argument at all or a complete residual on the "
-            "BF16 query path, like num_splits > 1"
+            "balance_pages needs either no residual argument at all or a complete residual, "
+            "like num_splits > 1"
         )
     if num_splits > 1 and not splittable:
         raise ValueError(
             "num_splits > 1 needs either no residual argument at all or a "
-            "complete residual on the BF16 query path; this combination "
-            "runs on the single-tile path only"
+            "complete residual; this combination runs on the single-tile path only"
         )
     if num_splits > 1 and out_indices is not None:
         raise ValueError(

@@ -147,7 +147,7 @@ class LayerRuntime:
         """Bytes of scratch a step of this shape needs when cut into pieces of ``piece`` pages:
         the arithmetic of ``nvfp4_decode_balanced_workspace_bytes`` (partial outputs and LSEs of
         every possible piece, the list of pieces, two ints per row; each part rounded up to 16)."""
-        capacity = rows + rows * columns // piece
+        capacity = 2 * rows + rows * columns // piece
         up16 = lambda n: (n + 15) & ~15   # noqa: E731
         return (up16(capacity * heads_q * 128 * 4) + up16(capacity * heads_q * 4) + up16(capacity * 16)
                 + 2 * up16(rows * 4))

@@ -559,17 +559,32 @@ def split_page_range(n_pages: int, split: int, num_splits: int):
 
 
 def balanced_split_counts(seqused_fp4, target_pages: int):
-    """Split count per row of the balanced split (an extension of this build, no counterpart in the
-    reference, whose ``num_splits`` is one number per batch): ``ceil(pages / target_pages)``, one
-    for a row without FP4 pages (its tail still needs a piece).  Piece ``s`` of a row with count
-    ``c`` owns ``split_page_range(pages, s, c)``; piece 0 owns the tail."""
+    """Page pieces per row of the balanced split (an extension of this build, no counterpart in
+    the reference, whose ``num_splits`` is one number per batch): ``ceil(pages / target_pages)``.
+    Piece ``s`` of a row with count ``c`` owns ``split_page_range(pages, s, c)`` and never the
+    tail: a row that holds a BF16 tail gets one more piece for the tail alone
+    (:func:`balanced_pieces`).  A row with neither pages nor a tail keeps one empty piece."""
     pages = np.asarray(seqused_fp4, dtype=np.int64) // PAGE
-    return np.maximum(1, -(-pages // int(target_pages))).astype(np.int64)
+    return (-(-pages // int(target_pages))).astype(np.int64)
+
+
+def balanced_pieces(seqused_fp4, seqused_tail, target_pages: int):
+    """Per row the pieces of the balanced split as ``[(first_page, last_page, owns_tail), ...]``:
+    the tail piece (no pages) when the row holds a tail, then the page pieces."""
+    counts = balanced_split_counts(seqused_fp4, target_pages)
+    out = []
+    for r, count in enumerate(counts):
+        pages = int(seqused_fp4[r]) // PAGE
+        tail = seqused_tail is not None and int(seqused_tail[r]) > 0
+        row = [(0, 0, True)] if tail else []
+        row += [split_page_range(pages, s, int(count)) + (False,) for s in range(int(count))]
+        out.append(row or [(0, 0, False)])
+    return out
 
 
 def balanced_capacity(rows: int, max_pages: int, target_pages: int) -> int:
-    """Upper bound on the number of pieces: every row at ``max_pages`` pages."""
-    return rows + rows * max_pages // target_pages
+    """Upper bound on the number of pieces: every row at ``max_pages`` pages, with a tail."""
+    return 2 * rows + rows * max_pages // target_pages
 
 
 # --------------------------------------------------------------------------

@@ -90,10 +90,12 @@ class Problem:
         args.update(kw)
         return _decode.decode_fp4(**args)
 
-    def oracle_from_bytes(self, rows=None, splits: int = 1):
+    def oracle_from_bytes(self, rows=None, splits: int = 1, dequantised_tail_query: bool = False):
         """Oracle fed with the library's dequantised Q/K/V bytes.  With ``splits`` > 1 the
         oracle runs once per page range (the tail goes with range 0) and the partials are
-        merged by LSE weight, which is what the split path computes."""
+        merged by LSE weight, which is what the split path computes.
+        ``dequantised_tail_query``: the tail meets the dequantised NVFP4 query instead of the
+        BF16 one (a pre-quantised query passed without its BF16 copy)."""
         from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _quantize
 
         q_fp4, q_sf = _quantize.quantize_query(self.q, heads_kv=self.heads_kv)
@@ -109,7 +111,8 @@ class Problem:
             tail_key=c["k_pages"], tail_value=c["v_pages"], tail_ids=c["residual_page_ids"][sel],
             seqused_residual=c["seqused_residual"][sel], softmax_scale=c["softmax_scale"],
         )
-        args = (c["q"][sel], q_dq[sel], k_dq, v_dq, c["page_table"][sel], c["seqused_fp4"][sel])
+        args = (q_dq[sel] if dequantised_tail_query else c["q"][sel], q_dq[sel], k_dq, v_dq,
+                c["page_table"][sel], c["seqused_fp4"][sel])
         if splits == 1:
             return O.attention_from_dequantized(*args, **common)
         # an int means the split rule itself; a list gives (page_range function, owns_tail) pieces
@@ -122,6 +125,16 @@ class Problem:
             parts.append(o)
             lses.append(lse)
         return O.lse_merge(np.stack(parts), np.stack(lses))
+
+
+def oracle_balanced(prob: "Problem", row: int, target_pages: int):
+    """The oracle over the pieces the balanced split cuts ``row`` into: the tail alone (when the
+    row holds one), then ceil(pages / target_pages) page ranges; merged by LSE weight."""
+    c = prob.case
+    pieces = O.balanced_pieces(c["seqused_fp4"][[row]], c["seqused_residual"][[row]], target_pages)[0]
+    as_ranges = [((lambda n, first=first, last=last: (first, last)), owns_tail)
+                 for first, last, owns_tail in pieces]
+    return prob.oracle_from_bytes(rows=[row], splits=as_ranges)
 
 
 def persistent_ctas(device) -> int:

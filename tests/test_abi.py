@@ -108,7 +108,7 @@ def test_argument_errors_are_reported_without_a_device():
     with pytest.raises(ValueError, match="non-negative"):
         L.check(L.ERR_INVALID)
     args = L.DecodeArgs()
-    args.rows, args.heads_q, args.heads_kv = 1, 24, 8
+    args.rows, args.heads_q, args.heads_kv = 1, 72, 8   # 9 query heads per KV head: refused
     assert lib.nvfp4_decode(ctypes.byref(args), None) == L.ERR_UNSUPPORTED
     args.heads_q = 32
     args.softmax_scale = 0.0

@@ -91,6 +91,60 @@ def test_prequantised_query_equals_bf16_query(cuda_device, impl):
     assert torch.equal(a, b)
 
 
+def test_prequantised_query_with_a_tail_and_no_bf16_copy(cuda_device, impl):
+    """The reference refuses a pre-quantised query next to a BF16 residual unless the padded BF16
+    query comes along (src/nvfp4_decode_kernel/_decode.py:703-707).  Here the call is served: the
+    tail meets the dequantised NVFP4 query.  Checked against the oracle given that same query for
+    the tail, whole rows and split; and it differs from the BF16-query result (the tail saw
+    another query), within the quantisation error of the query."""
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _quantize, fp4_decode
+
+    case = inputs.attention_case(44, 4, 8, 2, (128 * 3 + 100, 127, 128 * 5 + 1, 128 * 2), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    q_fp4, q_sf = _quantize.quantize_query(prob.q, heads_kv=2)
+    tail = dict(residual_key_pages_bf16=prob.k_pages, residual_value_pages_bf16=prob.v_pages,
+                residual_page_ids=prob.residual_page_ids, seqused_residual=prob.seqused_residual)
+    common = (prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, prob.page_table, prob.seqused_fp4)
+    for splits in (1, 2):
+        got = to_np(fp4_decode(None, *common, query_fp4=q_fp4, query_scales=q_sf, num_splits=splits, **tail))
+        want = prob.oracle_from_bytes(splits=splits, dequantised_tail_query=True)
+        assert np.abs(got - want).max() <= TOL, splits
+    with_bf16 = to_np(prob.decode())
+    assert 0 < np.abs(got - with_bf16).max() <= 0.25
+
+
+@pytest.mark.parametrize("heads", [(24, 8), (40, 8), (12, 2), (28, 4)])
+def test_group_sizes_that_do_not_divide_128(cuda_device, impl, heads):
+    """3, 5, 6 and 7 query heads per KV head (28/4 and 40/8 are shapes of published models).  The
+    reference refuses them (src/nvfp4_decode_kernel/_decode.py:617-622: its product packs tokens x
+    heads into 128 rows); here the heads are the N side of the product and any count up to 8 fits
+    the N = 8 tile.  Whole rows, the uniform split and (tensor-core kernel) the balanced split with
+    the tail's own piece, each against the oracle; the query quantised inside the launch equals
+    the query quantiser's bytes fed back in."""
+    from helpers import oracle_balanced
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _quantize, fp4_decode
+
+    hq, hkv = heads
+    _skip_if_unsupported(impl, hq, hkv)
+    lengths = (128 * 4 + 77, 128 * 2, 90, 128 * 7 + 127)
+    case = inputs.attention_case(500 + hq, len(lengths), hq, hkv, lengths, 1.0, 0.2)
+    prob = Problem(case, cuda_device)
+    whole = prob.decode()
+    assert np.abs(to_np(whole) - prob.oracle_from_bytes()).max() <= TOL
+    assert np.abs(to_np(prob.decode(num_splits=4)) - prob.oracle_from_bytes(splits=4)).max() <= TOL
+    if impl == "sm100":
+        out = to_np(prob.decode(balance_pages=2))
+        for row in range(len(lengths)):
+            assert np.abs(out[row] - oracle_balanced(prob, row, 2)[0]).max() <= TOL, row
+    q_fp4, q_sf = _quantize.quantize_query(prob.q, heads_kv=hkv)
+    padded = torch.zeros(len(lengths), 128, hq, 128, dtype=torch.bfloat16, device=cuda_device)
+    padded[:, 0] = prob.q
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode
+
+    two_launch = prob.decode_direct(query_fp4=q_fp4, query_scales=q_sf, query_padded_bf16=padded, query_bf16=None)
+    assert torch.equal(whole, two_launch)
+
+
 def test_rows_without_keys_and_padding_rows(cuda_device, impl):
     """CUDA-graph padding rows arrive with both lengths 0 and a tail id of -1; they
     must write zeros, fault nothing and leave live rows bit-identical."""
@@ -265,7 +319,7 @@ def test_refusals(cuda_device):
     out = torch.zeros(2, 16, 128, dtype=torch.bfloat16, device=cuda_device)
     with pytest.raises(ValueError, match="cannot be combined with out_indices"):
         fp4_decode(prob.q, *common, out=out, out_indices=idx, num_splits=2)
-    with pytest.raises(ValueError, match="complete residual on the BF16 query"):
+    with pytest.raises(ValueError, match="complete residual"):
         fp4_decode(prob.q, *common, residual_key_pages_bf16=prob.k_pages, num_splits=2)
     with pytest.raises(ValueError, match="must be provided together"):
         fp4_decode(prob.q, *common, residual_key_pages_bf16=prob.k_pages)
@@ -458,12 +512,14 @@ def test_fused_tail_append_equals_append_then_decode(cuda_device, impl, with_shi
                 tail_k.data_ptr(), tail_v.data_ptr(), tail_k.stride(0), starts.data_ptr(), seq_lens.data_ptr(),
                 common["seqused_fp4"].data_ptr(), common["residual_page_ids"].data_ptr(), rows, rows, heads_kv,
                 torch.cuda.current_stream().cuda_stream))
-        out = fp4_decode(prob.q, prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, num_splits=splits,
+        out = fp4_decode(prob.q, prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, **mode,
                          residual_key_pages_bf16=tail_k, residual_value_pages_bf16=tail_v, **common, **extra)
         torch.cuda.synchronize()
         return out, tail_k, tail_v
 
-    for splits in (1, 2):      # with splits, the split that owns the residual appends
+    # with splits, the split that owns the residual appends; with the balanced split, the tail's own piece
+    modes = [dict(num_splits=1), dict(num_splits=2)] + ([dict(balance_pages=2)] if impl == "sm100" else [])
+    for mode in modes:
         want, want_k, want_v = run(False)
         got, got_k, got_v = run(True)
         assert torch.equal(got_k, want_k) and torch.equal(got_v, want_v)
@@ -500,22 +556,44 @@ def test_wide_groups_run_on_the_tensor_core_kernel(cuda_device, heads):
 
 @pytest.mark.parametrize("target", [1, 3, 8])
 def test_balanced_split_gives_every_row_its_own_split_count(cuda_device, target):
-    """Row r is cut into ceil(pages_r / target) ranges: checked row by row against the oracle
-    run with that row's count, and against the library's own uniform split of that row."""
+    """Row r is cut into ceil(pages_r / target) page ranges plus a piece for its tail alone: checked
+    row by row against the oracle run over exactly those pieces."""
+    from helpers import oracle_balanced
+
     _set_impl("auto")
-    lengths = (1024 + 17, 128 * 5, 60, 128 * 13, 128)
+    lengths = (1024 + 17, 128 * 5, 60, 128 * 13, 128, 128 * 2 + 127, 1)
     case = inputs.attention_case(61, len(lengths), 8, 2, lengths, 1.0, 0.0)
     prob = Problem(case, cuda_device)
     out = to_np(prob.decode(balance_pages=target))
-    for row, length in enumerate(lengths):
-        pages = length // 128
-        count = max(1, -(-pages // target))
-        want = prob.oracle_from_bytes(rows=[row], splits=count)
-        assert np.abs(out[row] - want[0]).max() <= TOL, (row, count)
-    # a uniform batch cut into a power-of-two count: the very bytes of num_splits = that count
-    even = inputs.attention_case(62, 3, 8, 2, (128 * 8 + 5, 128 * 8, 128 * 8 + 127), 1.0, 0.0)
+    for row in range(len(lengths)):
+        want = oracle_balanced(prob, row, target)
+        assert np.abs(out[row] - want[0]).max() <= TOL, (row, target)
+    # rows without a tail, cut into a power-of-two count: the very bytes of num_splits = that count
+    even = inputs.attention_case(62, 3, 8, 2, (128 * 8, 128 * 8, 128 * 8), 1.0, 0.0)
+    even["seqused_fp4"] = np.full(3, 128 * 8, dtype=np.int32)      # all eight pages quantised,
+    even["seqused_residual"] = np.zeros(3, dtype=np.int32)         # nothing left in the tail
     prob = Problem(even, cuda_device)
     assert torch.equal(prob.decode(balance_pages=2), prob.decode(num_splits=4))
+
+
+@pytest.mark.parametrize("heads", [(8, 8), (8, 4), (8, 2), (32, 8), (8, 1), (32, 2), (32, 1)])
+def test_tail_piece_of_the_balanced_split(cuda_device, heads):
+    """The tail's own piece (keys and values staged in shared memory by bulk copies) for every
+    group size, tail lengths 1..127 and 128, rows with and without pages, with the step's token
+    appended inside the launch: equal to appending first and then decoding, and inside the
+    parity bound of the oracle over the same pieces."""
+    from helpers import oracle_balanced
+
+    _set_impl("auto")
+    hq, hkv = heads
+    lengths = (128 * 3 + 1, 127, 128 * 2 + 64, 128 * 6, 128 + 127, 33, 128 * 4 + 2)
+    case = inputs.attention_case(640 + hq + hkv, len(lengths), hq, hkv, lengths, 1.0, 0.3)
+    prob = Problem(case, cuda_device)
+    out = to_np(prob.decode(balance_pages=2))
+    assert np.isfinite(out).all()
+    for row in range(len(lengths)):
+        want = oracle_balanced(prob, row, 2)
+        assert np.abs(out[row] - want[0]).max() <= TOL, (row, heads)
 
 
 def test_balanced_split_workspace_graph_replay_and_refusals(cuda_device):
@@ -529,15 +607,17 @@ def test_balanced_split_workspace_graph_replay_and_refusals(cuda_device):
     columns = prob.page_table.shape[1]
     need = balanced_workspace_bytes(3, 8, columns, 4)
     capacity = _lib.load().nvfp4_decode_balanced_capacity(3, columns, 4)
-    assert capacity == 3 + 3 * columns // 4
+    assert capacity == 2 * 3 + 3 * columns // 4
     assert need >= capacity * 8 * 129 * 4 + capacity * 16 + 2 * 3 * 4
     # garbage in the workspace must not matter: every slot the merge reads is written by the call
     space = torch.randint(0, 256, (need,), dtype=torch.uint8, device=cuda_device)
     out = torch.empty(3, 8, 128, dtype=torch.bfloat16, device=cuda_device)
     first = prob.decode(balance_pages=4, balance_workspace=space, out=out, trusted_metadata=True).clone()
     want = to_np(first)
-    for row, length in enumerate(lengths):
-        ref = prob.oracle_from_bytes(rows=[row], splits=-(-(length // 128) // 4))
+    from helpers import oracle_balanced
+
+    for row in range(len(lengths)):
+        ref = oracle_balanced(prob, row, 4)
         assert np.abs(want[row] - ref[0]).max() <= TOL
     # another layer of the same step: other query, same lengths - the list in the workspace is reused
     other = (prob.q.float() * -0.5 + 0.25).to(torch.bfloat16)
@@ -562,8 +642,8 @@ def test_balanced_split_workspace_graph_replay_and_refusals(cuda_device):
     case2 = dict(case)
     case2["seqused_fp4"] = np.array([256, 128, 128 * 17], dtype=np.int32)
     prob.case = case2
-    for row, pages in enumerate((2, 1, 17)):
-        ref = prob.oracle_from_bytes(rows=[row], splits=-(-pages // 4))
+    for row in range(3):
+        ref = oracle_balanced(prob, row, 4)
         assert np.abs(shorter[row] - ref[0]).max() <= TOL
     with pytest.raises(ValueError, match="balance_pages"):
         prob.decode(balance_pages=4, num_splits=2)
