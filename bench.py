@@ -182,6 +182,22 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
+REPEATS = 5   # timed regions per number; the number is their median
+
+
+class StepState:
+    """Device state that a serving step advances (the lengths and the slot table): kept after
+    the warm-up and put back before every repeat, so that the repeats time the same steps."""
+
+    def __init__(self, plane, seq_lens):
+        self.tensors = [seq_lens, plane.slot_keys, plane.slot_last_seq, plane.slot_last_seen, plane.step]
+        self.saved = [t.clone() for t in self.tensors]
+
+    def restore(self):
+        for t, s in zip(self.tensors, self.saved):
+            t.copy_(s)
+
+
 def build_pools(device, rows=None, pages_per_row=None, num_pools=None, hkv=None):
     """Disjoint page pools in the vLLM block layout, filled by the library's quantisers."""
     import torch
@@ -396,7 +412,6 @@ def run_gpu(args) -> None:
             dist.barrier()
         return ms
 
-    REPEATS = 5
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -792,7 +807,7 @@ def run_ragged(args) -> None:
     import nvfp4_attn_kernel_b200._lib as L
     from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode
     from nvfp4_attn_kernel_b200.nvfp4_vllm import layout
-    from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane
+    from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane, WorkListPlan
     from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import quantize_kv_kernel as qkv
 
     if int(os.environ.get("WORLD_SIZE", "1")) != 1:
@@ -871,10 +886,15 @@ def run_ragged(args) -> None:
         balance, splits = None, 1
         how = dict(persistent_workspace=_decode.persistent_workspace(rows, HQ, HKV, device))
 
+    # with the balanced split the control step lists the pieces in its own launch
+    plan = WorkListPlan(rows, columns, balance, HQ, space) if balance else None
+    if plan:
+        how["reuse_work_list"] = True
+
     def step():
         seq_lens.add_(1)
         ctl = plane.prepare(block_table=block_table, seq_lens=seq_lens, query_start_loc=starts,
-                            num_reqs=rows, num_actual_tokens=rows)
+                            num_reqs=rows, num_actual_tokens=rows, work_list=plan)
         _decode.decode_fp4(
             query_fp4=None, query_scales=None, query_padded_bf16=None, query_bf16=q,
             key_pages_fp4=k_fp4, key_scales=k_sf, value_pages_fp4=v_fp4, value_scales=v_sf,
@@ -907,14 +927,20 @@ def run_ragged(args) -> None:
         graph.replay()
     torch.cuda.synchronize()
     reps = max(1, args.steps // per_graph)
+    state = StepState(plane, seq_lens)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(reps):
-        graph.replay()
-    end.record()
-    torch.cuda.synchronize()
+    repeat_ms = []
+    for _ in range(REPEATS):       # the same steps each time: the state is put back in between
+        state.restore()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(reps):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        repeat_ms.append(start.elapsed_time(end) / (reps * per_graph))
     clocks = sampler.stop()
-    ms_step = start.elapsed_time(end) / (reps * per_graph)
+    ms_step = _median(repeat_ms)
     errors = int(plane.error_code.item())
     # algorithmic bytes of the timed steps, from the lengths each of them saw
     first = done_before + warm * per_graph
@@ -939,9 +965,10 @@ def run_ragged(args) -> None:
         "config": {
             "workload": "ragged serving step: 32 seq, lengths log-uniform in [128, 32768] growing one token "
                         "per step, BF16 tails, block tables from a shuffled pool of 20000 pages, key shift on",
-            "step": "slot control plane + one decode launch (query quantised and K/V token appended "
+            "step": "slot control plane (which also lists the decode pieces) + one decode launch (query "
+                    "quantised and K/V token appended "
                     "inside, " + ("one persistent launch of two CTAs per SM" if args.persistent else
-                                  f"work list launch + pieces of {balance} pages per row + merge launch"
+                                  f"pieces of {balance} pages per row and one piece per tail + merge launch"
                                   if balance else
                                   f"{splits} KV splits" + (" + merge launch" if splits > 1 else ""))
                     + ") + tail flush, all timed",
@@ -953,7 +980,8 @@ def run_ragged(args) -> None:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": "measured" if peaks else "fallback",
                      "traffic": None},
-        "cpu_baseline": None, "e2e": None, "gpu_launches": reps * per_graph * (5 if balance else 4 if splits > 1 else 3),
+        "cpu_baseline": None, "e2e": None, "gpu_launches": REPEATS * reps * per_graph * (4 if balance else 4 if splits > 1 else 3),
+        "repeats": {"count": REPEATS, "ms_per_step": repeat_ms, "median": ms_step, "min": min(repeat_ms), "max": max(repeat_ms)},
         "clocks": clocks, "control_plane_error_word": errors,
     }), flush=True)
 
@@ -976,7 +1004,7 @@ def run_model_step(args, sub: bool = False):
     import nvfp4_attn_kernel_b200._lib as L
     from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode
     from nvfp4_attn_kernel_b200.nvfp4_vllm import layout
-    from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane
+    from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane, WorkListPlan
     from nvfp4_attn_kernel_b200.nvfp4_vllm.runtime import piece_pages
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -1035,13 +1063,16 @@ def run_model_step(args, sub: bool = False):
     space = torch.empty(_decode.balanced_workspace_bytes(rows, hq, columns, piece) if piece else 16,
                         dtype=torch.uint8, device=device)
 
+    # with the balanced split the control step lists the pieces in its own launch
+    plan = WorkListPlan(rows, columns, piece, hq, space) if piece and not args.persistent else None
+
     def step():
         seq_lens.add_(1)
         ctl = plane.prepare(block_table=block_table, seq_lens=seq_lens, query_start_loc=starts,
-                            num_reqs=rows, num_actual_tokens=rows)
+                            num_reqs=rows, num_actual_tokens=rows, work_list=plan)
         for layer in range(layers):
             k_fp4, k_sf, v_fp4, v_sf = views[layer]
-            how = dict(balance_pages=piece, workspace=space, reuse_work_list=layer > 0) if piece else {}
+            how = dict(balance_pages=piece, workspace=space, reuse_work_list=True) if piece else {}
             if args.wide:
                 how["wide_form"] = True
             if args.persistent:
@@ -1076,20 +1107,29 @@ def run_model_step(args, sub: bool = False):
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
+    state = StepState(plane, seq_lens)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(args.steps):
-        graph.replay()
-    end.record()
-    torch.cuda.synchronize()
-    ms = start.elapsed_time(end)
+    repeat_ms = []
+    for _ in range(REPEATS):       # the same steps each time: the state is put back in between
+        state.restore()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(args.steps):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        repeat_ms.append(ms / args.steps)
     if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
         dist.barrier()
     clocks = sampler.stop() if sampler else None
-    ms_step = ms / args.steps
+    ms_step = _median(repeat_ms)
     errors = int(plane.error_code.item())
     # algorithmic bytes of the timed steps on this GPU, from the lengths each of them saw
     first = 1 + max(3, args.warmup)
@@ -1104,7 +1144,7 @@ def run_model_step(args, sub: bool = False):
     achieved = kv / (ms_step * 1e-3) / 1e9
     line = None
     if rank == 0:
-        launches = layers * ((2 if piece else 1)) + (1 if piece else 0) + 2
+        launches = layers * ((2 if piece else 1)) + 2   # control (lists the pieces too), decode (+ merge) per layer, flush
         line = ({
             "metric": METRIC, "value": rows / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
@@ -1115,8 +1155,9 @@ def run_model_step(args, sub: bool = False):
                             "uniform in [1024, 16384] growing one token per step, BF16 tails, key shift on; tensor "
                             "parallel by KV head over 8 GPUs: 1 KV head and 4 query heads per GPU",
                 "step": "slot control plane once + per layer one decode call (query quantised and K/V token "
-                        "appended inside" + (f", rows cut into pieces of {piece} pages: work list in layer 0, "
-                                              "reused by the others, + merge launch" if piece else "")
+                        "appended inside" + (f", rows cut into pieces of {piece} pages and one piece per tail: the list is "
+                                              "built by the control step's launch and reused by every layer, "
+                                              "+ merge launch" if piece else "")
                         + ") + one tail flush over all layers, all timed",
                 "ranks": "every rank runs this shape on its own heads (no data-path collective); value is the "
                          "batch's tokens per second of attention time, ms_per_step the max over ranks",
@@ -1128,7 +1169,8 @@ def run_model_step(args, sub: bool = False):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": "measured" if peaks else "fallback",
                          "traffic": None},
-            "cpu_baseline": None, "e2e": None, "gpu_launches": args.steps * launches,
+            "cpu_baseline": None, "e2e": None, "gpu_launches": REPEATS * args.steps * launches,
+            "repeats": {"count": REPEATS, "ms_per_step": repeat_ms, "median": ms_step, "min": min(repeat_ms), "max": max(repeat_ms)},
             "clocks": clocks, "control_plane_error_word": errors,
         })
         if not sub:

@@ -342,6 +342,25 @@ int nvfp4_control_step(const int32_t* block_table, int64_t block_table_stride, i
                        int num_reqs, int num_actual_tokens, int num_slots, void* stream);
 
 /*
+ * The same step that also builds, in the same launch, the balanced split's list of pieces
+ * (nvfp4_decode_balanced) for the first decode_rows rows of the batch, from the lengths it has
+ * just computed (every live row holds a tail, so every live row gets its tail piece).  No
+ * counterpart in the reference project.  workspace / max_pages / target_pages / heads_q: exactly
+ * what the step's nvfp4_decode_balanced calls will be given (rows = decode_rows); those calls
+ * then all pass NVFP4_DECODE_REUSE_WORK_LIST.  error_code bit 64: the list did not fit its
+ * capacity (cannot happen with nvfp4_decode_balanced_capacity).
+ */
+int nvfp4_control_step_balanced(const int32_t* block_table, int64_t block_table_stride, int block_table_columns,
+                                const int32_t* seq_lens, const int32_t* query_start_loc, int32_t* slot_keys,
+                                int32_t* slot_last_seq, int64_t* slot_last_seen, int64_t* step,
+                                int32_t* row_to_slot, int32_t* token_to_slot, int32_t* seqused_fp4,
+                                int32_t* seqused_residual, int32_t* promotion_source_tokens,
+                                int32_t* promotion_pages, int32_t* error_code, int num_reqs,
+                                int num_actual_tokens, int num_slots, int decode_rows, int max_pages,
+                                int target_pages, int heads_q, void* workspace, size_t workspace_bytes,
+                                void* stream);
+
+/*
  * Page work table of a step: for row r and page column c < columns_per_row,
  * source_tokens[r*columns+c] = query_start_loc[r] + 128*c and destination_pages[...] =
  * block_table[r][c] if the row is a fresh prefill (more than one query token, owns a slot) and

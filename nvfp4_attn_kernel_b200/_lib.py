@@ -37,6 +37,7 @@ EXPORTS = (
     "nvfp4_lse_merge_ptrs",
     "nvfp4_peer_merge",
     "nvfp4_control_step",
+    "nvfp4_control_step_balanced",
     "nvfp4_work_table",
     "nvfp4_write_kv",
     "nvfp4_key_sum_accumulate",
@@ -186,6 +187,9 @@ class ExchangeArgs(ctypes.Structure):
 def _declare_control(lib) -> None:
     lib.nvfp4_control_step.restype = c_int
     lib.nvfp4_control_step.argtypes = [c_void_p, c_int64, c_int] + [c_void_p] * 13 + [c_int, c_int, c_int, c_void_p]
+    lib.nvfp4_control_step_balanced.restype = c_int
+    lib.nvfp4_control_step_balanced.argtypes = ([c_void_p, c_int64, c_int] + [c_void_p] * 13 + [c_int] * 7
+                                                + [c_void_p, c_size_t, c_void_p])
     lib.nvfp4_decode_exchange.restype = c_int
     lib.nvfp4_decode_exchange.argtypes = [ctypes.POINTER(DecodeArgs), ctypes.POINTER(ExchangeArgs), c_void_p]
     lib.nvfp4_push_merge.restype = c_int

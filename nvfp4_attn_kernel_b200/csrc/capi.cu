@@ -578,12 +578,15 @@ int nvfp4_lse_merge_ptrs(const float* const* o_part_ptrs, const float* const* ls
   return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "lse_merge_ptrs launch");
 }
 
-int nvfp4_control_step(const int32_t* block_table, int64_t block_table_stride, int block_table_columns,
-                       const int32_t* seq_lens, const int32_t* query_start_loc, int32_t* slot_keys,
-                       int32_t* slot_last_seq, int64_t* slot_last_seen, int64_t* step, int32_t* row_to_slot,
-                       int32_t* token_to_slot, int32_t* seqused_fp4, int32_t* seqused_residual,
-                       int32_t* promotion_source_tokens, int32_t* promotion_pages, int32_t* error_code,
-                       int num_reqs, int num_actual_tokens, int num_slots, void* stream) {
+namespace {
+int control_call(const int32_t* block_table, int64_t block_table_stride, int block_table_columns,
+                 const int32_t* seq_lens, const int32_t* query_start_loc, int32_t* slot_keys,
+                 int32_t* slot_last_seq, int64_t* slot_last_seen, int64_t* step, int32_t* row_to_slot,
+                 int32_t* token_to_slot, int32_t* seqused_fp4, int32_t* seqused_residual,
+                 int32_t* promotion_source_tokens, int32_t* promotion_pages, int32_t* error_code,
+                 int num_reqs, int num_actual_tokens, int num_slots, bool with_list, int decode_rows,
+                 int max_pages, int target_pages, int heads_q, void* workspace, size_t workspace_bytes,
+                 void* stream) {
   if (num_slots < 1 || num_slots > 128)
     return fail(NVFP4_ERR_INVALID, "control_step: the slot table holds 1 to 128 slots, got %d", num_slots);
   if (num_reqs < 0 || num_reqs > num_slots)
@@ -597,9 +600,58 @@ int nvfp4_control_step(const int32_t* block_table, int64_t block_table_stride, i
   nvfp4::ControlArgs a{block_table, block_table_stride, block_table_columns, seq_lens, query_start_loc,
                        slot_keys, slot_last_seq, slot_last_seen, step, row_to_slot, token_to_slot,
                        seqused_fp4, seqused_residual, promotion_source_tokens, promotion_pages, error_code,
-                       num_reqs, num_actual_tokens, num_slots};
+                       num_reqs, num_actual_tokens, num_slots, nullptr, nullptr, nullptr, 0, 0, 0, 0};
+  if (with_list) {
+    if (decode_rows < 1 || decode_rows > num_reqs || max_pages < 0 || target_pages < 1 || heads_q < 1)
+      return fail(NVFP4_ERR_INVALID,
+                  "control_step_balanced: needs 1 <= decode_rows <= num_reqs, max_pages >= 0, target_pages >= 1");
+    const int64_t capacity = nvfp4_decode_balanced_capacity(decode_rows, max_pages, target_pages);
+    if (capacity > 65535)
+      return fail(NVFP4_ERR_INVALID, "control_step_balanced: %lld pieces; raise target_pages", (long long)capacity);
+    const BalancedLayout bal = balanced_layout(decode_rows, heads_q, capacity);
+    if (!workspace || workspace_bytes < bal.total || !aligned16(workspace))
+      return fail(NVFP4_ERR_INVALID, "control_step_balanced: needs a 16-byte aligned workspace of %zu bytes, got %zu",
+                  bal.total, workspace_bytes);
+    char* base = static_cast<char*>(workspace);
+    a.work = reinterpret_cast<int4*>(base + bal.work);
+    a.work_row_offset = reinterpret_cast<int32_t*>(base + bal.row_offset);
+    a.work_row_count = reinterpret_cast<int32_t*>(base + bal.row_count);
+    a.work_rows = decode_rows;
+    a.work_capacity = (int)capacity;
+    a.work_max_pages = max_pages;
+    a.work_target_pages = target_pages;
+  }
   cudaError_t e = nvfp4::launch_control(a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "control_step launch");
+}
+}  // namespace
+
+int nvfp4_control_step(const int32_t* block_table, int64_t block_table_stride, int block_table_columns,
+                       const int32_t* seq_lens, const int32_t* query_start_loc, int32_t* slot_keys,
+                       int32_t* slot_last_seq, int64_t* slot_last_seen, int64_t* step, int32_t* row_to_slot,
+                       int32_t* token_to_slot, int32_t* seqused_fp4, int32_t* seqused_residual,
+                       int32_t* promotion_source_tokens, int32_t* promotion_pages, int32_t* error_code,
+                       int num_reqs, int num_actual_tokens, int num_slots, void* stream) {
+  return control_call(block_table, block_table_stride, block_table_columns, seq_lens, query_start_loc, slot_keys,
+                      slot_last_seq, slot_last_seen, step, row_to_slot, token_to_slot, seqused_fp4,
+                      seqused_residual, promotion_source_tokens, promotion_pages, error_code, num_reqs,
+                      num_actual_tokens, num_slots, false, 0, 0, 0, 0, nullptr, 0, stream);
+}
+
+int nvfp4_control_step_balanced(const int32_t* block_table, int64_t block_table_stride, int block_table_columns,
+                                const int32_t* seq_lens, const int32_t* query_start_loc, int32_t* slot_keys,
+                                int32_t* slot_last_seq, int64_t* slot_last_seen, int64_t* step,
+                                int32_t* row_to_slot, int32_t* token_to_slot, int32_t* seqused_fp4,
+                                int32_t* seqused_residual, int32_t* promotion_source_tokens,
+                                int32_t* promotion_pages, int32_t* error_code, int num_reqs,
+                                int num_actual_tokens, int num_slots, int decode_rows, int max_pages,
+                                int target_pages, int heads_q, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  return control_call(block_table, block_table_stride, block_table_columns, seq_lens, query_start_loc, slot_keys,
+                      slot_last_seq, slot_last_seen, step, row_to_slot, token_to_slot, seqused_fp4,
+                      seqused_residual, promotion_source_tokens, promotion_pages, error_code, num_reqs,
+                      num_actual_tokens, num_slots, true, decode_rows, max_pages, target_pages, heads_q,
+                      workspace, workspace_bytes, stream);
 }
 
 int nvfp4_work_table(const int32_t* query_start_loc, const int32_t* seqused_fp4, const int32_t* row_to_slot,

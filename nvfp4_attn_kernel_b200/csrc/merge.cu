@@ -4,6 +4,7 @@
 // split stride or behind one pointer per split (buffers of peer GPUs mapped into this
 // process are read with plain loads).
 #include "decode_common.cuh"
+#include "worklist.cuh"
 
 namespace nvfp4 {
 
@@ -292,60 +293,43 @@ namespace nvfp4 {
 // BF16 tail gets one more piece for the tail alone (entry.w = 1), which the decode kernel serves
 // with a path of its own that stages the tail in shared memory - so the tail is never walked in
 // front of a piece's page stream.  A row with neither pages nor a tail keeps one (empty) piece.
-// The pieces are listed longest first (sixteen size classes, the tail pieces after them; within
-// a class in no particular order - a row's result does not depend on where its pieces sit),
+// A row's pieces sit side by side, the tail piece first.  The rows are listed by the length of
+// their pieces, longest first (sixteen size classes; within a class in no particular order - a
+// row's result does not depend on where its pieces sit),
 // because the CTAs of the decode grid start in list order and the last ones to start should be
 // the short ones.  Entries past the end get row -1.
-constexpr int kSizeClasses = 16;
-
-__device__ __forceinline__ void balanced_row(const int32_t* seqused_fp4, const int32_t* seqused_tail, int row,
-                                             int max_pages, int target_pages, int& count, int& size_class,
-                                             int& tail) {
-  const int fp4 = seqused_fp4[row];
-  int n = fp4 >> 7;
-  if (fp4 < 0 || n > max_pages) n = fp4 < 0 ? 0 : max_pages;   // the decode kernel reports it
-  tail = seqused_tail != nullptr && seqused_tail[row] > 0 ? 1 : 0;
-  count = n > 0 ? (n + target_pages - 1) / target_pages : 1 - tail;
-  const int piece = count > 0 ? (n + count - 1) / count : 0;   // pages of the row's longest piece
-  size_class = kSizeClasses - 1 - min(kSizeClasses - 1, piece * kSizeClasses / (target_pages + 1));
-}
-
 __global__ void __launch_bounds__(1024)
 balanced_worklist_kernel(const int32_t* __restrict__ seqused_fp4, const int32_t* __restrict__ seqused_tail,
                          int rows, int max_pages, int target_pages, int4* __restrict__ work, int capacity,
                          int32_t* __restrict__ row_offset, int32_t* __restrict__ row_count,
                          uint32_t* __restrict__ status) {
-  // class kSizeClasses: the tail pieces
-  __shared__ int class_total[kSizeClasses + 1], class_cursor[kSizeClasses + 1];
+  __shared__ int class_total[kSizeClasses], class_cursor[kSizeClasses];
   __shared__ int used;
   const int tid = threadIdx.x;
-  if (tid <= kSizeClasses) class_total[tid] = 0;
+  if (tid < kSizeClasses) class_total[tid] = 0;
   __syncthreads();
   for (int row = tid; row < rows; row += 1024) {
-    int count, size_class, tail;
-    balanced_row(seqused_fp4, seqused_tail, row, max_pages, target_pages, count, size_class, tail);
+    int count, size_class;
+    const int tail = seqused_tail != nullptr && seqused_tail[row] > 0 ? 1 : 0;
+    balanced_pieces_of_row(seqused_fp4[row], tail, max_pages, target_pages, count, size_class);
     // a row's partials sit side by side: its tail piece is counted with its page pieces
     atomicAdd(&class_total[size_class], count + tail);
   }
   __syncthreads();
   if (tid == 0) {
     int at = 0;
-    for (int c = 0; c <= kSizeClasses; ++c) { class_cursor[c] = at; at += class_total[c]; }
+    for (int c = 0; c < kSizeClasses; ++c) { class_cursor[c] = at; at += class_total[c]; }
     used = at;
   }
   __syncthreads();
   for (int row = tid; row < rows; row += 1024) {
-    int count, size_class, tail;
-    balanced_row(seqused_fp4, seqused_tail, row, max_pages, target_pages, count, size_class, tail);
+    int count, size_class;
+    const int tail = seqused_tail != nullptr && seqused_tail[row] > 0 ? 1 : 0;
+    balanced_pieces_of_row(seqused_fp4[row], tail, max_pages, target_pages, count, size_class);
     const int first = atomicAdd(&class_cursor[size_class], count + tail);
     row_offset[row] = first;
     row_count[row] = count + tail;
-    for (int s = 0; s < count + tail; ++s) {
-      // the tail piece comes first within the row: it is the quickest to finish
-      const int4 entry = s < tail ? make_int4(row, 0, 1, 1) : make_int4(row, s - tail, count, 0);
-      if (first + s < capacity) work[first + s] = entry;
-      else set_status(status, NVFP4_STATUS_BAD_LENGTH);   // cannot happen with the documented capacity
-    }
+    if (!balanced_write_row(work, capacity, first, row, count, tail)) set_status(status, NVFP4_STATUS_BAD_LENGTH);
   }
   for (int w = used + tid; w < capacity; w += 1024) work[w] = make_int4(-1, 0, 0, 0);
 }

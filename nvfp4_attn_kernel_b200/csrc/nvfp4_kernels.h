@@ -131,6 +131,10 @@ struct ControlArgs {
   int32_t* row_to_slot; int32_t* token_to_slot; int32_t* seqused_fp4; int32_t* seqused_residual;
   int32_t* promotion_source_tokens; int32_t* promotion_pages; int32_t* error_code;
   int num_reqs, num_actual_tokens, num_slots;
+  // optional (work null: off): the balanced split's list of pieces for the first work_rows rows
+  // of this step, built from the lengths this launch computes (see launch_balanced_worklist)
+  int4* work; int32_t* work_row_offset; int32_t* work_row_count;
+  int work_rows, work_capacity, work_max_pages, work_target_pages;
 };
 
 cudaError_t launch_control(const ControlArgs& a, cudaStream_t stream);

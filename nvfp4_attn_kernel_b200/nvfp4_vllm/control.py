@@ -28,6 +28,7 @@ ERR_STALE_SLOT_HISTORY = 4
 ERR_NO_FREE_SLOT = 8
 ERR_DUPLICATE_KEY = 16
 ERR_PROMOTION_COLUMN = 32
+ERR_WORK_LIST_FULL = 64   # only with a work-list plan; no counterpart in the reference
 
 ERROR_NAMES = {
     ERR_CONTINUATION_PREFILL: "a prompt arrived split across steps",
@@ -36,6 +37,7 @@ ERROR_NAMES = {
     ERR_NO_FREE_SLOT: "a row needing a slot found none free",
     ERR_DUPLICATE_KEY: "two live rows share a physical block",
     ERR_PROMOTION_COLUMN: "a promotion column is past the block table",
+    ERR_WORK_LIST_FULL: "the list of decode pieces outgrew its capacity",
 }
 
 
@@ -50,6 +52,22 @@ class ControlOutputs:
     promotion_source_tokens: torch.Tensor   # full slot-table width
     promotion_pages: torch.Tensor           # full slot-table width, -1 = nothing to seal
     error_code: torch.Tensor
+
+
+@dataclass(frozen=True)
+class WorkListPlan:
+    """What the step's balanced-split decode calls will be given, so that the control step can
+    build their list of pieces in its own launch (an extension; the reference has neither the
+    balanced split nor a list): the first ``decode_rows`` rows of the batch, a page table
+    ``max_pages`` columns wide, pieces of ``target_pages`` pages, ``heads_q`` query heads and the
+    ``workspace`` (uint8, ``balanced_workspace_bytes`` long) the calls share.  The calls then pass
+    ``balance_reuse=True`` in every layer."""
+
+    decode_rows: int
+    max_pages: int
+    target_pages: int
+    heads_q: int
+    workspace: torch.Tensor
 
 
 class ControlPlaneError(RuntimeError):
@@ -116,8 +134,9 @@ class ControlPlane:
 
     def prepare(self, *, block_table: torch.Tensor, seq_lens: torch.Tensor,
                 query_start_loc: torch.Tensor, num_reqs: int,
-                num_actual_tokens: int) -> ControlOutputs:
-        """Advance the slot table by one step; ``seq_lens`` already counts this step's tokens."""
+                num_actual_tokens: int, work_list: WorkListPlan | None = None) -> ControlOutputs:
+        """Advance the slot table by one step; ``seq_lens`` already counts this step's tokens.
+        With ``work_list`` the same launch also lists the pieces of the step's decode rows."""
         if block_table.ndim != 2:
             raise ValueError(f"block_table must be 2-D, got {block_table.ndim}-D")
         if num_reqs > self.num_slots:
@@ -133,16 +152,25 @@ class ControlPlane:
                 raise ValueError(f"{name} must be INT32 on {self.device}")
         if block_table.stride(1) != 1 and block_table.shape[1] > 1:
             raise ValueError("block_table rows must be contiguous")
+        common = (
+            block_table.data_ptr(), block_table.stride(0), block_table.shape[1],
+            seq_lens.data_ptr(), query_start_loc.data_ptr(), self.slot_keys.data_ptr(),
+            self.slot_last_seq.data_ptr(), self.slot_last_seen.data_ptr(), self.step.data_ptr(),
+            self.row_to_slot.data_ptr(), self.token_to_slot.data_ptr(),
+            self.seqused_fp4.data_ptr(), self.seqused_residual.data_ptr(),
+            self.promotion_source_tokens.data_ptr(), self.promotion_pages.data_ptr(),
+            self.error_code.data_ptr(), num_reqs, num_actual_tokens, self.num_slots)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
         with torch.cuda.device(self.device):
-            _lib.check(_lib.load().nvfp4_control_step(
-                block_table.data_ptr(), block_table.stride(0), block_table.shape[1],
-                seq_lens.data_ptr(), query_start_loc.data_ptr(), self.slot_keys.data_ptr(),
-                self.slot_last_seq.data_ptr(), self.slot_last_seen.data_ptr(), self.step.data_ptr(),
-                self.row_to_slot.data_ptr(), self.token_to_slot.data_ptr(),
-                self.seqused_fp4.data_ptr(), self.seqused_residual.data_ptr(),
-                self.promotion_source_tokens.data_ptr(), self.promotion_pages.data_ptr(),
-                self.error_code.data_ptr(), num_reqs, num_actual_tokens, self.num_slots,
-                torch.cuda.current_stream(self.device).cuda_stream))
+            if work_list is None:
+                _lib.check(_lib.load().nvfp4_control_step(*common, stream))
+            else:
+                space = work_list.workspace
+                if space.dtype is not torch.uint8 or space.device != self.device or not space.is_contiguous():
+                    raise ValueError(f"the work list's workspace must be contiguous UINT8 on {self.device}")
+                _lib.check(_lib.load().nvfp4_control_step_balanced(
+                    *common, work_list.decode_rows, work_list.max_pages, work_list.target_pages,
+                    work_list.heads_q, space.data_ptr(), space.numel(), stream))
         return ControlOutputs(
             row_to_slot=self.row_to_slot[:num_reqs],
             token_to_slot=self.token_to_slot[:num_actual_tokens],

@@ -150,3 +150,69 @@ def test_error_flags(cuda_device):
                       seq_lens=torch.zeros(5, dtype=torch.int32, device=cuda_device),
                       query_start_loc=torch.zeros(6, dtype=torch.int32, device=cuda_device),
                       num_reqs=5, num_actual_tokens=0)
+
+
+def _list_regions(space, rows, heads_q, capacity):
+    """(work [capacity, 4], row_offset [rows], row_count [rows]) of a balanced-split workspace:
+    partial outputs, their LSEs, the list, the rows' first slots, the rows' piece counts, each
+    region rounded up to 16 bytes."""
+    up = lambda b: (b + 15) & ~15
+    at = up(capacity * heads_q * 128 * 4) + up(capacity * heads_q * 4)
+    work = space[at:at + capacity * 16].view(torch.int32).view(capacity, 4)
+    at += up(capacity * 16)
+    row_offset = space[at:at + rows * 4].view(torch.int32)
+    at += up(rows * 4)
+    row_count = space[at:at + rows * 4].view(torch.int32)
+    return work.cpu().numpy(), row_offset.cpu().numpy(), row_count.cpu().numpy()
+
+
+@pytest.mark.parametrize("target", [2, 5])
+def test_control_step_builds_the_decode_work_list_in_its_own_launch(cuda_device, target):
+    """The control step given a work-list plan leaves in the workspace the list the stand-alone
+    builder makes from the same lengths (row by row: the tail piece, then the page pieces; rows
+    ordered by size class), the oracle's pieces for every row, and a decode that reuses that list
+    equals the decode that builds its own, bit for bit."""
+    import inputs
+    from helpers import Problem
+    from nvfp4_attn_kernel_b200 import _lib
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel._decode import balanced_workspace_bytes
+    from nvfp4_attn_kernel_b200.nvfp4_vllm.control import ControlPlane, WorkListPlan
+
+    lengths = (128 * 9 + 3, 128 * 2 + 90, 128 * 30, 77, 128, 128 * 4 + 1)
+    rows, hq, hkv = len(lengths), 8, 2
+    case = inputs.attention_case(71, rows, hq, hkv, lengths, 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    columns = prob.page_table.shape[1]
+    plane = ControlPlane(max_num_seqs=8, max_num_batched_tokens=8192, device=cuda_device)
+    # the engine's block table: column 0 of a row keys its slot (any non-zero id)
+    table = (prob.page_table + 1).contiguous()
+    need = balanced_workspace_bytes(rows, hq, columns, target)
+    space = torch.randint(0, 256, (need,), dtype=torch.uint8, device=cuda_device)
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=cuda_device)
+    out = plane.prepare(block_table=table, seq_lens=t(list(lengths)),
+                        query_start_loc=t([0] + list(np.cumsum(lengths))), num_reqs=rows,
+                        num_actual_tokens=int(sum(lengths)),
+                        work_list=WorkListPlan(rows, columns, target, hq, space))
+    torch.cuda.synchronize()
+    assert int(out.error_code.item()) == 0
+    assert out.seqused_fp4.tolist() == case["seqused_fp4"].tolist()
+    assert out.seqused_residual.tolist() == case["seqused_residual"].tolist()
+    capacity = int(_lib.load().nvfp4_decode_balanced_capacity(rows, columns, target))
+    work, offset, count = _list_regions(space, rows, hq, capacity)
+    pieces = O.balanced_pieces(case["seqused_fp4"], case["seqused_residual"], target)
+    used = 0
+    for row in range(rows):
+        mine = work[offset[row]:offset[row] + count[row]]
+        page_pieces = [p for p in pieces[row] if not p[2]]
+        want = [[row, 0, 1, 1]] + [[row, s, len(page_pieces), 0] for s in range(len(page_pieces))]
+        assert mine.tolist() == want, row
+        used += count[row]
+    assert (work[used:, 0] == -1).all() and (work[:used, 0] >= 0).all()
+    # a decode that reuses the list = a decode that builds its own
+    slots = out.row_to_slot[:rows]
+    tails = dict(residual_page_ids=prob.residual_page_ids, seqused_residual=out.seqused_residual[:rows])
+    reused = prob.decode(balance_pages=target, balance_workspace=space, balance_reuse=True,
+                         seqused_fp4=out.seqused_fp4[:rows], trusted_metadata=True, **tails)
+    fresh = prob.decode(balance_pages=target)
+    assert slots.tolist() == list(range(rows))   # a fresh table hands out slots in row order
+    assert torch.equal(reused, fresh)
