@@ -890,6 +890,8 @@ def run_ragged(args) -> None:
     plan = WorkListPlan(rows, columns, balance, HQ, space) if balance else None
     if plan:
         how["reuse_work_list"] = True
+        if args.merge_in_launch:
+            how["merge_in_launch"] = True
 
     def step():
         seq_lens.add_(1)
@@ -980,7 +982,7 @@ def run_ragged(args) -> None:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": "measured" if peaks else "fallback",
                      "traffic": None},
-        "cpu_baseline": None, "e2e": None, "gpu_launches": REPEATS * reps * per_graph * (4 if balance else 4 if splits > 1 else 3),
+        "cpu_baseline": None, "e2e": None, "gpu_launches": REPEATS * reps * per_graph * (3 if splits <= 1 and not balance else 4),
         "repeats": {"count": REPEATS, "ms_per_step": repeat_ms, "median": ms_step, "min": min(repeat_ms), "max": max(repeat_ms)},
         "clocks": clocks, "control_plane_error_word": errors,
     }), flush=True)
@@ -1072,7 +1074,8 @@ def run_model_step(args, sub: bool = False):
                             num_reqs=rows, num_actual_tokens=rows, work_list=plan)
         for layer in range(layers):
             k_fp4, k_sf, v_fp4, v_sf = views[layer]
-            how = dict(balance_pages=piece, workspace=space, reuse_work_list=True) if piece else {}
+            how = dict(balance_pages=piece, workspace=space, reuse_work_list=True,
+                       merge_in_launch=args.merge_in_launch) if piece else {}
             if args.wide:
                 how["wide_form"] = True
             if args.persistent:
@@ -1144,7 +1147,7 @@ def run_model_step(args, sub: bool = False):
     achieved = kv / (ms_step * 1e-3) / 1e9
     line = None
     if rank == 0:
-        launches = layers * ((2 if piece else 1)) + 2   # control (lists the pieces too), decode (+ merge) per layer, flush
+        launches = layers * (2 if piece else 1) + 2   # control (lists the pieces too), decode (+ merge) per layer, flush
         line = ({
             "metric": METRIC, "value": rows / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
@@ -1362,6 +1365,9 @@ def main() -> None:
     ap.add_argument("--wide", action="store_true",
                     help="ragged / model-step workloads: cut the rows, from their host-side lengths, into at "
                          "most one piece per SM and run the decode on the kernel's wide form")
+    ap.add_argument("--merge-in-launch", action="store_true",
+                    help="ragged / model-step workloads with the balanced split: the piece of a row that finishes "
+                         "last merges the row's pieces inside the decode launch (no merge launch)")
     ap.add_argument("--persistent", action="store_true",
                     help="ragged / model-step workloads: run the decode as one persistent launch "
                          "(NVFP4_DECODE_PERSISTENT) instead of work list + pieces + merge")

@@ -285,6 +285,8 @@ int nvfp4_decode_persistent_supported(int rows, int heads_q, int heads_kv);
  * results are the same bits either way except for the row sum's association (see the kernel).
  */
 #define NVFP4_DECODE_WIDE_FORM 8u
+/* nvfp4_decode_balanced only: merge the pieces inside the decode launch (see there). */
+#define NVFP4_DECODE_MERGE_IN_LAUNCH 16u
 
 /*
  * With out != NULL the merged bf16 result is written (for num_splits > 1 the
@@ -424,16 +426,22 @@ int nvfp4_decode_exchange(const nvfp4_decode_args* args, const nvfp4_exchange_ar
  * longest row, so short rows are cut into pieces far smaller than a CTA's fixed cost is worth, or
  * the long rows into pieces too long.
  *
- * Row r is cut into ceil(pages_r / target_pages) pieces (one piece if it has no FP4 page; its tail
- * goes to the first piece, as in nvfp4_decode).  Each piece is computed exactly as split s of
- * num_splits = that count would be, and the pieces of a row are merged by their log-sum-exp, so the
- * result equals nvfp4_decode + nvfp4_lse_merge run row by row with that count.  Three launches on
- * the stream (work list, decode, merge); the list is built on the device from seqused_fp4, so the
- * call needs no host knowledge of the lengths and can be captured in a CUDA graph.
+ * Row r is cut into ceil(pages_r / target_pages) pieces of pages, and a row that holds a BF16
+ * tail gets one more piece for the tail alone (served out of shared memory, never walked in front
+ * of a piece's page stream); a row with neither keeps one empty piece.  A page piece is computed
+ * exactly as split s of num_splits = that count would be (without the tail), and the pieces of a
+ * row are merged by their log-sum-exp.  Three launches on the stream: the work list (built on
+ * the device from seqused_fp4 and seqused_tail, so the call needs no host knowledge of the lengths
+ * and can be captured in a CUDA graph), the decode, and the merge of every row's pieces.
  *
  *  - args as for nvfp4_decode with num_splits = 1, out != NULL, o_partial = lse_partial =
  *    out_indices = NULL, no NVFP4_DECODE_PROGRAMMATIC_LAUNCH; tensor-core kernel only.
- *  - args.flags may carry NVFP4_DECODE_REUSE_WORK_LIST (two launches instead of three).
+ *  - args.flags may carry NVFP4_DECODE_REUSE_WORK_LIST (no list launch: the list of an earlier
+ *    call or of nvfp4_control_step_balanced is still in the workspace) and
+ *    NVFP4_DECODE_MERGE_IN_LAUNCH (no merge launch: the piece of a (row, KV head) that finishes
+ *    last merges the row's pieces inside the decode launch - same arithmetic, same order, the
+ *    same bits whichever piece is last.  Measured slower than the merge launch on a B200: every
+ *    piece pays a device-wide fence before it counts its arrival; kept as an option).
  *  - args.workspace must hold nvfp4_decode_balanced_workspace_bytes(rows, heads_q, max_pages,
  *    target_pages) bytes (args.max_pages is the bound on a row's page count that the list's
  *    capacity, nvfp4_decode_balanced_capacity, is derived from).

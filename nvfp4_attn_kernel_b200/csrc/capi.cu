@@ -287,7 +287,7 @@ int64_t nvfp4_decode_balanced_capacity(int rows, int max_pages, int target_pages
 
 namespace {
 struct BalancedLayout {
-  size_t o_part, lse_part, work, row_offset, row_count, total;
+  size_t o_part, lse_part, work, row_offset, row_count, counters, total;
 };
 BalancedLayout balanced_layout(int rows, int heads_q, int64_t capacity) {
   BalancedLayout l;
@@ -298,6 +298,7 @@ BalancedLayout balanced_layout(int rows, int heads_q, int64_t capacity) {
   l.work = take((size_t)capacity * sizeof(int4));
   l.row_offset = take((size_t)rows * sizeof(int32_t));
   l.row_count = take((size_t)rows * sizeof(int32_t));
+  l.counters = take((size_t)rows * heads_q * sizeof(int32_t));   // arrivals per (row, KV head); heads_q bounds heads_kv
   l.total = at;
   return l;
 }
@@ -407,8 +408,10 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   p.num_splits = a->num_splits;
   p.status = a->status;
   if (a->flags & ~(NVFP4_DECODE_PROGRAMMATIC_LAUNCH | NVFP4_DECODE_REUSE_WORK_LIST | NVFP4_DECODE_PERSISTENT |
-                   NVFP4_DECODE_WIDE_FORM))
+                   NVFP4_DECODE_WIDE_FORM | NVFP4_DECODE_MERGE_IN_LAUNCH))
     return fail(NVFP4_ERR_INVALID, "decode: unknown flag bits %#x", a->flags);
+  if ((a->flags & NVFP4_DECODE_MERGE_IN_LAUNCH) && !target_pages)
+    return fail(NVFP4_ERR_INVALID, "decode: only nvfp4_decode_balanced merges pieces");
   if ((a->flags & NVFP4_DECODE_REUSE_WORK_LIST) && !target_pages)
     return fail(NVFP4_ERR_INVALID, "decode: only nvfp4_decode_balanced has a work list to reuse");
   p.pdl = (a->flags & NVFP4_DECODE_PROGRAMMATIC_LAUNCH) ? 1 : 0;
@@ -453,6 +456,11 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
     p.lse_partial = lse_part = reinterpret_cast<float*>(base + bal.lse_part);
     p.work_list = reinterpret_cast<const int4*>(base + bal.work);
     p.work_capacity = (int)capacity;
+    // on request the row's pieces are merged by the piece that arrives last instead of a merge launch
+    p.list_row_offset = reinterpret_cast<const int32_t*>(base + bal.row_offset);
+    p.list_row_count = reinterpret_cast<const int32_t*>(base + bal.row_count);
+    p.list_counters = (a->flags & NVFP4_DECODE_MERGE_IN_LAUNCH) ? reinterpret_cast<int*>(base + bal.counters) : nullptr;
+    p.out = static_cast<uint16_t*>(a->out);
   } else if (direct) {
     p.emit_partial = 0;
     p.out = static_cast<uint16_t*>(a->out);
@@ -520,7 +528,9 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
     e = (a->flags & NVFP4_DECODE_REUSE_WORK_LIST) ? cudaSuccess : nvfp4::launch_balanced_worklist(a->seqused_fp4, (a->tail_key && a->seqused_tail) ? a->seqused_tail : nullptr, a->rows, a->max_pages, target_pages,
                                         reinterpret_cast<int4*>(base + bal.work), (int)capacity,
                                         reinterpret_cast<int32_t*>(base + bal.row_offset),
-                                        reinterpret_cast<int32_t*>(base + bal.row_count), a->status, st);
+                                        reinterpret_cast<int32_t*>(base + bal.row_count),
+                                        reinterpret_cast<int32_t*>(base + bal.counters), a->rows * a->heads_q,
+                                        a->status, st);
     if (e != cudaSuccess) return cuda_fail(e, "work list launch");
   }
   if (impl == NVFP4_IMPL_SM100) {
@@ -534,13 +544,13 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
   }
   if (e != cudaSuccess) return cuda_fail(e, "decode launch");
 
-  if (target_pages) {
+  if (target_pages && !(a->flags & NVFP4_DECODE_MERGE_IN_LAUNCH)) {
     const char* base = static_cast<const char*>(a->workspace);
     e = nvfp4::launch_lse_merge_ranges(o_part, lse_part, reinterpret_cast<const int32_t*>(base + bal.row_offset),
                                        reinterpret_cast<const int32_t*>(base + bal.row_count), a->rows,
                                        a->heads_q, a->out, st);
     if (e != cudaSuccess) return cuda_fail(e, "lse_merge launch");
-  } else if (!direct && a->out) {
+  } else if (!target_pages && !direct && a->out) {
     e = nvfp4::launch_lse_merge(o_part, (int64_t)a->rows * a->heads_q * 128, lse_part,
                                 (int64_t)a->rows * a->heads_q, nullptr, nullptr, a->num_splits,
                                 a->rows, a->heads_q, a->out, 0, a->out_indices, nullptr, st);
@@ -600,7 +610,7 @@ int control_call(const int32_t* block_table, int64_t block_table_stride, int blo
   nvfp4::ControlArgs a{block_table, block_table_stride, block_table_columns, seq_lens, query_start_loc,
                        slot_keys, slot_last_seq, slot_last_seen, step, row_to_slot, token_to_slot,
                        seqused_fp4, seqused_residual, promotion_source_tokens, promotion_pages, error_code,
-                       num_reqs, num_actual_tokens, num_slots, nullptr, nullptr, nullptr, 0, 0, 0, 0};
+                       num_reqs, num_actual_tokens, num_slots, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0};
   if (with_list) {
     if (decode_rows < 1 || decode_rows > num_reqs || max_pages < 0 || target_pages < 1 || heads_q < 1)
       return fail(NVFP4_ERR_INVALID,
@@ -616,6 +626,8 @@ int control_call(const int32_t* block_table, int64_t block_table_stride, int blo
     a.work = reinterpret_cast<int4*>(base + bal.work);
     a.work_row_offset = reinterpret_cast<int32_t*>(base + bal.row_offset);
     a.work_row_count = reinterpret_cast<int32_t*>(base + bal.row_count);
+    a.work_counters = reinterpret_cast<int32_t*>(base + bal.counters);
+    a.work_counter_words = decode_rows * heads_q;
     a.work_rows = decode_rows;
     a.work_capacity = (int)capacity;
     a.work_max_pages = max_pages;

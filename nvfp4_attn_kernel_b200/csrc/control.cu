@@ -183,6 +183,7 @@ __global__ void __launch_bounds__(kMaxSlots) control_kernel(const ControlArgs a)
       if (!balanced_write_row(a.work, a.work_capacity, first, i, count, tail)) atomicOr(a.error_code, kErrWorkListFull);
     }
     for (int w = list_used + i; w < a.work_capacity; w += kMaxSlots) a.work[w] = make_int4(-1, 0, 0, 0);
+    for (int w = i; w < a.work_counter_words; w += kMaxSlots) a.work_counters[w] = 0;
   }
 
   // a token belongs to the row whose [q_begin, q_end) holds it (the rows' ranges ascend)

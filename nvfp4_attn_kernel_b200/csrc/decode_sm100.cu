@@ -283,6 +283,52 @@ __device__ __forceinline__ void exchange_tile(const DecodeParams& p, const TileW
   }
 }
 
+// In-launch merge of a row's pieces (work list only).  Called by 128 threads (thread t is
+// channel t) right after they stored their piece's partial: the piece of a (row, KV head) that
+// arrives last folds the partials of all the row's pieces into the BF16 output, with the
+// arithmetic and in the order of the merge launch (lse_merge_ranges_kernel), so the bits are
+// the same whichever piece happens to be last.  No piece waits for another.
+template <int G>
+__device__ __forceinline__ void finish_piece(const DecodeParams& p, int row, int kvh, int t) {
+  __shared__ int last_arrival;
+  __threadfence();   // this piece's partial is visible before its arrival is counted
+  asm volatile("bar.sync 6, 128;" ::: "memory");
+  const int count = __ldg(p.list_row_count + row);
+  if (t == 0) {
+    int* counter = p.list_counters + row * p.heads_kv + kvh;
+    const int seen = atomicAdd(counter, 1);
+    last_arrival = seen == count - 1;
+    if (last_arrival) *counter = 0;   // ready for the next launch that reuses the list
+  }
+  asm volatile("bar.sync 6, 128;" ::: "memory");
+  if (!last_arrival) return;
+  __threadfence();
+  const int first = __ldg(p.list_row_offset + row);
+  const int64_t orow = p.out_indices ? (int64_t)p.out_indices[row] : (int64_t)row;
+#pragma unroll 1
+  for (int q = 0; q < G; ++q) {
+    const int head = kvh * G + q;
+    float mx = -INFINITY;
+#pragma unroll 4
+    for (int s = 0; s < count; ++s) mx = fmaxf(mx, __ldcg(p.lse_partial + (int64_t)(first + s) * p.heads_q + head));
+    float acc = 0.f, tot = 0.f;
+    if (mx != -INFINITY) {
+#pragma unroll 4
+      for (int s = 0; s < count; ++s) {
+        const int64_t idx = (int64_t)(first + s) * p.heads_q + head;
+        const float ls = __ldcg(p.lse_partial + idx);
+        const float ov = __ldcg(p.o_partial + idx * kHeadDim + t);
+        if (ls == -INFINITY) continue;
+        const float wgt = expf(ls - mx);
+        tot += wgt;
+        acc = fmaf(wgt, ov, acc);
+      }
+    }
+    const float val = tot > 0.f ? __fdiv_rn(acc, tot) : 0.f;
+    p.out[(orow * p.heads_q + head) * kHeadDim + t] = __bfloat16_as_ushort(__float2bfloat16_rn(val));
+  }
+}
+
 // ---- a work-list piece that holds nothing but a row's BF16 tail ----
 // The balanced split lists a row's tail as a piece of its own.  Its CTA needs none of the page
 // machinery (no ring, no tensor memory): every K and V row of the tail is fetched into shared
@@ -395,6 +441,7 @@ __device__ __noinline__ void tail_piece(const DecodeParams& p, const TileWork& w
         p.o_partial[idx * kHeadDim + tid] = 0.f;
         if (tid == 0) p.lse_partial[idx] = -INFINITY;
       }
+      if (p.list_counters) finish_piece<G>(p, w.row, w.kvh, tid);
     }
     return;
   }
@@ -466,6 +513,7 @@ __device__ __noinline__ void tail_piece(const DecodeParams& p, const TileWork& w
       p.o_partial[idx * kHeadDim + d] = val;
       if (d == 0) p.lse_partial[idx] = lq > 0.f ? (ts.m[q] + log2f(lq)) * kLn2 : -INFINITY;
     }
+    if (p.list_counters) finish_piece<G>(p, w.row, w.kvh, d);
   }
 }
 
@@ -516,6 +564,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
           p.o_partial[idx * kHeadDim + tid] = 0.f;
           if (tid == 0) p.lse_partial[idx] = -INFINITY;
         }
+        if (p.work_list && p.list_counters) finish_piece<G>(p, w0.row, w0.kvh, tid);
       }
       return;
     }
@@ -950,6 +999,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
     }
     if (p.xchg_inbox) exchange_tile<G>(p, w, sm, t, stored, xchg_epoch);
+    else if (p.work_list && p.list_counters) finish_piece<G>(p, w.row, w.kvh, t);
   } else if (is_producer) {
     // =====================  producers (K ring: warp 8, V ring: warp 11)  =====================
     if constexpr (kGroups == 1) {

@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(1024)
 balanced_worklist_kernel(const int32_t* __restrict__ seqused_fp4, const int32_t* __restrict__ seqused_tail,
                          int rows, int max_pages, int target_pages, int4* __restrict__ work, int capacity,
                          int32_t* __restrict__ row_offset, int32_t* __restrict__ row_count,
-                         uint32_t* __restrict__ status) {
+                         int32_t* __restrict__ counters, int counter_words, uint32_t* __restrict__ status) {
   __shared__ int class_total[kSizeClasses], class_cursor[kSizeClasses];
   __shared__ int used;
   const int tid = threadIdx.x;
@@ -332,6 +332,8 @@ balanced_worklist_kernel(const int32_t* __restrict__ seqused_fp4, const int32_t*
     if (!balanced_write_row(work, capacity, first, row, count, tail)) set_status(status, NVFP4_STATUS_BAD_LENGTH);
   }
   for (int w = used + tid; w < capacity; w += 1024) work[w] = make_int4(-1, 0, 0, 0);
+  if (counters != nullptr)
+    for (int w = tid; w < counter_words; w += 1024) counters[w] = 0;
 }
 
 // LSE merge where row r's partials are slots [row_offset[r], row_offset[r] + row_count[r]).
@@ -360,10 +362,11 @@ lse_merge_ranges_kernel(const float* __restrict__ o_parts, const float* __restri
 
 cudaError_t launch_balanced_worklist(const int32_t* seqused_fp4, const int32_t* seqused_tail, int rows,
                                      int max_pages, int target_pages, int4* work, int capacity,
-                                     int32_t* row_offset, int32_t* row_count, uint32_t* status,
-                                     cudaStream_t stream) {
+                                     int32_t* row_offset, int32_t* row_count, int32_t* counters,
+                                     int counter_words, uint32_t* status, cudaStream_t stream) {
   balanced_worklist_kernel<<<1, 1024, 0, stream>>>(seqused_fp4, seqused_tail, rows, max_pages, target_pages, work,
-                                                   capacity, row_offset, row_count, status);
+                                                   capacity, row_offset, row_count, counters, counter_words,
+                                                   status);
   return cudaGetLastError();
 }
 

@@ -96,6 +96,11 @@ struct DecodeParams {
   // and entry w stores its partial in slot w.
   const int4* work_list;
   int work_capacity;
+  // With a work list the row's pieces can be merged inside the launch (list_counters non-null):
+  // the piece of a (row, KV head) that arrives last - arrival counters, [rows][heads_kv] ints that
+  // the list builder zeroes and the last arrival leaves at zero - folds the row's partials, slots
+  // list_row_offset[row] .. + list_row_count[row], into `out` with the arithmetic of the merge launch.
+  const int32_t* list_row_offset; const int32_t* list_row_count; int* list_counters;
   // Persistent kernel: launch counter and leaving CTAs of the scratch slots.
   int* tile_counters;
   int wide_hint;              // 1: the caller expects at most one busy CTA per SM
@@ -133,7 +138,7 @@ struct ControlArgs {
   int num_reqs, num_actual_tokens, num_slots;
   // optional (work null: off): the balanced split's list of pieces for the first work_rows rows
   // of this step, built from the lengths this launch computes (see launch_balanced_worklist)
-  int4* work; int32_t* work_row_offset; int32_t* work_row_count;
+  int4* work; int32_t* work_row_offset; int32_t* work_row_count; int32_t* work_counters; int work_counter_words;
   int work_rows, work_capacity, work_max_pages, work_target_pages;
 };
 
@@ -148,10 +153,11 @@ cudaError_t launch_work_table(const int32_t* query_start_loc, const int32_t* seq
 // (nullable) says it holds a BF16 tail, one piece for the tail alone; at least one piece.
 // work [capacity] entries (row, piece, page pieces of the row, 1 for the tail piece), row_offset /
 // row_count [rows]: first partial slot and piece count of a row.
+// counters (nullable): `counter_words` ints zeroed for the in-launch merge of the pieces.
 cudaError_t launch_balanced_worklist(const int32_t* seqused_fp4, const int32_t* seqused_tail, int rows,
                                      int max_pages, int target_pages, int4* work, int capacity,
-                                     int32_t* row_offset, int32_t* row_count, uint32_t* status,
-                                     cudaStream_t stream);
+                                     int32_t* row_offset, int32_t* row_count, int32_t* counters,
+                                     int counter_words, uint32_t* status, cudaStream_t stream);
 cudaError_t launch_lse_merge_ranges(const float* o_parts, const float* lse_parts, const int32_t* row_offset,
                                     const int32_t* row_count, int rows, int heads_q, void* out,
                                     cudaStream_t stream);

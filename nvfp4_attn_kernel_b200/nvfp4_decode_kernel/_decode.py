@@ -195,6 +195,7 @@ def decode_fp4(
     reuse_work_list: bool = False,
     persistent_workspace: torch.Tensor | None = None,
     wide_form: bool = False,
+    merge_in_launch: bool = False,
 ) -> torch.Tensor | None:
     """Validate every tensor contract and launch the decode on the current stream.
 
@@ -592,6 +593,8 @@ def decode_fp4(
         args.flags |= _lib.DECODE_PERSISTENT
     if wide_form:
         args.flags |= _lib.DECODE_WIDE_FORM
+    if merge_in_launch:   # balanced split only: the last piece of a row merges, no merge launch
+        args.flags |= _lib.DECODE_MERGE_IN_LAUNCH
     if args.page_table_row_stride < args.max_pages:
         raise ValueError("fp4_page_table rows overlap")
     with torch.cuda.device(device):

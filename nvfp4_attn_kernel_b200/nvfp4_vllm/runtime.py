@@ -150,7 +150,7 @@ class LayerRuntime:
         capacity = 2 * rows + rows * columns // piece
         up16 = lambda n: (n + 15) & ~15   # noqa: E731
         return (up16(capacity * heads_q * 128 * 4) + up16(capacity * heads_q * 4) + up16(capacity * 16)
-                + 2 * up16(rows * 4))
+                + 2 * up16(rows * 4) + up16(rows * heads_q * 4))
 
     def balance_workspace(self, rows: int, heads_q: int, columns: int, balance_pages: int):
         """Scratch for a decode with a split count per row, or None when the reserved scratch is

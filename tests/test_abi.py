@@ -47,7 +47,7 @@ def test_workspace_size():
 
 def test_balanced_split_sizes_and_refusals():
     """Host arithmetic of the balanced split: the capacity bounds the number of pieces of any
-    batch, the workspace holds partials, list and the per-row ranges, and the entry refuses what
+    batch, the workspace holds partials, list, the per-row ranges and the arrival counters, and the entry refuses what
     its header says it refuses - all before anything is launched."""
     import numpy as np
 
@@ -62,13 +62,14 @@ def test_balanced_split_sizes_and_refusals():
         capacity = lib.nvfp4_decode_balanced_capacity(rows, max_pages, target)
         assert capacity == O.balanced_capacity(rows, max_pages, target)
         lengths = rng.integers(0, max_pages + 1, rows) * 128
-        assert int(O.balanced_split_counts(lengths, target).sum()) <= capacity
+        assert int(O.balanced_split_counts(lengths, target).sum()) + rows <= capacity   # + a tail piece each
         full = np.full(rows, max_pages * 128)
-        assert int(O.balanced_split_counts(full, target).sum()) <= capacity
+        assert int(O.balanced_split_counts(full, target).sum()) + rows <= capacity
         heads_q = int(rng.choice([8, 32, 64]))
         need = lib.nvfp4_decode_balanced_workspace_bytes(rows, heads_q, max_pages, target)
-        floor = capacity * heads_q * 129 * 4 + capacity * 16 + 2 * rows * 4
-        assert floor <= need <= floor + 5 * 16
+        # partials and their LSEs, the list, first slot and piece count per row, arrival counters
+        floor = capacity * heads_q * 129 * 4 + capacity * 16 + 2 * rows * 4 + rows * heads_q * 4
+        assert floor <= need <= floor + 6 * 16
     assert lib.nvfp4_decode_balanced_capacity(0, 32, 8) == 0
     assert lib.nvfp4_decode_balanced_capacity(4, 32, 0) == 0
     assert lib.nvfp4_decode_balanced_workspace_bytes(4, 0, 32, 8) == 0

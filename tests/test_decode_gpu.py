@@ -594,6 +594,14 @@ def test_tail_piece_of_the_balanced_split(cuda_device, heads):
     for row in range(len(lengths)):
         want = oracle_balanced(prob, row, 2)
         assert np.abs(out[row] - want[0]).max() <= TOL, (row, heads)
+    # on request the pieces are merged inside the decode launch by whichever piece finishes last
+    # instead of by the merge launch: the same bits, call after call
+    own_launch = prob.decode_direct(balance_pages=2, trusted_metadata=True)
+    in_launch = prob.decode_direct(balance_pages=2, trusted_metadata=True, merge_in_launch=True)
+    assert torch.equal(in_launch, own_launch)
+    assert np.array_equal(to_np(own_launch), out)
+    for _ in range(3):
+        assert torch.equal(prob.decode_direct(balance_pages=2, trusted_metadata=True, merge_in_launch=True), in_launch)
 
 
 def test_balanced_split_workspace_graph_replay_and_refusals(cuda_device):
