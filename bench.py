@@ -869,7 +869,7 @@ def run_ragged(args) -> None:
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         balance = _decode.balance_pages_heuristic(int(full.sum()), HKV, sms=sms)
     if args.wide:
-        balance = _decode.wide_piece_pages((lens + total_steps) // PAGE, HKV,
+        balance = _decode.wide_piece_pages((lens + total_steps) // PAGE, HKV, tail_pieces=rows,
                                            sms=torch.cuda.get_device_properties(device).multi_processor_count)
     if balance:
         splits = 1
@@ -1058,9 +1058,13 @@ def run_model_step(args, sub: bool = False):
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     piece = piece_pages(rows, hkv, columns, sms) if args.balance_pages < 0 else max(0, args.balance_pages)
     if args.wide:
-        piece = _decode.wide_piece_pages((lens + total_steps) // PAGE, hkv, sms=sms)
+        piece = _decode.wide_piece_pages((lens + total_steps) // PAGE, hkv, sms=sms, tail_pieces=rows)
     if piece >= columns:
         piece = 0
+    # what a scheduler knows on the host, the lengths, says whether the step makes at most one CTA
+    # per SM: then the decode runs on the kernel's wide form
+    wide_form = args.wide or (piece > 0 and not args.persistent and _decode.wide_form_fits(
+        (lens + total_steps) // PAGE, hkv, piece, sms=sms, tail_pieces=rows))
     pws = _decode.persistent_workspace(rows, hq, hkv, device) if args.persistent else None
     space = torch.empty(_decode.balanced_workspace_bytes(rows, hq, columns, piece) if piece else 16,
                         dtype=torch.uint8, device=device)
@@ -1076,7 +1080,7 @@ def run_model_step(args, sub: bool = False):
             k_fp4, k_sf, v_fp4, v_sf = views[layer]
             how = dict(balance_pages=piece, workspace=space, reuse_work_list=True,
                        merge_in_launch=args.merge_in_launch) if piece else {}
-            if args.wide:
+            if wide_form:
                 how["wide_form"] = True
             if args.persistent:
                 how = dict(persistent_workspace=pws)
@@ -1162,6 +1166,8 @@ def run_model_step(args, sub: bool = False):
                                               "built by the control step's launch and reused by every layer, "
                                               "+ merge launch" if piece else "")
                         + ") + one tail flush over all layers, all timed",
+                "kernel_form": ("wide (the host-side lengths give at most one CTA per SM)" if wide_form
+                                else "narrow (two CTAs per SM)"),
                 "ranks": "every rank runs this shape on its own heads (no data-path collective); value is the "
                          "batch's tokens per second of attention time, ms_per_step the max over ranks",
                 "l2": f"{kv / 1e6:.0f} MB of pages and tails per step and GPU against a 126 MB L2",

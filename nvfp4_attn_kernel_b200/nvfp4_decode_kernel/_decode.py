@@ -67,15 +67,18 @@ def balance_pages_heuristic(total_pages: int, heads_kv: int, *, sms: int, floor:
     return max(floor, math.ceil(1.5 * share))
 
 
-def wide_piece_pages(page_counts, heads_kv: int, *, sms: int, floor: int = 4) -> int:
+def wide_piece_pages(page_counts, heads_kv: int, *, sms: int, floor: int = 4, tail_pieces: int = 0) -> int:
     """Piece length, in pages, that cuts rows of ``page_counts`` FP4 pages into at most ``sms``
     pieces per KV head set - one busy CTA per SM, the launch shape of the kernel's wide form
     (``wide_form=True``) - from lengths the caller knows on the host.  The smallest such length,
-    never below ``floor``."""
+    never below ``floor``.  ``tail_pieces``: rows that hold a BF16 tail; the balanced split gives
+    each of them a piece of its own, which takes an SM as well."""
     counts = [int(n) for n in page_counts if int(n) > 0]
     if not counts or heads_kv < 1 or sms < heads_kv:
         return floor
-    budget = sms // heads_kv
+    budget = sms // heads_kv - max(0, int(tail_pieces))
+    if budget < 1:
+        return max(floor, max(counts))
     lo, hi = floor, max(floor, max(counts))
     if sum(-(-n // lo) for n in counts) <= budget:
         return lo
@@ -86,6 +89,14 @@ def wide_piece_pages(page_counts, heads_kv: int, *, sms: int, floor: int = 4) ->
         else:
             lo = mid + 1
     return lo
+
+
+def wide_form_fits(page_counts, heads_kv: int, piece_pages: int, *, sms: int, tail_pieces: int = 0) -> bool:
+    """Whether rows of ``page_counts`` FP4 pages cut into pieces of ``piece_pages`` pages (0: whole
+    rows), plus ``tail_pieces`` tail pieces, make at most one CTA per SM - the case the kernel's
+    wide form (``wide_form=True``) is built for.  Host arithmetic on lengths the caller knows."""
+    pieces = sum(-(-int(n) // piece_pages) if piece_pages > 0 else 1 for n in page_counts if int(n) > 0)
+    return heads_kv >= 1 and (pieces + max(0, int(tail_pieces))) * heads_kv <= sms
 
 
 def _need_cuda(tensor: torch.Tensor, name: str, device: torch.device) -> None:

@@ -172,3 +172,19 @@ def test_wide_piece_pages_fills_one_cta_per_sm():
     assert wide_piece_pages([0, 0], 8, sms=148) == 4
     assert wide_piece_pages([50], 8, sms=4) == 4           # fewer SMs than KV heads: the floor
     assert wide_piece_pages([32] * 16, 8, sms=148, floor=2) == 32
+
+
+def test_wide_form_fits_counts_pieces_and_tails():
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel._decode import wide_form_fits, wide_piece_pages
+
+    assert wide_form_fits([32] * 16, 8, 0, sms=148)                 # 16 whole rows x 8 heads = 128 CTAs
+    assert not wide_form_fits([32] * 16, 8, 16, sms=148)            # 32 pieces x 8 heads
+    assert not wide_form_fits([32] * 16, 8, 0, sms=148, tail_pieces=16)
+    assert wide_form_fits([68] * 32, 1, 22, sms=148)                # 32 x 4 = 128 pieces
+    assert not wide_form_fits([68] * 32, 1, 22, sms=148, tail_pieces=32)
+    assert wide_form_fits([60] * 32, 1, 22, sms=148, tail_pieces=32)   # 96 pieces + 32 tails
+    # the wide piece length leaves room for the tails it is told about
+    t = wide_piece_pages([68] * 32, 1, sms=148, tail_pieces=32)
+    assert wide_form_fits([68] * 32, 1, t, sms=148, tail_pieces=32)
+    assert not wide_form_fits([68] * 32, 1, t - 1, sms=148, tail_pieces=32)
+    assert wide_piece_pages([50], 8, sms=148, tail_pieces=40) == 50   # no room at all: whole rows
