@@ -568,13 +568,10 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
       return;
     }
-    // (the narrow form with 16 or 32 query heads per KV head - only the cross-GPU exchange runs
-    // it, never a work list - has no room for the staging; there the general path below serves)
-    if constexpr (sizeof(TailSmem<G>) <= sizeof(Smem<G, kGroups>)) {
-      if (p.work_list && entry.w) {
-        tail_piece<G, kThreads>(p, w0, *reinterpret_cast<TailSmem<G>*>(&sm));
-        return;
-      }
+    if (p.work_list && entry.w) {
+      static_assert(sizeof(TailSmem<G>) <= sizeof(Smem<G, kGroups>), "the tail piece lives in the ring's memory");
+      tail_piece<G, kThreads>(p, w0, *reinterpret_cast<TailSmem<G>*>(&sm));
+      return;
     }
   }
 
@@ -1228,8 +1225,13 @@ static cudaError_t launch_form(const DecodeParams& p, const CUtensorMap& km, con
   }
   const int64_t ctas = p.work_list ? (int64_t)p.heads_kv * p.work_capacity
                                    : (int64_t)p.num_splits * p.heads_kv * p.rows;
-  const bool wide = !p.xchg_inbox && (G >= 16 || ctas <= n || p.wide_hint);
-  return wide ? launch_g<G, 2>(p, km, vm, stream) : launch_g<G, 1>(p, km, vm, stream);
+  // 16 and 32 query heads per KV head exist in the wide form only
+  if constexpr (G >= 16) {
+    return launch_g<G, 2>(p, km, vm, stream);
+  } else {
+    const bool wide = ctas <= n || p.wide_hint;
+    return wide ? launch_g<G, 2>(p, km, vm, stream) : launch_g<G, 1>(p, km, vm, stream);
+  }
 }
 
 }  // namespace sm100
