@@ -56,7 +56,13 @@ __device__ __forceinline__ TileWork resolve_work(const DecodeParams& p, int row,
                                                  int num_splits, int64_t slot, int what = kSplitZeroOwnsTail) {
   TileWork w;
   w.row = row; w.kvh = kvh; w.split = split; w.slot = slot;
+  // the row's three words are fetched side by side (a length, then the tail's length, then its
+  // id, each behind a branch on the one before, were three round trips at the head of every CTA)
+  const bool may_own_tail = (what == kTailOnly || (what == kSplitZeroOwnsTail && split == 0)) &&
+                            p.tail_key != nullptr && p.seqused_tail != nullptr;
   int fp4 = p.seqused_fp4[row];
+  int len = may_own_tail ? p.seqused_tail[row] : 0;
+  const int id = may_own_tail && p.tail_ids != nullptr ? p.tail_ids[row] : -1;
   int n = fp4 >> 7;
   if (fp4 < 0 || (fp4 & 127) || n > p.max_pages) {
     set_status(p.status, NVFP4_STATUS_BAD_LENGTH);
@@ -68,18 +74,13 @@ __device__ __forceinline__ TileWork resolve_work(const DecodeParams& p, int row,
   if (what == kTailOnly) w.first_page = w.last_page = 0;
   w.tail_len = 0;
   w.tail_id = -1;
-  if ((what == kTailOnly || (what == kSplitZeroOwnsTail && split == 0)) && p.tail_key != nullptr &&
-      p.seqused_tail != nullptr) {
-    int len = p.seqused_tail[row];
-    if (len > 0) {
-      if (len > kPage) { set_status(p.status, NVFP4_STATUS_BAD_LENGTH); len = kPage; }
-      const int id = p.tail_ids[row];
-      if (id < 0 || (int64_t)id >= p.tail_pages) {
-        set_status(p.status, NVFP4_STATUS_BAD_TAIL_ID);
-      } else {
-        w.tail_len = len;
-        w.tail_id = id;
-      }
+  if (len > 0) {
+    if (len > kPage) { set_status(p.status, NVFP4_STATUS_BAD_LENGTH); len = kPage; }
+    if (id < 0 || (int64_t)id >= p.tail_pages) {
+      set_status(p.status, NVFP4_STATUS_BAD_TAIL_ID);
+    } else {
+      w.tail_len = len;
+      w.tail_id = id;
     }
   }
   return w;
@@ -134,13 +135,56 @@ __device__ __forceinline__ float exp2_rel(float z, float m) {
 // +0.5 us, 16 in flight +2.8 us on a batch without any tail).
 constexpr int kTailValueBatch = 4;
 
+// Loads that say "shared" (through a generic pointer the compiler may not know the address is
+// in shared memory, and a generic load costs more than twice the latency).
+__device__ __forceinline__ uint32_t shared_address(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ uint4 lds_u4(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float4 lds_f4(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float lds_f1(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return v;
+}
+
+// A tail staged in shared memory by tensor copies with the 128-byte swizzle: two halves of
+// [tokens][128 bytes] (channels 0-63, then 64-127; `half_bytes` apart), the 16-byte chunks of a
+// row permuted by the row's low three bits - so a thread per token and a thread per channel
+// both read without bank conflicts.  Address of byte `byte` (0..255) of token `t`'s row.
+__device__ __forceinline__ const uint8_t* tail_staged_address(const uint8_t* staged, int half_bytes, int t,
+                                                              int byte) {
+  const int half = byte >> 7, in_half = byte & 127;
+  return staged + half * half_bytes + t * 128 + ((((in_half >> 4) ^ (t & 7)) << 4) | (in_half & 15));
+}
+
 // The BF16 tail block, first half: thread = kv position.  Seeds the running max m and the
 // per-thread partial sums l, and leaves P (rounded to BF16, as floats) in pf[G][128].
 //   qb : [G][128] floats, the BF16 query of this KV head's G query heads
-template <int G>
+//   staged : null, or the tail's key rows already in shared memory in the layout of
+//            tail_staged_address (the step's own token, if any, is not among them); P is then
+//            left transposed, pf[position][G], for tail_pv_staged
+// The code of the tail runs once per CTA, so it is fetched cold: where the rows are in shared
+// memory (kStaged) the loop over the row's chunks stays rolled - unrolled, fetching its
+// instructions took longer (3 us) than executing them.
+template <int G, bool kStaged = false>
 __device__ __forceinline__ void tail_scores(const DecodeParams& p, const TileWork& w, const float* qb,
                                             float* pf, float* red, int tid, int bar_id,
-                                            float (&m)[G], float (&l)[G]) {
+                                            float (&m)[G], float (&l)[G], const uint8_t* staged = nullptr,
+                                            int half_bytes = 0) {
   const int len = w.tail_len;
   const int64_t tok0 = (int64_t)w.tail_id * kPage;
   float z[G];
@@ -161,37 +205,96 @@ __device__ __forceinline__ void tail_scores(const DecodeParams& p, const TileWor
     float acc[G];
 #pragma unroll
     for (int q = 0; q < G; ++q) acc[q] = 0.f;
-#pragma unroll 4
-    for (int c = 0; c < 16; ++c) {
-      float kf[8];
-      if (fresh) {
-        uint4 k = __ldg(ksrc + c);
-        if (p.key_shift) {
-          float x[8], y[8];
-          unpack_bf16x8(k, x);
-          unpack_bf16x8(__ldg(shift + c), y);
-          uint32_t pk[4];
+    if constexpr (kStaged) {
+      // Rows in shared memory.  A warp issues in order, so a product right behind its load waits
+      // out the load's latency every time (measured: 2.5 us for this loop): per chunk, the next
+      // chunk's key load and all the query loads go first, the products after them.
+      const uint32_t q_base = shared_address(qb);
+      auto key_chunk = [&](int c) {
+        uint4 k;
+        if (fresh) {
+          k = __ldg(ksrc + c);
+          if (p.key_shift) {
+            float x[8], y[8];
+            unpack_bf16x8(k, x);
+            unpack_bf16x8(__ldg(shift + c), y);
+            uint32_t pk[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const __nv_bfloat16 a = __float2bfloat16_rn(x[2 * i] - y[2 * i]);
-            const __nv_bfloat16 b = __float2bfloat16_rn(x[2 * i + 1] - y[2 * i + 1]);
-            pk[i] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+            for (int i = 0; i < 4; ++i) {
+              const __nv_bfloat16 a = __float2bfloat16_rn(x[2 * i] - y[2 * i]);
+              const __nv_bfloat16 b = __float2bfloat16_rn(x[2 * i + 1] - y[2 * i + 1]);
+              pk[i] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+            }
+            k = make_uint4(pk[0], pk[1], pk[2], pk[3]);
           }
-          k = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          const_cast<uint4*>(krow)[c] = k;
+        } else {
+          k = lds_u4(shared_address(tail_staged_address(staged, half_bytes, tid, c * 16)));
         }
-        const_cast<uint4*>(krow)[c] = k;
-        unpack_bf16x8(k, kf);
-      } else {
-        unpack_bf16x8(__ldg(krow + c), kf);
-      }
+        return k;
+      };
+      constexpr int QC = G < 4 ? G : 4;   // query heads per batch of loads
+      uint4 k_now = key_chunk(0);
+#pragma unroll 1
+      for (int c = 0; c < 16; ++c) {
+        const uint4 k_next = c + 1 < 16 ? key_chunk(c + 1) : k_now;
+        float kf[8];
+        unpack_bf16x8(k_now, kf);
 #pragma unroll
-      for (int q = 0; q < G; ++q) {
-        const float4 qa = *reinterpret_cast<const float4*>(qb + q * kHeadDim + c * 8);
-        const float4 qc = *reinterpret_cast<const float4*>(qb + q * kHeadDim + c * 8 + 4);
-        acc[q] = fmaf(kf[0], qa.x, acc[q]); acc[q] = fmaf(kf[1], qa.y, acc[q]);
-        acc[q] = fmaf(kf[2], qa.z, acc[q]); acc[q] = fmaf(kf[3], qa.w, acc[q]);
-        acc[q] = fmaf(kf[4], qc.x, acc[q]); acc[q] = fmaf(kf[5], qc.y, acc[q]);
-        acc[q] = fmaf(kf[6], qc.z, acc[q]); acc[q] = fmaf(kf[7], qc.w, acc[q]);
+        for (int q0 = 0; q0 < G; q0 += QC) {
+          float4 qa[QC], qc[QC];
+#pragma unroll
+          for (int i = 0; i < QC; ++i)
+            if (q0 + i < G) {
+              qa[i] = lds_f4(q_base + ((q0 + i) * kHeadDim + c * 8) * 4);
+              qc[i] = lds_f4(q_base + ((q0 + i) * kHeadDim + c * 8 + 4) * 4);
+            }
+#pragma unroll
+          for (int i = 0; i < QC; ++i)
+            if (q0 + i < G) {
+              float a = acc[q0 + i];
+              a = fmaf(kf[0], qa[i].x, a); a = fmaf(kf[1], qa[i].y, a);
+              a = fmaf(kf[2], qa[i].z, a); a = fmaf(kf[3], qa[i].w, a);
+              a = fmaf(kf[4], qc[i].x, a); a = fmaf(kf[5], qc[i].y, a);
+              a = fmaf(kf[6], qc[i].z, a); a = fmaf(kf[7], qc[i].w, a);
+              acc[q0 + i] = a;
+            }
+        }
+        k_now = k_next;
+      }
+    } else {
+  #pragma unroll 4
+      for (int c = 0; c < 16; ++c) {
+        float kf[8];
+        if (fresh) {
+          uint4 k = __ldg(ksrc + c);
+          if (p.key_shift) {
+            float x[8], y[8];
+            unpack_bf16x8(k, x);
+            unpack_bf16x8(__ldg(shift + c), y);
+            uint32_t pk[4];
+  #pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const __nv_bfloat16 a = __float2bfloat16_rn(x[2 * i] - y[2 * i]);
+              const __nv_bfloat16 b = __float2bfloat16_rn(x[2 * i + 1] - y[2 * i + 1]);
+              pk[i] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+            }
+            k = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          }
+          const_cast<uint4*>(krow)[c] = k;
+          unpack_bf16x8(k, kf);
+        } else {
+          unpack_bf16x8(__ldg(krow + c), kf);
+        }
+  #pragma unroll
+        for (int q = 0; q < G; ++q) {
+          const float4 qa = *reinterpret_cast<const float4*>(qb + q * kHeadDim + c * 8);
+          const float4 qc = *reinterpret_cast<const float4*>(qb + q * kHeadDim + c * 8 + 4);
+          acc[q] = fmaf(kf[0], qa.x, acc[q]); acc[q] = fmaf(kf[1], qa.y, acc[q]);
+          acc[q] = fmaf(kf[2], qa.z, acc[q]); acc[q] = fmaf(kf[3], qa.w, acc[q]);
+          acc[q] = fmaf(kf[4], qc.x, acc[q]); acc[q] = fmaf(kf[5], qc.y, acc[q]);
+          acc[q] = fmaf(kf[6], qc.z, acc[q]); acc[q] = fmaf(kf[7], qc.w, acc[q]);
+        }
       }
     }
 #pragma unroll
@@ -207,7 +310,7 @@ __device__ __forceinline__ void tail_scores(const DecodeParams& p, const TileWor
     const float pe = exp2_rel(z[q], bm[q]);
     l[q] = pe;
     // P of the tail meets V as BF16
-    pf[q * kHeadDim + tid] = __bfloat162float(__float2bfloat16_rn(pe));
+    pf[kStaged ? tid * G + q : q * kHeadDim + tid] = __bfloat162float(__float2bfloat16_rn(pe));
   }
 }
 
@@ -287,6 +390,73 @@ __device__ __forceinline__ void tail_pv(const DecodeParams& p, const TileWork& w
                                    (int64_t)w.kvh * kHeadDim + ch0
                              : nullptr;
   tail_pv_walk<G>(vbase, vstride, vnew, len, fresh, pf, tid, o);
+}
+
+// The second half out of shared memory: the tail's value rows were staged there in the layout of
+// tail_staged_address, P lies transposed (pf[position][G]).  Thread tid is channel tid; the step's
+// own token, if any, comes from the source and is stored to the tail page, as in tail_pv.
+template <int G>
+__device__ __forceinline__ void tail_pv_staged(const DecodeParams& p, const TileWork& w, const float* pf,
+                                               const uint8_t* staged, int half_bytes, int tid, float (&o)[G]) {
+  const int len = w.tail_len;
+  const int fresh = p.append_value != nullptr ? len - 1 : -1;
+  float v_fresh = 0.f;
+  if (fresh >= 0) {
+    const uint16_t raw = __ldg(p.append_value + (int64_t)w.row * p.append_value_stride +
+                               (int64_t)w.kvh * kHeadDim + tid);
+    const_cast<uint16_t*>(p.tail_value)[(((int64_t)w.tail_id * kPage + fresh) * p.heads_kv + w.kvh) * kHeadDim + tid] = raw;
+    v_fresh = __uint_as_float((uint32_t)raw << 16);
+  }
+#pragma unroll
+  for (int q = 0; q < G; ++q) o[q] = 0.f;
+  const int body = fresh >= 0 ? len - 1 : len;
+  // this thread's two bytes of row t sit at base + t * 128 + ((chunk ^ (t & 7)) << 4): eight
+  // rows at a time, so that the permutation is a constant per unrolled step
+  const int chunk = (tid & 63) >> 3;
+  const uint32_t base = shared_address(staged + (tid >> 6) * half_bytes + (tid & 7) * 2);
+  const uint32_t pbase = shared_address(pf);
+  // full groups of eight rows: the eight loads first, then the products (with a test per row in
+  // between, every row waited for its own load: 100 cycles a row); then the rows left over
+  int t0 = 0;
+  for (; t0 + 8 <= body; t0 += 8) {
+    uint32_t raw[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) raw[j] = lds_u16(base + (t0 + j) * 128 + ((chunk ^ j) << 4));
+    if constexpr (G == 4) {
+      float4 w4[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w4[j] = lds_f4(pbase + (t0 + j) * 16);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float vf = __uint_as_float(raw[j] << 16);
+        o[0] = fmaf(w4[j].x, vf, o[0]);
+        o[1] = fmaf(w4[j].y, vf, o[1]);
+        o[2] = fmaf(w4[j].z, vf, o[2]);
+        o[3] = fmaf(w4[j].w, vf, o[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float vf = __uint_as_float(raw[j] << 16);
+        const uint32_t pw = pbase + (t0 + j) * G * 4;
+        float wq[G];
+#pragma unroll
+        for (int q = 0; q < G; ++q) wq[q] = lds_f1(pw + q * 4);
+#pragma unroll
+        for (int q = 0; q < G; ++q) o[q] = fmaf(wq[q], vf, o[q]);
+      }
+    }
+  }
+#pragma unroll 1
+  for (int t = t0; t < body; ++t) {
+    const float vf = __uint_as_float(lds_u16(base + t * 128 + ((chunk ^ (t & 7)) << 4)) << 16);
+#pragma unroll
+    for (int q = 0; q < G; ++q) o[q] = fmaf(lds_f1(pbase + (t * G + q) * 4), vf, o[q]);
+  }
+  if (fresh >= 0) {
+#pragma unroll
+    for (int q = 0; q < G; ++q) o[q] = fmaf(pf[fresh * G + q], v_fresh, o[q]);
+  }
 }
 
 // Both halves on the same 128 threads (the CUDA-core kernel).

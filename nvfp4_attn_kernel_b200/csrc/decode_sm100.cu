@@ -43,6 +43,8 @@
 //
 // Every device-side wait is bounded; on expiry the CTA raises NVFP4_STATUS_WAIT_TIMEOUT,
 // drains what it has in flight, frees its tensor memory and returns.
+#include <cstring>
+
 #include "sm100_device.cuh"
 
 namespace nvfp4 {
@@ -83,6 +85,18 @@ struct Cols {
   static_assert(kGroups == 1 || kSfP + 16 >= kSfP + 8 * kGroups, "scale columns of the second P issuer");
 };
 
+// The tensor maps of a launch: K and V page tiles, and the BF16 tail caches (unused without tails).
+struct TileMaps {
+  CUtensorMap k, v, tail_k, tail_v;
+};
+
+// The BF16 tail of a tile that also walks pages is staged in shared memory too: its key rows,
+// then its value rows, are fetched by bulk copies (one round trip each instead of a dozen
+// through registers) into the LAST kTailSlots slots of the V ring, which the V producer leaves
+// alone until the tail is consumed.
+constexpr int kTailPitch = kHeadDim + 8;   // elements; rows 272 bytes apart: 16-byte aligned, no bank conflicts
+constexpr int kTailSlots = (2 * kPage * 128 + kSlotBytes - 1) / kSlotBytes;   // 4: a full tail's 32 KB
+
 template <int G, int kGroups>
 struct __align__(1024) Smem {
   static constexpr int kKS = KSlots<G, kGroups>::value, kVS = VSlots<G, kGroups>::value;
@@ -102,11 +116,12 @@ struct __align__(1024) Smem {
   float fin[2][2 * NQ];                         // per score group: row sums and the maxima they refer to
   volatile float m_val[2][NQ];                  // running maximum handed from one score group to the other, [pairs done & 1]
   volatile int m_seq[4];                        // [score warp] pairs whose maximum m_val already holds
-  volatile int page_ok[32];                     // [walk step & 31] 0: the page id was refused
+  volatile uint8_t page_ok[32];                 // [walk step & 31] 0: the page id was refused
   __align__(8) uint64_t k_full[kKS];
   uint64_t k_empty[kKS], v_full[kVS], v_empty[kVS];
   uint64_t s_full[2], s_free[2], p_full[2], o_full[2], o_free[2];
   uint64_t q_ready, drain[4];
+  uint64_t tail_full, tail_done;                // the BF16 tail staged in the V ring's last slots (see kTailSlots)
   uint32_t tmem_base;
   volatile int abort_flag;
   volatile int xchg_last, xchg_ready;           // hand-overs among the output threads during the exchange
@@ -289,8 +304,8 @@ __device__ __forceinline__ void exchange_tile(const DecodeParams& p, const TileW
 // arithmetic and in the order of the merge launch (lse_merge_ranges_kernel), so the bits are
 // the same whichever piece happens to be last.  No piece waits for another.
 template <int G>
-__device__ __forceinline__ void finish_piece(const DecodeParams& p, int row, int kvh, int t) {
-  __shared__ int last_arrival;
+__device__ __forceinline__ void finish_piece(const DecodeParams& p, int row, int kvh, int t,
+                                             volatile int& last_arrival) {
   __threadfence();   // this piece's partial is visible before its arrival is counted
   asm volatile("bar.sync 6, 128;" ::: "memory");
   const int count = __ldg(p.list_row_count + row);
@@ -336,7 +351,6 @@ __device__ __forceinline__ void finish_piece(const DecodeParams& p, int row, int
 // instead of the dozen a walk with loads into registers takes), and the scores, the softmax
 // and P . V run out of shared memory.  Arithmetic as in tail_scores / tail_pv: BF16 query
 // against BF16 keys, P rounded to BF16 before it meets V, the row sum over the unrounded P.
-constexpr int kTailPitch = kHeadDim + 8;   // elements; rows 272 bytes apart: 16-byte aligned, no bank conflicts
 
 template <int G>
 struct __align__(128) TailSmem {
@@ -347,6 +361,7 @@ struct __align__(128) TailSmem {
   __align__(16) float o2[G * kHeadDim];   // the odd positions' share of the output
   float red[4 * G];
   float m[G], l[G];
+  volatile int last_arrival;
   __align__(8) uint64_t bar;
 };
 
@@ -441,7 +456,7 @@ __device__ __noinline__ void tail_piece(const DecodeParams& p, const TileWork& w
         p.o_partial[idx * kHeadDim + tid] = 0.f;
         if (tid == 0) p.lse_partial[idx] = -INFINITY;
       }
-      if (p.list_counters) finish_piece<G>(p, w.row, w.kvh, tid);
+      if (p.list_counters) finish_piece<G>(p, w.row, w.kvh, tid, ts.last_arrival);
     }
     return;
   }
@@ -513,7 +528,7 @@ __device__ __noinline__ void tail_piece(const DecodeParams& p, const TileWork& w
       p.o_partial[idx * kHeadDim + d] = val;
       if (d == 0) p.lse_partial[idx] = lq > 0.f ? (ts.m[q] + log2f(lq)) * kLn2 : -INFINITY;
     }
-    if (p.list_counters) finish_piece<G>(p, w.row, w.kvh, d);
+    if (p.list_counters) finish_piece<G>(p, w.row, w.kvh, d, ts.last_arrival);
   }
 }
 
@@ -523,8 +538,7 @@ template <int kGroups> struct ThreadsOf { static constexpr int value = 384 + 256
 
 template <int G, int kGroups>
 __global__ void __launch_bounds__(ThreadsOf<kGroups>::value, kGroups == 1 ? 2 : 1)
-decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                    const __grid_constant__ DecodeParams p) {
+decode_sm100_kernel(const __grid_constant__ TileMaps maps, const __grid_constant__ DecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   Smem<G, kGroups>& sm =
       *reinterpret_cast<Smem<G, kGroups>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -564,7 +578,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
           p.o_partial[idx * kHeadDim + tid] = 0.f;
           if (tid == 0) p.lse_partial[idx] = -INFINITY;
         }
-        if (p.work_list && p.list_counters) finish_piece<G>(p, w0.row, w0.kvh, tid);
+        if (p.work_list && p.list_counters) finish_piece<G>(p, w0.row, w0.kvh, tid, sm.xchg_last);
       }
       return;
     }
@@ -616,6 +630,8 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     }
     mbar_init(&sm.q_ready, 128);
     for (int b = 0; b < 4; ++b) mbar_init(&sm.drain[b], 1);
+    mbar_init(&sm.tail_full, 1);
+    mbar_init(&sm.tail_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kQkWarp) {
@@ -650,11 +666,11 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     if (pid >= 0) {
       mbar_expect_tx(bar, kSlotBytes);
       if (is_k) {
-        tma_load_4d(smem_u32(st), &k_map, bar, 0, w.kvh, 0, (int)pid);
+        tma_load_4d(smem_u32(st), &maps.k, bar, 0, w.kvh, 0, (int)pid);
         bulk_load(smem_u32(st + kTileBytes), p.k_sf + pid * p.k_sf_pitch + (int64_t)w.kvh * kSfBlockBytes,
                   kSfBlockBytes, bar);
       } else {
-        tma_load_4d(smem_u32(st), &v_map, bar, 0, 0, w.kvh, (int)pid);
+        tma_load_4d(smem_u32(st), &maps.v, bar, 0, 0, w.kvh, (int)pid);
         bulk_load(smem_u32(st + kTileBytes), p.v_sf + pid * p.v_sf_pitch + (int64_t)w.kvh * kSfBlockBytes,
                   kSfBlockBytes, bar);
       }
@@ -667,9 +683,24 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       mbar_arrive(bar);
     }
   };
+  static_assert(kVS > kTailSlots, "the V producer keeps at least one slot while the tail is staged");
+  const bool has_tail = w.tail_len > 0;
+  // Tail staging geometry: boxes of kTailBoxRows tokens; a half (64 channels) of the staged keys
+  // is tail_half bytes long.  Up to two boxes (64 tokens) keys AND values fit side by side and
+  // are fetched together; a longer tail's values follow its keys into the same place.
+  const int tail_copied = p.append_key != nullptr ? w.tail_len - 1 : w.tail_len;   // the step's own token is not in the cache yet
+  const int tail_boxes = (tail_copied + kTailBoxRows - 1) / kTailBoxRows;
+  const int tail_half = tail_boxes * kTailBoxRows * 128;
+  const bool tail_together = tail_boxes <= 2;
+  // slots a producer may fill at once at the start: all of its ring, except that the V ring's
+  // last slots hold the tail until tail_done - as many as this tail needs, at most kTailSlots
+  const int tail_bytes = (tail_together ? 4 : 2) * tail_half;
+  const int tail_slots = (tail_bytes + kSlotBytes - 1) / kSlotBytes;
+  uint8_t* const tail_rows = sm.v_slot[kVS - kTailSlots] + (kTailSlots * kSlotBytes - tail_slots * kSlotBytes);
+  const int open_slots = is_k_producer ? kKS : (has_tail ? kVS - tail_slots : kVS);
   // ids: lane l of a producer warp holds the page id of walk step 32c + l of the current chunk c
   int ids = -1, issued = 0;
-  if (second_producer) issued = n_pages < (is_k_producer ? kKS : kVS) ? n_pages : (is_k_producer ? kKS : kVS);
+  if (second_producer) issued = n_pages < open_slots ? n_pages : open_slots;
   if (is_producer && !second_producer) {
     const int slots = is_k_producer ? kKS : kVS;
     // chunk 0 out of the columns fetched ahead; every lane executes the same four shuffles
@@ -684,7 +715,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     }
     if (live && idx0 >= 128) v = p.page_table[(int64_t)w.row * p.page_table_row_stride + idx0];
     ids = v;
-    const int first = n_pages < slots ? n_pages : slots;
+    const int first = n_pages < open_slots ? n_pages : open_slots;
     for (int i = 0; i < first; ++i) {
       int64_t pid = __shfl_sync(0xffffffffu, ids, i);
       if (pid < 0 || pid >= p.num_pages) {
@@ -754,12 +785,16 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       quantize_group16(x, lo, hi, sf);
       *reinterpret_cast<uint2*>(sm.q_tile + sw64_offset(q, g * 8)) = make_uint2(lo, hi);
       sm.q_sf[sf_offset(q, g)] = sf;
+      if (has_tail) {   // the same BF16 values meet the tail: kept as floats, no second fetch
+#pragma unroll
+        for (int i = 0; i < 16; ++i) sm.qb[q * kHeadDim + g * 16 + i] = x[i];
+      }
     }
     fence_proxy_async();
     mbar_arrive(&sm.q_ready);
 
     if (w.tail_len > 0) {
-      for (int it = tid; it < G * 16; it += 128) {
+      if (p.q_fp4) for (int it = tid; it < G * 16; it += 128) {
         const int q = it >> 4, c = it & 15;
         float f[8];
         if (p.q_bf16) {
@@ -779,7 +814,10 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
       float m[G], l[G];
       asm volatile("bar.sync 1, 128;" ::: "memory");  // qb visible
-      tail_scores<G>(p, w, sm.qb, sm.pf, sm.red_io, tid, 1, m, l);
+      // the key rows were staged by the first output warp; a wait that expires leaves the
+      // status word set and the launch aborting, whatever is computed here
+      mbar_wait(&sm.tail_full, 0, sm, p.status);
+      tail_scores<G, true>(p, w, sm.qb, sm.pf, sm.red_io, tid, 1, m, l, tail_rows, tail_half);
       asm volatile("bar.sync 2, 256;" ::: "memory");  // P of the tail visible to the output threads
       block_sum_128<G>(l, sm.red_io, tid, 1);
 #pragma unroll
@@ -943,8 +981,46 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 #pragma unroll
     for (int q = 0; q < G; ++q) o[q] = 0.f;
     if (w.tail_len > 0) {
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      tail_pv<G>(p, w, sm.pf, t, o);
+      // The tail's rows come into shared memory by tensor copies (boxes of kTailBoxRows tokens x
+      // half a row, 128-byte swizzle; a copy per row was tried first: the copy engine takes
+      // some 35 ns per instruction, 9 us for a full tail), issued by this group's first warp:
+      // the key rows at once; the value rows into the same place as soon as the score threads
+      // are done with the keys (the barrier below).  The step's own token is not in the cache
+      // yet: it is taken from the source by the threads that handle its position.
+      uint8_t* const value_rows = tail_together ? tail_rows + 2 * tail_half : tail_rows;
+      auto stage = [&](const CUtensorMap* map, uint8_t* dst) {
+        if (lane < 2 * tail_boxes) {
+          const int half = lane & 1, b = lane >> 1;
+          tma_load_3d(smem_u32(dst + half * tail_half + b * kTailBoxRows * 128), map, &sm.tail_full,
+                      half * 128, w.kvh, w.tail_id * kPage + b * kTailBoxRows);
+        }
+      };
+      auto expect = [&](int parts) {   // parts: 1 = keys or values, 2 = both
+        if (lane == 0) {
+          if (tail_boxes > 0) mbar_expect_tx(&sm.tail_full, (uint32_t)(parts * 2 * tail_half));
+          else mbar_arrive(&sm.tail_full);
+        }
+        __syncwarp();
+      };
+      if (warp == 4) {
+        expect(tail_together ? 2 : 1);
+        stage(&maps.tail_k, tail_rows);
+        if (tail_together) stage(&maps.tail_v, value_rows);
+      }
+      asm volatile("bar.sync 2, 256;" ::: "memory");   // P of the tail is there; the keys are no longer read
+      if (!tail_together) {
+        if (warp == 4) {
+          fence_proxy_async();
+          expect(1);
+          stage(&maps.tail_v, value_rows);
+        }
+        mbar_wait(&sm.tail_full, 1, sm, p.status);
+      } else {
+        mbar_wait(&sm.tail_full, 0, sm, p.status);
+      }
+      tail_pv_staged<G>(p, w, sm.pf, value_rows, tail_half, t, o);
+      asm volatile("bar.sync 6, 128;" ::: "memory");   // every output thread is done with the rows
+      if (t == 0) mbar_arrive(&sm.tail_done);           // the V producer may have the slots
     }
     bool alive = true;
     for (int kb = 0; kb < n_batches && alive; ++kb) {
@@ -996,7 +1072,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       }
     }
     if (p.xchg_inbox) exchange_tile<G>(p, w, sm, t, stored, xchg_epoch);
-    else if (p.work_list && p.list_counters) finish_piece<G>(p, w.row, w.kvh, t);
+    else if (p.work_list && p.list_counters) finish_piece<G>(p, w.row, w.kvh, t, sm.xchg_last);
   } else if (is_producer) {
     // =====================  producers (K ring: warp 8, V ring: warp 11)  =====================
     if constexpr (kGroups == 1) {
@@ -1015,6 +1091,11 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
             pid = -1;
           }
           const int s = i % slots;
+          if (has_tail && !is_k_producer && i < slots && s >= open_slots) {
+            // first use of a slot that held the tail: wait until the tail is consumed
+            if (!mbar_wait(&sm.tail_done, 0, sm, p.status)) break;
+            fence_proxy_async();
+          }
           uint64_t* freed = is_k_producer ? &sm.k_empty[s] : &sm.v_empty[s];
           if (!mbar_wait(freed, ((i / slots) & 1) ^ 1, sm, p.status)) break;
           issue_slot(is_k_producer, s, i, pid);
@@ -1052,8 +1133,12 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
               pid = -1;
             }
             const int i = base + j, s = i % slots;
+            if (has_tail && !is_k_producer && i < slots && s >= open_slots) {
+              if (!mbar_wait(&sm.tail_done, 0, sm, p.status)) alive = 0;
+              fence_proxy_async();
+            }
             uint64_t* freed = is_k_producer ? &sm.k_empty[s] : &sm.v_empty[s];
-            if (!mbar_wait(freed, ((i / slots) & 1) ^ 1, sm, p.status)) alive = 0;
+            if (!alive || !mbar_wait(freed, ((i / slots) & 1) ^ 1, sm, p.status)) alive = 0;
             else issue_slot(is_k_producer, s, i, pid);
           }
           alive = __shfl_sync(0xffffffffu, alive, 0);
@@ -1177,7 +1262,7 @@ decode_sm100_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
 
 
 template <int G, int kGroups>
-static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const CUtensorMap& vm,
+static cudaError_t launch_g(const DecodeParams& p, const TileMaps& maps,
                             cudaStream_t stream) {
   const size_t smem = sizeof(Smem<G, kGroups>) + 1024;
   static_assert(sizeof(Smem<G, kGroups>) + 1024 <= (kGroups == 1 ? 115712 : 232448),
@@ -1189,6 +1274,20 @@ static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const 
   if (dev < 0 || dev >= 64 || !configured[dev]) {
     e = cudaFuncSetAttribute(decode_sm100_kernel<G, kGroups>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(decode_sm100_kernel<G, kGroups>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
+    // The narrow form is built for two CTAs per SM: 2 x (shared memory of a CTA + 1 KB the
+    // system keeps per CTA) must fit the SM's 228 KB.  A static shared variable anywhere in the
+    // kernel counts too, and 16 bytes of it once halved the residency (and the page stream)
+    // unnoticed: checked once per device, refused loudly.  (The occupancy calculator is no help:
+    // it answers 1 for this kernel at any size.)
+    if constexpr (kGroups == 1) {
+      cudaFuncAttributes fa{};
+      e = cudaFuncGetAttributes(&fa, decode_sm100_kernel<G, kGroups>);
+      if (e != cudaSuccess) return e;
+      if (fa.sharedSizeBytes + smem > 115712) return cudaErrorLaunchOutOfResources;
+    }
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   dim3 grid(p.num_splits, p.heads_kv, p.rows);
@@ -1205,14 +1304,14 @@ static cudaError_t launch_g(const DecodeParams& p, const CUtensorMap& km, const 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, decode_sm100_kernel<G, kGroups>, km, vm, p);
+  return cudaLaunchKernelEx(&cfg, decode_sm100_kernel<G, kGroups>, maps, p);
 }
 
 // The wide form pays when a CTA's own page period, not HBM, bounds the launch: at most one CTA
 // per SM.  Sixteen and more query heads per KV head always take it (their score threads need its
 // register budget).
 template <int G>
-static cudaError_t launch_form(const DecodeParams& p, const CUtensorMap& km, const CUtensorMap& vm,
+static cudaError_t launch_form(const DecodeParams& p, const TileMaps& maps,
                                cudaStream_t stream) {
   static int sms[64] = {};
   int dev = 0;
@@ -1227,10 +1326,10 @@ static cudaError_t launch_form(const DecodeParams& p, const CUtensorMap& km, con
                                    : (int64_t)p.num_splits * p.heads_kv * p.rows;
   // 16 and 32 query heads per KV head exist in the wide form only
   if constexpr (G >= 16) {
-    return launch_g<G, 2>(p, km, vm, stream);
+    return launch_g<G, 2>(p, maps, stream);
   } else {
     const bool wide = ctas <= n || p.wide_hint;
-    return wide ? launch_g<G, 2>(p, km, vm, stream) : launch_g<G, 1>(p, km, vm, stream);
+    return wide ? launch_g<G, 2>(p, maps, stream) : launch_g<G, 1>(p, maps, stream);
   }
 }
 
@@ -1246,22 +1345,30 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, cudaStream_t stream) {
   if (p.rows == 0) return cudaSuccess;
   if (!decode_sm100_supports(p)) return cudaErrorNotSupported;
   if (p.num_pages < 1 || p.num_pages > 0x7FFFFFFF) return cudaErrorInvalidValue;
-  CUtensorMap km, vm;
-  cudaError_t e = sm100::make_map(0, p.k_packed, p.k_pitch, p.num_pages, p.heads_kv, &km);
+  sm100::TileMaps maps;
+  std::memset(&maps, 0, sizeof(maps));
+  cudaError_t e = sm100::make_map(0, p.k_packed, p.k_pitch, p.num_pages, p.heads_kv, &maps.k);
   if (e != cudaSuccess) return e;
-  e = sm100::make_map(1, p.v_packed, p.v_pitch, p.num_pages, p.heads_kv, &vm);
+  e = sm100::make_map(1, p.v_packed, p.v_pitch, p.num_pages, p.heads_kv, &maps.v);
   if (e != cudaSuccess) return e;
+  if (p.tail_key != nullptr && p.tail_value != nullptr && p.tail_pages > 0) {
+    if (p.tail_pages > (int64_t)0x7FFFFFFF / 128) return cudaErrorInvalidValue;
+    e = sm100::make_map(2, p.tail_key, 0, p.tail_pages, p.heads_kv, &maps.tail_k);
+    if (e != cudaSuccess) return e;
+    e = sm100::make_map(2, p.tail_value, 0, p.tail_pages, p.heads_kv, &maps.tail_v);
+    if (e != cudaSuccess) return e;
+  }
   switch (p.heads_q / p.heads_kv) {
-    case 1: return sm100::launch_form<1>(p, km, vm, stream);
-    case 2: return sm100::launch_form<2>(p, km, vm, stream);
-    case 3: return sm100::launch_form<3>(p, km, vm, stream);
-    case 4: return sm100::launch_form<4>(p, km, vm, stream);
-    case 5: return sm100::launch_form<5>(p, km, vm, stream);
-    case 6: return sm100::launch_form<6>(p, km, vm, stream);
-    case 7: return sm100::launch_form<7>(p, km, vm, stream);
-    case 8: return sm100::launch_form<8>(p, km, vm, stream);
-    case 16: return sm100::launch_form<16>(p, km, vm, stream);
-    case 32: return sm100::launch_form<32>(p, km, vm, stream);
+    case 1: return sm100::launch_form<1>(p, maps, stream);
+    case 2: return sm100::launch_form<2>(p, maps, stream);
+    case 3: return sm100::launch_form<3>(p, maps, stream);
+    case 4: return sm100::launch_form<4>(p, maps, stream);
+    case 5: return sm100::launch_form<5>(p, maps, stream);
+    case 6: return sm100::launch_form<6>(p, maps, stream);
+    case 7: return sm100::launch_form<7>(p, maps, stream);
+    case 8: return sm100::launch_form<8>(p, maps, stream);
+    case 16: return sm100::launch_form<16>(p, maps, stream);
+    case 32: return sm100::launch_form<32>(p, maps, stream);
     default: return cudaErrorNotSupported;
   }
 }

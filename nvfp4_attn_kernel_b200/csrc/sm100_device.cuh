@@ -141,6 +141,15 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0,
+                                            int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                :
@@ -263,7 +272,9 @@ struct MapKey {
 };
 struct MapEntry { MapKey key; CUtensorMap map; bool valid; };
 
-// K: bytes [64] x heads x tokens [128] x pages ; V: bytes [64] x channels [128] x heads x pages
+// K: bytes [64] x heads x tokens [128] x pages ; V: bytes [64] x channels [128] x heads x pages ;
+// which = 2: a BF16 tail cache (pitch unused)
+constexpr int kTailBoxRows = 32;   // tokens per box of a tail map
 inline cudaError_t make_map(int which, const void* base, int64_t pitch, int64_t pages, int heads,
                             CUtensorMap* out) {
   thread_local MapEntry cache[8] = {};
@@ -279,16 +290,23 @@ inline cudaError_t make_map(int which, const void* base, int64_t pitch, int64_t 
     dims[0] = 64; dims[1] = heads; dims[2] = 128; dims[3] = pages;
     strides[0] = 64; strides[1] = (cuuint64_t)heads * 64; strides[2] = pitch;
     box[0] = 64; box[1] = 1; box[2] = 128; box[3] = 1;
-  } else {
+  } else if (which == 1) {
     dims[0] = 64; dims[1] = 128; dims[2] = heads; dims[3] = pages;
     strides[0] = 64; strides[1] = 128 * 64; strides[2] = pitch;
     box[0] = 64; box[1] = 128; box[2] = 1; box[3] = 1;
+  } else {
+    // BF16 tail pages, [pages * 128 tokens][heads][128 channels] seen as bytes: a box is half a
+    // row (128 of its 256 bytes) of one head for kTailBoxRows tokens, 128-byte swizzle
+    // (a map of rank 3)
+    dims[0] = 256; dims[1] = heads; dims[2] = (cuuint64_t)pages * 128; dims[3] = 1;
+    strides[0] = 256; strides[1] = (cuuint64_t)heads * 256; strides[2] = 0;
+    box[0] = 128; box[1] = 1; box[2] = kTailBoxRows; box[3] = 1;
   }
   CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
   CUtensorMap map;
-  CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, promo,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, which >= 2 ? 3 : 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, which >= 2 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   cache[next] = MapEntry{key, map, true};
   next = (next + 1) % 8;
