@@ -34,7 +34,7 @@ NUM_POOLS = 2                              # alternate so that L2 (126 MB) canno
 KV_BYTES = ROWS * CTX * HKV * 144          # algorithmic bytes of one step (144 B per token-head)
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch of the default workload, from
 # an ncu capture of that kernel (a constant: this program does not measure it)
-NCU_TRAFFIC_BYTES = 151_684_608 + 6_503_680
+NCU_TRAFFIC_BYTES = 151_752_448 + 5_598_592   # read + written, mean of the two captured launches
 METRIC = "decode_attn_tokens_per_s"
 UNIT = "tokens/s"
 WORKLOAD = ("uniform batch decode: 32 seq x 4096 ctx, Hq32/Hkv8/D128, page 128, "
