@@ -467,15 +467,21 @@ def run_gpu(args) -> None:
     q_dev = torch.empty_like(q)
     host_steps = [host_io_step(q_dev, p["k"], p["ksf"], p["v"], p["vsf"], p["table"], seqused, out=out)
                   for p in pools]
+    # the same step without copy operations: the kernel reads and writes the pinned buffers itself
+    direct_steps = [host_io_step(q_dev, p["k"], p["ksf"], p["v"], p["vsf"], p["table"], seqused, out=out,
+                                 direct=True) for p in pools]
+    out_host_direct = torch.empty_like(out, device="cpu").pin_memory()
 
-    def e2e_region(n):
+    def e2e_region(n, steps=None, sink=None):
+        steps = steps or host_steps
+        sink = out_host if sink is None else sink
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s2.record()
         for i in range(n):
-            host_steps[i % NUM_POOLS](q_host, out_host)
+            steps[i % NUM_POOLS](q_host, sink)
         e2.record()
         torch.cuda.synchronize()
         ms = s2.elapsed_time(e2)
@@ -489,6 +495,11 @@ def run_gpu(args) -> None:
     e2e_region(max(3, min(args.warmup, 20)))
     e2e_ms = [e2e_region(e2e_steps) for _ in range(REPEATS)]
     e2e_step = _median(e2e_ms)
+    e2e_region(max(3, min(args.warmup, 20)), direct_steps, out_host_direct)
+    direct_ms = [e2e_region(e2e_steps, direct_steps, out_host_direct) for _ in range(REPEATS)]
+    host_steps[0](q_host, out_host)
+    direct_steps[0](q_host, out_host_direct)
+    direct_same = bool(torch.equal(out_host, out_host_direct))
     if world > 1:
         dist.barrier()
 
@@ -579,7 +590,13 @@ def run_gpu(args) -> None:
             "e2e": {"value": world * ROWS / (e2e_step * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
                     "ms_per_step": e2e_step, "steps": e2e_steps,
-                    "call": "host_io_step: nvfp4_decode_host_io (copy in, decode, copy out, wait) per step"},
+                    "call": "host_io_step: nvfp4_decode_host_io (copy in, decode, copy out, wait) per step",
+                    "without_copy_operations": {
+                        "ms_per_step": _median(direct_ms), "min": min(direct_ms), "max": max(direct_ms),
+                        "value": world * ROWS / (_median(direct_ms) * 1e-3),
+                        "bitwise_equal_to_the_copy_form": direct_same,
+                        "call": "host_io_step(direct=True): NVFP4_DECODE_HOST_IO_DIRECT, the kernel reads the "
+                                "pinned query and writes the pinned rows over PCIe itself; one launch and the wait"}},
             "gpu_launches": launches,
             "clocks": clocks,
             "device_status_word": bad,

@@ -287,6 +287,8 @@ int nvfp4_decode_persistent_supported(int rows, int heads_q, int heads_kv);
 #define NVFP4_DECODE_WIDE_FORM 8u
 /* nvfp4_decode_balanced only: merge the pieces inside the decode launch (see there). */
 #define NVFP4_DECODE_MERGE_IN_LAUNCH 16u
+/* nvfp4_decode_host_io only: no copy operations, the kernel reads and writes the pinned host buffers (see there). */
+#define NVFP4_DECODE_HOST_IO_DIRECT 32u
 
 /*
  * With out != NULL the merged bf16 result is written (for num_splits > 1 the
@@ -509,6 +511,10 @@ int nvfp4_peer_merge(const float* const* o_part_ptrs, const float* const* lse_pa
  * its strides lays it out) to args->q_bf16 on `stream`, runs nvfp4_decode(args), copies
  * out_bytes of args->out to out_host (pinned) and waits for the stream.  Everything args points
  * to stays device memory, the KV pages stay resident.  Returns after the result is in out_host.
+ * With NVFP4_DECODE_HOST_IO_DIRECT in args->flags there are no copy operations: pinned host memory
+ * is mapped into the device's address space, so the decode kernel reads the query from q_host and
+ * writes the rows to out_host over PCIe itself (every byte crosses once, as with the copies;
+ * args->q_bf16 and args->out then only describe the layout).  One launch and the wait.
  */
 int nvfp4_decode_host_io(const nvfp4_decode_args* args, const void* q_host, size_t q_bytes, void* out_host,
                          size_t out_bytes, void* stream);

@@ -19,6 +19,7 @@ DECODE_REUSE_WORK_LIST = 2
 DECODE_PERSISTENT = 4
 DECODE_WIDE_FORM = 8
 DECODE_MERGE_IN_LAUNCH = 16
+DECODE_HOST_IO_DIRECT = 32
 STATUS_BAD_PAGE_ID, STATUS_BAD_TAIL_ID, STATUS_WAIT_TIMEOUT, STATUS_BAD_LENGTH = 1, 2, 4, 8
 ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED = 1, 2, 3
 

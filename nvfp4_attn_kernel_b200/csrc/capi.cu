@@ -252,7 +252,27 @@ int nvfp4_decode_host_io(const nvfp4_decode_args* a, const void* q_host, size_t 
   if (!a->q_bf16 || !a->out)
     return fail(NVFP4_ERR_INVALID, "decode_host_io: args must carry the device BF16 query buffer and out");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = cudaMemcpyAsync(const_cast<void*>(a->q_bf16), q_host, q_bytes, cudaMemcpyHostToDevice, st);
+  cudaError_t e;
+  // Pinned host memory is mapped into the device's address space: the kernel then reads the
+  // query and writes the rows over PCIe itself (every byte crosses once, as with the copies),
+  // which saves the two copy operations' own latency - a third of the step.
+  if (a->flags & NVFP4_DECODE_HOST_IO_DIRECT) {
+    cudaPointerAttributes qa{}, oa{};
+    if (cudaPointerGetAttributes(&qa, q_host) != cudaSuccess || cudaPointerGetAttributes(&oa, out_host) != cudaSuccess ||
+        qa.type != cudaMemoryTypeHost || oa.type != cudaMemoryTypeHost || !qa.devicePointer || !oa.devicePointer) {
+      (void)cudaGetLastError();
+      return fail(NVFP4_ERR_INVALID, "decode_host_io: the direct form needs pinned (mapped) host buffers");
+    }
+    nvfp4_decode_args direct = *a;
+    direct.flags &= ~NVFP4_DECODE_HOST_IO_DIRECT;
+    direct.q_bf16 = qa.devicePointer;
+    direct.out = oa.devicePointer;
+    const int rc = decode_call(&direct, nullptr, 0, stream);
+    if (rc != NVFP4_OK) return rc;
+    e = cudaStreamSynchronize(st);
+    return e == cudaSuccess ? NVFP4_OK : cuda_fail(e, "decode_host_io: stream synchronisation");
+  }
+  e = cudaMemcpyAsync(const_cast<void*>(a->q_bf16), q_host, q_bytes, cudaMemcpyHostToDevice, st);
   if (e != cudaSuccess) return cuda_fail(e, "decode_host_io: query copy");
   const int rc = decode_call(a, nullptr, 0, stream);
   if (rc != NVFP4_OK) return rc;

@@ -66,6 +66,7 @@ FUSE_QUERY_QUANT = True
 # cache off (every call is then validated from scratch).
 CACHE_CALL_PLANS = True
 _PLANS: dict = {}
+_LAST_PLAN = None   # the plan the latest one-launch call ran from or left behind (HostIoStep takes it)
 _MAX_PLANS = 256
 
 
@@ -107,7 +108,7 @@ class HostIoStep:
     and the step's metadata tensors stay on the device and are read afresh on every call.
     """
 
-    def __init__(self, query: torch.Tensor, *args, out: torch.Tensor, **kwargs):
+    def __init__(self, query: torch.Tensor, *args, out: torch.Tensor, direct: bool = False, **kwargs):
         from ._decode import decode_fp4  # noqa: F401  (validates through fp4_decode_impl below)
 
         if not _kernel_can_quantise(query):
@@ -116,35 +117,67 @@ class HostIoStep:
             raise ValueError("out must be a contiguous BF16 CUDA tensor")
         global CACHE_CALL_PLANS
         kwargs = dict(kwargs, out=out, trusted_metadata=True)
+        global _LAST_PLAN
         before, CACHE_CALL_PLANS = CACHE_CALL_PLANS, True
+        _LAST_PLAN = None
         try:
             fp4_decode_impl(query, *args, **kwargs)      # validates, runs once, leaves its plan behind
         finally:
             CACHE_CALL_PLANS = before
-        plan = next((p for p in reversed(list(_PLANS.values()))
-                     if p[0].q_bf16 == query.data_ptr() and p[0].out == out.data_ptr()), None)
+        # the plan of THIS call (a step built twice over the same query and output buffers, for
+        # two page pools say, must not pick up the other's)
+        plan = _LAST_PLAN
+        if plan is not None and not (plan[0].q_bf16 == query.data_ptr() and plan[0].out == out.data_ptr()):
+            plan = None
         if plan is None:
             raise RuntimeError("this call does not run as one launch (num_splits, balance_pages or "
                                "query_row_indices were given)")
         self._args = plan[0]
+        if direct:
+            # no copy operations: the kernel reads and writes the pinned host buffers itself
+            # (NVFP4_DECODE_HOST_IO_DIRECT); a copy of the block, the cached plan stays as it is
+            import ctypes
+
+            from .. import _lib as lib_module
+
+            block = lib_module.DecodeArgs()
+            ctypes.memmove(ctypes.byref(block), ctypes.byref(plan[0]), ctypes.sizeof(block))
+            block.flags |= lib_module.DECODE_HOST_IO_DIRECT
+            self._args = block
         self._device = plan[3]
         self._keep = (query, out, args, kwargs)   # the argument block holds raw addresses
         self.query_bytes = query.shape[0] * query.stride(0) * 2 if query.shape[0] > 1 else query.numel() * 2
         self.out_bytes = plan[1] * plan[2] * 128 * 2
+        self._checked = None
+        self._held = None
+        from .. import _lib
+
+        self._call = _lib.load().nvfp4_decode_host_io
 
     def __call__(self, query_host: torch.Tensor, out_host: torch.Tensor) -> None:
         from .. import _lib
 
-        if not (query_host.is_pinned() and out_host.is_pinned()):
-            raise ValueError("query_host and out_host must be pinned host tensors")
-        if query_host.numel() * query_host.element_size() < self.query_bytes or \
-                out_host.numel() * out_host.element_size() < self.out_bytes:
-            raise ValueError("host buffers are smaller than the device query / result")
+        # the checks of a pair of host buffers are made once (the step is called in a loop with the
+        # same two tensors; every check is a call into torch and the whole step is tens of us)
+        pair = (query_host.data_ptr(), out_host.data_ptr(), query_host.numel(), out_host.numel())
+        if pair != self._checked:
+            if not (query_host.is_pinned() and out_host.is_pinned()):
+                raise ValueError("query_host and out_host must be pinned host tensors")
+            if query_host.numel() * query_host.element_size() < self.query_bytes or \
+                    out_host.numel() * out_host.element_size() < self.out_bytes:
+                raise ValueError("host buffers are smaller than the device query / result")
+            self._checked = pair
+            self._held = (query_host, out_host)   # keeps the checked addresses alive
         index = self._device.index
         stream = torch._C._cuda_getCurrentRawStream(index)
-        with torch.cuda.device(index):
-            _lib.check(_lib.load().nvfp4_decode_host_io(self._args, query_host.data_ptr(), self.query_bytes,
-                                                        out_host.data_ptr(), self.out_bytes, stream))
+        call = self._call
+        if torch.cuda.current_device() == index:
+            code = call(self._args, pair[0], self.query_bytes, pair[1], self.out_bytes, stream)
+        else:
+            with torch.cuda.device(index):
+                code = call(self._args, pair[0], self.query_bytes, pair[1], self.out_bytes, stream)
+        if code:
+            _lib.check(code)
 
 
 def _kernel_can_quantise(query: torch.Tensor) -> bool:
@@ -216,6 +249,8 @@ def fp4_decode_impl(
         )
         plan = _PLANS.get(plan_key)
         if plan is not None:
+            global _LAST_PLAN
+            _LAST_PLAN = plan
             return _launch_plan(plan, out)
 
     bf16_query = query is not None
@@ -330,4 +365,5 @@ def fp4_decode_impl(
         if len(_PLANS) >= _MAX_PLANS:
             _PLANS.clear()
         _PLANS[plan_key] = (args, rows, heads_q, device, out is not None, out_indices is not None)
+        _LAST_PLAN = _PLANS[plan_key]
     return result

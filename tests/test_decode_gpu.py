@@ -716,3 +716,49 @@ def test_kv_head_shard_of_a_large_batch_matches_under_the_same_kernel_form(cuda_
         got = Problem(local, cuda_device).decode_direct(trusted_metadata=True)
         assert torch.equal(got, wide[:, q_heads]), rank
         assert (got.float() - narrow[:, q_heads].float()).abs().max().item() <= 2e-3
+
+
+def test_host_io_step_copies_and_direct_form(cuda_device):
+    """``host_io_step``: query from pinned host memory, rows to pinned host memory, one call into
+    the library.  With the copy operations and without them (the kernel reads and writes the
+    pinned buffers itself) the rows equal ``fp4_decode`` on the same query bit for bit; a tail,
+    several query rows, repeated calls with a changing query; unpinned buffers are refused."""
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import fp4_decode, host_io_step
+
+    _set_impl("auto")
+    case = inputs.attention_case(77, 5, 32, 8, (128 * 6 + 9, 128 * 2, 100, 128 * 9 + 127, 128 * 4 + 1), 1.0, 0.0)
+    prob = Problem(case, cuda_device)
+    tails = dict(residual_key_pages_bf16=prob.k_pages, residual_value_pages_bf16=prob.v_pages,
+                 residual_page_ids=prob.residual_page_ids, seqused_residual=prob.seqused_residual)
+    q_dev = torch.empty_like(prob.q)
+    out_dev = torch.zeros(5, 32, 128, dtype=torch.bfloat16, device=cuda_device)
+    q_dev.copy_(prob.q)
+    common = (prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, prob.page_table, prob.seqused_fp4)
+    for direct in (False, True):
+        step = host_io_step(q_dev, *common, out=out_dev, direct=direct, **tails)
+        for scale in (1.0, -0.5):
+            query = (prob.q.float() * scale).to(torch.bfloat16)
+            want = fp4_decode(query, *common, **tails)
+            q_host = query.cpu().pin_memory()
+            out_host = torch.zeros(5, 32, 128, dtype=torch.bfloat16).pin_memory()
+            step(q_host, out_host)
+            assert torch.equal(out_host.to(cuda_device), want), (direct, scale)
+        with pytest.raises((ValueError, RuntimeError)):
+            step(query.cpu(), out_host)          # not pinned
+    # steps over the same device query / output buffers but different caches (two page pools of a
+    # benchmark, two layers): each keeps its own cache, in whatever order they are built
+    other = Problem(inputs.attention_case(78, 5, 32, 8, (128 * 3, 128 * 5 + 7, 128, 128 * 2 + 1, 60), 1.0, 0.0), cuda_device)
+    other_common = (other.k_fp4, other.k_sf, other.v_fp4, other.v_sf, other.page_table, other.seqused_fp4)
+    other_tails = dict(residual_key_pages_bf16=other.k_pages, residual_value_pages_bf16=other.v_pages,
+                       residual_page_ids=other.residual_page_ids, seqused_residual=other.seqused_residual)
+    built = [host_io_step(q_dev, *common, out=out_dev, **tails),
+             host_io_step(q_dev, *other_common, out=out_dev, **other_tails),
+             host_io_step(q_dev, *common, out=out_dev, direct=True, **tails),
+             host_io_step(q_dev, *other_common, out=out_dev, direct=True, **other_tails)]
+    q_host = prob.q.cpu().pin_memory()
+    out_host = torch.zeros(5, 32, 128, dtype=torch.bfloat16).pin_memory()
+    wants = [fp4_decode(prob.q, *common, **tails), fp4_decode(prob.q, *other_common, **other_tails)]
+    assert not torch.equal(wants[0], wants[1])
+    for i, step in enumerate(built):
+        step(q_host, out_host)
+        assert torch.equal(out_host.to(cuda_device), wants[i % 2]), i
