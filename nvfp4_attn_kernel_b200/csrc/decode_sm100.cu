@@ -41,6 +41,12 @@
 // and with them the folded output, are those of the narrow form; only the row sum is kept in two
 // parts that are joined at the end.
 //
+// A tile's BF16 tail is processed first, out of shared memory: its key rows, then its value rows,
+// are fetched by tensor copies into the last slots of the V ring (see kTailSlots).  With a work
+// list (balanced split) a row's tail is an entry of its own, served by tail_piece without any of
+// the page machinery, and the pieces of a row are merged by a later launch or, on request, by
+// the piece that finishes last (finish_piece).
+//
 // Every device-side wait is bounded; on expiry the CTA raises NVFP4_STATUS_WAIT_TIMEOUT,
 // drains what it has in flight, frees its tensor memory and returns.
 #include <cstring>
