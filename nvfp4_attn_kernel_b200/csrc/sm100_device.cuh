@@ -277,11 +277,20 @@ struct MapEntry { MapKey key; CUtensorMap map; bool valid; };
 constexpr int kTailBoxRows = 32;   // tokens per box of a tail map
 inline cudaError_t make_map(int which, const void* base, int64_t pitch, int64_t pages, int heads,
                             CUtensorMap* out) {
-  thread_local MapEntry cache[8] = {};
-  thread_local int next = 0;
+  // four maps per launch (K, V and the two tail caches) and one set per layer of a model: a
+  // direct-mapped cache by address, so that an eager step does not encode maps at every call
+  constexpr int kCached = 256;
+  thread_local MapEntry cache[kCached] = {};
   const MapKey key{base, pitch, pages, heads, which};
-  for (auto& e : cache)
-    if (e.valid && e.key == key) { *out = e.map; return cudaSuccess; }
+  const unsigned long long h =
+      (static_cast<unsigned long long>(reinterpret_cast<uintptr_t>(base)) + (unsigned long long)which) *
+      0x9E3779B97F4A7C15ull;
+  // two candidate places per key: the maps of one launch rarely push each other out
+  MapEntry* slot = &cache[(h >> 56) % kCached];
+  if (slot->valid && slot->key == key) { *out = slot->map; return cudaSuccess; }
+  MapEntry* second = &cache[((h >> 48) ^ 0x55u) % kCached];
+  if (second->valid && second->key == key) { *out = second->map; return cudaSuccess; }
+  if (slot->valid && !second->valid) slot = second;
   EncodeTiledFn fn = encode_fn();
   if (!fn) return cudaErrorNotSupported;
   cuuint64_t dims[4], strides[3];
@@ -308,8 +317,7 @@ inline cudaError_t make_map(int which, const void* base, int64_t pitch, int64_t 
                   CU_TENSOR_MAP_INTERLEAVE_NONE, which >= 2 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                   promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-  cache[next] = MapEntry{key, map, true};
-  next = (next + 1) % 8;
+  *slot = MapEntry{key, map, true};
   *out = map;
   return cudaSuccess;
 }
