@@ -540,15 +540,24 @@ __device__ __noinline__ void tail_piece(const DecodeParams& p, const TileWork& w
 
 // narrow: 12 warps; wide: plus a second group of four score warps (12-15), a second pair of
 // issuers (16, 17) and a second pair of producers (18, 19)
-template <int kGroups> struct ThreadsOf { static constexpr int value = 384 + 256 * (kGroups - 1); };
+// The wide form's second producers and issuers shorten the page period of a CTA whose score work
+// is light; with 16 or 32 query heads per KV head the score threads bound the period, and what
+// those instantiations need is registers: they run without the four extra warps, 512 threads at
+// 128 registers instead of 640 at 96.
+template <int G, int kGroups> struct SecondSet { static constexpr bool value = kGroups == 2 && G < 16; };
+template <int G, int kGroups> struct ThreadsOf {
+  static constexpr int value = kGroups == 1 ? 384 : SecondSet<G, kGroups>::value ? 640 : 512;
+};
 
 template <int G, int kGroups>
-__global__ void __launch_bounds__(ThreadsOf<kGroups>::value, kGroups == 1 ? 2 : 1)
+__global__ void __launch_bounds__(ThreadsOf<G, kGroups>::value, kGroups == 1 ? 2 : 1)
 decode_sm100_kernel(const __grid_constant__ TileMaps maps, const __grid_constant__ DecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   Smem<G, kGroups>& sm =
       *reinterpret_cast<Smem<G, kGroups>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr int kThreads = ThreadsOf<kGroups>::value;
+  constexpr int kThreads = ThreadsOf<G, kGroups>::value;
+  constexpr bool kSecond = SecondSet<G, kGroups>::value;   // second producers (warps 18, 19) and issuers (16, 17)
+  constexpr int kIssuers = kSecond ? 2 : 1;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr int kKS = KSlots<G, kGroups>::value, kVS = VSlots<G, kGroups>::value;
   constexpr int NQ = QuerySlots<G>::value;
@@ -600,9 +609,10 @@ decode_sm100_kernel(const __grid_constant__ TileMaps maps, const __grid_constant
   // set-up barrier, so the first page tiles are in flight while tensor memory is allocated.
   // (the wide form's second producers, warps 18 / 19, take the odd walk steps; they join in after
   // the set-up barrier)
-  const bool is_k_producer = warp == kKProducerWarp || warp == 18, is_v_producer = warp == kVProducerWarp || warp == 19;
+  const bool is_k_producer = warp == kKProducerWarp || (kSecond && warp == 18);
+  const bool is_v_producer = warp == kVProducerWarp || (kSecond && warp == 19);
   const bool is_producer = is_k_producer || is_v_producer;
-  const bool second_producer = warp >= 18;
+  const bool second_producer = kSecond && warp >= 18;
   int spec[4] = {-1, -1, -1, -1};
   if (is_producer && !second_producer) {
     if (lane == 0) {
@@ -649,7 +659,7 @@ decode_sm100_kernel(const __grid_constant__ TileMaps maps, const __grid_constant
   }
   // rows G..7 of the N = 8 operands and their scale rows stay zero for the whole kernel
   if (!is_producer) {
-    constexpr int kWorkers = kThreads - 64 * kGroups;
+    constexpr int kWorkers = kThreads - 64 * kIssuers;   // all but the producer warps
     // warps 0-7, 9, 10 -> 0..319, the second score group's warps 12-15 -> 320..447
     const int wt = tid < kKProducerWarp * 32 ? tid : tid < kVProducerWarp * 32 ? tid - 32 : tid - 64;
     for (int i = wt; i < NQ * 64 / 16; i += kWorkers) reinterpret_cast<uint4*>(sm.q_tile)[i] = make_uint4(0, 0, 0, 0);
@@ -1131,7 +1141,7 @@ decode_sm100_kernel(const __grid_constant__ TileMaps maps, const __grid_constant
         }
         const int in_chunk = min(32, n_pages - base);
         for (int j = (base == 0 ? issued : 0); j < in_chunk; ++j) {
-          if (kGroups == 2 && (j & 1) != parity) continue;   // the other producer of the kind takes it
+          if (kSecond && (j & 1) != parity) continue;   // the other producer of the kind takes it
           int64_t pid = __shfl_sync(0xffffffffu, ids, j);
           if (lane == 0) {
             if (pid < 0 || pid >= p.num_pages) {
@@ -1154,7 +1164,7 @@ decode_sm100_kernel(const __grid_constant__ TileMaps maps, const __grid_constant
     }
     }
     __syncwarp();
-  } else if (warp == kQkWarp || warp == 16) {
+  } else if (warp == kQkWarp || (kSecond && warp == 16)) {
     // =====================  MMA issuer 1: S^T = K . Q^T  =====================
     // Issuing a tcgen05 instruction costs the issuing thread some 60 cycles and a barrier
     // wait about twice that, so the two products of a page are issued by two threads - and in
@@ -1171,7 +1181,7 @@ decode_sm100_kernel(const __grid_constant__ TileMaps maps, const __grid_constant
         cp_sf(sfq + 4, smem_u32(sm.q_sf + 512));
       }
       const uint64_t q_desc = desc_sw64(smem_u32(sm.q_tile));
-      for (int kb = ig; kb < n_batches && alive; kb += kGroups) {
+      for (int kb = ig; kb < n_batches && alive; kb += kIssuers) {
         const int set = kb & 1;
         alive = mbar_wait(&sm.s_free[set], ((kb >> 1) & 1) ^ 1, sm, p.status);
         for (int u = 0; u < kBatch && alive; ++u) {
@@ -1197,13 +1207,13 @@ decode_sm100_kernel(const __grid_constant__ TileMaps maps, const __grid_constant
       mbar_wait(&sm.drain[ig], 0, sm, p.status);
     }
     __syncwarp();
-  } else if (warp == kPvWarp || warp == 17) {
+  } else if (warp == kPvWarp || (kSecond && warp == 17)) {
     // =====================  MMA issuer 2: O^T = V^T . P^T  =====================
     const int ig = warp == kPvWarp ? 0 : 1;
     if (lane == 0 && n_pages > 0) {
       bool alive = true;
       const uint32_t sfp = tmem + C::kSfP + 8 * ig;
-      for (int kb = ig; kb < n_batches && alive; kb += kGroups) {
+      for (int kb = ig; kb < n_batches && alive; kb += kIssuers) {
         const int set = kb & 1;
         // The V slots of a pair land long before its probabilities are ready: their scale
         // blocks go to tensor memory now (columns of their own per page of the pair), which
@@ -1302,7 +1312,7 @@ static cudaError_t launch_g(const DecodeParams& p, const TileMaps& maps,
   if (p.work_list) grid = dim3(p.heads_kv, p.work_capacity, 1);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(ThreadsOf<kGroups>::value);
+  cfg.blockDim = dim3(ThreadsOf<G, kGroups>::value);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
