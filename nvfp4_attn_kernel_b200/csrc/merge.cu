@@ -17,18 +17,39 @@ lse_merge_kernel(const float* __restrict__ o_parts, int64_t o_split_stride,
                  const int32_t* __restrict__ out_indices, float* __restrict__ lse_out) {
   const int head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
   const int64_t idx = (int64_t)row * heads_q + head;
+  // the first kAhead splits' LSEs and outputs are fetched side by side before anything is
+  // computed (one round trip instead of two); the arithmetic and its order do not change
+  constexpr int kAhead = 8;
+  float ls_ahead[kAhead], o_ahead[kAhead];
+  const bool ahead = lse_ptrs == nullptr && o_ptrs == nullptr;
+#pragma unroll
+  for (int s = 0; s < kAhead; ++s) {
+    const bool live = ahead && s < num_splits;
+    ls_ahead[s] = live ? lse_parts[s * lse_split_stride + idx] : -INFINITY;
+    o_ahead[s] = live ? o_parts[s * o_split_stride + idx * kHeadDim + d] : 0.f;
+  }
+  const int from = ahead ? (num_splits < kAhead ? num_splits : kAhead) : 0;
   float mx = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) {
+#pragma unroll
+  for (int s = 0; s < kAhead; ++s) mx = fmaxf(mx, ls_ahead[s]);
+  for (int s = from; s < num_splits; ++s) {
     const float* lp = lse_ptrs ? lse_ptrs[s] : lse_parts + s * lse_split_stride;
     mx = fmaxf(mx, lp[idx]);
   }
   float acc = 0.f, tot = 0.f;
   if (mx != -INFINITY) {
-    for (int s = 0; s < num_splits; ++s) {
+#pragma unroll
+    for (int s = 0; s < kAhead; ++s) {
+      if (s >= from || ls_ahead[s] == -INFINITY) continue;  // an empty split weighs nothing, whatever its O holds
+      const float wgt = expf(ls_ahead[s] - mx);
+      tot += wgt;
+      acc = fmaf(wgt, o_ahead[s], acc);
+    }
+    for (int s = from; s < num_splits; ++s) {
       const float* lp = lse_ptrs ? lse_ptrs[s] : lse_parts + s * lse_split_stride;
       const float* op = o_ptrs ? o_ptrs[s] : o_parts + s * o_split_stride;
       const float ls = lp[idx];
-      if (ls == -INFINITY) continue;  // an empty split weighs nothing, whatever its O holds
+      if (ls == -INFINITY) continue;
       const float wgt = expf(ls - mx);
       tot += wgt;
       acc = fmaf(wgt, op[idx * kHeadDim + d], acc);
@@ -337,17 +358,37 @@ balanced_worklist_kernel(const int32_t* __restrict__ seqused_fp4, const int32_t*
 }
 
 // LSE merge where row r's partials are slots [row_offset[r], row_offset[r] + row_count[r]).
+// The launch is a chain of round trips to memory (the row's range, the pieces' LSEs, their
+// outputs), so the first kMergeAhead pieces' LSEs AND outputs are fetched side by side before
+// anything is computed; the arithmetic and its order are those of lse_merge_kernel.
+constexpr int kMergeAhead = 8;
 __global__ void __launch_bounds__(128)
 lse_merge_ranges_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
                         const int32_t* __restrict__ row_offset, const int32_t* __restrict__ row_count,
                         int heads_q, uint16_t* __restrict__ out) {
   const int head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
   const int first = row_offset[row], count = row_count[row];
+  float ls_ahead[kMergeAhead], o_ahead[kMergeAhead];
+#pragma unroll
+  for (int s = 0; s < kMergeAhead; ++s) {
+    const int64_t idx = (int64_t)(first + (s < count ? s : 0)) * heads_q + head;
+    ls_ahead[s] = s < count ? lse_parts[idx] : -INFINITY;
+    o_ahead[s] = s < count ? o_parts[idx * kHeadDim + d] : 0.f;
+  }
   float mx = -INFINITY;
-  for (int s = 0; s < count; ++s) mx = fmaxf(mx, lse_parts[(int64_t)(first + s) * heads_q + head]);
+#pragma unroll
+  for (int s = 0; s < kMergeAhead; ++s) mx = fmaxf(mx, ls_ahead[s]);
+  for (int s = kMergeAhead; s < count; ++s) mx = fmaxf(mx, lse_parts[(int64_t)(first + s) * heads_q + head]);
   float acc = 0.f, tot = 0.f;
   if (mx != -INFINITY) {
-    for (int s = 0; s < count; ++s) {
+#pragma unroll
+    for (int s = 0; s < kMergeAhead; ++s) {
+      if (s >= count || ls_ahead[s] == -INFINITY) continue;
+      const float wgt = expf(ls_ahead[s] - mx);
+      tot += wgt;
+      acc = fmaf(wgt, o_ahead[s], acc);
+    }
+    for (int s = kMergeAhead; s < count; ++s) {
       const int64_t idx = (int64_t)(first + s) * heads_q + head;
       const float ls = lse_parts[idx];
       if (ls == -INFINITY) continue;
