@@ -188,3 +188,48 @@ def test_wide_form_fits_counts_pieces_and_tails():
     assert wide_form_fits([68] * 32, 1, t, sms=148, tail_pieces=32)
     assert not wide_form_fits([68] * 32, 1, t - 1, sms=148, tail_pieces=32)
     assert wide_piece_pages([50], 8, sms=148, tail_pieces=40) == 50   # no room at all: whole rows
+
+
+def test_entry_points_added_beside_the_reference_refuse_bad_arguments_before_any_launch():
+    """The entry points without a counterpart in the reference validate on the host, like the
+    others: a refused call returns a code and a message and touches no device."""
+    lib = L.load()
+    # K-mean accumulation of the calibration
+    assert lib.nvfp4_key_sum_accumulate(None, 1024, 0, 8, None, None) == 0            # nothing to do
+    assert lib.nvfp4_key_sum_accumulate(None, 1024, 4, 8, None, None) == L.ERR_INVALID
+    assert "null" in L.last_error()
+    assert lib.nvfp4_key_sum_accumulate(16, 512, 4, 8, 64, None) == L.ERR_INVALID       # stride below a token
+    assert "stride" in L.last_error()
+    assert lib.nvfp4_key_sum_accumulate(16, 1024, -1, 8, 64, None) == L.ERR_INVALID
+    # host-buffer decode
+    assert lib.nvfp4_decode_host_io(None, None, 0, None, 0, None) == L.ERR_INVALID
+    assert "null" in L.last_error()
+    args = L.DecodeArgs()
+    assert lib.nvfp4_decode_host_io(ctypes.byref(args), 16, 16, 16, 16, None) == L.ERR_INVALID
+    assert "query buffer and out" in L.last_error()
+    # control step that also lists the decode pieces: the list's arguments are checked after the
+    # slot table's
+    ptrs = [16] * 13
+    base = [16, 8, 8] + ptrs
+    assert lib.nvfp4_control_step_balanced(*base, 4, 4, 8, 0, 32, 8, 32, 16, 1 << 20, None) == L.ERR_INVALID   # decode_rows 0
+    assert "decode_rows" in L.last_error()
+    assert lib.nvfp4_control_step_balanced(*base, 4, 4, 8, 4, 32, 0, 32, 16, 1 << 20, None) == L.ERR_INVALID   # target_pages 0
+    assert lib.nvfp4_control_step_balanced(*base, 4, 4, 8, 4, 32, 8, 32, 16, 64, None) == L.ERR_INVALID        # workspace too small
+    assert "workspace" in L.last_error()
+    assert lib.nvfp4_control_step_balanced(*base, 4, 4, 200, 4, 32, 8, 32, 16, 1 << 20, None) == L.ERR_INVALID  # too many slots
+    assert "128 slots" in L.last_error()
+    # flags that belong to one entry point are refused by the others
+    args = L.DecodeArgs()
+    args.rows, args.heads_q, args.heads_kv, args.softmax_scale, args.num_splits = 1, 32, 8, 0.1, 1
+    for k in ("k_packed", "k_sf", "v_packed", "v_sf", "page_table", "seqused_fp4", "q_bf16", "out"):
+        setattr(args, k, 4096)
+    args.k_pitch = args.v_pitch = 128 * 8 * 64
+    args.k_sf_pitch = args.v_sf_pitch = 8 * 1024
+    args.num_pages, args.max_pages, args.page_table_row_stride = 4, 4, 4
+    args.q_bf16_row_stride, args.q_bf16_head_stride = 32 * 128, 128
+    args.flags = L.DECODE_MERGE_IN_LAUNCH
+    assert lib.nvfp4_decode(ctypes.byref(args), None) == L.ERR_INVALID
+    assert "balanced" in L.last_error()
+    args.flags = 1 << 20
+    assert lib.nvfp4_decode(ctypes.byref(args), None) == L.ERR_INVALID
+    assert "unknown flag" in L.last_error()
