@@ -793,20 +793,31 @@ def page_range_check(device, world, rank, exchange):
                     residual_page_ids=prob.residual_page_ids, seqused_residual=prob.seqused_residual)
     out = torch.zeros(4, HQ, D, dtype=torch.bfloat16, device=device)
     same = True
-    want = prob.decode(num_splits=world)
+    # The exchange's launch has 4 rows x 8 KV heads CTAs per rank: the kernel's wide form.  The two
+    # forms add a row's pages in a different order, so the one-GPU comparison runs on the same form.
+    from nvfp4_attn_kernel_b200.nvfp4_decode_kernel import _decode
+    want = _decode.decode_fp4_split(
+        query_fp4=None, query_scales=None, query_bf16=prob.q, key_pages_fp4=prob.k_fp4, key_scales=prob.k_sf,
+        value_pages_fp4=prob.v_fp4, value_scales=prob.v_sf, fp4_page_table=prob.page_table,
+        seqused_fp4=prob.seqused_fp4, softmax_scale=prob.softmax_scale, num_splits=world,
+        residual_key_pages_bf16=prob.k_pages, residual_value_pages_bf16=prob.v_pages,
+        residual_page_ids=prob.residual_page_ids, seqused_residual=prob.seqused_residual, wide_form=True)
     for _ in range(3):
         sharding.decode_page_range(grp, prob.q, prob.k_fp4, prob.k_sf, prob.v_fp4, prob.v_sf, table, lseq,
                                    out=out, softmax_scale=prob.softmax_scale, **tail)
         torch.cuda.synchronize()
         same = same and bool(torch.equal(out, want))
+    gap = float((out.float() - want.float()).abs().max())
     err = None
     if rank == 0:
         oracle = torch.from_numpy(prob.oracle_from_bytes(splits=world)).to(device)
         err = float((out.float() - oracle).abs().max())
     flags = [None] * world
-    dist.all_gather_object(flags, (same, int(grp.status.item())))
+    dist.all_gather_object(flags, (same, int(grp.status.item()), gap))
     return {"check": {"problem": f"4 rows of {lens} tokens with tails, page ranges over {world} GPUs",
                       "bitwise_equal_to_one_gpu_split": all(f[0] for f in flags),
+                      "max_abs_vs_one_gpu_split": max(f[2] for f in flags),
+                      "one_gpu_split_kernel_form": "wide",
                       "device_status_words": [f[1] for f in flags],
                       "max_abs_vs_oracle_rows": err, "bound": 2e-2}}
 

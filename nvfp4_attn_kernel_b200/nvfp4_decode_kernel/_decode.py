@@ -649,6 +649,7 @@ def decode_fp4_split(
     append_key: torch.Tensor | None = None,
     append_value: torch.Tensor | None = None,
     key_shift: torch.Tensor | None = None,
+    wide_form: bool = False,
 ):
     """Split-KV decode: split ``s`` owns pages ``[s*ceil(n/S), min((s+1)*ceil(n/S), n))``,
     the residual belongs to split 0; partials are merged by LSE weight.
@@ -678,6 +679,7 @@ def decode_fp4_split(
         append_key=append_key,      # the split that owns the residual (split 0) appends
         append_value=append_value,
         key_shift=key_shift,
+        wide_form=wide_form,
     )
     if num_splits <= 1 and not return_partials:
         return decode_fp4(**common)
