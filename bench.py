@@ -520,6 +520,11 @@ def run_gpu(args) -> None:
         sub = argparse.Namespace(**vars(args))
         sub.steps, sub.warmup = 200, 20
         extras["long_context"] = run_long_context(sub, sub=True)
+        # the same exchange at a size where streaming the pages outweighs the launch and the
+        # exchange chain: 16 x 32768, four times the pages
+        big = argparse.Namespace(**vars(sub))
+        big.lc_rows, big.steps, big.warmup = 16, 96, 12
+        extras["long_context_16_rows"] = run_long_context(big, sub=True, check=False)
         sub.steps, sub.warmup = 24, 4
         extras["tp_model_step"] = run_model_step(sub, sub=True)
 
@@ -607,12 +612,13 @@ def run_gpu(args) -> None:
         dist.destroy_process_group()
 
 
-def run_long_context(args, sub: bool = False):
-    """Long-context workload: 4 sequences x 32768 context, the KV pages of every sequence split
-    by page range over the ranks (rank r holds only its pages), partial results merged over
-    NVLink.  Strong scaling: the total work is fixed as the number of GPUs grows.
+def run_long_context(args, sub: bool = False, check: bool = True):
+    """Long-context workload: 4 sequences x 32768 context (``--lc-rows`` / ``--lc-ctx`` change the
+    size), the KV pages of every sequence split by page range over the ranks (rank r holds only
+    its pages), partial results merged over NVLink.  Strong scaling: the total work is fixed as
+    the number of GPUs grows.
     ``sub``: called by the headline run on an initialised process group; returns the record
-    (rank 0) instead of printing a line."""
+    (rank 0) instead of printing a line.  ``check``: also run the small correctness problem."""
     import torch
     import torch.distributed as dist
 
@@ -629,7 +635,7 @@ def run_long_context(args, sub: bool = False):
     if world > 1 and not sub:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=device)
-    rows, ctx = getattr(args, "lc_rows", 4), getattr(args, "lc_ctx", 32768)
+    rows, ctx = args.lc_rows, args.lc_ctx
     pages = ctx // PAGE
     if pages % world:
         if sub:
@@ -726,7 +732,7 @@ def run_long_context(args, sub: bool = False):
     done = reps * num_pools
     ms_step = ms / done
     status = int(grp.status.item()) if grp is not None else 0
-    check = page_range_check(device, world, rank, args.exchange) if world > 1 else None
+    check = page_range_check(device, world, rank, args.exchange) if world > 1 and check else None
     line = None
     if rank == 0:
         peaks = load_peaks()
@@ -737,7 +743,7 @@ def run_long_context(args, sub: bool = False):
             "steps": done, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
             "config": {
-                "workload": "long-context split-KV: 4 seq x 32768 ctx, Hq32/Hkv8/D128, KV pages of every "
+                "workload": f"long-context split-KV: {rows} seq x {ctx} ctx, Hq32/Hkv8/D128, KV pages of every "
                             "sequence partitioned by page range over the GPUs, partial (O, LSE) merged over NVLink",
                 "exchange": (f"{args.exchange}, {splits} local splits per GPU" if world > 1
                              else f"one GPU, num_splits={splits}"),
@@ -1419,6 +1425,8 @@ def main() -> None:
                          "model-step: 32 layers of one GPU's head shard (1 KV head, 4 query heads), "
                          "contexts uniform in [1024, 16384]")
     ap.add_argument("--exchange", default="fused", choices=["fused", "push", "peer", "nccl"])
+    ap.add_argument("--lc-rows", type=int, default=4, help="sequences of the long-context workload")
+    ap.add_argument("--lc-ctx", type=int, default=32768, help="context of the long-context workload")
     ap.add_argument("--pdl", action=argparse.BooleanOptionalAction, default=True,
                     help="launch the decode with programmatic stream serialization: a launch's set-up "
                          "and first page loads overlap the previous launch's drain")
