@@ -406,6 +406,7 @@ size_t nvfp4_push_merge_inbox_floats(int world, int rows, int heads_q);
  * the merged rows to x->out: tiles that finish early are exchanged while others still stream.
  * Inbox, flags and epoch_state are those of nvfp4_push_merge (the two entry points produce the
  * same bits); tile_counters: device int32 [rows * heads_kv], zero-filled once.
+ * heads_q / heads_kv <= 8 (16 and 32 heads per KV head take nvfp4_push_merge as a second launch),
  * world * (heads_q / heads_kv) <= 128.  The ranks' kernels must run on different GPUs.
  */
 typedef struct nvfp4_exchange_args {

@@ -528,6 +528,9 @@ static int decode_call(const nvfp4_decode_args* a, const nvfp4_exchange_args* x,
       return fail(NVFP4_ERR_UNSUPPORTED, "decode_exchange: only the tensor-core kernel carries the exchange");
     if (a->num_splits > 256)
       return fail(NVFP4_ERR_UNSUPPORTED, "decode_exchange: at most 256 local splits");
+    if (a->heads_q / a->heads_kv > 8)
+      return fail(NVFP4_ERR_UNSUPPORTED,
+                  "decode_exchange: at most 8 query heads per KV head (use nvfp4_push_merge for 16 and 32)");
     if (x->world * (a->heads_q / a->heads_kv) > 128)
       return fail(NVFP4_ERR_UNSUPPORTED, "decode_exchange: world * (heads_q / heads_kv) must not exceed 128");
     p.xchg_inbox = x->inbox_ptrs;

@@ -1087,8 +1087,15 @@ decode_sm100_kernel(const __grid_constant__ TileMaps maps, const __grid_constant
         }
       }
     }
-    if (p.xchg_inbox) exchange_tile<G>(p, w, sm, t, stored, xchg_epoch);
-    else if (p.work_list && p.list_counters) finish_piece<G>(p, w.row, w.kvh, t, sm.xchg_last);
+    // The exchange serves up to eight query heads per KV head (its fold keeps five values per
+    // head and thread in registers; at sixteen and more heads that code spilled, and the spill
+    // slots were the only stack these instantiations had).  The host refuses the combination.
+    if constexpr (G <= 8) {
+      if (p.xchg_inbox) exchange_tile<G>(p, w, sm, t, stored, xchg_epoch);
+      else if (p.work_list && p.list_counters) finish_piece<G>(p, w.row, w.kvh, t, sm.xchg_last);
+    } else {
+      if (p.work_list && p.list_counters) finish_piece<G>(p, w.row, w.kvh, t, sm.xchg_last);
+    }
   } else if (is_producer) {
     // =====================  producers (K ring: warp 8, V ring: warp 11)  =====================
     if constexpr (kGroups == 1) {

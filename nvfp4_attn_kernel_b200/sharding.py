@@ -75,8 +75,8 @@ class PageRangeGroup:
     """Exchange + merge of per-rank partial results for the KV page-range split.
 
     ``exchange="fused"``: as "push", but done by the decode kernel for each (row, KV head)
-    tile as it completes (``nvfp4_decode_exchange``); needs ``heads_kv`` and the tensor-core
-    kernel.  ``exchange="push"``: every rank owns an inbox in symmetric memory; ``merge`` is ONE kernel
+    tile as it completes (``nvfp4_decode_exchange``); needs ``heads_kv``, the tensor-core
+    kernel and at most 8 query heads per KV head.  ``exchange="push"``: every rank owns an inbox in symmetric memory; ``merge`` is ONE kernel
     launch per rank (``nvfp4_push_merge``) that also folds the rank's local splits, and nothing
     is loaded over NVLink.  ``exchange="peer"``: partials live in symmetric memory that every
     rank of the group has mapped; ``merge`` is one launch per rank (``nvfp4_peer_merge``) that
@@ -93,6 +93,9 @@ class PageRangeGroup:
             raise ValueError("exchange must be 'fused', 'push', 'peer' or 'nccl'")
         if exchange == "fused" and not heads_kv:
             raise ValueError("the fused exchange counts arrivals per (row, KV head): pass heads_kv")
+        if exchange == "fused" and heads_q // heads_kv > 8:
+            raise ValueError("the fused exchange serves at most 8 query heads per KV head; "
+                             "use exchange='push' for 16 and 32")
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)

@@ -97,6 +97,18 @@ def _worker(rank, world, port, result):
         dist.destroy_process_group()
 
 
+def test_fused_exchange_refuses_more_than_eight_heads_per_kv_head():
+    """The exchange done by the decode kernel serves group sizes up to 8 (the kernel's 16- and
+    32-head instantiations are built without it); the refusal comes before anything is set up."""
+    cpu = torch.device("cpu")
+    with pytest.raises(ValueError, match="at most 8 query heads per KV head"):
+        sharding.PageRangeGroup(None, 4, 32, cpu, exchange="fused", heads_kv=2)
+    with pytest.raises(ValueError, match="at most 8 query heads per KV head"):
+        sharding.PageRangeGroup(None, 4, 32, cpu, exchange="fused", heads_kv=1)
+    with pytest.raises(ValueError, match="pass heads_kv"):
+        sharding.PageRangeGroup(None, 4, 32, cpu, exchange="fused")
+
+
 def test_two_ranks_merge_to_the_split_oracle():
     ctx = mp.get_context("spawn")
     result = ctx.Queue()
